@@ -1,0 +1,215 @@
+/* zllm_cuda: a CUDA (sm_100a) host for zllm's backend command stream.
+ *
+ * The B200 counterpart of the reference's native D3D12 host: a thin C
+ * interface (compare src/agility/agility.h:21-130) that the Zig side binds
+ * through translate-c, with the same conventions: opaque handles, int32
+ * results where negative means failure, a last-error string per context,
+ * serialized access per context, explicit timeouts on every wait.
+ *
+ * Two levels are exported:
+ *   1. zcu_execute: interprets one batch of the command stream exactly as
+ *      src/gpu/cmd.zig:21-59 encodes it and src/agility/host.zig:311-607
+ *      executes it (writes first, ops in order, blocking submit, one
+ *      completion per read and per submit).
+ *   2. zcu_launch and the buffer calls: one kernel dispatch with explicit
+ *      bindings, for callers that hold device pointers already (benchmarks,
+ *      the kernel check, the tuning sweep).
+ *
+ * Kernel identities are the values of the reference's `Kernel` enum
+ * (src/kernels/kernels.zig:24-101); parameter blocks are its `params.*`
+ * extern structs (src/kernels/kernels.zig:432-650), bit for bit; bindings
+ * follow each kernel's declared binding order.
+ */
+#ifndef ZLLM_CUDA_H
+#define ZLLM_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ZCU_ABI_VERSION 1u
+
+typedef struct zcu_context zcu_context;
+typedef int32_t zcu_result;
+
+/* Results. Negative values are failures and map onto the Zig host's error
+ * set (src/agility/host.zig:38, src/gpu/cmd.zig:222). */
+enum {
+    ZCU_OK = 0,
+    ZCU_E_GPU = -1,                /* error.GpuError */
+    ZCU_E_DEVICE_LOST = -2,        /* error.DeviceLost */
+    ZCU_E_BAD_COMMAND = -3,        /* error.BadCommand */
+    ZCU_E_BAD_ID = -4,             /* error.BadId */
+    ZCU_E_NO_TIMESTAMPS = -5,      /* error.NoTimestamps */
+    ZCU_E_UNSUPPORTED_KERNEL = -6, /* error.UnsupportedKernel */
+    ZCU_E_UNSUPPORTED_PREFILL = -7,/* error.UnsupportedPrefill */
+    ZCU_E_TRUNCATED = -8,          /* cmd.DecodeError.Truncated */
+    ZCU_E_BAD_LENGTH = -9,         /* cmd.DecodeError.BadLength */
+    ZCU_E_OUT_OF_MEMORY = -10,     /* error.OutOfMemory */
+    ZCU_E_TIMEOUT = -11,           /* a wait ran out (reported as GpuError upstream) */
+    ZCU_E_INVALID = -12            /* a bad argument to this interface */
+};
+
+/* Kernel identities: @intFromEnum(kernels.Kernel), src/kernels/kernels.zig:24-101.
+ * Only the identities of the decode/prefill path are implemented; the rest
+ * report "missing" (an empty artifact) exactly as a backend that lacks a
+ * kernel does (src/kernels/kernels.zig:752-755). */
+enum {
+    ZCU_K_RMSNORM = 0,
+    ZCU_K_MATMUL_BF16 = 1,
+    ZCU_K_MATMUL_F16 = 2,
+    ZCU_K_MATMUL_REDUCE = 3,
+    ZCU_K_MATVEC_BF16 = 4,
+    ZCU_K_MATVEC_F16 = 5,
+    ZCU_K_SILU_MUL = 6,
+    ZCU_K_EMBED_BF16 = 7,
+    ZCU_K_EMBED_F16 = 8,
+    ZCU_K_ROPE_APPEND = 9,
+    ZCU_K_ATTN_SPLIT = 10,
+    ZCU_K_ATTN_SPLIT_WIDE = 11,
+    ZCU_K_ATTN_COMBINE = 13,
+    ZCU_K_DELTA_PREP = 18,
+    ZCU_K_DELTA_RULE = 19,
+    ZCU_K_GATED_NORM = 20,
+    ZCU_K_REPACK_Q8_0 = 38,
+    ZCU_K_QUANTIZE_Q8 = 39,
+    ZCU_K_MATVEC_Q8_0 = 40,
+    ZCU_K_MATVEC_Q4_K = 42,
+    ZCU_K_MATMUL_Q8_0 = 45,
+    ZCU_K_MATMUL_Q4_K = 48,
+    ZCU_K_EMBED_Q8_0 = 51,
+    ZCU_K_EMBED_Q4_K = 53,
+    ZCU_K_COUNT = 57
+};
+
+/* Variant ids of a matvec pipeline (create_kernel's `variant`). 0 is the
+ * default. The reference packs (wg/32) | lanes<<8 | rows<<16 | act_div<<24
+ * (src/kernels/kernels.zig:330-333); this backend reads the same word as
+ * rows-per-CTA tile count (byte 0), in-CTA split-K (byte 1), and kernel
+ * family (byte 2: 1 = scalar f32 FMA, 2 = tensor-core fragments). Reserved
+ * prefill rungs keep the reference's ids (src/kernels/kernels.zig:798-822). */
+#define ZCU_VARIANT(tiles, splitk, family) ((uint32_t)(tiles) | ((uint32_t)(splitk) << 8) | ((uint32_t)(family) << 16))
+#define ZCU_FAMILY_SCALAR 1u
+#define ZCU_FAMILY_MMA 2u
+#define ZCU_VARIANT_PREFILL_BF16_TC 0xfffc0000u
+
+typedef struct zcu_options {
+    uint32_t abi_version;  /* ZCU_ABI_VERSION */
+    uint32_t device_index; /* CUDA ordinal (the reference's adapter index, src/gpu/host.zig:52-57) */
+    uint32_t dry_run;      /* 1: no device; buffers live in host memory, dispatches are validated
+                              and counted but never executed (command-stream tests on a CPU box) */
+    uint32_t reserved;
+    void *stream;          /* a cudaStream_t to launch on, or NULL for a stream the context owns */
+} zcu_options;
+
+typedef struct zcu_caps {
+    uint32_t abi_version;
+    uint32_t sm_major;
+    uint32_t sm_minor;
+    uint32_t sm_count;
+    uint32_t max_shared_per_block;
+    uint32_t l2_bytes;
+    uint64_t total_bytes;
+    uint64_t free_bytes;
+    uint32_t max_binding_lo; /* Device.limits(): max_binding (u64 split), offset_align */
+    uint32_t max_binding_hi;
+    uint32_t offset_align;
+    uint32_t dry_run;
+    char device_name[128];
+} zcu_caps;
+
+/* cmd.Completion (src/gpu/cmd.zig:89-95). */
+typedef struct zcu_completion {
+    uint32_t token;
+    uint32_t status; /* 0 ok, 1 failed */
+} zcu_completion;
+
+/* One bound range: a device pointer (buffer base + offset) and its size. */
+typedef struct zcu_binding {
+    void *ptr;
+    uint64_t size;
+} zcu_binding;
+
+/* gpu.Timings rows (src/gpu/timings.zig:6-27): totals per (kernel, grid). */
+typedef struct zcu_timing {
+    uint32_t kernel;
+    uint32_t variant;
+    uint32_t grid[3];
+    uint32_t count;
+    double total_us;
+} zcu_timing;
+
+/* ---- context (replaces Device.open/deinit/limits/memoryBudget/adapter/errorMessage/forceLoss,
+ *      src/gpu/host.zig:48-136; vel_create/vel_get_caps/vel_last_error/vel_remove_device/vel_destroy,
+ *      src/agility/agility.h:72-73,107-111,130) */
+zcu_result zcu_create(const zcu_options *options, zcu_context **out_context);
+zcu_result zcu_destroy(zcu_context *context, uint32_t timeout_ms);
+zcu_result zcu_get_caps(zcu_context *context, zcu_caps *out_caps);
+/* Copies the last error message (NUL-terminated); returns its length. */
+size_t zcu_last_error(zcu_context *context, char *out, size_t capacity);
+/* Marks the device lost on the host: every later call fails with
+ * ZCU_E_DEVICE_LOST. No GPU fault is raised (lost-device tests,
+ * src/gpu/host.zig:130-135). */
+zcu_result zcu_force_loss(zcu_context *context);
+/* Device.memoryBudget (src/gpu/host.zig:76-84): bytes a model may take. */
+zcu_result zcu_memory_budget(zcu_context *context, uint64_t *out_bytes);
+/* A string that changes whenever any kernel of this backend changes: the
+ * plan-cache key input `backendSource` (src/plan/cache.zig:56-85). */
+const char *zcu_backend_source(void);
+/* The artifact `kernels.artifact(.cuda, k, variant)` passes to create_kernel
+ * (src/kernels/kernels.zig:904-922): a short name, or an empty string (length
+ * 0) for an identity or variant this backend lacks. Returns its length. */
+size_t zcu_artifact(uint32_t kernel, uint32_t variant, char *out, size_t capacity);
+/* Device.supportsPrefill(rung) (src/gpu/host.zig:120-128): 1 or 0. */
+int32_t zcu_supports_prefill(zcu_context *context, uint32_t rung_variant);
+
+/* ---- command stream (replaces Host.execute/setFile/startProfile/stopProfile/timings,
+ *      src/gpu/host.zig:138-191; semantics of src/agility/host.zig:293-607) */
+/* `words` is one batch (src/gpu/cmd.zig:9-13). Blocks at every submit until the
+ * device has finished it (or timeout_ms passes). Appends completions to `out`
+ * (capacity `cap`), the count to `n_out`. The caller owns `words`, every
+ * write source and every read destination until this returns. */
+zcu_result zcu_execute(zcu_context *context, const uint32_t *words, size_t n_words, zcu_completion *out,
+                       size_t cap, size_t *n_out, uint32_t timeout_ms);
+/* The mapped model file that write_file commands copy from. */
+zcu_result zcu_set_file(zcu_context *context, const void *mapped, uint64_t length, const char *path);
+zcu_result zcu_start_profile(zcu_context *context);
+zcu_result zcu_stop_profile(zcu_context *context);
+/* Copies up to `cap` timing rows; `n_out` gets the number available. */
+zcu_result zcu_read_timings(zcu_context *context, zcu_timing *out, size_t cap, size_t *n_out);
+
+/* ---- direct level (replaces vel_create_resource / vel_dispatch / vel_readback / vel_wait_compute,
+ *      src/agility/agility.h:103-123, for callers that skip the stream) */
+zcu_result zcu_alloc(zcu_context *context, uint64_t bytes, void **out_ptr);
+zcu_result zcu_free(zcu_context *context, void *ptr);
+zcu_result zcu_upload(zcu_context *context, void *dst, const void *src, uint64_t bytes);   /* async on the stream */
+zcu_result zcu_download(zcu_context *context, void *dst, const void *src, uint64_t bytes); /* blocks */
+zcu_result zcu_memset(zcu_context *context, void *dst, int value, uint64_t bytes);
+/* One dispatch of `kernel` in `variant`. `params` is the kernel's binding-0
+ * block (host memory, `params_bytes` long); `bindings[i]` is binding i+1.
+ * `grid` is the reference's workgroup grid for the dispatch
+ * (kernels.Grid, src/kernels/kernels.zig:990-1043): this backend takes the
+ * token count and key blocks from it and sizes its own CUDA grid. */
+zcu_result zcu_launch(zcu_context *context, uint32_t kernel, uint32_t variant, const void *params,
+                      uint32_t params_bytes, const zcu_binding *bindings, uint32_t n_bindings,
+                      const uint32_t grid[3]);
+zcu_result zcu_sync(zcu_context *context, uint32_t timeout_ms);
+/* Number of kernel launches this context has issued (dry runs count too). */
+uint64_t zcu_launch_count(zcu_context *context);
+
+/* Replays of a fixed launch list: everything issued between begin and end
+ * is captured into one CUDA graph instead of running. Step-dependent kernels
+ * read their Step block (src/kernels/kernels.zig:436) from device memory, so
+ * one graph serves every step whose grids do not change. */
+zcu_result zcu_capture_begin(zcu_context *context);
+zcu_result zcu_capture_end(zcu_context *context, uint32_t *out_graph);
+zcu_result zcu_graph_launch(zcu_context *context, uint32_t graph);
+zcu_result zcu_graph_destroy(zcu_context *context, uint32_t graph);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

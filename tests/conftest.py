@@ -20,3 +20,21 @@ def ref():
     r.build()
     r.lib()
     return r
+
+
+@pytest.fixture(scope="session")
+def gpu():
+    """A context on cuda:0 through the C ABI. Fails (does not skip) without the
+    built library or a device: the GPU tier must never pass on a fallback."""
+    from zllm_b200 import abi
+
+    ctx = abi.Context(0)
+    yield ctx
+    ctx.close()
+
+
+@pytest.fixture()
+def launcher(gpu):
+    from zllm_b200 import kernels
+
+    return kernels.Launcher(gpu)

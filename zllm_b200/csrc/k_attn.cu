@@ -1,0 +1,264 @@
+// GQA decode attention over the KV cache, split over blocks of 64 cache
+// positions (flash-decoding) and merged by a second kernel. Replaces the
+// reference's attn_split / attn_split_wide / attn_combine
+// (src/kernels/attn_split.wgsl, src/kernels/attn_combine.wgsl) with the same
+// parameter block (params.Attention), bindings and partials layout:
+//   part[((t * heads + head) * max_blocks + b) * (head_dim + 2)] = {block max, block sum, o[0..head_dim)}
+// Cache layout pos * (kv_heads * head_dim) + g * head_dim + d, f16 pairs per
+// word (kv = 1) or f32 (kv = 0). Each K and V row is read once for the whole
+// GQA group. A token's result depends only on its position and the fixed
+// 64-key blocks, not on how the step was split.
+
+#include <cfloat>
+#include <cuda_fp16.h>
+
+#include "zcu_internal.h"
+
+namespace {
+
+constexpr int AT_THREADS = 256;
+constexpr int AT_BLOCK = 64;       // cache positions per CTA (kernels.attn_block)
+constexpr int AT_MAX_GROUP = 12;   // kernels.attn_max_group_wide
+constexpr int AT_SPLIT = AT_THREADS / AT_BLOCK;  // threads per key
+
+template <bool F16>
+__device__ __forceinline__ void load8(const void* base, size_t elem, float* out) {
+    if (F16) {
+        const uint4 v = *reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(base) + elem);
+        const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const float2 f = __half22float2(h[i]);
+            out[2 * i] = f.x;
+            out[2 * i + 1] = f.y;
+        }
+    } else {
+        const float4* p = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(base) + elem);
+        const float4 a = p[0], b = p[1];
+        out[0] = a.x; out[1] = a.y; out[2] = a.z; out[3] = a.w;
+        out[4] = b.x; out[5] = b.y; out[6] = b.z; out[7] = b.w;
+    }
+}
+
+template <bool F16>
+__device__ __forceinline__ float2 load2(const void* base, size_t elem) {
+    if (F16) return __half22float2(*reinterpret_cast<const __half2*>(reinterpret_cast<const __half*>(base) + elem));
+    return *reinterpret_cast<const float2*>(reinterpret_cast<const float*>(base) + elem);
+}
+
+// grid (kv_heads, blocks, rows). Dynamic shared memory:
+//   qs[group * hd] | sc[group * 64] | stat[2 * group] | pv[parts * group * hd]
+template <bool F16, int GROUP_CAP>
+__global__ void __launch_bounds__(AT_THREADS) attn_split_kernel(PAttention p, const float* __restrict__ qg,
+                                                               const void* __restrict__ kc,
+                                                               const void* __restrict__ vc, float* __restrict__ part,
+                                                               const PStep* __restrict__ step) {
+    extern __shared__ __align__(16) float sm[];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = blockIdx.x, b = blockIdx.y, t = blockIdx.z;
+    const int hd = (int)p.head_dim;
+    const int group = (int)(p.heads / p.kv_heads);
+    const int row = (int)p.row0 + t;
+    const int keys = (int)step->pos0 + row + 1;
+    const int k0 = b * AT_BLOCK;
+    const size_t kv_stride = (size_t)p.kv_heads * hd;
+    const int q_head = p.gated ? 2 * hd : hd;
+    const int dpairs = hd / 2;
+    const int parts = AT_THREADS / dpairs > 0 ? min(AT_THREADS / dpairs, AT_BLOCK) : 1;
+
+    float* qs = sm;
+    float* sc = qs + group * hd;
+    float* stat = sc + group * AT_BLOCK;
+    float* pv = stat + 2 * AT_MAX_GROUP;
+
+    for (int i = tid; i < group * hd; i += AT_THREADS) {
+        const int h = g * group + i / hd;
+        qs[i] = qg[(size_t)row * p.q_row + (size_t)h * q_head + i % hd];
+    }
+    __syncthreads();
+
+    // Scores: thread (key j, quarter s) over dims [s*hd/4, (s+1)*hd/4).
+    const int j = tid / AT_SPLIT, s = tid % AT_SPLIT;
+    const int key = k0 + j;
+    const bool live = key < keys;
+    const int span = hd / AT_SPLIT;
+    float dot[GROUP_CAP];
+#pragma unroll
+    for (int h = 0; h < GROUP_CAP; h++) dot[h] = 0.f;
+    if (live) {
+        const size_t kb = (size_t)key * kv_stride + (size_t)g * hd + (size_t)s * span;
+        for (int d = 0; d < span; d += 8) {
+            float kk[8];
+            load8<F16>(kc, kb + d, kk);
+            const int e = s * span + d;
+#pragma unroll
+            for (int h = 0; h < GROUP_CAP; h++) {
+                if (h < group) {
+                    const float4 q0 = *reinterpret_cast<const float4*>(qs + h * hd + e);
+                    const float4 q1 = *reinterpret_cast<const float4*>(qs + h * hd + e + 4);
+                    float a = dot[h];
+                    a = __fmaf_rn(q0.x, kk[0], a);
+                    a = __fmaf_rn(q0.y, kk[1], a);
+                    a = __fmaf_rn(q0.z, kk[2], a);
+                    a = __fmaf_rn(q0.w, kk[3], a);
+                    a = __fmaf_rn(q1.x, kk[4], a);
+                    a = __fmaf_rn(q1.y, kk[5], a);
+                    a = __fmaf_rn(q1.z, kk[6], a);
+                    a = __fmaf_rn(q1.w, kk[7], a);
+                    dot[h] = a;
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int h = 0; h < GROUP_CAP; h++) {
+        if (h < group) {
+            float v = dot[h];
+            v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 1));
+            v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 2));
+            if (s == 0) sc[h * AT_BLOCK + j] = live ? v * p.scale : -FLT_MAX;
+        }
+    }
+    __syncthreads();
+
+    // Block softmax per head: one warp per head, two keys per lane.
+    const int n = min(AT_BLOCK, keys - min(keys, k0));
+    for (int h = warp; h < group; h += AT_THREADS / 32) {
+        const float s0 = lane < n ? sc[h * AT_BLOCK + lane] : -FLT_MAX;
+        const float s1 = lane + 32 < n ? sc[h * AT_BLOCK + lane + 32] : -FLT_MAX;
+        float mx = fmaxf(s0, s1);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        const float e0 = (lane < n && s0 != -FLT_MAX) ? expf(s0 - mx) : 0.f;
+        const float e1 = (lane + 32 < n && s1 != -FLT_MAX) ? expf(s1 - mx) : 0.f;
+        sc[h * AT_BLOCK + lane] = e0;
+        sc[h * AT_BLOCK + lane + 32] = e1;
+        float sum = __fadd_rn(e0, e1);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sum = __fadd_rn(sum, __shfl_xor_sync(0xffffffffu, sum, o));
+        if (lane == 0) {
+            stat[2 * h] = mx;
+            stat[2 * h + 1] = sum;
+        }
+    }
+    __syncthreads();
+
+    // sum exp * v: thread (key part kp, dim pair dp); each V pair is read once for the group.
+    const int dp = tid % dpairs, kp = tid / dpairs;
+    float acc[GROUP_CAP][2];
+#pragma unroll
+    for (int h = 0; h < GROUP_CAP; h++) acc[h][0] = acc[h][1] = 0.f;
+    if (kp < parts) {
+        for (int i = kp; i < n; i += parts) {
+            const float2 v = load2<F16>(vc, (size_t)(k0 + i) * kv_stride + (size_t)g * hd + 2 * dp);
+#pragma unroll
+            for (int h = 0; h < GROUP_CAP; h++) {
+                if (h < group) {
+                    const float w = sc[h * AT_BLOCK + i];
+                    acc[h][0] = __fmaf_rn(w, v.x, acc[h][0]);
+                    acc[h][1] = __fmaf_rn(w, v.y, acc[h][1]);
+                }
+            }
+        }
+#pragma unroll
+        for (int h = 0; h < GROUP_CAP; h++) {
+            if (h < group) {
+                pv[((size_t)kp * group + h) * hd + 2 * dp] = acc[h][0];
+                pv[((size_t)kp * group + h) * hd + 2 * dp + 1] = acc[h][1];
+            }
+        }
+    }
+    __syncthreads();
+    for (int i = tid; i < group * hd; i += AT_THREADS) {
+        const int h = i / hd, d = i % hd;
+        float o = 0.f;
+        for (int q = 0; q < parts; q++) o = __fadd_rn(o, pv[((size_t)q * group + h) * hd + d]);
+        const int head = g * group + h;
+        const size_t base = (((size_t)t * p.heads + head) * p.max_blocks + b) * (hd + 2);
+        part[base + 2 + d] = o;
+        if (d == 0) {
+            part[base] = stat[2 * h];
+            part[base + 1] = stat[2 * h + 1];
+        }
+    }
+}
+
+// grid (heads, rows): one thread per output dim (src/kernels/attn_combine.wgsl).
+// Bindings: qg, part, out, step.
+__global__ void __launch_bounds__(256) attn_combine_kernel(PAttention p, const float* __restrict__ qg,
+                                                          const float* __restrict__ part, float* __restrict__ out,
+                                                          const PStep* __restrict__ step) {
+    const int d = threadIdx.x, h = blockIdx.x, t = blockIdx.y;
+    const int hd = (int)p.head_dim;
+    if (d >= hd) return;
+    const int row = (int)p.row0 + t;
+    const int keys = (int)step->pos0 + row + 1;
+    const int blocks = (keys + AT_BLOCK - 1) / AT_BLOCK;
+    const size_t base0 = ((size_t)t * p.heads + h) * p.max_blocks * (hd + 2);
+    float mx = -FLT_MAX;
+    for (int b = 0; b < blocks; b++) mx = fmaxf(mx, part[base0 + (size_t)b * (hd + 2)]);
+    float l = 0.f, o = 0.f;
+    for (int b = 0; b < blocks; b++) {
+        const size_t base = base0 + (size_t)b * (hd + 2);
+        const float w = expf(part[base] - mx);
+        l = __fmaf_rn(part[base + 1], w, l);
+        o = __fmaf_rn(part[base + 2 + d], w, o);
+    }
+    const size_t oi = ((size_t)row * p.heads + h) * hd + d;
+    if (!p.gated) {
+        out[oi] = o / l;
+        return;
+    }
+    const float gate = qg[(size_t)row * p.q_row + (size_t)2 * h * hd + hd + d];
+    out[oi] = o / l / (1.0f + expf(-gate));
+}
+
+template <bool F16>
+zcu_result launch_split_fmt(const LaunchArgs& a, const PAttention& p, dim3 grid, size_t smem, int group) {
+    const float* qg = (const float*)a.b[0].ptr;
+    float* part = (float*)a.b[3].ptr;
+    const PStep* step = (const PStep*)a.b[4].ptr;
+    if (group <= 4) {
+        attn_split_kernel<F16, 4><<<grid, AT_THREADS, smem, a.stream>>>(p, qg, a.b[1].ptr, a.b[2].ptr, part, step);
+    } else if (group <= 8) {
+        attn_split_kernel<F16, 8><<<grid, AT_THREADS, smem, a.stream>>>(p, qg, a.b[1].ptr, a.b[2].ptr, part, step);
+    } else {
+        attn_split_kernel<F16, AT_MAX_GROUP><<<grid, AT_THREADS, smem, a.stream>>>(p, qg, a.b[1].ptr, a.b[2].ptr, part, step);
+    }
+    ZCU_CHECK_LAUNCH(a);
+    return ZCU_OK;
+}
+
+}  // namespace
+
+zcu_result launch_attn_split(const LaunchArgs& a) {
+    PAttention p;
+    ZCU_NEED(a, a.params_bytes >= sizeof(p) && a.nb >= 5, "attn_split: bad parameter block or bindings");
+    memcpy(&p, a.params, sizeof(p));
+    ZCU_NEED(a, p.kv_heads > 0 && p.heads % p.kv_heads == 0, "attn_split: heads %u over kv_heads %u", p.heads, p.kv_heads);
+    const int group = (int)(p.heads / p.kv_heads);
+    ZCU_NEED(a, group <= AT_MAX_GROUP, "attn_split: GQA group %d above %d", group, AT_MAX_GROUP);
+    ZCU_NEED(a, p.head_dim % 32 == 0 && p.head_dim <= 256 && p.head_dim >= 32, "attn_split: head_dim %u", p.head_dim);
+    ZCU_NEED(a, p.kv == KV_F32 || p.kv == KV_F16, "attn_split: cache format %u is not built", p.kv);
+    ZCU_NEED(a, a.grid[1] <= p.max_blocks, "attn_split: %u key blocks above max_blocks %u", a.grid[1], p.max_blocks);
+    if (a.grid[1] == 0 || a.grid[2] == 0) return ZCU_OK;
+    const int hd = (int)p.head_dim;
+    const int dpairs = hd / 2;
+    const int parts = AT_THREADS / dpairs > AT_BLOCK ? AT_BLOCK : AT_THREADS / dpairs;
+    const size_t smem = ((size_t)group * hd + (size_t)group * AT_BLOCK + 2 * AT_MAX_GROUP + (size_t)parts * group * hd) * sizeof(float);
+    ZCU_NEED(a, smem <= 48 * 1024, "attn_split: %zu bytes of shared memory", smem);
+    const dim3 grid(p.kv_heads, a.grid[1], a.grid[2]);
+    return p.kv == KV_F16 ? launch_split_fmt<true>(a, p, grid, smem, group) : launch_split_fmt<false>(a, p, grid, smem, group);
+}
+
+zcu_result launch_attn_combine(const LaunchArgs& a) {
+    PAttention p;
+    ZCU_NEED(a, a.params_bytes >= sizeof(p) && a.nb >= 4, "attn_combine: bad parameter block or bindings");
+    memcpy(&p, a.params, sizeof(p));
+    ZCU_NEED(a, p.head_dim <= 256, "attn_combine: head_dim %u", p.head_dim);
+    if (a.grid[0] == 0 || a.grid[1] == 0) return ZCU_OK;
+    attn_combine_kernel<<<dim3(p.heads, a.grid[1]), 256, 0, a.stream>>>(p, (const float*)a.b[0].ptr, (const float*)a.b[1].ptr,
+                                                                        (float*)a.b[2].ptr, (const PStep*)a.b[3].ptr);
+    ZCU_CHECK_LAUNCH(a);
+    return ZCU_OK;
+}

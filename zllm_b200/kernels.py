@@ -1,0 +1,160 @@
+"""Kernel identities, parameter blocks and launch helpers: the host-side mirror
+of the reference's kernel catalog (src/kernels/kernels.zig) for the CUDA backend.
+
+Identities are `@intFromEnum(Kernel)` (kernels.zig:24-101); parameter blocks are
+its `params.*` extern structs (kernels.zig:432-650); `Launcher.launch` takes the
+same (kernel, params, args, groups) as the reference's (kernels.zig:938-960).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+
+from . import abi
+
+# kernels.Kernel
+RMSNORM, MATMUL_BF16, MATMUL_F16, MATMUL_REDUCE, MATVEC_BF16, MATVEC_F16, SILU_MUL = 0, 1, 2, 3, 4, 5, 6
+EMBED_BF16, EMBED_F16, ROPE_APPEND, ATTN_SPLIT, ATTN_SPLIT_WIDE, ATTN_SPLIT_SPARSE, ATTN_COMBINE = 7, 8, 9, 10, 11, 12, 13
+DELTA_PREP, DELTA_RULE, GATED_NORM = 18, 19, 20
+REPACK_Q8_0, QUANTIZE_Q8, MATVEC_Q8_0, MATVEC_Q4_K = 38, 39, 40, 42
+MATMUL_Q8_0, MATMUL_Q4_K, EMBED_Q8_0, EMBED_Q4_K = 45, 48, 51, 53
+KERNEL_COUNT = 57
+
+# MatvecBf16.Flags (kernels.zig:485-493)
+NORM, ACCUMULATE, SILU_PAIR = 1, 2, 4
+
+# plan.common.KvFormat
+KV_F32, KV_F16 = 0, 1
+
+ATTN_BLOCK = 64        # kernels.attn_block
+ATTN_ROWS = 32         # kernels.attn_rows
+DECODE_MAX_ROWS = 4    # kernels.decode_max_rows
+ATTN_MAX_GROUP = 8     # kernels.attn_max_group
+ATTN_MAX_GROUP_WIDE = 12
+
+FAMILY_SCALAR, FAMILY_MMA = 1, 2
+
+
+def variant(tiles: int = 0, splitk: int = 0, family: int = 0) -> int:
+    """ZCU_VARIANT: this backend's matvec variant word (0 = default)."""
+    return tiles | (splitk << 8) | (family << 16)
+
+
+# Candidates the tuning sweep tries (the cuda arm of MatvecVariant.candidates).
+MATVEC_CANDIDATES = [variant(0, ks, FAMILY_MMA) for ks in (1, 2, 4, 8)] + [variant(0, 0, FAMILY_SCALAR)]
+
+u32, f32 = C.c_uint32, C.c_float
+
+
+def _struct(name, fields):
+    return type(name, (C.Structure,), {"_fields_": fields})
+
+
+Step = _struct("Step", [("m", u32), ("pos0", u32), ("u", f32), ("keep", u32)])
+RmsNorm = _struct("RmsNorm", [("rows", u32), ("dim", u32), ("eps", f32), ("w_rows", u32)])
+MatmulBf16 = _struct("MatmulBf16", [("rows", u32), ("n", u32), ("k", u32), ("col0", u32), ("out_stride", u32),
+                                    ("accumulate", u32), ("_pad", u32 * 2)])
+Matvec = _struct("MatvecBf16", [("n", u32), ("k", u32), ("col0", u32), ("out_stride", u32), ("eps", f32),
+                                ("flags", u32), ("half", u32), ("x_stride", u32)])
+RepackQ80 = _struct("RepackQ80", [("rows", u32), ("k", u32), ("_pad", u32 * 2)])
+SiluMul = _struct("SiluMul", [("count", u32), ("width", u32), ("_pad", u32 * 2)])
+Embed = _struct("EmbedBf16", [("dim", u32), ("row0", u32), ("chunk_rows", u32), ("stride", u32)])
+RopeAppend = _struct("RopeAppend", [("heads", u32), ("kv_heads", u32), ("head_dim", u32), ("n_rot", u32), ("row", u32),
+                                    ("k_off", u32), ("v_off", u32), ("kv", u32), ("eps", f32), ("gated", u32),
+                                    ("qk_norm", u32), ("normal", u32), ("scales", u32), ("_pad", u32 * 3)])
+Attention = _struct("Attention", [("heads", u32), ("kv_heads", u32), ("head_dim", u32), ("kv", u32), ("scale", f32),
+                                  ("max_blocks", u32), ("q_row", u32), ("row0", u32), ("gated", u32), ("scales", u32),
+                                  ("_pad", u32 * 2)])
+DeltaPrep = _struct("DeltaPrep", [("channels", u32), ("taps", u32), ("key_channels", u32), ("head", u32), ("row", u32),
+                                  ("v_heads", u32), ("beta_off", u32), ("alpha_off", u32), ("eps", f32),
+                                  ("_pad", u32 * 3)])
+DeltaRule = _struct("DeltaRule", [("k_heads", u32), ("v_heads", u32), ("dim", u32), ("conv_stride", u32), ("taps", u32),
+                                  ("row", u32), ("kept_hist", u32), ("_pad", u32)])
+GatedNorm = _struct("GatedNorm", [("v_heads", u32), ("dim", u32), ("eps", f32), ("z_row", u32), ("z_off", u32),
+                                  ("sigmoid", u32), ("_pad", u32 * 2)])
+
+assert C.sizeof(Matvec) == 32 and C.sizeof(RopeAppend) == 64 and C.sizeof(Attention) == 48
+assert C.sizeof(DeltaPrep) == 48 and C.sizeof(DeltaRule) == 32 and C.sizeof(GatedNorm) == 32
+
+
+def row_bytes(ttype: str, k: int) -> int:
+    """Bytes per row as the kernels read it (kernels.rowBytes, kernels.zig:157-160)."""
+    if ttype == "q8_0":
+        return (k + k // 16 + 15) & ~15
+    if ttype == "q4_k":
+        return k // 256 * 144
+    if ttype in ("bf16", "f16"):
+        return 2 * k
+    raise ValueError(ttype)
+
+
+MATVEC_KERNEL = {"q4_k": MATVEC_Q4_K, "q8_0": MATVEC_Q8_0, "bf16": MATVEC_BF16, "f16": MATVEC_F16}
+EMBED_KERNEL = {"q4_k": EMBED_Q4_K, "q8_0": EMBED_Q8_0, "bf16": EMBED_BF16, "f16": EMBED_F16}
+
+
+def elementwise(count: int):
+    """Launcher.elementwise (kernels.zig:981-986)."""
+    groups = -(-count // 256)
+    if groups <= 65535:
+        return (groups, 1, 1)
+    return (65535, -(-groups // 65535), 1)
+
+
+class Launcher:
+    """Immediate launches on a context (kernels.Launcher, kernels.zig:925-960)."""
+
+    def __init__(self, ctx: abi.Context):
+        self.ctx = ctx
+
+    def launch(self, kernel: int, params, args, groups, variant: int = 0):
+        self.ctx.launch(kernel, params, args, groups, variant)
+
+    # -- the decode multiply: grid (ceil(n / groupRows), m, 1) in the reference; only m matters here
+    def matvec(self, ttype, x, w, out, n, k, m=1, col0=0, out_stride=None, flags=0, eps=0.0, half=0, x_stride=0,
+               norm_w=None, variant=0):
+        p = Matvec(n, k, col0, out_stride if out_stride is not None else n, eps, flags, half, x_stride)
+        args = [x, w, out] + ([norm_w] if norm_w is not None else [])
+        self.launch(MATVEC_KERNEL[ttype], p, args, (-(-n // 8), m, 1), variant)
+
+    def matmul(self, ttype, x, w, out, rows, n, k, col0=0, out_stride=None, accumulate=False):
+        p = MatmulBf16(rows, n, k, col0, out_stride if out_stride is not None else n, int(accumulate))
+        self.launch(MATMUL_BF16 if ttype == "bf16" else MATMUL_F16, p, [x, w, out], (-(-n // 64), -(-rows // 16), 1))
+
+    def rmsnorm(self, x, w, y, rows, dim, eps, w_rows=0):
+        self.launch(RMSNORM, RmsNorm(rows, dim, eps, w_rows), [x, w, y], (rows, 1, 1))
+
+    def silu_mul(self, gu, act, rows, width):
+        self.launch(SILU_MUL, SiluMul(rows * width, width), [gu, act], elementwise(rows * width))
+
+    def embed(self, ttype, tokens, w, out, m, dim, row0, chunk_rows, stride=0):
+        self.launch(EMBED_KERNEL[ttype], Embed(dim, row0, chunk_rows, stride), [tokens, w, out], (m, 1, 1))
+
+    def repack_q8_0(self, src, dst, rows, k):
+        self.launch(REPACK_Q8_0, RepackQ80(rows, k), [src, dst], elementwise(rows * row_bytes("q8_0", k) // 4))
+
+    def rope_append(self, p: "RopeAppend", qkv, q_norm, k_norm, rope, kc, vc, step, m):
+        self.launch(ROPE_APPEND, p, [qkv, q_norm, k_norm, rope, kc, vc, step], (p.heads + p.kv_heads, m, 1))
+
+    def attn_split(self, p: "Attention", qg, kc, vc, part, step, keys, rows):
+        group = p.heads // p.kv_heads
+        kern = ATTN_SPLIT if group <= ATTN_MAX_GROUP else ATTN_SPLIT_WIDE
+        self.launch(kern, p, [qg, kc, vc, part, step], (p.kv_heads, -(-keys // ATTN_BLOCK), rows))
+
+    def attn_combine(self, p: "Attention", qg, part, out, step, rows):
+        self.launch(ATTN_COMBINE, p, [qg, part, out, step], (p.heads, rows, 1))
+
+    def delta_rule(self, p: "DeltaRule", conv, g, beta, state, out, step, proj=None, hist=None, kept=None):
+        args = [conv, g, beta, state, out, step]
+        if proj is not None:
+            args += [proj, hist, kept]
+        self.launch(DELTA_RULE, p, args, (p.v_heads, -(-p.dim // 32), 1))
+
+    def delta_prep(self, p: "DeltaPrep", proj, conv_w, hist, out, dt_bias, a, g, beta, m):
+        self.launch(DELTA_PREP, p, [proj, conv_w, hist, out, dt_bias, a, g, beta], (p.channels // p.head + 1, m, 1))
+
+    def gated_norm(self, p: "GatedNorm", o, z, w, m):
+        self.launch(GATED_NORM, p, [o, z, w], (p.v_heads, m, 1))
+
+
+def attention_scale(head_dim: int) -> float:
+    return 1.0 / math.sqrt(head_dim)
