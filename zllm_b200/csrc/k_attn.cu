@@ -8,6 +8,10 @@
 // word (kv = 1) or f32 (kv = 0). Each K and V row is read once for the whole
 // GQA group. A token's result depends only on its position and the fixed
 // 64-key blocks, not on how the step was split.
+//
+// Extension for batches of independent sequences (the reference runs one sequence at a time): with
+// params._pad[0] = S != 0, row r is sequence r: its cache starts S elements after row r-1's, and its
+// position comes from one more binding (u32 per row) after `step`.
 
 #include <cfloat>
 #include <cuda_fp16.h>
@@ -52,14 +56,18 @@ template <bool F16, int GROUP_CAP>
 __global__ void __launch_bounds__(AT_THREADS) attn_split_kernel(PAttention p, const float* __restrict__ qg,
                                                                const void* __restrict__ kc,
                                                                const void* __restrict__ vc, float* __restrict__ part,
-                                                               const PStep* __restrict__ step) {
+                                                               const PStep* __restrict__ step,
+                                                               const uint32_t* __restrict__ seq_pos) {
     extern __shared__ __align__(16) float sm[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = blockIdx.x, b = blockIdx.y, t = blockIdx.z;
     const int hd = (int)p.head_dim;
     const int group = (int)(p.heads / p.kv_heads);
     const int row = (int)p.row0 + t;
-    const int keys = (int)step->pos0 + row + 1;
+    // Batched sequences (an extension for independent sequences in one step): row r reads its own
+    // cache, seq_stride elements further on, at its own position.
+    const size_t seq_off = (size_t)row * p._pad[0];
+    const int keys = (seq_pos ? (int)seq_pos[row] : (int)step->pos0 + row) + 1;
     const int k0 = b * AT_BLOCK;
     const size_t kv_stride = (size_t)p.kv_heads * hd;
     const int q_head = p.gated ? 2 * hd : hd;
@@ -86,7 +94,7 @@ __global__ void __launch_bounds__(AT_THREADS) attn_split_kernel(PAttention p, co
 #pragma unroll
     for (int h = 0; h < GROUP_CAP; h++) dot[h] = 0.f;
     if (live) {
-        const size_t kb = (size_t)key * kv_stride + (size_t)g * hd + (size_t)s * span;
+        const size_t kb = seq_off + (size_t)key * kv_stride + (size_t)g * hd + (size_t)s * span;
         for (int d = 0; d < span; d += 8) {
             float kk[8];
             load8<F16>(kc, kb + d, kk);
@@ -150,7 +158,7 @@ __global__ void __launch_bounds__(AT_THREADS) attn_split_kernel(PAttention p, co
     for (int h = 0; h < GROUP_CAP; h++) acc[h][0] = acc[h][1] = 0.f;
     if (kp < parts) {
         for (int i = kp; i < n; i += parts) {
-            const float2 v = load2<F16>(vc, (size_t)(k0 + i) * kv_stride + (size_t)g * hd + 2 * dp);
+            const float2 v = load2<F16>(vc, seq_off + (size_t)(k0 + i) * kv_stride + (size_t)g * hd + 2 * dp);
 #pragma unroll
             for (int h = 0; h < GROUP_CAP; h++) {
                 if (h < group) {
@@ -187,12 +195,13 @@ __global__ void __launch_bounds__(AT_THREADS) attn_split_kernel(PAttention p, co
 // Bindings: qg, part, out, step.
 __global__ void __launch_bounds__(256) attn_combine_kernel(PAttention p, const float* __restrict__ qg,
                                                           const float* __restrict__ part, float* __restrict__ out,
-                                                          const PStep* __restrict__ step) {
+                                                          const PStep* __restrict__ step,
+                                                          const uint32_t* __restrict__ seq_pos) {
     const int d = threadIdx.x, h = blockIdx.x, t = blockIdx.y;
     const int hd = (int)p.head_dim;
     if (d >= hd) return;
     const int row = (int)p.row0 + t;
-    const int keys = (int)step->pos0 + row + 1;
+    const int keys = (seq_pos ? (int)seq_pos[row] : (int)step->pos0 + row) + 1;
     const int blocks = (keys + AT_BLOCK - 1) / AT_BLOCK;
     const size_t base0 = ((size_t)t * p.heads + h) * p.max_blocks * (hd + 2);
     float mx = -FLT_MAX;
@@ -204,7 +213,9 @@ __global__ void __launch_bounds__(256) attn_combine_kernel(PAttention p, const f
         l = __fmaf_rn(part[base + 1], w, l);
         o = __fmaf_rn(part[base + 2 + d], w, o);
     }
-    const size_t oi = ((size_t)row * p.heads + h) * hd + d;
+    // _pad[1] != 0 (extension): floats between output rows, for writing a rank's head columns of a wider row.
+    const size_t orow = p._pad[1] ? (size_t)p._pad[1] : (size_t)p.heads * hd;
+    const size_t oi = (size_t)row * orow + (size_t)h * hd + d;
     if (!p.gated) {
         out[oi] = o / l;
         return;
@@ -218,12 +229,13 @@ zcu_result launch_split_fmt(const LaunchArgs& a, const PAttention& p, dim3 grid,
     const float* qg = (const float*)a.b[0].ptr;
     float* part = (float*)a.b[3].ptr;
     const PStep* step = (const PStep*)a.b[4].ptr;
+    const uint32_t* seq_pos = (a.nb >= 6 && p._pad[0] != 0) ? (const uint32_t*)a.b[5].ptr : nullptr;
     if (group <= 4) {
-        attn_split_kernel<F16, 4><<<grid, AT_THREADS, smem, a.stream>>>(p, qg, a.b[1].ptr, a.b[2].ptr, part, step);
+        attn_split_kernel<F16, 4><<<grid, AT_THREADS, smem, a.stream>>>(p, qg, a.b[1].ptr, a.b[2].ptr, part, step, seq_pos);
     } else if (group <= 8) {
-        attn_split_kernel<F16, 8><<<grid, AT_THREADS, smem, a.stream>>>(p, qg, a.b[1].ptr, a.b[2].ptr, part, step);
+        attn_split_kernel<F16, 8><<<grid, AT_THREADS, smem, a.stream>>>(p, qg, a.b[1].ptr, a.b[2].ptr, part, step, seq_pos);
     } else {
-        attn_split_kernel<F16, AT_MAX_GROUP><<<grid, AT_THREADS, smem, a.stream>>>(p, qg, a.b[1].ptr, a.b[2].ptr, part, step);
+        attn_split_kernel<F16, AT_MAX_GROUP><<<grid, AT_THREADS, smem, a.stream>>>(p, qg, a.b[1].ptr, a.b[2].ptr, part, step, seq_pos);
     }
     ZCU_CHECK_LAUNCH(a);
     return ZCU_OK;
@@ -257,8 +269,9 @@ zcu_result launch_attn_combine(const LaunchArgs& a) {
     memcpy(&p, a.params, sizeof(p));
     ZCU_NEED(a, p.head_dim <= 256, "attn_combine: head_dim %u", p.head_dim);
     if (a.grid[0] == 0 || a.grid[1] == 0) return ZCU_OK;
+    const uint32_t* seq_pos = (a.nb >= 5 && p._pad[0] != 0) ? (const uint32_t*)a.b[4].ptr : nullptr;
     attn_combine_kernel<<<dim3(p.heads, a.grid[1]), 256, 0, a.stream>>>(p, (const float*)a.b[0].ptr, (const float*)a.b[1].ptr,
-                                                                        (float*)a.b[2].ptr, (const PStep*)a.b[3].ptr);
+                                                                        (float*)a.b[2].ptr, (const PStep*)a.b[3].ptr, seq_pos);
     ZCU_CHECK_LAUNCH(a);
     return ZCU_OK;
 }

@@ -152,7 +152,8 @@ __global__ void __launch_bounds__(256) rope_append_kernel(PRopeAppend p, float* 
                                                          const float* __restrict__ q_norm,
                                                          const float* __restrict__ k_norm,
                                                          const float2* __restrict__ rope, uint32_t* __restrict__ kc,
-                                                         uint32_t* __restrict__ vc, const PStep* __restrict__ step) {
+                                                         uint32_t* __restrict__ vc, const PStep* __restrict__ step,
+                                                         const uint32_t* __restrict__ seq_pos) {
     __shared__ double red[32];
     __shared__ float vals[256];
     const uint32_t i = threadIdx.x, xh = blockIdx.x, t = blockIdx.y;
@@ -175,7 +176,9 @@ __global__ void __launch_bounds__(256) rope_append_kernel(PRopeAppend p, float* 
     }
     __syncthreads();
     const uint32_t half = p.n_rot / 2;
-    const uint32_t pos = step->pos0 + t;
+    // Batched sequences (an extension): with _pad[0] = S != 0, row t is sequence t, with its own position
+    // (one more binding, u32 per row) and its own cache, S elements after row t-1's.
+    const uint32_t pos = seq_pos ? seq_pos[t] : step->pos0 + t;
     float r0 = 0.f, r1 = 0.f;
     uint32_t a = 0, b = 0;
     if (i < half) {
@@ -198,7 +201,7 @@ __global__ void __launch_bounds__(256) rope_append_kernel(PRopeAppend p, float* 
         return;
     }
     const size_t width = (size_t)p.kv_heads * hd;
-    const size_t e = (size_t)pos * width + (size_t)g * hd;
+    const size_t e = (size_t)t * p._pad[0] + (size_t)pos * width + (size_t)g * hd;
     const size_t vb = (size_t)t * p.row + p.v_off + (size_t)g * hd;
     if (i < hd / 2) {
         const float k0 = vals[2 * i], k1 = vals[2 * i + 1];
@@ -359,7 +362,8 @@ zcu_result launch_rope_append(const LaunchArgs& a) {
     if (m == 0) return ZCU_OK;
     rope_append_kernel<<<dim3(p.heads + p.kv_heads, m), 256, 0, a.stream>>>(
         p, (float*)a.b[0].ptr, (const float*)a.b[1].ptr, (const float*)a.b[2].ptr, (const float2*)a.b[3].ptr,
-        (uint32_t*)a.b[4].ptr, (uint32_t*)a.b[5].ptr, (const PStep*)a.b[6].ptr);
+        (uint32_t*)a.b[4].ptr, (uint32_t*)a.b[5].ptr, (const PStep*)a.b[6].ptr,
+        (a.nb >= 8 && p._pad[0] != 0) ? (const uint32_t*)a.b[7].ptr : nullptr);
     ZCU_CHECK_LAUNCH(a);
     return ZCU_OK;
 }

@@ -1,0 +1,248 @@
+"""The decode-step program of a Llama-shaped dense model: the host-side mirror of the reference's plan for
+dense models (src/plan/qwen35.zig:218-280 upload, :451-692 build, :766-805 recordStep,
+LayerBuilder.attention :989-1036, ffn :1039-1052), driving the CUDA backend.
+
+Per layer the reference records seven dispatches, and so does this program:
+  1. matvec  Wq|Wk|Wv  with the RMSNorm prologue          (plan/qwen35.zig:1006)
+  2. rope_append                                           (:1008-1022)
+  3. attn_split   4. attn_combine                          (:1023-1034)
+  5. matvec  Wo, ACCUMULATE into the residual stream       (:1034)
+  6. matvec  gate|up with NORM + SILU_PAIR                 (:1048)
+  7. matvec  Wdown, ACCUMULATE                             (:1049)
+then the output norm fused into the LM-head matvec (:609), after one embed_* at the front (:549-551).
+Weights that share an input are stacked by rows (Q|K|V, gate|up: :255-262).
+
+Two things go beyond the reference, which runs one sequence on one GPU:
+  * a batch of B independent sequences, each with its own KV cache and position (rows of the step are
+    sequences; attention and rope_append take the per-sequence cache stride and positions);
+  * tensor parallelism over W ranks: every weight matrix is sharded by rows per part (query heads and
+    their KV heads together, matching gate and up rows together), the KV cache by KV head, and each
+    sharded output that a later kernel reads whole is all-gathered (`gather` callback).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+from dataclasses import dataclass
+
+import numpy as np
+
+from . import kernels as K
+
+
+@dataclass
+class DenseConfig:
+    layers: int = 32
+    hidden: int = 4096
+    heads: int = 32
+    kv_heads: int = 8
+    head_dim: int = 128
+    ff: int = 14336
+    vocab: int = 128256
+    rope_base: float = 500000.0
+    eps: float = 1e-5
+    max_ctx: int = 8192 + 64
+    body_type: str = "q4_k"
+    head_type: str = "q8_0"
+    embed_type: str = "q4_k"
+
+    @property
+    def q_dim(self):
+        return self.heads * self.head_dim
+
+    @property
+    def kv_dim(self):
+        return self.kv_heads * self.head_dim
+
+
+def shard_rows(total: int, rank: int, world: int):
+    """Rows [lo, hi) of `total` that rank owns (contiguous, equal parts)."""
+    assert total % world == 0, (total, world)
+    per = total // world
+    return rank * per, (rank + 1) * per
+
+
+@dataclass
+class Shard:
+    """What one rank holds of the model (world = 1: everything)."""
+    rank: int = 0
+    world: int = 1
+
+    def heads(self, cfg: DenseConfig):
+        return shard_rows(cfg.heads, self.rank, self.world)
+
+    def kv_heads(self, cfg: DenseConfig):
+        return shard_rows(cfg.kv_heads, self.rank, self.world)
+
+
+def layer_weight_shapes(cfg: DenseConfig, sh: Shard):
+    """name -> (rows held by this rank, k) for every matrix of a layer."""
+    h0, h1 = sh.heads(cfg)
+    g0, g1 = sh.kv_heads(cfg)
+    hd = cfg.head_dim
+    ff0, ff1 = shard_rows(cfg.ff, sh.rank, sh.world)
+    e0, e1 = shard_rows(cfg.hidden, sh.rank, sh.world)
+    return {
+        "wqkv": ((h1 - h0) * hd + 2 * (g1 - g0) * hd, cfg.hidden),
+        "wo": (e1 - e0, cfg.q_dim),
+        "wgu": (2 * (ff1 - ff0), cfg.hidden),
+        "wdown": (e1 - e0, cfg.ff),
+    }
+
+
+def slice_full_weights(cfg: DenseConfig, sh: Shard, name: str, full: np.ndarray) -> np.ndarray:
+    """The rows of a full (unsharded, stacked) weight matrix [rows, row_bytes] that this rank holds, in
+    the order the sharded program expects. Used by tests to shard one seeded model for every world size."""
+    hd = cfg.head_dim
+    h0, h1 = sh.heads(cfg)
+    g0, g1 = sh.kv_heads(cfg)
+    if name == "wqkv":
+        q = full[h0 * hd:h1 * hd]
+        k = full[cfg.q_dim + g0 * hd:cfg.q_dim + g1 * hd]
+        v = full[cfg.q_dim + cfg.kv_dim + g0 * hd:cfg.q_dim + cfg.kv_dim + g1 * hd]
+        return np.concatenate([q, k, v])
+    if name == "wgu":
+        f0, f1 = shard_rows(cfg.ff, sh.rank, sh.world)
+        return np.concatenate([full[f0:f1], full[cfg.ff + f0:cfg.ff + f1]])
+    if name in ("wo", "wdown"):
+        e0, e1 = shard_rows(cfg.hidden, sh.rank, sh.world)
+        return full[e0:e1]
+    if name == "head":
+        v0, v1 = shard_rows(cfg.vocab, sh.rank, sh.world)
+        return full[v0:v1]
+    raise KeyError(name)
+
+
+class DenseProgram:
+    """Buffers and the launch list of one decode step for `batch` sequences on one rank.
+
+    `weights`: {"embed": buf, "head": buf, "out_norm": buf, "layers": [{"wqkv","wo","wgu","wdown",
+    "attn_norm","ffn_norm"}]} of device buffers (anything with .ptr/.nbytes or (ptr, size)) in the kernels'
+    layouts. `alloc(nbytes)` returns a zeroed device buffer. `gather(buf, batch, width_total)`, for
+    world > 1, makes every rank's column slice of a [batch, width_total] f32 buffer visible on all ranks.
+    """
+
+    def __init__(self, ctx, cfg: DenseConfig, weights, batch: int, alloc, shard: Shard | None = None, gather=None,
+                 variants: dict | None = None):
+        self.ctx, self.cfg, self.w, self.B = ctx, cfg, weights, batch
+        self.sh = shard or Shard()
+        self.gather = gather
+        self.L = K.Launcher(ctx)
+        self.variants = variants or {}
+        self.launches_per_step = 0
+        sh, hd = self.sh, cfg.head_dim
+        h0, h1 = sh.heads(cfg)
+        g0, g1 = sh.kv_heads(cfg)
+        self.lh, self.lg = h1 - h0, g1 - g0                  # local query / KV heads
+        self.h0, self.g0 = h0, g0
+        self.qkv_row = (self.lh + 2 * self.lg) * hd
+        self.lff = cfg.ff // sh.world
+        self.le = cfg.hidden // sh.world
+        self.lv = cfg.vocab // sh.world
+        B, e = batch, cfg.hidden
+        f4 = 4
+        self.tokens = alloc(B * 4)
+        self.positions = alloc(B * 4)
+        self.step = alloc(16)
+        self.x = alloc(B * e * f4)
+        self.qkv = alloc(B * self.qkv_row * f4)
+        self.att = alloc(B * cfg.q_dim * f4)          # full width: column slices are gathered
+        self.act = alloc(B * cfg.ff * f4)
+        self.logits = alloc(B * cfg.vocab * f4)
+        self.max_blocks = -(-cfg.max_ctx // K.ATTN_BLOCK)
+        self.part = alloc(B * self.lh * self.max_blocks * (hd + 2) * f4)
+        self.seq_stride = cfg.max_ctx * self.lg * hd          # cache elements per sequence
+        self.kc = [alloc(B * self.seq_stride * 2) for _ in range(cfg.layers)]
+        self.vc = [alloc(B * self.seq_stride * 2) for _ in range(cfg.layers)]
+        self.dummy = alloc(256)
+        self.rope = None
+
+    # ---- host-built tables and per-step state
+    def set_rope_table(self, table_buf):
+        """(cos, sin) per (position, pair), built on the host (src/kernels/kernels.zig:730-744)."""
+        self.rope = table_buf
+
+    @staticmethod
+    def rope_table(cfg: DenseConfig) -> np.ndarray:
+        """The reference's table formula in f32: theta = pos * base^(-2i/n_rot) (src/ref/ops.zig:95-99)."""
+        half = cfg.head_dim // 2
+        i = np.arange(half, dtype=np.float32)
+        exponent = (np.float32(-2.0) * i / np.float32(cfg.head_dim)).astype(np.float32)
+        inv = np.power(np.float32(cfg.rope_base), exponent, dtype=np.float32)
+        pos = np.arange(cfg.max_ctx, dtype=np.float32)[:, None]
+        theta = (pos * inv[None, :]).astype(np.float32)
+        return np.stack([np.cos(theta), np.sin(theta)], axis=-1).astype(np.float32).reshape(-1)
+
+    def write_step(self, tokens: np.ndarray, positions: np.ndarray):
+        """The step's inputs: one token id and one position per sequence."""
+        assert tokens.size == self.B and positions.size == self.B
+        self.tokens.upload(np.ascontiguousarray(tokens, dtype=np.uint32))
+        self.positions.upload(np.ascontiguousarray(positions, dtype=np.uint32))
+        self.step.upload(np.array([self.B, int(positions[0]), 0, 0], dtype=np.uint32))
+
+    # ---- the launch list
+    def _matvec(self, ttype, x, w, out, n, k, **kw):
+        self.L.matvec(ttype, x, w, out, n, k, m=self.B, variant=self.variants.get((ttype, n, k), 0), **kw)
+        self.launches_per_step += 1
+
+    def _gather(self, buf, width):
+        if self.gather is not None:
+            self.gather(buf, self.B, width)
+
+    def record_step(self, max_keys: int):
+        """Issues the step's launches on the context's stream (inside a graph capture they are captured).
+        `max_keys`: the largest position + 1 of the batch (sizes the attention grid)."""
+        cfg, B, hd, sh = self.cfg, self.B, self.cfg.head_dim, self.sh
+        e = cfg.hidden
+        self.launches_per_step = 0
+        # embedding rows of the step's tokens (replicated on every rank)
+        self.L.embed(cfg.embed_type, self.tokens, self.w["embed"], self.x, B, e, 0, cfg.vocab)
+        self.launches_per_step += 1
+        rp = K.RopeAppend(self.lh, self.lg, hd, hd, self.qkv_row, self.lh * hd, (self.lh + self.lg) * hd, K.KV_F16,
+                          cfg.eps, 0, 0, 1, 0)
+        rp._pad[0] = self.seq_stride
+        ap = K.Attention(self.lh, self.lg, hd, K.KV_F16, K.attention_scale(hd), self.max_blocks, self.qkv_row, 0, 0, 0)
+        ap._pad[0] = self.seq_stride
+        ap._pad[1] = cfg.q_dim                                  # att rows are full width on every rank
+        blocks = -(-max_keys // K.ATTN_BLOCK)
+        att_cols = self.att.at(self.h0 * hd * 4)                # this rank's head columns of att
+        for il in range(cfg.layers):
+            lw = self.w["layers"][il]
+            # 1. fused attn_norm + Q|K|V projection (local heads)
+            self._matvec(cfg.body_type, self.x, lw["wqkv"], self.qkv, self.qkv_row, e, flags=K.NORM, eps=cfg.eps,
+                         norm_w=lw["attn_norm"])
+            # 2. RoPE (normal pairs) and the cache append at each sequence's position
+            self.L.launch(K.ROPE_APPEND, rp, [self.qkv, self.dummy, self.dummy, self.rope, self.kc[il], self.vc[il],
+                                              self.step, self.positions], (self.lh + self.lg, B, 1))
+            # 3-4. split attention over each sequence's cache, merged into this rank's head columns of att
+            self.L.launch(K.ATTN_SPLIT, ap, [self.qkv, self.kc[il], self.vc[il], self.part, self.step, self.positions],
+                          (self.lg, blocks, B))
+            self.L.launch(K.ATTN_COMBINE, ap, [self.qkv, self.part, att_cols, self.step, self.positions], (self.lh, B, 1))
+            self.launches_per_step += 3
+            self._gather(self.att, cfg.q_dim)
+            # 5. Wo rows of this rank, accumulated into the residual stream's slice
+            self._matvec(cfg.body_type, self.att, lw["wo"], self.x, self.le, cfg.q_dim, col0=sh.rank * self.le,
+                         out_stride=e, flags=K.ACCUMULATE)
+            self._gather(self.x, e)
+            # 6. fused ffn_norm + gate|up + SwiGLU (local ff rows)
+            self._matvec(cfg.body_type, self.x, lw["wgu"], self.act, self.lff, e, col0=sh.rank * self.lff,
+                         out_stride=cfg.ff, flags=K.NORM | K.SILU_PAIR, eps=cfg.eps, half=self.lff,
+                         norm_w=lw["ffn_norm"])
+            self._gather(self.act, cfg.ff)
+            # 7. Wdown rows of this rank, accumulated
+            self._matvec(cfg.body_type, self.act, lw["wdown"], self.x, self.le, cfg.ff, col0=sh.rank * self.le,
+                         out_stride=e, flags=K.ACCUMULATE)
+            self._gather(self.x, e)
+        # output norm fused into the LM head
+        self._matvec(cfg.head_type, self.x, self.w["head"], self.logits, self.lv, e, col0=sh.rank * self.lv,
+                     out_stride=cfg.vocab, flags=K.NORM, eps=cfg.eps, norm_w=self.w["out_norm"])
+        self._gather(self.logits, cfg.vocab)
+
+    def algorithmic_bytes(self, positions: np.ndarray) -> dict:
+        """Bytes one step must move on this rank: every weight once, K and V of every cached position."""
+        cfg = self.cfg
+        shapes = layer_weight_shapes(cfg, self.sh)
+        body = sum(r * K.row_bytes(cfg.body_type, k) for r, k in shapes.values()) * cfg.layers
+        head = self.lv * K.row_bytes(cfg.head_type, cfg.hidden)
+        kv = sum(2 * (int(p) + 1) * self.lg * cfg.head_dim * 2 for p in positions) * cfg.layers
+        return {"weights": body + head, "kv": kv, "total": body + head + kv}
