@@ -144,13 +144,13 @@ class MatvecQ4K:
     n, k = 14336, 4096
     name = "matvec_q4_k"
 
-    def __init__(self, dist: Dist, batch: int = 1):
+    def __init__(self, dist: Dist, batch: int = 1, variant: int = 0):
         import torch
 
         from zllm_b200 import abi, synth
         from zllm_b200 import kernels as K
 
-        self.torch, self.K, self.dist, self.batch = torch, K, dist, batch
+        self.torch, self.K, self.dist, self.batch, self.variant = torch, K, dist, batch, variant
         self.dev = torch.device("cuda", dist.local)
         torch.cuda.set_device(self.dev)
         self.stream = torch.cuda.Stream(self.dev)
@@ -193,11 +193,12 @@ class MatvecQ4K:
             if self.dist.on:
                 dst = (self.local_out[c].data_ptr(), self.local_out[c].numel() * 4)
                 self.launcher.matvec("q4_k", (self.x.data_ptr(), self.x.numel() * 4),
-                                     (self.w[c].data_ptr(), self.w[c].numel()), dst, self.rows, self.k, m=self.batch)
+                                     (self.w[c].data_ptr(), self.w[c].numel()), dst, self.rows, self.k, m=self.batch, variant=self.variant)
             else:
                 self.launcher.matvec("q4_k", (self.x.data_ptr(), self.x.numel() * 4),
                                      (self.w[c].data_ptr(), self.w[c].numel()),
-                                     (self.out[c].data_ptr(), self.out[c].numel() * 4), self.n, self.k, m=self.batch)
+                                     (self.out[c].data_ptr(), self.out[c].numel() * 4), self.n, self.k, m=self.batch,
+                                     variant=self.variant)
 
     def step(self):
         """One pass over every weight copy, inputs resident in HBM."""
@@ -277,7 +278,7 @@ def run_cuda(args):
     import torch
 
     dist = Dist(args.gpus)
-    wl = WORKLOADS[args.workload](dist)
+    wl = WORKLOADS[args.workload](dist, batch=args.batch, variant=int(args.variant, 0))
     torch.cuda.set_device(dist.local)
     for _ in range(max(args.warmup, 3)):
         wl.step()
@@ -322,7 +323,7 @@ def run_cuda(args):
         "clocks": clocks,
         "e2e": {"value": wl.value(e2e_s / args.steps), "unit": unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "gpu_launches": launches,
-        "roofline": {"bound": "hbm", "kernel": "matvec_mma<Q4_K>", "achieved": achieved, "peak": peak, "unit": "GB/s",
+        "roofline": {"bound": "hbm", "kernel": "matvec_imma<Q4_K>", "achieved": achieved, "peak": peak, "unit": "GB/s",
                      "frac": achieved / peak, "peak_kind": f"of {peak_kind}", "frac_of_8000_nominal": achieved / 8000.0,
                      "traffic": None, "bytes_per_launch": wl.bytes_per_launch(), "us_per_launch": per_launch_s * 1e6},
     }
@@ -376,6 +377,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--workload", default="matvec_q4_k", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="cuda", choices=["cuda", "reference"])
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--variant", default="0", help="matvec variant word (see include/zllm_cuda.h)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
     args = ap.parse_args()
     if args.impl == "reference":

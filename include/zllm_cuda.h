@@ -88,8 +88,9 @@ enum {
 /* Variant ids of a matvec pipeline (create_kernel's `variant`). 0 is the
  * default. The reference packs (wg/32) | lanes<<8 | rows<<16 | act_div<<24
  * (src/kernels/kernels.zig:330-333); this backend reads the same word as
- * rows-per-CTA tile count (byte 0), in-CTA split-K (byte 1), and kernel
- * family (byte 2: 1 = scalar f32 FMA, 2 = tensor-core fragments). Reserved
+ * weight tiles in flight per warp (byte 0: 2, 4 or 6; 0 = as deep as fits),
+ * byte 1 reserved (0), and kernel family (byte 2: 1 = scalar f32 FMA,
+ * 2 = integer tensor-core fragments). Reserved
  * prefill rungs keep the reference's ids (src/kernels/kernels.zig:798-822). */
 #define ZCU_VARIANT(tiles, splitk, family) ((uint32_t)(tiles) | ((uint32_t)(splitk) << 8) | ((uint32_t)(family) << 16))
 #define ZCU_FAMILY_SCALAR 1u

@@ -40,8 +40,13 @@ def truth(ref, x, mat, norm_w=None, eps=0.0):
     return xs @ mat.dense().astype(np.float64).T
 
 
-def variants_for(ttype):
-    return QUANT_VARIANTS if ttype in ("q4_k", "q8_0") else [0]
+def variants_for(ttype, k=1024):
+    if ttype == "q4_k":
+        return QUANT_VARIANTS
+    if ttype == "q8_0":
+        # the tensor-core family takes Q8_0 rows of whole 128-weight tiles; the default falls back to scalar
+        return QUANT_VARIANTS if k % 128 == 0 else [0, K.variant(0, 0, K.FAMILY_SCALAR)]
+    return [0]
 
 
 @pytest.mark.parametrize("ttype", ["q4_k", "q8_0", "bf16", "f16"])
@@ -90,7 +95,7 @@ def test_matvec_silu_pair_and_tiles(ref, gpu, launcher, ttype, k):
     gate, up = full[:, :pairs], full[:, pairs:]
     want = gate / (1 + np.exp(-gate)) * up
     dx, dw = gpu.put(x), gpu.put(wbytes)
-    for v in variants_for(ttype):
+    for v in variants_for(ttype, k):
         out = gpu.zeros(m * pairs * 4)
         launcher.matvec(ttype, dx, dw, out, pairs, k, m=m, flags=K.SILU_PAIR, half=pairs, variant=v)
         got = out.download(np.float32).reshape(m, pairs)

@@ -35,7 +35,7 @@ def _stale(target: Path, deps: list[Path]) -> bool:
 
 def build(verbose: bool = False, force: bool = False) -> Path:
     OBJ.mkdir(exist_ok=True)
-    headers = sorted(CSRC.glob("*.h")) + sorted((HERE.parent / "include").glob("*.h"))
+    headers = sorted(CSRC.glob("*.h")) + sorted(CSRC.glob("*.cuh")) + sorted((HERE.parent / "include").glob("*.h"))
     jobs = []
     for src in sources():
         obj = OBJ / (src.stem + ".o")

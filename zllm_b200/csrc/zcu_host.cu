@@ -97,6 +97,7 @@ struct zcu_context {
     bool capturing = false;
     std::vector<cudaGraphExec_t> graphs;
     uint8_t* pinned = nullptr;  // staging for uploads and readbacks
+    int* status = nullptr;      // mapped host word kernels set when a bounded wait gives up
     size_t pinned_cap = 0;
 };
 
@@ -173,6 +174,10 @@ zcu_result wait_stream(zcu_context* c, uint32_t timeout_ms) {
         }
     }
     cudaEventDestroy(ev);
+    if (c->status && *(volatile int*)c->status != 0) {
+        *c->status = 0;
+        return fail(c, ZCU_E_GPU, "a kernel gave up a bounded wait (a copy or a peer never arrived); its results are invalid");
+    }
     return ZCU_OK;
 }
 
@@ -189,6 +194,7 @@ zcu_result dispatch_kernel(zcu_context* c, uint32_t kernel, uint32_t variant, co
     a.grid[2] = grid[2];
     a.variant = variant;
     a.sm_count = c->dry ? 148 : c->prop.multiProcessorCount;
+    a.status = c->status;
     a.err = c->err;
     a.err_cap = sizeof(c->err);
     char name[64];
@@ -689,6 +695,12 @@ ZCU_EXPORT zcu_result zcu_create(const zcu_options* options, zcu_context** out_c
             }
             c->own_stream = true;
         }
+        if (cudaHostAlloc((void**)&c->status, 64, cudaHostAllocMapped) != cudaSuccess) {
+            cudaGetLastError();
+            c->status = nullptr;
+        } else {
+            *c->status = 0;
+        }
     }
     *out_context = c;
     return ZCU_OK;
@@ -709,6 +721,7 @@ ZCU_EXPORT zcu_result zcu_destroy(zcu_context* c, uint32_t timeout_ms) {
             else cudaFree(c->buffers[i].ptr);
         }
     if (c->pinned) cudaFreeHost(c->pinned);
+    if (c->status) cudaFreeHost(c->status);
     if (c->own_stream) cudaStreamDestroy(c->stream);
     delete c;
     return ZCU_OK;

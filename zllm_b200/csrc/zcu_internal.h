@@ -96,6 +96,7 @@ struct LaunchArgs {
     uint32_t grid[3];              // the reference's workgroup grid
     uint32_t variant;
     int sm_count;
+    int* status;                   // device-visible word a kernel sets when a bounded wait gives up
     char* err;                     // message buffer on failure
     size_t err_cap;
 };

@@ -41,7 +41,8 @@ def variant(tiles: int = 0, splitk: int = 0, family: int = 0) -> int:
 
 
 # Candidates the tuning sweep tries (the cuda arm of MatvecVariant.candidates).
-MATVEC_CANDIDATES = [variant(0, ks, FAMILY_MMA) for ks in (1, 2, 4, 8)] + [variant(0, 0, FAMILY_SCALAR)]
+# Tensor-core family: tiles in flight per warp (byte 0); scalar family: one shape.
+MATVEC_CANDIDATES = [variant(st, 0, FAMILY_MMA) for st in (2, 4, 6)] + [variant(0, 0, FAMILY_SCALAR)]
 
 u32, f32 = C.c_uint32, C.c_float
 
