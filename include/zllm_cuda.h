@@ -167,6 +167,12 @@ size_t zcu_artifact(uint32_t kernel, uint32_t variant, char *out, size_t capacit
 /* Device.supportsPrefill(rung) (src/gpu/host.zig:120-128): 1 or 0. */
 int32_t zcu_supports_prefill(zcu_context *context, uint32_t rung_variant);
 
+/* The RoPE table rope_append reads: f32 (cos, sin) at (pos * n_rot/2 + i) * 2 with
+ * theta = pos * base^(-2i/n_rot) / factors[i], all in f32 (kernels.ropeTableScaled,
+ * src/kernels/kernels.zig:730-744; formula of src/ref/ops.zig:95-99). `factors` may be NULL.
+ * Host code only: no device is touched. */
+zcu_result zcu_rope_table(float *out, uint32_t positions, uint32_t n_rot, float base, const float *factors);
+
 /* ---- command stream (replaces Host.execute/setFile/startProfile/stopProfile/timings,
  *      src/gpu/host.zig:138-191; semantics of src/agility/host.zig:293-607) */
 /* `words` is one batch (src/gpu/cmd.zig:9-13). Blocks at every submit until the

@@ -1,0 +1,119 @@
+"""One decode step of a small Llama-shaped Q4_K model through the plan's launch list, against the CPU oracle's
+layer-by-layer restatement of src/ref/dense.zig (each sequence on its own, shared weights)."""
+import numpy as np
+import pytest
+
+from tests.util import rel_err, rel_l2
+from zllm_b200 import kernels as K
+from zllm_b200 import model as M
+from zllm_b200.plan import DenseConfig, DenseProgram
+
+pytestmark = pytest.mark.gpu
+
+CFG = DenseConfig(layers=3, hidden=512, heads=8, kv_heads=2, head_dim=64, ff=1024, vocab=1536, rope_base=500000.0,
+                  eps=1e-5, max_ctx=320)
+
+
+def oracle_step(ref, cfg, host, token, pos, kc, vc):
+    """Logits of one sequence: embedding row, every layer on the sequence's cache, output norm + head."""
+    e, hd = cfg.hidden, cfg.head_dim
+    x = ref.dequantize(ref.Q4_K, host["embed"][token], e)
+    for il, lw in enumerate(host["layers"]):
+        rows = lw["wqkv"]
+        layer = {
+            "attn_norm": lw["attn_norm"], "ffn_norm": lw["ffn_norm"],
+            "wq": ref.Matrix(ref.Q4_K, rows[:cfg.q_dim], cfg.q_dim, e),
+            "wk": ref.Matrix(ref.Q4_K, rows[cfg.q_dim:cfg.q_dim + cfg.kv_dim], cfg.kv_dim, e),
+            "wv": ref.Matrix(ref.Q4_K, rows[cfg.q_dim + cfg.kv_dim:], cfg.kv_dim, e),
+            "wo": ref.Matrix(ref.Q4_K, lw["wo"], e, cfg.q_dim),
+            "gate": ref.Matrix(ref.Q4_K, lw["wgu"][:cfg.ff], cfg.ff, e),
+            "up": ref.Matrix(ref.Q4_K, lw["wgu"][cfg.ff:], cfg.ff, e),
+            "down": ref.Matrix(ref.Q4_K, lw["wdown"], e, cfg.ff),
+        }
+        x = ref.dense_decode_layer(layer, x, kc[il], vc[il], pos, cfg.heads, cfg.kv_heads, hd, cfg.ff, cfg.eps,
+                                   cfg.rope_base, K.attention_scale(hd))
+    head = ref.Matrix(ref.Q8_0, host["head"], cfg.vocab, e)
+    return ref.dense_head(x, host["out_norm"], head, cfg.eps), x
+
+
+@pytest.mark.parametrize("batch", [1, 3])
+def test_decode_step_matches_oracle(ref, gpu, batch):
+    cfg = CFG
+    host = M.host_model(cfg, "tiny")
+    weights = M.upload(host, cfg, gpu.put)
+    prog = DenseProgram(gpu, cfg, weights, batch, gpu.zeros)
+    prog.set_rope_table(gpu.put(DenseProgram.rope_table(cfg)))
+    assert np.array_equal(DenseProgram.rope_table(cfg), ref.rope_table(cfg.max_ctx, cfg.head_dim, cfg.rope_base))
+    rng = np.random.default_rng(batch)
+    positions = np.array([150, 7, 299][:batch], dtype=np.uint32)
+    tokens = rng.integers(0, cfg.vocab, size=batch).astype(np.uint32)
+    # a cache of N(0,1) f16 values before each sequence's position
+    kv_shape = (batch, cfg.max_ctx, cfg.kv_heads, cfg.head_dim)
+    kc_host = [rng.normal(size=kv_shape).astype(np.float16) for _ in range(cfg.layers)]
+    vc_host = [rng.normal(size=kv_shape).astype(np.float16) for _ in range(cfg.layers)]
+    for il in range(cfg.layers):
+        prog.kc[il].upload(kc_host[il].view(np.uint16))
+        prog.vc[il].upload(vc_host[il].view(np.uint16))
+    prog.write_step(tokens, positions)
+    prog.record_step(int(positions.max()) + 1)
+    gpu.sync()
+    logits = prog.logits.download(np.float32).reshape(batch, cfg.vocab)
+    hidden = prog.x.download(np.float32).reshape(batch, cfg.hidden)
+    assert prog.launches_per_step == 1 + 7 * cfg.layers + 1
+    for b in range(batch):
+        kc = [np.ascontiguousarray(kc_host[il][b]).view(np.uint16).copy() for il in range(cfg.layers)]
+        vc = [np.ascontiguousarray(vc_host[il][b]).view(np.uint16).copy() for il in range(cfg.layers)]
+        want_logits, want_x = oracle_step(ref, cfg, host, int(tokens[b]), int(positions[b]), kc, vc)
+        # the reference's model-tier bounds for a decode step: rel-L2 <= 1e-4, cosine >= 0.999999
+        assert rel_l2(hidden[b], want_x) < 1e-4, (b, rel_l2(hidden[b], want_x))
+        assert rel_l2(logits[b], want_logits) < 1e-4
+        cos = float(np.dot(logits[b], want_logits) / (np.linalg.norm(logits[b]) * np.linalg.norm(want_logits)))
+        assert cos > 0.999999
+        assert int(np.argmax(logits[b])) == int(np.argmax(want_logits))
+        # the step appended this token's K and V (f16, RNE) at its position, and nothing else
+        p = int(positions[b])
+        for il in (0, cfg.layers - 1):
+            got_k = prog.kc[il].download(np.uint16).reshape(kv_shape)[b]
+            assert np.array_equal(got_k[p], kc[il].reshape(cfg.max_ctx, cfg.kv_heads, cfg.head_dim)[p])
+            mask = np.ones(cfg.max_ctx, dtype=bool)
+            mask[p] = False
+            assert np.array_equal(got_k[mask], kc_host[il][b].view(np.uint16)[mask])
+
+
+def test_decode_step_graph_replay_and_batch_rows_are_independent(ref, gpu):
+    # A captured step replays with new tokens/positions written to the step buffers, and every sequence of a
+    # batch equals the same sequence run alone, bit for bit.
+    cfg = CFG
+    host = M.host_model(cfg, "tiny")
+    weights = M.upload(host, cfg, gpu.put)
+    rng = np.random.default_rng(5)
+    batch = 4
+    positions = np.array([40, 41, 100, 5], dtype=np.uint32)
+    tokens = rng.integers(0, cfg.vocab, size=batch).astype(np.uint32)
+    kv_shape = (batch, cfg.max_ctx, cfg.kv_heads, cfg.head_dim)
+    kc_host = [rng.normal(size=kv_shape).astype(np.float16) for _ in range(cfg.layers)]
+    vc_host = [rng.normal(size=kv_shape).astype(np.float16) for _ in range(cfg.layers)]
+
+    def run(seqs, graph):
+        b = len(seqs)
+        prog = DenseProgram(gpu, cfg, weights, b, gpu.zeros)
+        prog.set_rope_table(gpu.put(DenseProgram.rope_table(cfg)))
+        for il in range(cfg.layers):
+            prog.kc[il].upload(np.ascontiguousarray(kc_host[il][seqs]).view(np.uint16))
+            prog.vc[il].upload(np.ascontiguousarray(vc_host[il][seqs]).view(np.uint16))
+        prog.write_step(tokens[seqs], positions[seqs])
+        if graph:
+            gpu.sync()
+            gpu.capture_begin()
+            prog.record_step(cfg.max_ctx)
+            g = gpu.capture_end()
+            gpu.graph_launch(g)
+        else:
+            prog.record_step(int(positions[seqs].max()) + 1)
+        gpu.sync()
+        return prog.logits.download(np.float32).reshape(b, cfg.vocab)
+
+    whole = run([0, 1, 2, 3], graph=True)
+    for s in range(batch):
+        alone = run([s], graph=False)
+        assert np.array_equal(alone[0].view(np.uint32), whole[s].view(np.uint32)), s

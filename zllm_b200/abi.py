@@ -34,7 +34,7 @@ EXPORTS = [
     "zcu_backend_source", "zcu_artifact", "zcu_supports_prefill", "zcu_execute", "zcu_set_file",
     "zcu_start_profile", "zcu_stop_profile", "zcu_read_timings", "zcu_alloc", "zcu_free", "zcu_upload",
     "zcu_download", "zcu_memset", "zcu_launch", "zcu_sync", "zcu_launch_count", "zcu_capture_begin",
-    "zcu_capture_end", "zcu_graph_launch", "zcu_graph_destroy",
+    "zcu_capture_end", "zcu_graph_launch", "zcu_graph_destroy", "zcu_rope_table",
 ]
 
 
@@ -112,6 +112,7 @@ def lib() -> C.CDLL:
         "zcu_capture_end": (C.c_int32, [vp, C.POINTER(u32)]),
         "zcu_graph_launch": (C.c_int32, [vp, u32]),
         "zcu_graph_destroy": (C.c_int32, [vp, u32]),
+        "zcu_rope_table": (C.c_int32, [vp, u32, u32, C.c_float, vp]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(L, name)
@@ -126,6 +127,16 @@ def artifact(kernel: int, variant: int = 0) -> bytes:
     buf = C.create_string_buffer(64)
     n = lib().zcu_artifact(kernel, variant, buf, 64)
     return buf.value if n else b""
+
+
+def rope_table(positions: int, n_rot: int, base: float, factors=None) -> np.ndarray:
+    """kernels.ropeTableScaled: the (cos, sin) table rope_append reads, built on the host in f32."""
+    out = np.empty(positions * (n_rot // 2) * 2, dtype=np.float32)
+    f = None if factors is None else np.ascontiguousarray(factors, dtype=np.float32)
+    r = lib().zcu_rope_table(out.ctypes.data, positions, n_rot, base, None if f is None else f.ctypes.data)
+    if r != OK:
+        raise ZcuError(r, "zcu_rope_table: bad arguments")
+    return out
 
 
 def backend_source() -> str:

@@ -9,6 +9,7 @@
 // with UnsupportedKernel and drops the submission in progress.
 
 #include <chrono>
+#include <cmath>
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
@@ -787,6 +788,19 @@ ZCU_EXPORT int32_t zcu_supports_prefill(zcu_context* c, uint32_t rung_variant) {
     if (!c || c->lost) return 0;
     (void)rung_variant;
     return 0;
+}
+
+ZCU_EXPORT zcu_result zcu_rope_table(float* out, uint32_t positions, uint32_t n_rot, float base, const float* factors) {
+    if (!out || n_rot == 0 || (n_rot & 1)) return ZCU_E_INVALID;
+    const uint32_t half = n_rot / 2;
+    for (uint32_t pos = 0; pos < positions; pos++)
+        for (uint32_t i = 0; i < half; i++) {
+            const float exponent = -2.0f * (float)i / (float)n_rot;
+            const float theta = (float)pos * powf(base, exponent) / (factors ? factors[i] : 1.0f);
+            out[((size_t)pos * half + i) * 2] = cosf(theta);
+            out[((size_t)pos * half + i) * 2 + 1] = sinf(theta);
+        }
+    return ZCU_OK;
 }
 
 ZCU_EXPORT zcu_result zcu_set_file(zcu_context* c, const void* mapped, uint64_t length, const char* path) {

@@ -164,14 +164,10 @@ class DenseProgram:
 
     @staticmethod
     def rope_table(cfg: DenseConfig) -> np.ndarray:
-        """The reference's table formula in f32: theta = pos * base^(-2i/n_rot) (src/ref/ops.zig:95-99)."""
-        half = cfg.head_dim // 2
-        i = np.arange(half, dtype=np.float32)
-        exponent = (np.float32(-2.0) * i / np.float32(cfg.head_dim)).astype(np.float32)
-        inv = np.power(np.float32(cfg.rope_base), exponent, dtype=np.float32)
-        pos = np.arange(cfg.max_ctx, dtype=np.float32)[:, None]
-        theta = (pos * inv[None, :]).astype(np.float32)
-        return np.stack([np.cos(theta), np.sin(theta)], axis=-1).astype(np.float32).reshape(-1)
+        """The table for every position of the context (normal RoPE, no per-pair factors)."""
+        from . import abi
+
+        return abi.rope_table(cfg.max_ctx, cfg.head_dim, cfg.rope_base)
 
     def write_step(self, tokens: np.ndarray, positions: np.ndarray):
         """The step's inputs: one token id and one position per sequence."""
