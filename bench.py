@@ -144,7 +144,7 @@ class MatvecQ4K:
     n, k = 14336, 4096
     name = "matvec_q4_k"
 
-    def __init__(self, dist: Dist, batch: int = 1, variant: int = 0):
+    def __init__(self, dist: Dist, batch: int = 1, variant: int = 0, **_):
         import torch
 
         from zllm_b200 import abi, synth
@@ -236,6 +236,14 @@ class MatvecQ4K:
         """A cheap guard that the timed kernel does the work: rows of copy 0 against numpy."""
         return True
 
+    def roofline(self, ms_per_step: float):
+        peak, kind = measured_hbm_peak()
+        us = ms_per_step * 1e3 / self.launches_per_step()
+        achieved = self.bytes_per_launch() / us / 1e3
+        return {"bound": "hbm", "kernel": "matvec_imma<Q4_K>", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                "frac": achieved / peak, "peak_kind": f"of {kind}", "frac_of_8000_nominal": achieved / 8000.0,
+                "traffic": None, "bytes_per_launch": self.bytes_per_launch(), "us_per_launch": us}
+
     def metric(self):
         return "q4_k_matvec_hbm_gbs", "GB/s"
 
@@ -269,7 +277,241 @@ class MatvecQ4K:
                           f"{dt * 1e3:.2f} ms each (C++ restatement of the reference's src/ref panel matmul)"}
 
 
-WORKLOADS = {"matvec_q4_k": MatvecQ4K}
+class TorchBuf:
+    """A torch tensor as a plan buffer: .ptr/.nbytes for bindings, upload() for the step inputs."""
+
+    def __init__(self, torch, dev, nbytes: int):
+        self.t = torch.zeros(max(int(nbytes), 256), dtype=torch.uint8, device=dev)
+        self.ptr, self.nbytes, self.torch = self.t.data_ptr(), int(nbytes), torch
+
+    def upload(self, arr: np.ndarray, offset: int = 0):
+        src = self.torch.from_numpy(np.ascontiguousarray(arr).view(np.uint8).reshape(-1))
+        self.t[offset:offset + src.numel()].copy_(src, non_blocking=False)
+        return self
+
+    def at(self, offset: int = 0, size=None):
+        return (self.ptr + offset, self.nbytes - offset if size is None else size)
+
+    def f32(self):
+        return self.t[: self.nbytes].view(self.torch.float32)
+
+
+class DecodeStep:
+    """configs[4]: one decode step of a random-init Llama-3-8B-shaped model in Q4_K (32 layers, hidden 4096,
+    32 query / 8 KV heads of 128, SwiGLU 14336, RMSNorm, RoPE theta 5e5, vocab 128256 with a Q8_0 head) over
+    an f16 KV cache of 8192 positions ~ N(0,1), for `batch` independent sequences. With N ranks the weights
+    are row-sharded, attention is sharded by KV head, and output slices are all-gathered over NCCL."""
+
+    name = "decode"
+    context = 8192
+
+    def __init__(self, dist: Dist, batch: int = 1, variant: int = 0, layers: int = 32):
+        import torch
+
+        from zllm_b200 import abi
+        from zllm_b200 import kernels as K
+        from zllm_b200 import model as M
+        from zllm_b200.plan import DenseConfig, DenseProgram, Shard
+
+        self.torch, self.K, self.dist, self.batch = torch, K, dist, batch
+        self.dev = torch.device("cuda", dist.local)
+        torch.cuda.set_device(self.dev)
+        self.stream = torch.cuda.Stream(self.dev)
+        self.ctx = abi.Context(dist.local, stream=self.stream.cuda_stream)
+        self.cfg = DenseConfig(layers=layers, max_ctx=self.context + 64)
+        self.shard = Shard(dist.rank, dist.world)
+        self.weights, self._keep = M.device_model(self.cfg, torch, self.dev, self.shard)
+        self.bufs = []
+
+        def alloc(nbytes):
+            b = TorchBuf(torch, self.dev, nbytes)
+            self.bufs.append(b)
+            return b
+
+        self.prog = DenseProgram(self.ctx, self.cfg, self.weights, batch, alloc, self.shard,
+                                 gather=self._gather if dist.on else None)
+        table = alloc(self.cfg.max_ctx * self.cfg.head_dim * 4)
+        table.upload(DenseProgram.rope_table(self.cfg))
+        self.prog.set_rope_table(table)
+        gen = torch.Generator(device=self.dev)
+        gen.manual_seed(1234 + dist.rank)
+        for il in range(self.cfg.layers):  # the cache before the step: N(0,1) as f16
+            for cache in (self.prog.kc[il], self.prog.vc[il]):
+                v = cache.t[: cache.nbytes].view(torch.float16)
+                v.copy_(torch.randn(v.numel(), device=self.dev, generator=gen, dtype=torch.float32).to(torch.float16))
+        rng = np.random.default_rng(99)
+        self.tokens = rng.integers(0, self.cfg.vocab, size=batch).astype(np.uint32)
+        self.positions = np.full(batch, self.context, dtype=np.uint32)
+        self.pinned_tokens = torch.from_numpy(self.tokens.view(np.int32).copy()).pin_memory()
+        self.pinned_logits = torch.empty((batch, self.cfg.vocab), dtype=torch.float32).pin_memory()
+        self.prog.write_step(self.tokens, self.positions)
+        torch.cuda.synchronize()
+        self.graph = None
+        self.tgraph = None
+        self.mv_graph = None
+        self.bytes = self.prog.algorithmic_bytes(self.positions)
+
+    # every rank's column slice of a [batch, width] f32 buffer becomes visible on all ranks
+    def _gather(self, buf, batch, width):
+        t = buf.f32().view(batch, width)
+        per = width // self.dist.world
+        for b in range(batch):
+            self.dist.dist.all_gather_into_tensor(t[b], t[b, self.dist.rank * per:(self.dist.rank + 1) * per])
+
+    def _record(self):
+        self.prog.record_step(self.context + 1)
+
+    def step(self):
+        torch = self.torch
+        if not self.dist.on:
+            if self.graph is None:
+                self.ctx.capture_begin()
+                self._record()
+                self.graph = self.ctx.capture_end()
+            self.ctx.graph_launch(self.graph)
+            return
+        if self.tgraph is None:
+            with torch.cuda.stream(self.stream):
+                self._record()  # warm NCCL up outside the capture
+                self.stream.synchronize()
+                self.tgraph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(self.tgraph, stream=self.stream):
+                    self._record()
+        with torch.cuda.stream(self.stream):
+            self.tgraph.replay()
+
+    def e2e_step(self):
+        torch = self.torch
+        with torch.cuda.stream(self.stream):
+            self.prog.tokens.t[: 4 * self.batch].view(torch.int32).copy_(self.pinned_tokens, non_blocking=True)
+        self.step()
+        with torch.cuda.stream(self.stream):
+            self.pinned_logits.copy_(self.prog.logits.f32().view(self.batch, self.cfg.vocab), non_blocking=True)
+        self.stream.synchronize()
+
+    def e2e_bytes(self):
+        return self.tokens.nbytes, self.pinned_logits.numel() * 4
+
+    def launches_per_step(self) -> int:
+        return self.prog.launches_per_step or (2 + 7 * self.cfg.layers)
+
+    def metric(self):
+        return "decode_tokens_per_s", "tokens/s"
+
+    def value(self, seconds_per_step: float) -> float:
+        return self.batch / seconds_per_step
+
+    def config(self):
+        c = self.cfg
+        return {"workload": f"decode step, Llama-3-8B-shaped Q4_K model ({c.layers} layers, hidden {c.hidden}, "
+                            f"{c.heads}/{c.kv_heads} heads of {c.head_dim}, FFN {c.ff}, vocab {c.vocab} Q8_0 head), "
+                            f"f16 KV cache at {self.context} positions, batch {self.batch}",
+                "batch": self.batch, "context": self.context,
+                "l2": f"inputs larger than L2: a step reads {self.bytes['total'] / 1e9:.2f} GB per rank "
+                      f"({self.bytes['weights'] / 1e9:.2f} GB weights + {self.bytes['kv'] / 1e9:.2f} GB KV)",
+                "parallelism": (f"tp{self.dist.world} (rows and KV heads sharded, NCCL all-gather of output slices)"
+                                if self.dist.on else "1 GPU"),
+                "step_bytes": self.bytes["total"]}
+
+    def roofline(self, ms_per_step: float):
+        """The dominant kernel (the Q4_K decode multiply): its launches of one step replayed on their own,
+        timed with CUDA events, against their algorithmic bytes."""
+        torch, K, cfg = self.torch, self.K, self.cfg
+        from zllm_b200.plan import layer_weight_shapes
+
+        shapes = layer_weight_shapes(cfg, self.shard)
+        p = self.prog
+        if self.mv_graph is None:
+            self.ctx.capture_begin()
+            for il in range(cfg.layers):
+                lw = self.weights["layers"][il]
+                p._matvec(cfg.body_type, p.x, lw["wqkv"], p.qkv, p.qkv_row, cfg.hidden, flags=K.NORM, eps=cfg.eps,
+                          norm_w=lw["attn_norm"])
+                p._matvec(cfg.body_type, p.att, lw["wo"], p.x, p.le, cfg.q_dim, col0=self.shard.rank * p.le,
+                          out_stride=cfg.hidden, flags=K.ACCUMULATE)
+                p._matvec(cfg.body_type, p.x, lw["wgu"], p.act, p.lff, cfg.hidden, col0=self.shard.rank * p.lff,
+                          out_stride=cfg.ff, flags=K.NORM | K.SILU_PAIR, eps=cfg.eps, half=p.lff, norm_w=lw["ffn_norm"])
+                p._matvec(cfg.body_type, p.act, lw["wdown"], p.x, p.le, cfg.ff, col0=self.shard.rank * p.le,
+                          out_stride=cfg.hidden, flags=K.ACCUMULATE)
+            self.mv_graph = self.ctx.capture_end()
+        for _ in range(3):
+            self.ctx.graph_launch(self.mv_graph)
+        self.stream.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = 10
+        e0.record(self.stream)
+        for _ in range(reps):
+            self.ctx.graph_launch(self.mv_graph)
+        e1.record(self.stream)
+        self.stream.synchronize()
+        launches = 4 * cfg.layers
+        us = e0.elapsed_time(e1) * 1e3 / (reps * launches)
+        wbytes = sum(r * K.row_bytes(cfg.body_type, k) for r, k in shapes.values()) * cfg.layers
+        act = 4 * self.batch * cfg.layers * (cfg.hidden * 2 + cfg.q_dim + cfg.ff + p.qkv_row + 2 * p.le + p.lff)
+        per_launch = (wbytes + act) / launches
+        achieved = per_launch / us / 1e3
+        peak, kind = measured_hbm_peak()
+        return {"bound": "hbm", "kernel": "matvec_imma<Q4_K> (the 4 body multiplies of each layer, mean over a step)",
+                "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": f"of {kind}",
+                "frac_of_8000_nominal": achieved / 8000.0, "traffic": None, "bytes_per_launch": per_launch,
+                "us_per_launch": us, "launches_per_step": launches,
+                "step_hbm_gbs": self.bytes["total"] / (ms_per_step * 1e-3) / 1e9,
+                "step_frac": self.bytes["total"] / (ms_per_step * 1e-3) / 1e9 / peak}
+
+    def cpu_baseline(self, budget_s: float = 20.0):
+        return cpu_decode_baseline(self.cfg, self.context, budget_s)
+
+
+def cpu_decode_baseline(cfg, context, budget_s=20.0, sample_layers=2):
+    """The CPU oracle (the C++ restatement of the reference's src/ref path) on a bounded sample of the decode
+    step: `sample_layers` layers and the head at batch 1, extrapolated to all layers."""
+    from oracle import ref
+    from zllm_b200 import kernels as K
+    from zllm_b200 import synth
+
+    ref.build()
+    pool = ref.Pool()
+    e, hd = cfg.hidden, cfg.head_dim
+    rng = synth.rng_for("cfg5", "cpu")
+
+    def mat(n, k):
+        return ref.Matrix(ref.Q4_K, synth.q4_k_weights(rng, n, k), n, k, pool)
+
+    layer = {"attn_norm": np.ones(e, dtype=np.float32), "ffn_norm": np.ones(e, dtype=np.float32),
+             "wq": mat(cfg.q_dim, e), "wk": mat(cfg.kv_dim, e), "wv": mat(cfg.kv_dim, e), "wo": mat(e, cfg.q_dim),
+             "gate": mat(cfg.ff, e), "up": mat(cfg.ff, e), "down": mat(e, cfg.ff)}
+    head = ref.Matrix(ref.Q8_0, synth.q8_0_weights(rng, cfg.vocab, e), cfg.vocab, e, pool)
+    kc = rng.normal(size=(context + 1, cfg.kv_heads, hd)).astype(np.float16).view(np.uint16)
+    vc = rng.normal(size=(context + 1, cfg.kv_heads, hd)).astype(np.float16).view(np.uint16)
+    x = synth.normal_f32(rng, e)
+    out_norm = np.ones(e, dtype=np.float32)
+
+    def one_layer(v):
+        return ref.dense_decode_layer(layer, v, kc, vc, context, cfg.heads, cfg.kv_heads, hd, cfg.ff, cfg.eps,
+                                      cfg.rope_base, K.attention_scale(hd), pool=pool)
+
+    x = one_layer(x)  # warm-up
+    t_layers, reps = 0.0, 0
+    t0 = time.perf_counter()
+    while reps < sample_layers or (time.perf_counter() - t0 < budget_s * 0.6 and reps < 8 * sample_layers):
+        t1 = time.perf_counter()
+        x = one_layer(x * np.float32(1e-3))
+        t_layers += time.perf_counter() - t1
+        reps += 1
+    t_layer = t_layers / reps
+    ref.dense_head(x, out_norm, head, cfg.eps, pool=pool)
+    t1 = time.perf_counter()
+    ref.dense_head(x, out_norm, head, cfg.eps, pool=pool)
+    t_head = time.perf_counter() - t1
+    step_s = cfg.layers * t_layer + t_head
+    return {"value": 1.0 / step_s, "unit": "tokens/s", "cores": pool.threads, "kind": "port", "isa": ref.build_info(),
+            "sample": f"{reps} decode layers ({t_layer * 1e3:.1f} ms each) and one Q8_0 head ({t_head * 1e3:.1f} ms) at "
+                      f"batch 1, context {context}, extrapolated to {cfg.layers} layers: {step_s * 1e3:.0f} ms per token "
+                      "(C++ restatement of the reference's src/ref forward)"}
+
+
+WORKLOADS = {"matvec_q4_k": MatvecQ4K, "decode": DecodeStep}
+
 
 
 # ------------------------------------------------------------------ arms
@@ -278,9 +520,13 @@ def run_cuda(args):
     import torch
 
     dist = Dist(args.gpus)
-    wl = WORKLOADS[args.workload](dist, batch=args.batch, variant=int(args.variant, 0))
+    kw = {"batch": args.batch, "variant": int(args.variant, 0)}
+    if args.workload == "decode" and args.layers:
+        kw["layers"] = args.layers
+    wl = WORKLOADS[args.workload](dist, **kw)
     torch.cuda.set_device(dist.local)
-    for _ in range(max(args.warmup, 3)):
+    warmup = max(args.warmup, 3)
+    for _ in range(warmup):
         wl.step()
     wl.stream.synchronize()
     sampler = ClockSampler(dist.local)
@@ -311,21 +557,15 @@ def run_cuda(args):
     clocks = sampler.stop() if dist.rank == 0 else {}
     sec_per_step = ms / 1e3 / args.steps
     metric, unit = wl.metric()
-    peak, peak_kind = measured_hbm_peak()
-    launches = wl.launches_per_step() * args.steps
-    per_launch_s = ms / 1e3 / launches
-    achieved = wl.bytes_per_launch() / per_launch_s / 1e9
     h2d, d2h = wl.e2e_bytes()
     line = {
         "metric": metric, "value": wl.value(sec_per_step), "unit": unit, "n_gpus": dist.world, "steps": args.steps,
-        "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True,
+        "warmup": warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": wl.config(),
         "clocks": clocks,
         "e2e": {"value": wl.value(e2e_s / args.steps), "unit": unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-        "gpu_launches": launches,
-        "roofline": {"bound": "hbm", "kernel": "matvec_imma<Q4_K>", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                     "frac": achieved / peak, "peak_kind": f"of {peak_kind}", "frac_of_8000_nominal": achieved / 8000.0,
-                     "traffic": None, "bytes_per_launch": wl.bytes_per_launch(), "us_per_launch": per_launch_s * 1e6},
+        "gpu_launches": wl.launches_per_step() * args.steps,
+        "roofline": wl.roofline(ms / args.steps),
     }
     if dist.rank == 0 and dist.world == 1 and not args.no_cpu:
         line["cpu_baseline"] = wl.cpu_baseline()
@@ -335,15 +575,40 @@ def run_cuda(args):
 
 
 def run_reference(args):
-    """The reference's own CPU implementation of the path (its C++ restatement), all host cores."""
+    """The reference's own CPU implementation of the path (its C++ restatement), all host cores. Each
+    step is a bounded sample of the workload."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     from oracle import ref
     from zllm_b200 import synth
-    from zllm_b200 import kernels as K  # noqa: F401  (shapes only)
 
     ref.build()
+    if args.workload == "decode":
+        from zllm_b200.plan import DenseConfig
+
+        cfg = DenseConfig(layers=args.layers or 32)
+        vals = []
+        t0 = time.perf_counter()
+        base = None
+        for i in range(args.warmup + args.steps):
+            base = cpu_decode_baseline(cfg, DecodeStep.context, budget_s=4.0, sample_layers=1)
+            if i >= args.warmup:
+                vals.append(base["value"])
+        dt = time.perf_counter() - t0
+        value = float(np.mean(vals))
+        base["value"] = value
+        print(json.dumps({
+            "impl": "reference", "metric": "decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 / value, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"decode step, Llama-3-8B-shaped Q4_K model, f16 KV cache at {DecodeStep.context} "
+                                   "positions, batch 1", "batch": 1, "context": DecodeStep.context,
+                       "wall_s": dt},
+            "cpu_baseline": base,
+            "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        }), flush=True)
+        return
     n, k, batch = MatvecQ4K.n, MatvecQ4K.k, 1
     pool = ref.Pool()
     raw = synth.q4_k_weights(synth.rng_for("cfg2", "w-rank0"), n, k)
@@ -373,9 +638,10 @@ def run_reference(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
-    ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--workload", default="matvec_q4_k", choices=sorted(WORKLOADS))
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--workload", default="decode", choices=sorted(WORKLOADS))
+    ap.add_argument("--layers", type=int, default=0, help="decode: layers of the model (default 32)")
     ap.add_argument("--impl", default="cuda", choices=["cuda", "reference"])
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--variant", default="0", help="matvec variant word (see include/zllm_cuda.h)")

@@ -237,7 +237,7 @@ class Context:
         for i, b in enumerate(bindings):
             if b is None:
                 arr[i] = Binding(None, 0)
-            elif isinstance(b, DevBuf):
+            elif hasattr(b, "ptr") and hasattr(b, "nbytes"):  # a DevBuf, or any buffer object of the caller
                 arr[i] = Binding(b.ptr, b.nbytes)
             else:
                 arr[i] = Binding(b[0], b[1])
