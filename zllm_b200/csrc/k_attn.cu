@@ -406,21 +406,38 @@ __global__ void __launch_bounds__(256) attn_combine_kernel(PAttention p, const f
     __syncthreads();
     for (int b = tid; b < blocks; b += 256) wsm[b] = expf(wsm[b] - mx);
     __syncthreads();
-    if (tid >= hd) return;
+    // Two halves of the blocks per dim (threads d and d + 128 when head_dim <= 128), eight loads in flight
+    // each; the halves are added low half first, so the order of the sum is fixed.
+    const int halves = hd <= 128 ? 2 : 1;
+    const int d = tid % (256 / halves), half = tid / (256 / halves);
+    const int per = (blocks + halves - 1) / halves;
+    const int b0 = half * per, b1 = min(blocks, b0 + per);
     float l = 0.f, o = 0.f;
-    for (int b = 0; b < blocks; b++) {
-        const float w = wsm[b];
-        l = __fmaf_rn(part[base0 + b * bs + 1], w, l);
-        o = __fmaf_rn(part[base0 + b * bs + 2 + tid], w, o);
+    if (d < hd) {
+#pragma unroll 8
+        for (int b = b0; b < b1; b++) {
+            const float w = wsm[b];
+            l = __fmaf_rn(part[base0 + b * bs + 1], w, l);
+            o = __fmaf_rn(part[base0 + b * bs + 2 + d], w, o);
+        }
     }
+    __shared__ float2 hi_half[128];
+    if (half == 1 && d < hd) hi_half[d] = make_float2(l, o);
+    __syncthreads();
+    if (half == 1 || d >= hd) return;
+    if (halves == 2) {
+        l = __fadd_rn(l, hi_half[d].x);
+        o = __fadd_rn(o, hi_half[d].y);
+    }
+    const int tid_d = d;
     // _pad[1] != 0 (extension): floats between output rows, for writing a rank's head columns of a wider row.
     const size_t orow = p._pad[1] ? (size_t)p._pad[1] : (size_t)p.heads * hd;
-    const size_t oi = (size_t)row * orow + (size_t)h * hd + tid;
+    const size_t oi = (size_t)row * orow + (size_t)h * hd + tid_d;
     if (!p.gated) {
         out[oi] = o / l;
         return;
     }
-    const float gate = qg[(size_t)row * p.q_row + (size_t)2 * h * hd + hd + tid];
+    const float gate = qg[(size_t)row * p.q_row + (size_t)2 * h * hd + hd + tid_d];
     out[oi] = o / l / (1.0f + expf(-gate));
 }
 
