@@ -571,6 +571,15 @@ def run_cuda(args):
         line["cpu_baseline"] = wl.cpu_baseline()
     if dist.rank == 0:
         print(json.dumps(line), flush=True)
+    if dist.on:
+        # Leave without tearing NCCL down: captured graphs still hold its kernels, and a teardown that
+        # waits on them has hung here. Every rank is past its last collective.
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
     dist.close()
 
 
