@@ -1,0 +1,140 @@
+"""CPU tier for the multi-GPU path: the plan's sharding arithmetic (which rows, heads and output columns a rank
+owns) and the all-gather plumbing, run as two `gloo` ranks. Each rank computes ITS shard of one decode layer
+with the CPU oracle in the order the sharded program launches its kernels, gathers where the program gathers,
+and the result must equal the unsharded oracle layer."""
+import os
+import tempfile
+
+import numpy as np
+import pytest
+
+from zllm_b200 import kernels as K
+from zllm_b200 import model as M
+from zllm_b200.plan import DenseConfig, Shard, layer_weight_shapes, shard_rows, slice_full_weights
+
+CFG = DenseConfig(layers=1, hidden=512, heads=8, kv_heads=4, head_dim=64, ff=1024, vocab=1024, max_ctx=64)
+
+
+def test_shard_shapes_cover_the_model_exactly():
+    for world in (1, 2, 4):
+        rows = {"wqkv": 0, "wo": 0, "wgu": 0, "wdown": 0}
+        for r in range(world):
+            for name, (n, k) in layer_weight_shapes(CFG, Shard(r, world)).items():
+                rows[name] += n
+        assert rows == {"wqkv": CFG.q_dim + 2 * CFG.kv_dim, "wo": CFG.hidden, "wgu": 2 * CFG.ff, "wdown": CFG.hidden}
+    assert shard_rows(12, 2, 4) == (6, 9)
+    with pytest.raises(AssertionError):
+        shard_rows(10, 0, 4)
+
+
+def test_slices_partition_every_stacked_matrix():
+    # Tag each row of the full matrices with its index; the ranks' slices must hold every row exactly once,
+    # and stacked parts must stay together (a rank's query heads with its KV heads, gate rows with up rows).
+    world = 4
+    full = {"wqkv": np.arange(CFG.q_dim + 2 * CFG.kv_dim)[:, None], "wgu": np.arange(2 * CFG.ff)[:, None],
+            "wo": np.arange(CFG.hidden)[:, None], "wdown": np.arange(CFG.hidden)[:, None], "head": np.arange(CFG.vocab)[:, None]}
+    for name, rows in full.items():
+        got = np.concatenate([slice_full_weights(CFG, Shard(r, world), name, rows) for r in range(world)]).ravel()
+        assert sorted(got.tolist()) == list(range(rows.shape[0])), name
+    sh = Shard(1, world)
+    qkv = slice_full_weights(CFG, sh, "wqkv", full["wqkv"]).ravel()
+    hd, lh, lg = CFG.head_dim, CFG.heads // world, CFG.kv_heads // world
+    assert qkv[0] == 1 * lh * hd and qkv[lh * hd] == CFG.q_dim + 1 * lg * hd
+    assert qkv[(lh + lg) * hd] == CFG.q_dim + CFG.kv_dim + 1 * lg * hd
+    gu = slice_full_weights(CFG, sh, "wgu", full["wgu"]).ravel()
+    lff = CFG.ff // world
+    assert gu[0] == lff and gu[lff] == CFG.ff + lff  # up row j sits `half` = lff rows after gate row j
+
+
+def _rank_main(rank: int, world: int, port: int, out_path: str):
+    import torch
+    import torch.distributed as dist
+
+    from oracle import ref
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    cfg, sh = CFG, Shard(rank, world)
+    e, hd = cfg.hidden, cfg.head_dim
+    host = M.host_model(cfg, "shard-test")
+    lw = host["layers"][0]
+    rng = np.random.default_rng(3)
+    pos = 40
+    x = rng.normal(size=e).astype(np.float32)
+    kc = rng.normal(size=(cfg.max_ctx, cfg.kv_heads, hd)).astype(np.float16)
+    vc = rng.normal(size=(cfg.max_ctx, cfg.kv_heads, hd)).astype(np.float16)
+
+    def gather(local: np.ndarray) -> np.ndarray:
+        parts = [torch.empty(local.size, dtype=torch.float32) for _ in range(world)]
+        dist.all_gather(parts, torch.from_numpy(np.ascontiguousarray(local, dtype=np.float32)))
+        return torch.cat(parts).numpy()
+
+    shapes = layer_weight_shapes(cfg, sh)
+    mats = {name: ref.Matrix(ref.Q4_K, slice_full_weights(cfg, sh, name, lw[name]), *shapes[name])
+            for name in ("wqkv", "wo", "wgu", "wdown")}
+    h0, h1 = sh.heads(cfg)
+    g0, g1 = sh.kv_heads(cfg)
+    lh, lg = h1 - h0, g1 - g0
+    e0, e1 = shard_rows(e, rank, world)
+    lff = cfg.ff // world
+    # 1. qkv of this rank's heads, 2. rope + cache append (its KV heads), 3-4. attention
+    h = ref.rms_norm(x, lw["attn_norm"], cfg.eps)
+    qkv = ref.matmul(h, mats["wqkv"])[0]
+    q = np.stack([ref.rope_normal(qkv[i * hd:(i + 1) * hd], pos, hd, cfg.rope_base) for i in range(lh)])
+    kc_l = np.ascontiguousarray(kc[:, g0:g1]).view(np.uint16).copy()
+    vc_l = np.ascontiguousarray(vc[:, g0:g1]).view(np.uint16).copy()
+    for i in range(lg):
+        k_i = ref.rope_normal(qkv[(lh + i) * hd:(lh + i + 1) * hd], pos, hd, cfg.rope_base)
+        kc_l[pos, i] = ref.to_f16_bits(k_i)
+        vc_l[pos, i] = ref.to_f16_bits(qkv[(lh + lg + i) * hd:(lh + lg + i + 1) * hd])
+    att_local = ref.attend_decode(q, kc_l, vc_l, pos + 1, lh, lg, hd, K.attention_scale(hd))
+    att = gather(att_local.ravel())                                    # gather 1: att
+    # 5. Wo rows of this rank, accumulated into its slice of x
+    x_new = gather(x[e0:e1] + ref.matmul(att, mats["wo"])[0])          # gather 2: x
+    # 6. gate|up rows of this rank with SwiGLU
+    h = ref.rms_norm(x_new, lw["ffn_norm"], cfg.eps)
+    gu = ref.matmul(h, mats["wgu"])[0]
+    lib = ref.lib()
+    act_local = np.array([lib.ref_silu(float(a)) for a in gu[:lff]], dtype=np.float32) * gu[lff:]
+    act = gather(act_local)                                            # gather 3: act
+    # 7. Wdown rows of this rank
+    x_out = gather(x_new[e0:e1] + ref.matmul(act, mats["wdown"])[0])   # gather 4: x
+    if rank == 0:
+        np.save(out_path, x_out)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_gloo_ranks_reproduce_the_unsharded_layer(ref):
+    import torch.multiprocessing as mp
+
+    cfg = CFG
+    e, hd = cfg.hidden, cfg.head_dim
+    with tempfile.TemporaryDirectory() as tmp:
+        out_path = os.path.join(tmp, "x.npy")
+        port = 29600 + os.getpid() % 300
+        mp.spawn(_rank_main, args=(2, port, out_path), nprocs=2, join=True)
+        got = np.load(out_path)
+    host = M.host_model(cfg, "shard-test")
+    lw = host["layers"][0]
+    rng = np.random.default_rng(3)
+    pos = 40
+    x = rng.normal(size=e).astype(np.float32)
+    kc = rng.normal(size=(cfg.max_ctx, cfg.kv_heads, hd)).astype(np.float16).view(np.uint16)
+    vc = rng.normal(size=(cfg.max_ctx, cfg.kv_heads, hd)).astype(np.float16).view(np.uint16)
+    rows = lw["wqkv"]
+    layer = {
+        "attn_norm": lw["attn_norm"], "ffn_norm": lw["ffn_norm"],
+        "wq": ref.Matrix(ref.Q4_K, rows[:cfg.q_dim], cfg.q_dim, e),
+        "wk": ref.Matrix(ref.Q4_K, rows[cfg.q_dim:cfg.q_dim + cfg.kv_dim], cfg.kv_dim, e),
+        "wv": ref.Matrix(ref.Q4_K, rows[cfg.q_dim + cfg.kv_dim:], cfg.kv_dim, e),
+        "wo": ref.Matrix(ref.Q4_K, lw["wo"], e, cfg.q_dim),
+        "gate": ref.Matrix(ref.Q4_K, lw["wgu"][:cfg.ff], cfg.ff, e),
+        "up": ref.Matrix(ref.Q4_K, lw["wgu"][cfg.ff:], cfg.ff, e),
+        "down": ref.Matrix(ref.Q4_K, lw["wdown"], e, cfg.ff),
+    }
+    want = ref.dense_decode_layer(layer, x, kc.copy(), vc.copy(), pos, cfg.heads, cfg.kv_heads, hd, cfg.ff, cfg.eps,
+                                  cfg.rope_base, K.attention_scale(hd))
+    # every output row, head and column is computed by exactly one rank with the same arithmetic: same bits
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
