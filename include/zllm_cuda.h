@@ -207,6 +207,24 @@ zcu_result zcu_sync(zcu_context *context, uint32_t timeout_ms);
 /* Number of kernel launches this context has issued (dry runs count too). */
 uint64_t zcu_launch_count(zcu_context *context);
 
+/* Decode attention (attn_split + attn_combine in one call) that allocates nothing. It has no counterpart
+ * in the reference. It exists for callers that cannot call cudaMalloc: hosts that were handed fixed input
+ * and output buffers and no memory budget of their own, or code on a path where an allocation's implicit
+ * device synchronisation is not acceptable. The per-block partials, which attn_split normally writes to a
+ * caller-allocated buffer, go to a fixed 4 MiB array inside the library instead (held by every GPU that
+ * loads the library until the process exits).
+ *   params:   the reference's Attention block (48 bytes); its max_blocks field is ignored
+ *   bindings: qg, kc, vc, out, step [, per-row positions when params._pad[0] != 0]
+ *   max_keys: the largest position + 1 any row attends to; rows: tokens (or sequences) in the step
+ * Limit: rows * heads * ceil(max_keys / 64) * (head_dim + 2) <= 1 Mi floats, else ZCU_E_INVALID with a
+ * message (e.g. 32 heads of 128 at up to 16 000 positions for one row). The first call on a device looks
+ * the array's address up; make that call before any stream capture. Every call uses the same array, so two
+ * calls that overlap on the GPU (different streams or contexts of one process) race; calls on one stream
+ * do not. Nothing in the array needs clearing between calls: each call writes every slot it later reads. */
+zcu_result zcu_attention_decode_static(zcu_context *context, const void *params, uint32_t params_bytes,
+                                       const zcu_binding *bindings, uint32_t n_bindings, uint32_t max_keys,
+                                       uint32_t rows);
+
 /* Replays of a fixed launch list: everything issued between begin and end
  * is captured into one CUDA graph instead of running. Step-dependent kernels
  * read their Step block (src/kernels/kernels.zig:436) from device memory, so

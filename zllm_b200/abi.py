@@ -35,6 +35,7 @@ EXPORTS = [
     "zcu_start_profile", "zcu_stop_profile", "zcu_read_timings", "zcu_alloc", "zcu_free", "zcu_upload",
     "zcu_download", "zcu_memset", "zcu_launch", "zcu_sync", "zcu_launch_count", "zcu_capture_begin",
     "zcu_capture_end", "zcu_graph_launch", "zcu_graph_destroy", "zcu_rope_table",
+    "zcu_attention_decode_static",
 ]
 
 
@@ -113,6 +114,7 @@ def lib() -> C.CDLL:
         "zcu_graph_launch": (C.c_int32, [vp, u32]),
         "zcu_graph_destroy": (C.c_int32, [vp, u32]),
         "zcu_rope_table": (C.c_int32, [vp, u32, u32, C.c_float, vp]),
+        "zcu_attention_decode_static": (C.c_int32, [vp, vp, u32, C.POINTER(Binding), u32, u32, u32]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(L, name)
@@ -243,6 +245,15 @@ class Context:
                 arr[i] = Binding(b[0], b[1])
         g = (C.c_uint32 * 3)(*grid)
         self._check(lib().zcu_launch(self.h, kernel, variant, pb, len(pb), arr, len(bindings), g))
+
+    def attention_decode_static(self, params, bindings, max_keys: int, rows: int):
+        """attn_split + attn_combine with the partials in the library's fixed 4 MiB array: for callers that
+        cannot allocate device memory. bindings: qg, kc, vc, out, step [, positions]."""
+        pb = bytes(params)
+        arr = (Binding * len(bindings))()
+        for i, b in enumerate(bindings):
+            arr[i] = Binding(b.ptr, b.nbytes) if hasattr(b, "ptr") else Binding(b[0], b[1])
+        self._check(lib().zcu_attention_decode_static(self.h, pb, len(pb), arr, len(bindings), max_keys, rows))
 
     def sync(self, timeout_ms: int = 60000):
         self._check(lib().zcu_sync(self.h, timeout_ms))

@@ -517,3 +517,76 @@ zcu_result launch_attn_combine(const LaunchArgs& a) {
     ZCU_CHECK_LAUNCH(a);
     return ZCU_OK;
 }
+
+// ---------------------------------------------------------------------------------------------------
+// Decode attention for callers that cannot allocate device memory.
+//
+// attn_split hands its per-block partials to attn_combine through a buffer the caller normally
+// allocates. Some callers cannot do that: a host that runs inside somebody else's memory budget
+// (a plugin that was given fixed input/output buffers and nothing more), or code on a path where
+// cudaMalloc is forbidden because it would synchronise the device or break a latency guarantee.
+// For them the partials live in the fixed array below, which is part of the library image: every GPU
+// that loads the library holds these 4 MiB until the process exits.
+//
+// `g_attn_partials` is a device symbol. In host code its name is only a stand-in; the device address
+// comes from cudaGetSymbolAddress, asked once per device with that device current.
+constexpr size_t ATTN_STATIC_FLOATS = (size_t)1 << 20;  // 4 MiB
+static __device__ __align__(256) float g_attn_partials[ATTN_STATIC_FLOATS];
+static float* g_attn_partials_ptr[64] = {};
+
+// Bindings: qg, kc, vc, out, step (+ per-row positions for batched sequences). `max_keys`: the largest
+// number of cache positions any row attends to (its position + 1). The partials are laid out as
+// attn_split lays them out, max_blocks = ceil(max_keys / 64) blocks per (row, head).
+zcu_result launch_attn_static(const LaunchArgs& a, uint32_t max_keys, uint32_t rows) {
+    PAttention p;
+    ZCU_NEED(a, a.params_bytes >= sizeof(p) && a.nb >= 5, "attention (static partials): bad parameter block or bindings");
+    memcpy(&p, a.params, sizeof(p));
+    ZCU_NEED(a, p.kv_heads > 0 && p.heads % p.kv_heads == 0 && max_keys > 0 && rows > 0,
+             "attention (static partials): heads %u over kv_heads %u, %u keys, %u rows", p.heads, p.kv_heads, max_keys, rows);
+    p.max_blocks = (max_keys + AT_BLOCK - 1) / AT_BLOCK;
+    const size_t need = (size_t)rows * p.heads * p.max_blocks * (p.head_dim + 2);
+    if (need > ATTN_STATIC_FLOATS)
+        return zcu_fail(a, ZCU_E_INVALID,
+                        "attention (static partials): %u rows x %u heads x %u blocks x (%u + 2) = %zu floats exceed the fixed "
+                        "%zu-float (4 MiB) array; use attn_split / attn_combine with a buffer of your own",
+                        rows, p.heads, p.max_blocks, p.head_dim, need, ATTN_STATIC_FLOATS);
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= 64) return zcu_fail(a, ZCU_E_GPU, "attention (static partials): no current device");
+    if (!g_attn_partials_ptr[dev]) {
+        // First call on this device: resolve the symbol's device address. Not a stream operation, so it
+        // should happen before any stream capture starts.
+        float* ptr = nullptr;
+        e = cudaGetSymbolAddress((void**)&ptr, g_attn_partials);
+        if (e != cudaSuccess || !ptr)
+            return zcu_fail(a, ZCU_E_GPU, "attention (static partials): cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+        g_attn_partials_ptr[dev] = ptr;
+    }
+    const zcu_binding part = {g_attn_partials_ptr[dev], need * sizeof(float)};
+    const bool batched = a.nb >= 6 && p._pad[0] != 0;
+    // attn_split: qg, kc, vc, part, step [, positions]; grid (kv_heads, 64-key blocks, rows)
+    zcu_binding sb[6] = {a.b[0], a.b[1], a.b[2], part, a.b[4], {nullptr, 0}};
+    if (batched) sb[5] = a.b[5];
+    LaunchArgs s = a;
+    s.params = &p;
+    s.params_bytes = sizeof(p);
+    s.b = sb;
+    s.nb = batched ? 6 : 5;
+    s.grid[0] = p.kv_heads;
+    s.grid[1] = p.max_blocks;
+    s.grid[2] = rows;
+    zcu_result r = launch_attn_split(s);
+    if (r != ZCU_OK) return r;
+    // attn_combine: qg, part, out, step [, positions]; grid (heads, rows)
+    zcu_binding cb[5] = {a.b[0], part, a.b[3], a.b[4], {nullptr, 0}};
+    if (batched) cb[4] = a.b[5];
+    LaunchArgs c = a;
+    c.params = &p;
+    c.params_bytes = sizeof(p);
+    c.b = cb;
+    c.nb = batched ? 5 : 4;
+    c.grid[0] = p.heads;
+    c.grid[1] = rows;
+    c.grid[2] = 1;
+    return launch_attn_combine(c);
+}

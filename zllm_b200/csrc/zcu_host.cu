@@ -931,6 +931,30 @@ ZCU_EXPORT zcu_result zcu_launch(zcu_context* c, uint32_t kernel, uint32_t varia
     if (!params || !grid || (!bindings && n_bindings)) return fail(c, ZCU_E_INVALID, "launch: null argument");
     return dispatch_kernel(c, kernel, variant, params, params_bytes, bindings, n_bindings, grid);
 }
+// Decode attention with the partials in the library's fixed array: no allocation on this path, for
+// callers that cannot allocate (see the header). Not available in a dry run (there is no device array).
+ZCU_EXPORT zcu_result zcu_attention_decode_static(zcu_context* c, const void* params, uint32_t params_bytes,
+                                                  const zcu_binding* bindings, uint32_t n_bindings, uint32_t max_keys,
+                                                  uint32_t rows) {
+    LIVE(c);
+    if (!params || !bindings) return fail(c, ZCU_E_INVALID, "attention (static partials): null argument");
+    if (c->dry) return fail(c, ZCU_E_INVALID, "attention (static partials): needs a device");
+    LaunchArgs a;
+    a.stream = c->stream;
+    a.params = params;
+    a.params_bytes = params_bytes;
+    a.b = bindings;
+    a.nb = n_bindings;
+    a.grid[0] = a.grid[1] = a.grid[2] = 0;
+    a.variant = 0;
+    a.sm_count = c->prop.multiProcessorCount;
+    a.status = c->status;
+    a.err = c->err;
+    a.err_cap = sizeof(c->err);
+    c->launches += 2;
+    return launch_attn_static(a, max_keys, rows);
+}
+
 ZCU_EXPORT zcu_result zcu_sync(zcu_context* c, uint32_t timeout_ms) {
     LIVE(c);
     return wait_stream(c, timeout_ms ? timeout_ms : 60000u);

@@ -118,6 +118,7 @@ zcu_result launch_attn_combine(const LaunchArgs& a);
 zcu_result launch_delta_prep(const LaunchArgs& a);
 zcu_result launch_delta_rule(const LaunchArgs& a);
 zcu_result launch_gated_norm(const LaunchArgs& a);
+zcu_result launch_attn_static(const LaunchArgs& a, uint32_t max_keys, uint32_t rows);
 
 // Whether (kernel, variant) exists, and its artifact name.
 bool matvec_variant_ok(uint32_t kernel, uint32_t variant);
