@@ -277,25 +277,6 @@ class MatvecQ4K:
                           f"{dt * 1e3:.2f} ms each (C++ restatement of the reference's src/ref panel matmul)"}
 
 
-class TorchBuf:
-    """A torch tensor as a plan buffer: .ptr/.nbytes for bindings, upload() for the step inputs."""
-
-    def __init__(self, torch, dev, nbytes: int):
-        self.t = torch.zeros(max(int(nbytes), 256), dtype=torch.uint8, device=dev)
-        self.ptr, self.nbytes, self.torch = self.t.data_ptr(), int(nbytes), torch
-
-    def upload(self, arr: np.ndarray, offset: int = 0):
-        src = self.torch.from_numpy(np.ascontiguousarray(arr).view(np.uint8).reshape(-1))
-        self.t[offset:offset + src.numel()].copy_(src, non_blocking=False)
-        return self
-
-    def at(self, offset: int = 0, size=None):
-        return (self.ptr + offset, self.nbytes - offset if size is None else size)
-
-    def f32(self):
-        return self.t[: self.nbytes].view(self.torch.float32)
-
-
 class DecodeStep:
     """configs[4]: one decode step of a random-init Llama-3-8B-shaped model in Q4_K (32 layers, hidden 4096,
     32 query / 8 KV heads of 128, SwiGLU 14336, RMSNorm, RoPE theta 5e5, vocab 128256 with a Q8_0 head) over
@@ -312,6 +293,7 @@ class DecodeStep:
         from zllm_b200 import kernels as K
         from zllm_b200 import model as M
         from zllm_b200.plan import DenseConfig, DenseProgram, Shard
+        from zllm_b200.torch_util import TorchBuf, nccl_gather
 
         self.torch, self.K, self.dist, self.batch = torch, K, dist, batch
         self.dev = torch.device("cuda", dist.local)
@@ -329,7 +311,7 @@ class DecodeStep:
             return b
 
         self.prog = DenseProgram(self.ctx, self.cfg, self.weights, batch, alloc, self.shard,
-                                 gather=self._gather if dist.on else None)
+                                 gather=nccl_gather(dist.dist, dist.rank, dist.world) if dist.on else None)
         table = alloc(self.cfg.max_ctx * self.cfg.head_dim * 4)
         table.upload(DenseProgram.rope_table(self.cfg))
         self.prog.set_rope_table(table)
@@ -350,13 +332,6 @@ class DecodeStep:
         self.tgraph = None
         self.mv_graph = None
         self.bytes = self.prog.algorithmic_bytes(self.positions)
-
-    # every rank's column slice of a [batch, width] f32 buffer becomes visible on all ranks
-    def _gather(self, buf, batch, width):
-        t = buf.f32().view(batch, width)
-        per = width // self.dist.world
-        for b in range(batch):
-            self.dist.dist.all_gather_into_tensor(t[b], t[b, self.dist.rank * per:(self.dist.rank + 1) * per])
 
     def _record(self):
         self.prog.record_step(self.context + 1)

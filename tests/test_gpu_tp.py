@@ -1,0 +1,91 @@
+"""Tensor parallelism on real devices: a decode step sharded over two GPUs (rows, heads and KV heads per
+rank, NCCL all-gather of output slices) gives the logits of the same step on one GPU, bit for bit: every
+output row, head and column is computed by exactly one rank with the same arithmetic. Needs two GPUs."""
+import os
+import tempfile
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def _rank(rank: int, world: int, port: int, out_dir: str):
+    import torch
+    import torch.distributed as dist
+
+    from zllm_b200 import abi
+    from zllm_b200 import model as M
+    from zllm_b200.plan import DenseConfig, DenseProgram, Shard
+    from zllm_b200.torch_util import TorchBuf, nccl_gather
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    cfg = DenseConfig(layers=2, hidden=512, heads=8, kv_heads=2, head_dim=64, ff=1024, vocab=1536, max_ctx=320)
+    host = M.host_model(cfg, "tp-test")
+    rng = np.random.default_rng(17)
+    batch = 2
+    positions = np.array([100, 37], dtype=np.uint32)
+    tokens = rng.integers(0, cfg.vocab, size=batch).astype(np.uint32)
+    kv_shape = (batch, cfg.max_ctx, cfg.kv_heads, cfg.head_dim)
+    kc_host = [rng.normal(size=kv_shape).astype(np.float16) for _ in range(cfg.layers)]
+    vc_host = [rng.normal(size=kv_shape).astype(np.float16) for _ in range(cfg.layers)]
+    results = {}
+    for w in ((1, world) if rank == 0 else (world,)):
+        sh = Shard(rank if w > 1 else 0, w)
+        stream = torch.cuda.Stream(dev)
+        ctx = abi.Context(rank, stream=stream.cuda_stream)
+        keep = []
+
+        def alloc(n):
+            b = TorchBuf(torch, dev, n)
+            keep.append(b)
+            return b
+
+        def put(a):
+            a = np.ascontiguousarray(a)
+            return alloc(a.nbytes).upload(a)
+
+        weights = M.upload(host, cfg, put, sh)
+        prog = DenseProgram(ctx, cfg, weights, batch, alloc, sh, gather=nccl_gather(dist, rank, w) if w > 1 else None)
+        prog.set_rope_table(put(DenseProgram.rope_table(cfg)))
+        g0, g1 = sh.kv_heads(cfg)
+        for il in range(cfg.layers):
+            prog.kc[il].upload(np.ascontiguousarray(kc_host[il][:, :, g0:g1]).view(np.uint16))
+            prog.vc[il].upload(np.ascontiguousarray(vc_host[il][:, :, g0:g1]).view(np.uint16))
+        prog.write_step(tokens, positions)
+        torch.cuda.synchronize()
+        with torch.cuda.stream(stream):
+            prog.record_step(int(positions.max()) + 1)
+        stream.synchronize()
+        results[w] = prog.logits.download(np.float32).reshape(batch, cfg.vocab).copy()
+        ctx.close()
+    if rank == 0:
+        np.save(os.path.join(out_dir, "one.npy"), results[1])
+        np.save(os.path.join(out_dir, "two.npy"), results[world])
+    torch.cuda.synchronize()
+    dist.barrier()
+    os._exit(0)  # no NCCL teardown: see bench.py
+
+
+def test_two_gpus_give_the_single_gpu_logits():
+    import torch
+
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+
+    with tempfile.TemporaryDirectory() as tmp:
+        port = 29700 + os.getpid() % 200
+        ctx = mp.spawn(_rank, args=(2, port, tmp), nprocs=2, join=False)
+        if not ctx.join(timeout=240):
+            for p in ctx.processes:
+                p.kill()  # the two PIDs this test started
+            pytest.fail("the two ranks did not finish in 240 s")
+        one, two = np.load(os.path.join(tmp, "one.npy")), np.load(os.path.join(tmp, "two.npy"))
+    assert np.isfinite(one).all() and np.abs(one).max() > 0
+    assert np.array_equal(one.view(np.uint32), two.view(np.uint32))
