@@ -3,6 +3,7 @@ rank, NCCL all-gather of output slices) gives the logits of the same step on one
 output row, head and column is computed by exactly one rank with the same arithmetic. Needs two GPUs."""
 import os
 import tempfile
+import time
 
 import numpy as np
 import pytest
@@ -82,10 +83,12 @@ def test_two_gpus_give_the_single_gpu_logits():
     with tempfile.TemporaryDirectory() as tmp:
         port = 29700 + os.getpid() % 200
         ctx = mp.spawn(_rank, args=(2, port, tmp), nprocs=2, join=False)
-        if not ctx.join(timeout=240):
-            for p in ctx.processes:
-                p.kill()  # the two PIDs this test started
-            pytest.fail("the two ranks did not finish in 240 s")
+        deadline = time.monotonic() + 240
+        while not ctx.join(timeout=5):  # join() returns as soon as one rank ends; True once all have
+            if time.monotonic() > deadline:
+                for p in ctx.processes:
+                    p.kill()  # the two PIDs this test started
+                pytest.fail("the two ranks did not finish in 240 s")
         one, two = np.load(os.path.join(tmp, "one.npy")), np.load(os.path.join(tmp, "two.npy"))
     assert np.isfinite(one).all() and np.abs(one).max() > 0
     assert np.array_equal(one.view(np.uint32), two.view(np.uint32))
