@@ -38,6 +38,14 @@ def measured_hbm_peak():
         return FALLBACK_HBM_GBS, "fallback"
 
 
+def measured_tensor_peak():
+    """Dense bf16 TFLOP/s: the burst figure (a kernel timed alone over a short region)."""
+    try:
+        return float(json.loads(PEAKS_FILE.read_text())["bf16_tflops"]), "measured (burst)"
+    except Exception:
+        return 1590.0, "fallback"
+
+
 # ------------------------------------------------------------------ clocks
 
 class ClockSampler:
@@ -485,7 +493,114 @@ def cpu_decode_baseline(cfg, context, budget_s=20.0, sample_layers=2):
                       "(C++ restatement of the reference's src/ref forward)"}
 
 
-WORKLOADS = {"matvec_q4_k": MatvecQ4K, "decode": DecodeStep}
+class PrefillMatmul:
+    """configs[2]: activations bf16 [2048, 4096] ~ N(0,1); weights bf16 [4096, 4096] ~ N(0, 0.02); f32 accumulation
+    in tensor memory; bf16 out. The tensor-core prefill rung (tcgen05). With N ranks the weight rows are sharded
+    and every rank multiplies the full activations by its rows (no collective in the timed step)."""
+
+    rows, n, k = 2048, 4096, 4096
+    name = "prefill_matmul"
+    dtype = "bf16"
+
+    def __init__(self, dist: Dist, batch: int = 1, variant: int = 0, **_):
+        import torch
+
+        from zllm_b200 import abi
+        from zllm_b200 import kernels as K
+
+        self.torch, self.K, self.dist = torch, K, dist
+        self.dev = torch.device("cuda", dist.local)
+        torch.cuda.set_device(self.dev)
+        self.stream = torch.cuda.Stream(self.dev)
+        self.ctx = abi.Context(dist.local, stream=self.stream.cuda_stream)
+        self.launcher = K.Launcher(self.ctx)
+        self.copies = 8                                   # 8 distinct weight matrices: 268 MB > the 126 MB L2
+        self.ln = self.n // dist.world
+        gen = torch.Generator(device=self.dev)
+        gen.manual_seed(4321 + dist.rank)
+        self.w = (torch.randn((self.copies, self.ln, self.k), device=self.dev, generator=gen) * 0.02).to(torch.bfloat16)
+        self.pinned_x = torch.randn((self.rows, self.k), generator=torch.Generator().manual_seed(7)).to(torch.bfloat16).pin_memory()
+        self.x = self.pinned_x.to(self.dev)
+        self.out = torch.zeros((self.copies, self.rows, self.ln), dtype=torch.bfloat16, device=self.dev)
+        self.pinned_out = torch.empty((self.rows, self.ln), dtype=torch.bfloat16).pin_memory()
+        self.graph = None
+        torch.cuda.synchronize()
+
+    def flops_per_launch(self) -> float:
+        return 2.0 * self.rows * self.ln * self.k
+
+    def launches_per_step(self) -> int:
+        return self.copies
+
+    def _launch_all(self):
+        K = self.K
+        for c in range(self.copies):
+            self.launcher.matmul("bf16", (self.x.data_ptr(), self.x.numel() * 2), (self.w[c].data_ptr(), self.w[c].numel() * 2),
+                                 (self.out[c].data_ptr(), self.out[c].numel() * 2), self.rows, self.ln, self.k,
+                                 variant=K.VARIANT_PREFILL_TC, layout=K.X_HALF | K.OUT_HALF)
+
+    def step(self):
+        if self.graph is None:
+            self.ctx.capture_begin()
+            self._launch_all()
+            self.graph = self.ctx.capture_end()
+        self.ctx.graph_launch(self.graph)
+
+    def e2e_step(self):
+        torch = self.torch
+        with torch.cuda.stream(self.stream):
+            self.x.copy_(self.pinned_x, non_blocking=True)
+        self.step()
+        with torch.cuda.stream(self.stream):
+            self.pinned_out.copy_(self.out[self.copies - 1], non_blocking=True)
+        self.stream.synchronize()
+
+    def e2e_bytes(self):
+        return self.pinned_x.numel() * 2, self.pinned_out.numel() * 2
+
+    def roofline(self, ms_per_step: float):
+        peak, kind = measured_tensor_peak()
+        us = ms_per_step * 1e3 / self.launches_per_step()
+        achieved = self.flops_per_launch() / us / 1e6
+        return {"bound": "tensor", "kernel": "matmul_tc_kernel<bf16>", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                "frac": achieved / peak, "peak_kind": f"of {kind}", "traffic": None, "flops_per_launch": self.flops_per_launch(),
+                "us_per_launch": us}
+
+    def metric(self):
+        return "prefill_matmul_tflops", "TFLOP/s"
+
+    def value(self, seconds_per_step: float) -> float:
+        return self.flops_per_launch() * self.copies * self.dist.world / seconds_per_step / 1e12
+
+    def config(self):
+        return {"workload": f"BF16 prefill matmul, {self.rows} tokens x {self.n} x {self.k}, bf16 in/out, f32 accumulate (tcgen05)",
+                "matrices_per_step": self.copies,
+                "l2": f"inputs larger than L2: {self.copies} distinct weight matrices, {self.copies * self.ln * self.k * 2 / 1e6:.0f} MB per step per rank",
+                "parallelism": f"tp{self.dist.world} (weight rows sharded, no collective in the step)" if self.dist.on else "1 GPU"}
+
+    def cpu_baseline(self, budget_s: float = 12.0):
+        from oracle import ref
+        from zllm_b200 import synth
+
+        ref.build()
+        pool = ref.Pool()
+        rng = synth.rng_for("cfg3", "cpu")
+        rows = 64                                          # a bounded sample: 64 of the 2048 tokens
+        mat = ref.Matrix(ref.BF16, synth.bf16_weights(rng, self.n, self.k), self.n, self.k, pool)
+        x = ref.round_like_llama(ref.BF16, synth.normal_f32(rng, rows, self.k)).reshape(rows, self.k)
+        ref.matmul(x, mat, pool=pool)
+        t0, reps = time.perf_counter(), 0
+        while time.perf_counter() - t0 < budget_s and reps < 200:
+            ref.matmul(x, mat, pool=pool)
+            reps += 1
+        dt = (time.perf_counter() - t0) / reps
+        return {"value": 2.0 * rows * self.n * self.k / dt / 1e12, "unit": "TFLOP/s", "cores": pool.threads, "kind": "port",
+                "isa": ref.build_info(),
+                "sample": f"{reps} multiplies of {rows} tokens x {self.n} x {self.k} (bf16 weights, f32 accumulate), {dt * 1e3:.1f} ms each "
+                          "(C++ restatement of the reference's src/ref panel matmul)"}
+
+
+WORKLOADS = {"matvec_q4_k": MatvecQ4K, "decode": DecodeStep, "prefill_matmul": PrefillMatmul}
 
 
 
@@ -536,7 +651,7 @@ def run_cuda(args):
     line = {
         "metric": metric, "value": wl.value(sec_per_step), "unit": unit, "n_gpus": dist.world, "steps": args.steps,
         "warmup": warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
-        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": wl.config(),
+        "scaling": getattr(wl, "scaling", "strong"), "vs_baseline": None, "dtype": getattr(wl, "dtype", "f32"), "data": "synthetic", "config": wl.config(),
         "clocks": clocks,
         "e2e": {"value": wl.value(e2e_s / args.steps), "unit": unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "gpu_launches": wl.launches_per_step() * args.steps,
@@ -591,6 +706,24 @@ def run_reference(args):
                        "wall_s": dt},
             "cpu_baseline": base,
             "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        }), flush=True)
+        return
+    if args.workload == "prefill_matmul":
+        wl = PrefillMatmul.__new__(PrefillMatmul)  # shapes only; nothing on a GPU
+        vals, base = [], None
+        for i in range(args.warmup + args.steps):
+            base = wl.cpu_baseline(budget_s=3.0)
+            if i >= args.warmup:
+                vals.append(base["value"])
+        value = float(np.mean(vals))
+        base["value"] = value
+        print(json.dumps({
+            "impl": "reference", "metric": "prefill_matmul_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": 8 * 2.0 * wl.rows * wl.n * wl.k / value / 1e9,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"BF16 prefill matmul, {wl.rows} tokens x {wl.n} x {wl.k} (a 64-token sample per step)"},
+            "cpu_baseline": base,
+            "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         }), flush=True)
         return
     n, k, batch = MatvecQ4K.n, MatvecQ4K.k, 1

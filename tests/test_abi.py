@@ -42,6 +42,13 @@ def test_artifacts_and_missing_kernels():
         assert abi.artifact(K.MATVEC_Q4_K, v)
     assert abi.artifact(K.MATVEC_Q4_K, 0x00012008) == b""  # a WGSL variant id means nothing here
     assert abi.artifact(K.RMSNORM, 5) == b""
+    # the reserved prefill-rung id exists for the half-precision multiplies only, and mutated ids do not
+    # (src/agility/kernels.zig:200-232)
+    for k in (K.MATMUL_BF16, K.MATMUL_F16):
+        assert abi.artifact(k, K.VARIANT_PREFILL_TC)
+        for bit in range(32):
+            assert abi.artifact(k, K.VARIANT_PREFILL_TC ^ (1 << bit)) == b""
+    assert abi.artifact(K.RMSNORM, K.VARIANT_PREFILL_TC) == b"" and abi.artifact(K.MATMUL_BF16, 0xFFFF0000) == b""
     assert "sm_100a" in abi.backend_source()
 
 
@@ -56,6 +63,7 @@ def test_caps_and_budget(dry):
     caps = dry.caps()
     assert caps.abi_version == abi.ABI_VERSION and caps.dry_run == 1 and caps.offset_align == 256
     assert dry.memory_budget() > 0
+    assert dry.supports_prefill(0) and dry.supports_prefill(K.VARIANT_PREFILL_TC) and not dry.supports_prefill(0xFFFF0000)
 
 
 def test_writes_land_before_recorded_work_and_reads_complete(dry):

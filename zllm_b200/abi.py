@@ -215,6 +215,10 @@ class Context:
         self._check(lib().zcu_memory_budget(self.h, C.byref(v)))
         return v.value
 
+    def supports_prefill(self, rung_variant: int) -> bool:
+        """Device.supportsPrefill (src/gpu/host.zig:120-128) for a rung's reserved variant id."""
+        return bool(lib().zcu_supports_prefill(self.h, rung_variant))
+
     def force_loss(self):
         self._check(lib().zcu_force_loss(self.h))
 

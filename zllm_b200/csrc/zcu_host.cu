@@ -205,8 +205,8 @@ zcu_result dispatch_kernel(zcu_context* c, uint32_t kernel, uint32_t variant, co
     if (c->dry) return ZCU_OK;
     switch (kernel) {
         case ZCU_K_RMSNORM: return launch_rmsnorm(a);
-        case ZCU_K_MATMUL_BF16: return launch_matmul_bf16(a);
-        case ZCU_K_MATMUL_F16: return launch_matmul_f16(a);
+        case ZCU_K_MATMUL_BF16: return variant == ZCU_VARIANT_PREFILL_BF16_TC ? launch_matmul_tc(a, true) : launch_matmul_bf16(a);
+        case ZCU_K_MATMUL_F16: return variant == ZCU_VARIANT_PREFILL_BF16_TC ? launch_matmul_tc(a, false) : launch_matmul_f16(a);
         case ZCU_K_MATVEC_BF16: return launch_matvec_bf16(a);
         case ZCU_K_MATVEC_F16: return launch_matvec_f16(a);
         case ZCU_K_SILU_MUL: return launch_silu_mul(a);
@@ -649,8 +649,9 @@ ZCU_EXPORT size_t zcu_artifact(uint32_t kernel, uint32_t variant, char* out, siz
     bool ok = name != nullptr;
     if (ok) {
         const bool is_matvec = kernel == ZCU_K_MATVEC_Q4_K || kernel == ZCU_K_MATVEC_Q8_0 || kernel == ZCU_K_MATVEC_BF16 || kernel == ZCU_K_MATVEC_F16;
+        const bool has_rung = kernel == ZCU_K_MATMUL_BF16 || kernel == ZCU_K_MATMUL_F16;  // tensor-core prefill rung
         if (is_matvec) ok = matvec_variant_ok(kernel, variant);
-        else ok = variant == 0;
+        else ok = variant == 0 || (has_rung && variant == ZCU_VARIANT_PREFILL_BF16_TC);
     }
     if (!ok) {
         if (out && capacity) out[0] = 0;
@@ -786,8 +787,9 @@ ZCU_EXPORT zcu_result zcu_memory_budget(zcu_context* c, uint64_t* out_bytes) {
 
 ZCU_EXPORT int32_t zcu_supports_prefill(zcu_context* c, uint32_t rung_variant) {
     if (!c || c->lost) return 0;
-    (void)rung_variant;
-    return 0;
+    // 0 = the scalar f32 identities; the single-product half rung runs on the tensor cores; the
+    // compensated rung (0xffff0000) does not exist here
+    return rung_variant == 0 || rung_variant == ZCU_VARIANT_PREFILL_BF16_TC;
 }
 
 ZCU_EXPORT zcu_result zcu_rope_table(float* out, uint32_t positions, uint32_t n_rot, float base, const float* factors) {

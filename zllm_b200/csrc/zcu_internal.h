@@ -108,6 +108,7 @@ zcu_result launch_matvec_bf16(const LaunchArgs& a);
 zcu_result launch_matvec_f16(const LaunchArgs& a);
 zcu_result launch_matmul_bf16(const LaunchArgs& a);
 zcu_result launch_matmul_f16(const LaunchArgs& a);
+zcu_result launch_matmul_tc(const LaunchArgs& a, bool bf16);   // the tensor-core prefill rung of both
 zcu_result launch_rmsnorm(const LaunchArgs& a);
 zcu_result launch_silu_mul(const LaunchArgs& a);
 zcu_result launch_embed(const LaunchArgs& a, uint32_t kernel);

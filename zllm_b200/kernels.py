@@ -101,6 +101,12 @@ def elementwise(count: int):
     return (65535, -(-groups // 65535), 1)
 
 
+# The reserved variant of the lower-precision prefill rung (src/agility/kernels.zig:116-122) and the layout
+# bits this backend reads from MatmulBf16._pad[0] under it.
+VARIANT_PREFILL_TC = 0xFFFC0000
+X_HALF, OUT_HALF = 1, 2
+
+
 class Launcher:
     """Immediate launches on a context (kernels.Launcher, kernels.zig:925-960)."""
 
@@ -117,9 +123,13 @@ class Launcher:
         args = [x, w, out] + ([norm_w] if norm_w is not None else [])
         self.launch(MATVEC_KERNEL[ttype], p, args, (-(-n // 8), m, 1), variant)
 
-    def matmul(self, ttype, x, w, out, rows, n, k, col0=0, out_stride=None, accumulate=False):
+    def matmul(self, ttype, x, w, out, rows, n, k, col0=0, out_stride=None, accumulate=False, variant=0, layout=0):
+        """The prefill multiply on half-precision weights. `variant` 0 is the exact f32 identity;
+        VARIANT_PREFILL_TC is the tensor-core rung, where `layout` may say that x (X_HALF) and/or out (OUT_HALF)
+        hold the weights' half type instead of f32."""
         p = MatmulBf16(rows, n, k, col0, out_stride if out_stride is not None else n, int(accumulate))
-        self.launch(MATMUL_BF16 if ttype == "bf16" else MATMUL_F16, p, [x, w, out], (-(-n // 64), -(-rows // 16), 1))
+        p._pad[0] = layout
+        self.launch(MATMUL_BF16 if ttype == "bf16" else MATMUL_F16, p, [x, w, out], (-(-n // 64), -(-rows // 16), 1), variant)
 
     def rmsnorm(self, x, w, y, rows, dim, eps, w_rows=0):
         self.launch(RMSNORM, RmsNorm(rows, dim, eps, w_rows), [x, w, y], (rows, 1, 1))
