@@ -96,6 +96,9 @@ enum {
 #define ZCU_FAMILY_SCALAR 1u
 #define ZCU_FAMILY_MMA 2u
 #define ZCU_VARIANT_PREFILL_BF16_TC 0xfffc0000u
+/* delta_rule in its chunked form (64-token chunks, the remainder by the recurrent kernel). No reference
+ * counterpart: the reference runs every token serially. DeltaRule._pad must hold the step's token count. */
+#define ZCU_VARIANT_DELTA_CHUNK64 0xfffd0000u
 
 typedef struct zcu_options {
     uint32_t abi_version;  /* ZCU_ABI_VERSION */

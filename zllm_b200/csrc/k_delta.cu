@@ -48,13 +48,20 @@ __global__ void __launch_bounds__(DR_THREADS) delta_rule_kernel(PDeltaRule p, co
                                                                float* __restrict__ state, float* __restrict__ out,
                                                                const PStep* __restrict__ step,
                                                                const float* __restrict__ proj, float* __restrict__ hist,
-                                                               float* __restrict__ kept, int with_hist) {
+                                                               float* __restrict__ kept, int with_hist,
+                                                               uint32_t t_first, uint32_t m_expect, int* __restrict__ status) {
     constexpr int RG = DR_THREADS / COLS;
     __shared__ float qs[DR_MAX_DIM], ks[DR_MAX_DIM];
     __shared__ float red[DR_THREADS];
     __shared__ float delta[COLS];
     const PStep st = *step;
     const int lid = threadIdx.x;
+    // After the chunked form has consumed tokens [0, t_first): the host-side token count must be the step's, and
+    // a kept row inside the chunked part cannot be produced. Both are reported, not guessed around.
+    if (m_expect != 0xffffffffu && (st.m != m_expect || (st.keep != 0 && st.keep <= t_first))) {
+        if (lid == 0 && status) atomicExch(status, 3);
+        return;
+    }
     if (with_hist)
         advance_history(p, st, proj, hist, kept, (blockIdx.y * gridDim.x + blockIdx.x) * DR_THREADS + lid,
                         gridDim.x * gridDim.y * DR_THREADS);
@@ -74,7 +81,7 @@ __global__ void __launch_bounds__(DR_THREADS) delta_rule_kernel(PDeltaRule p, co
 #pragma unroll
     for (int i = 0; i < ROWS_CAP; i++) s[i] = (i < rows && in_head) ? state[s0 + (size_t)(a0 + i) * d + b] : 0.f;
 
-    for (uint32_t t = 0; t < st.m; t++) {
+    for (uint32_t t = t_first; t < st.m; t++) {
         const size_t row = (size_t)t * p.conv_stride;
         for (int i = lid; i < d; i += DR_THREADS) {
             qs[i] = conv[row + (size_t)kh * d + i];
@@ -137,6 +144,13 @@ __global__ void __launch_bounds__(DR_THREADS) delta_rule_kernel(PDeltaRule p, co
 // proj/hist/kept may be absent (fewer bindings): the history is then left alone,
 // which is what a caller that supplies q, k, v directly wants.
 zcu_result launch_delta_rule(const LaunchArgs& a) {
+    if (a.variant == ZCU_VARIANT_DELTA_CHUNK64) return launch_delta_chunked(a);
+    return launch_delta_recurrent(a, 0, 0xffffffffu);
+}
+
+// The recurrent kernel over tokens [t_first, step.m). m_expect: the host's idea of step.m (checked on the
+// device), or 0xffffffff for none.
+zcu_result launch_delta_recurrent(const LaunchArgs& a, uint32_t t_first, uint32_t m_expect) {
     PDeltaRule p;
     ZCU_NEED(a, a.params_bytes >= sizeof(p) && a.nb >= 6, "delta_rule: bad parameter block or bindings");
     memcpy(&p, a.params, sizeof(p));
@@ -152,7 +166,7 @@ zcu_result launch_delta_rule(const LaunchArgs& a) {
     const dim3 grid(p.v_heads, (p.dim + COLS - 1) / COLS);
     delta_rule_kernel<COLS, DR_MAX_DIM / (DR_THREADS / COLS)><<<grid, DR_THREADS, 0, a.stream>>>(
         p, (const float*)a.b[0].ptr, (const float*)a.b[1].ptr, (const float*)a.b[2].ptr, (float*)a.b[3].ptr,
-        (float*)a.b[4].ptr, (const PStep*)a.b[5].ptr, proj, hist, kept, with_hist);
+        (float*)a.b[4].ptr, (const PStep*)a.b[5].ptr, proj, hist, kept, with_hist, t_first, m_expect, a.status);
     ZCU_CHECK_LAUNCH(a);
     return ZCU_OK;
 }

@@ -176,7 +176,11 @@ zcu_result wait_stream(zcu_context* c, uint32_t timeout_ms) {
     }
     cudaEventDestroy(ev);
     if (c->status && *(volatile int*)c->status != 0) {
+        const int what = *(volatile int*)c->status;
         *c->status = 0;
+        if (what == 3)
+            return fail(c, ZCU_E_GPU, "delta_rule (chunked): the token count in the parameter block is not the step's, or a kept row "
+                                      "lies inside the chunked part; the step was not applied past its whole chunks");
         return fail(c, ZCU_E_GPU, "a kernel gave up a bounded wait (a copy or a peer never arrived); its results are invalid");
     }
     return ZCU_OK;
@@ -651,7 +655,8 @@ ZCU_EXPORT size_t zcu_artifact(uint32_t kernel, uint32_t variant, char* out, siz
         const bool is_matvec = kernel == ZCU_K_MATVEC_Q4_K || kernel == ZCU_K_MATVEC_Q8_0 || kernel == ZCU_K_MATVEC_BF16 || kernel == ZCU_K_MATVEC_F16;
         const bool has_rung = kernel == ZCU_K_MATMUL_BF16 || kernel == ZCU_K_MATMUL_F16;  // tensor-core prefill rung
         if (is_matvec) ok = matvec_variant_ok(kernel, variant);
-        else ok = variant == 0 || (has_rung && variant == ZCU_VARIANT_PREFILL_BF16_TC);
+        else ok = variant == 0 || (has_rung && variant == ZCU_VARIANT_PREFILL_BF16_TC) ||
+                  (kernel == ZCU_K_DELTA_RULE && variant == ZCU_VARIANT_DELTA_CHUNK64);
     }
     if (!ok) {
         if (out && capacity) out[0] = 0;

@@ -118,6 +118,8 @@ zcu_result launch_attn_split(const LaunchArgs& a);
 zcu_result launch_attn_combine(const LaunchArgs& a);
 zcu_result launch_delta_prep(const LaunchArgs& a);
 zcu_result launch_delta_rule(const LaunchArgs& a);
+zcu_result launch_delta_recurrent(const LaunchArgs& a, uint32_t t_first, uint32_t m_expect);
+zcu_result launch_delta_chunked(const LaunchArgs& a);          // 64-token chunks, then the recurrent tail
 zcu_result launch_gated_norm(const LaunchArgs& a);
 zcu_result launch_attn_static(const LaunchArgs& a, uint32_t max_keys, uint32_t rows);
 

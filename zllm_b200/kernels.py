@@ -105,6 +105,8 @@ def elementwise(count: int):
 # bits this backend reads from MatmulBf16._pad[0] under it.
 VARIANT_PREFILL_TC = 0xFFFC0000
 X_HALF, OUT_HALF = 1, 2
+# delta_rule in 64-token chunks; DeltaRule._pad carries the step's token count.
+VARIANT_DELTA_CHUNK64 = 0xFFFD0000
 
 
 class Launcher:
@@ -154,11 +156,17 @@ class Launcher:
     def attn_combine(self, p: "Attention", qg, part, out, step, rows):
         self.launch(ATTN_COMBINE, p, [qg, part, out, step], (p.heads, rows, 1))
 
-    def delta_rule(self, p: "DeltaRule", conv, g, beta, state, out, step, proj=None, hist=None, kept=None):
+    def delta_rule(self, p: "DeltaRule", conv, g, beta, state, out, step, proj=None, hist=None, kept=None, chunked_tokens=None):
+        """The gated delta rule over a step. `chunked_tokens` = the step's token count selects the chunked form
+        (64-token chunks, the remainder by the recurrent kernel; dim 128 only), which has no reference counterpart."""
         args = [conv, g, beta, state, out, step]
         if proj is not None:
             args += [proj, hist, kept]
-        self.launch(DELTA_RULE, p, args, (p.v_heads, -(-p.dim // 32), 1))
+        variant = 0
+        if chunked_tokens is not None:
+            p._pad = int(chunked_tokens)
+            variant = VARIANT_DELTA_CHUNK64
+        self.launch(DELTA_RULE, p, args, (p.v_heads, -(-p.dim // 32), 1), variant)
 
     def delta_prep(self, p: "DeltaPrep", proj, conv_w, hist, out, dt_bias, a, g, beta, m):
         self.launch(DELTA_PREP, p, [proj, conv_w, hist, out, dt_bias, a, g, beta], (p.channels // p.head + 1, m, 1))
