@@ -600,7 +600,123 @@ class PrefillMatmul:
                           "(C++ restatement of the reference's src/ref panel matmul)"}
 
 
-WORKLOADS = {"matvec_q4_k": MatvecQ4K, "decode": DecodeStep, "prefill_matmul": PrefillMatmul}
+class DeltaPrefill:
+    """configs[3], prefill: one Gated DeltaNet layer, batch 1, 4096 tokens, 16 heads of 128; q, k (L2-normalised)
+    and v hold bf16 values; beta = sigmoid(N(0,1)); log-decay = -softplus(N(0,1)); f32 state from zero. The chunked
+    form (chunk 64). With N ranks the heads are sharded (no collective: heads are independent)."""
+
+    tokens, heads, d = 4096, 16, 128
+    name = "deltanet_prefill"
+    dtype = "f32"
+
+    def __init__(self, dist: Dist, batch: int = 1, variant: int = 0, **_):
+        import torch
+
+        from zllm_b200 import abi, synth
+        from zllm_b200 import kernels as K
+
+        self.torch, self.K, self.dist = torch, K, dist
+        self.dev = torch.device("cuda", dist.local)
+        torch.cuda.set_device(self.dev)
+        self.stream = torch.cuda.Stream(self.dev)
+        self.ctx = abi.Context(dist.local, stream=self.stream.cuda_stream)
+        self.launcher = K.Launcher(self.ctx)
+        self.recurrent = variant == 1                     # --variant 1: the serial kernel, for comparison
+        self.lh = self.heads // dist.world
+        self.sets = 2                                     # two input sets alternate: 2 x 133 MB > the 126 MB L2
+        self.cd = 3 * self.lh * self.d
+        self.conv, self.g, self.beta = [], [], []
+        for i in range(self.sets):
+            conv, g, beta = synth.deltanet_inputs(synth.rng_for("cfg4", f"bench{dist.rank}-{i}"), self.tokens, self.lh, self.lh, self.d)
+            self.conv.append(torch.from_numpy(conv).pin_memory())
+            self.g.append(torch.from_numpy(g).to(self.dev))
+            self.beta.append(torch.from_numpy(beta).to(self.dev))
+        self.dconv = [c.to(self.dev) for c in self.conv]
+        self.state = torch.zeros((self.lh, self.d, self.d), dtype=torch.float32, device=self.dev)
+        self.out = [torch.zeros((self.tokens, self.lh * self.d), dtype=torch.float32, device=self.dev) for _ in range(self.sets)]
+        self.pinned_out = torch.empty((self.tokens, self.lh * self.d), dtype=torch.float32).pin_memory()
+        self.step_buf = torch.tensor([self.tokens, 0, 0, 0], dtype=torch.int32, device=self.dev)
+        self.turn = 0
+        torch.cuda.synchronize()
+
+    def launches_per_step(self) -> int:
+        return 1 if self.recurrent else 3
+
+    def _buf(self, t):
+        return (t.data_ptr(), t.numel() * t.element_size())
+
+    def step(self):
+        K, i = self.K, self.turn % self.sets
+        self.turn += 1
+        with self.torch.cuda.stream(self.stream):
+            self.state.zero_()
+        p = K.DeltaRule(self.lh, self.lh, self.d, self.cd, 1, self.cd, 0)
+        self.launcher.delta_rule(p, self._buf(self.dconv[i]), self._buf(self.g[i]), self._buf(self.beta[i]), self._buf(self.state),
+                                 self._buf(self.out[i]), self._buf(self.step_buf),
+                                 chunked_tokens=None if self.recurrent else self.tokens)
+
+    def e2e_step(self):
+        torch, i = self.torch, self.turn % self.sets
+        with torch.cuda.stream(self.stream):
+            self.dconv[i].copy_(self.conv[i], non_blocking=True)
+        self.step()
+        with torch.cuda.stream(self.stream):
+            self.pinned_out.copy_(self.out[i], non_blocking=True)
+        self.stream.synchronize()
+
+    def e2e_bytes(self):
+        return self.conv[0].numel() * 4, self.pinned_out.numel() * 4
+
+    def bytes_per_step(self) -> float:
+        # q, k, v in, o out (f32 here), g and beta, the state in and out
+        return 4.0 * self.tokens * (self.cd + self.lh * self.d + 2 * self.lh) + 2 * 4.0 * self.lh * self.d * self.d
+
+    def flops_per_step(self) -> float:
+        c, d = 64, self.d
+        return (6.0 * c * d * d + 8.0 * c * c * d) * (self.tokens / c) * self.lh
+
+    def roofline(self, ms_per_step: float):
+        peak, kind = measured_hbm_peak()
+        achieved = self.bytes_per_step() / (ms_per_step * 1e-3) / 1e9
+        return {"bound": "hbm", "kernel": "delta_chunk_scan + delta_chunk_prep" if not self.recurrent else "delta_rule_kernel",
+                "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": f"of {kind}",
+                "traffic": None, "bytes_per_launch": self.bytes_per_step(),
+                "f32_tflops": self.flops_per_step() / (ms_per_step * 1e-3) / 1e12,
+                "us_per_chunk_step": ms_per_step * 1e3 / (self.tokens / 64),
+                "note": "neither roofline binds: a head's 64 chunks are a serial chain; the chunk step's latency is the figure to lower"}
+
+    def metric(self):
+        return "deltanet_prefill_tokens_per_s", "tokens/s"
+
+    def value(self, seconds_per_step: float) -> float:
+        return self.tokens / seconds_per_step
+
+    def config(self):
+        return {"workload": f"Gated DeltaNet layer prefill, batch 1, {self.tokens} tokens, {self.heads} heads of {self.d}, "
+                            + ("recurrent form" if self.recurrent else "chunked form (chunk 64)"),
+                "l2": f"inputs larger than L2: {self.sets} input sets alternate, {self.bytes_per_step() / 1e6:.0f} MB each",
+                "parallelism": f"heads sharded over {self.dist.world} ranks, no collective" if self.dist.on else "1 GPU"}
+
+    def cpu_baseline(self, budget_s: float = 12.0):
+        from oracle import ref
+        from zllm_b200 import synth
+
+        ref.build()
+        sample = 512                                       # a bounded sample: the first 512 of the 4096 tokens
+        conv, g, beta = synth.deltanet_inputs(synth.rng_for("cfg4", "cpu"), sample, self.heads, self.heads, self.d)
+        zero = np.zeros((self.heads, self.d, self.d), dtype=np.float32)
+        ref.delta_rule(zero, conv, g, beta, sample, self.heads, self.heads, self.d)
+        t0, reps = time.perf_counter(), 0
+        while time.perf_counter() - t0 < budget_s and reps < 50:
+            ref.delta_rule(zero, conv, g, beta, sample, self.heads, self.heads, self.d)
+            reps += 1
+        dt = (time.perf_counter() - t0) / reps
+        return {"value": sample / dt, "unit": "tokens/s", "cores": min(ref.default_pool().threads, self.heads), "kind": "port", "isa": ref.build_info(),
+                "sample": f"{reps} runs of the first {sample} tokens, all {self.heads} heads, {dt * 1e3:.1f} ms each "
+                          "(C++ restatement of the reference's src/ref recurHead, one head per task)"}
+
+
+WORKLOADS = {"matvec_q4_k": MatvecQ4K, "decode": DecodeStep, "prefill_matmul": PrefillMatmul, "deltanet_prefill": DeltaPrefill}
 
 
 
