@@ -35,7 +35,8 @@ EXPORTS = [
     "zcu_start_profile", "zcu_stop_profile", "zcu_read_timings", "zcu_alloc", "zcu_free", "zcu_upload",
     "zcu_download", "zcu_memset", "zcu_launch", "zcu_sync", "zcu_launch_count", "zcu_capture_begin",
     "zcu_capture_end", "zcu_graph_launch", "zcu_graph_destroy", "zcu_rope_table",
-    "zcu_attention_decode_static",
+    "zcu_attention_decode_static", "zcu_program_begin", "zcu_program_end", "zcu_program_abandon", "zcu_program_launch",
+    "zcu_program_destroy",
 ]
 
 
@@ -115,6 +116,11 @@ def lib() -> C.CDLL:
         "zcu_graph_destroy": (C.c_int32, [vp, u32]),
         "zcu_rope_table": (C.c_int32, [vp, u32, u32, C.c_float, vp]),
         "zcu_attention_decode_static": (C.c_int32, [vp, vp, u32, C.POINTER(Binding), u32, u32, u32]),
+        "zcu_program_begin": (C.c_int32, [vp]),
+        "zcu_program_end": (C.c_int32, [vp, C.POINTER(u32)]),
+        "zcu_program_abandon": (C.c_int32, [vp]),
+        "zcu_program_launch": (C.c_int32, [vp, u32]),
+        "zcu_program_destroy": (C.c_int32, [vp, u32]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(L, name)
@@ -306,6 +312,21 @@ class Context:
 
     def graph_launch(self, graph: int):
         self._check(lib().zcu_graph_launch(self.h, graph))
+
+    # -- step programs: dispatches recorded, then replayed by one persistent kernel
+    def program_begin(self):
+        self._check(lib().zcu_program_begin(self.h))
+
+    def program_end(self) -> int:
+        g = C.c_uint32()
+        self._check(lib().zcu_program_end(self.h, C.byref(g)))
+        return g.value
+
+    def program_abandon(self):
+        lib().zcu_program_abandon(self.h)
+
+    def program_launch(self, program: int):
+        self._check(lib().zcu_program_launch(self.h, program))
 
     def close(self):
         if self.h:

@@ -1,0 +1,272 @@
+// The decode-attention fast path (f16 cache) and the merge of its partials, written for virtual blocks so that
+// the standalone kernels (k_attn.cu) and the persistent step program (k_program.cu) run the same code.
+#pragma once
+
+#include <cfloat>
+#include <cuda_fp16.h>
+
+#include "vblock.cuh"
+#include "zcu_internal.h"
+
+namespace attn {
+
+// ---- the fast path: f16 cache, GQA group <= 4, head_dim 64 or 128; 128 cache positions per CTA.
+// The cache and the queries are read past L1 (ld.global.cg): inside the step program the newest row of the
+// cache and the queries were written by another SM earlier in the same kernel.
+// Scores: 8 threads per key, each with its hd/8 dims of the group's queries in registers, so K is read
+// with 16-byte loads and no shared-memory traffic; the 8 partial dots meet by shuffles. Softmax: one warp
+// per head. Sum of exp * v: 16 threads per key (8 dims each, 16-byte V loads), 16 key groups per CTA
+// that meet in shared memory in group order.
+constexpr int AF_KEYS = 128;
+constexpr int AF_THREADS = 256;
+
+// Shared memory of one virtual block: scores [GROUP_CAP][128], statistics, then [8 warps][group][HD] partial sums.
+__host__ __device__ constexpr size_t attn_fast_smem(int group_cap, int group, int hd) {
+    return ((size_t)group_cap * AF_KEYS + 2 * group_cap + 8 + (size_t)(AF_THREADS / 32) * group * hd) * sizeof(float);
+}
+
+template <int HD, int GROUP_CAP>
+__device__ __forceinline__ void attn_split_fast_body(const VBlock& vb, const PAttention& p, const float* __restrict__ qg,
+                                                     const __half* __restrict__ kc, const __half* __restrict__ vc,
+                                                     float* __restrict__ part, const PStep* __restrict__ step,
+                                                     const uint32_t* __restrict__ seq_pos) {
+    constexpr int DPT = HD / 8;     // dims per thread in the score phase
+    constexpr int KPP = AF_THREADS / 8;  // keys per pass
+    constexpr int PASSES = AF_KEYS / KPP;
+    float (*sc)[AF_KEYS] = reinterpret_cast<float (*)[AF_KEYS]>(vb.smem);
+    float* stat = reinterpret_cast<float*>(vb.smem) + GROUP_CAP * AF_KEYS;
+    float* pv = stat + 2 * GROUP_CAP + 8;  // [8 warps][group][HD]; the offset keeps it 16-byte aligned
+    const int tid = vb.tid, lane = tid & 31, warp = tid >> 5;
+    const int g = vb.x, b = vb.y, t = vb.z;
+    const int group = (int)(p.heads / p.kv_heads);
+    const int row = (int)p.row0 + t;
+    const size_t seq_off = (size_t)row * p._pad[0];
+    const int keys = (seq_pos ? (int)seq_pos[row] : (int)step->pos0 + row) + 1;
+    const int k0 = b * AF_KEYS;
+    const size_t kv_stride = (size_t)p.kv_heads * HD;
+    const int q_head = p.gated ? 2 * HD : HD;
+    const int n = min(AF_KEYS, keys - min(keys, k0));
+
+    // ---- scores
+    const int kl = tid >> 3, sl = tid & 7;
+    float q[GROUP_CAP][DPT];
+#pragma unroll
+    for (int h = 0; h < GROUP_CAP; h++) {
+        const float* qp = qg + (size_t)row * p.q_row + (size_t)(g * group + min(h, group - 1)) * q_head + sl * DPT;
+#pragma unroll
+        for (int d = 0; d < DPT; d += 4) {
+            const float4 v = __ldcg(reinterpret_cast<const float4*>(qp + d));
+            q[h][d] = v.x; q[h][d + 1] = v.y; q[h][d + 2] = v.z; q[h][d + 3] = v.w;
+        }
+    }
+    uint4 kraw[PASSES][DPT / 8];
+#pragma unroll
+    for (int ps = 0; ps < PASSES; ps++) {
+        const int key = k0 + ps * KPP + kl;
+        const __half* kp = kc + seq_off + (size_t)min(key, keys - 1) * kv_stride + (size_t)g * HD + sl * DPT;
+#pragma unroll
+        for (int c = 0; c < DPT / 8; c++) kraw[ps][c] = __ldcg(reinterpret_cast<const uint4*>(kp) + c);
+    }
+#pragma unroll
+    for (int ps = 0; ps < PASSES; ps++) {
+        const int key = k0 + ps * KPP + kl;
+        float dot[GROUP_CAP];
+#pragma unroll
+        for (int h = 0; h < GROUP_CAP; h++) dot[h] = 0.f;
+#pragma unroll
+        for (int c = 0; c < DPT / 8; c++) {
+            const __half2* hp = reinterpret_cast<const __half2*>(&kraw[ps][c]);
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const float2 kk = __half22float2(hp[e]);
+#pragma unroll
+                for (int h = 0; h < GROUP_CAP; h++) {
+                    dot[h] = __fmaf_rn(q[h][8 * c + 2 * e], kk.x, dot[h]);
+                    dot[h] = __fmaf_rn(q[h][8 * c + 2 * e + 1], kk.y, dot[h]);
+                }
+            }
+        }
+#pragma unroll
+        for (int h = 0; h < GROUP_CAP; h++) {
+            float v = dot[h];
+            v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 1));
+            v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 2));
+            v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 4));
+            if (sl == 0 && h < group) sc[h][ps * KPP + kl] = key < keys ? v * p.scale : -FLT_MAX;
+        }
+    }
+    vb.sync();
+
+    // ---- block softmax: warp h takes head h, four keys per lane
+    if (warp < group) {
+        float s[4], mx = -FLT_MAX;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            s[i] = lane + 32 * i < n ? sc[warp][lane + 32 * i] : -FLT_MAX;
+            mx = fmaxf(mx, s[i]);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        float sum = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const float e = (lane + 32 * i < n && s[i] != -FLT_MAX) ? expf(s[i] - mx) : 0.f;
+            sc[warp][lane + 32 * i] = e;
+            sum = __fadd_rn(sum, e);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sum = __fadd_rn(sum, __shfl_xor_sync(0xffffffffu, sum, o));
+        if (lane == 0) {
+            stat[2 * warp] = mx;
+            stat[2 * warp + 1] = sum;
+        }
+    }
+    vb.sync();
+
+    // ---- sum exp * v: thread (key group kg of 16, dims 8 dl .. 8 dl + 7)
+    constexpr int TPK = HD / 8;            // threads per key
+    constexpr int KG = AF_THREADS / TPK;   // key groups
+    constexpr int KPT = AF_KEYS / KG;      // keys per thread
+    const int kg = tid / TPK, dl = tid % TPK;
+    float acc[GROUP_CAP][8];
+#pragma unroll
+    for (int h = 0; h < GROUP_CAP; h++)
+#pragma unroll
+        for (int d = 0; d < 8; d++) acc[h][d] = 0.f;
+    uint4 vraw[KPT];
+#pragma unroll
+    for (int i = 0; i < KPT; i++) {
+        const int key = k0 + kg + KG * i;
+        vraw[i] = __ldcg(reinterpret_cast<const uint4*>(vc + seq_off + (size_t)min(key, keys - 1) * kv_stride + (size_t)g * HD + 8 * dl));
+    }
+#pragma unroll
+    for (int i = 0; i < KPT; i++) {
+        const int ki = kg + KG * i;
+        if (ki < n) {
+            const __half2* hp = reinterpret_cast<const __half2*>(&vraw[i]);
+            float vv[8];
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const float2 f = __half22float2(hp[e]);
+                vv[2 * e] = f.x;
+                vv[2 * e + 1] = f.y;
+            }
+#pragma unroll
+            for (int h = 0; h < GROUP_CAP; h++) {
+                const float w = sc[h < group ? h : 0][ki];
+#pragma unroll
+                for (int d = 0; d < 8; d++) acc[h][d] = __fmaf_rn(w, vv[d], acc[h][d]);
+            }
+        }
+    }
+    // key groups of one warp first (shuffles, fixed order), then the warps through shared memory
+    constexpr int GPW = 32 / TPK;  // key groups per warp
+#pragma unroll
+    for (int h = 0; h < GROUP_CAP; h++)
+#pragma unroll
+        for (int d = 0; d < 8; d++) {
+            float v = acc[h][d];
+#pragma unroll
+            for (int o = TPK; o < 32; o <<= 1) v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, o));
+            acc[h][d] = v;
+        }
+    if (lane < TPK) {
+#pragma unroll
+        for (int h = 0; h < GROUP_CAP; h++)
+            if (h < group) {
+                float* dst = pv + ((size_t)warp * group + h) * HD + 8 * lane;
+                *reinterpret_cast<float4*>(dst) = make_float4(acc[h][0], acc[h][1], acc[h][2], acc[h][3]);
+                *reinterpret_cast<float4*>(dst + 4) = make_float4(acc[h][4], acc[h][5], acc[h][6], acc[h][7]);
+            }
+    }
+    (void)GPW;
+    vb.sync();
+    for (int i = tid; i < group * HD; i += AF_THREADS) {
+        const int h = i / HD, d = i % HD;
+        float o = 0.f;
+#pragma unroll
+        for (int wv = 0; wv < AF_THREADS / 32; wv++) o = __fadd_rn(o, pv[((size_t)wv * group + h) * HD + d]);
+        const int head = g * group + h;
+        const size_t base = (((size_t)t * p.heads + head) * p.max_blocks + b) * (HD + 2);
+        part[base + 2 + d] = o;
+        if (d == 0) {
+            part[base] = stat[2 * h];
+            part[base + 1] = stat[2 * h + 1];
+        }
+    }
+}
+
+// grid (heads, rows). Merges the blocks' partials (src/kernels/attn_combine.wgsl):
+//   M = max m_b,  L = sum l_b e^(m_b - M),  o = sum o_b e^(m_b - M) / L,  times sigmoid(gate) when gated.
+// Bindings: qg, part, out, step (+ per-row positions for batched sequences). `kb`: cache positions per block.
+// The block weights are computed once into shared memory; each thread then adds its dim over the blocks
+// in block order with independent loads.
+constexpr int AC_MAX_BLOCKS = 4096;
+__host__ __device__ constexpr size_t attn_combine_smem(int max_blocks) { return ((size_t)max_blocks + 32 + 2 + 2 * 128) * sizeof(float); }
+
+__device__ __forceinline__ void attn_combine_body(const VBlock& vb, const PAttention& p, const float* __restrict__ qg,
+                                                  const float* __restrict__ part, float* __restrict__ out,
+                                                  const PStep* __restrict__ step, const uint32_t* __restrict__ seq_pos,
+                                                  int kb) {
+    float* wsm = reinterpret_cast<float*>(vb.smem);  // [blocks] weights, [32] scratch, [128] float2 of the upper half
+    const int tid = vb.tid, lane = tid & 31, warp = tid >> 5, h = vb.x, t = vb.y;
+    const int hd = (int)p.head_dim;
+    const int row = (int)p.row0 + t;
+    const int keys = (seq_pos ? (int)seq_pos[row] : (int)step->pos0 + row) + 1;
+    const int blocks = (keys + kb - 1) / kb;
+    float* red = wsm + blocks;
+    const size_t base0 = ((size_t)t * p.heads + h) * p.max_blocks * (hd + 2);
+    const size_t bs = (size_t)hd + 2;
+    float mx = -FLT_MAX;
+    for (int b = tid; b < blocks; b += 256) {
+        const float m = __ldcg(part + base0 + b * bs);
+        wsm[b] = m;
+        mx = fmaxf(mx, m);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    if (lane == 0) red[warp] = mx;
+    vb.sync();
+    mx = red[0];
+#pragma unroll
+    for (int wv = 1; wv < 8; wv++) mx = fmaxf(mx, red[wv]);
+    vb.sync();
+    for (int b = tid; b < blocks; b += 256) wsm[b] = expf(wsm[b] - mx);
+    vb.sync();
+    // Two halves of the blocks per dim (threads d and d + 128 when head_dim <= 128), eight loads in flight
+    // each; the halves are added low half first, so the order of the sum is fixed.
+    const int halves = hd <= 128 ? 2 : 1;
+    const int d = tid % (256 / halves), half = tid / (256 / halves);
+    const int per = (blocks + halves - 1) / halves;
+    const int b0 = half * per, b1 = min(blocks, b0 + per);
+    float l = 0.f, o = 0.f;
+    if (d < hd) {
+#pragma unroll 8
+        for (int b = b0; b < b1; b++) {
+            const float w = wsm[b];
+            l = __fmaf_rn(__ldcg(part + base0 + b * bs + 1), w, l);
+            o = __fmaf_rn(__ldcg(part + base0 + b * bs + 2 + d), w, o);
+        }
+    }
+    float2* hi_half = reinterpret_cast<float2*>(wsm + ((blocks + 32 + 1) & ~1));  // 8-byte aligned
+    if (half == 1 && d < hd) hi_half[d] = make_float2(l, o);
+    vb.sync();
+    if (half == 1 || d >= hd) return;
+    if (halves == 2) {
+        l = __fadd_rn(l, hi_half[d].x);
+        o = __fadd_rn(o, hi_half[d].y);
+    }
+    const int tid_d = d;
+    // _pad[1] != 0 (extension): floats between output rows, for writing a rank's head columns of a wider row.
+    const size_t orow = p._pad[1] ? (size_t)p._pad[1] : (size_t)p.heads * hd;
+    const size_t oi = (size_t)row * orow + (size_t)h * hd + tid_d;
+    if (!p.gated) {
+        out[oi] = o / l;
+        return;
+    }
+    const float gate = __ldcg(qg + (size_t)row * p.q_row + (size_t)2 * h * hd + hd + tid_d);
+    out[oi] = o / l / (1.0f + expf(-gate));
+}
+
+
+}  // namespace attn

@@ -97,6 +97,8 @@ struct zcu_context {
     uint64_t launches = 0;
     bool capturing = false;
     std::vector<cudaGraphExec_t> graphs;
+    zcu_program* recording = nullptr;     // dispatches go into this step program instead of running
+    std::vector<zcu_program*> programs;
     uint8_t* pinned = nullptr;  // staging for uploads and readbacks
     int* status = nullptr;      // mapped host word kernels set when a bounded wait gives up
     size_t pinned_cap = 0;
@@ -205,6 +207,7 @@ zcu_result dispatch_kernel(zcu_context* c, uint32_t kernel, uint32_t variant, co
     char name[64];
     if (zcu_artifact(kernel, variant, name, sizeof(name)) == 0)
         return fail(c, ZCU_E_UNSUPPORTED_KERNEL, "kernel %u variant 0x%x is not implemented by the cuda backend", kernel, variant);
+    if (c->recording) return c->dry ? ZCU_OK : program_record(c->recording, kernel, a);
     c->launches++;
     if (c->dry) return ZCU_OK;
     switch (kernel) {
@@ -720,6 +723,8 @@ ZCU_EXPORT zcu_result zcu_destroy(zcu_context* c, uint32_t timeout_ms) {
         zcu_result r = wait_stream(c, timeout_ms);
         if (r == ZCU_E_TIMEOUT) return r;  // the handle stays valid for a retry
     }
+    for (zcu_program* pr : c->programs) program_free(pr);
+    program_free(c->recording);
     for (cudaGraphExec_t g : c->graphs)
         if (g) cudaGraphExecDestroy(g);
     for (size_t i = 0; i < c->buffers.size(); i++)
@@ -994,6 +999,60 @@ ZCU_EXPORT zcu_result zcu_graph_launch(zcu_context* c, uint32_t graph) {
     LIVE(c);
     if (graph >= c->graphs.size() || !c->graphs[graph]) return fail(c, ZCU_E_BAD_ID, "no graph %u", graph);
     CU(c, cudaGraphLaunch(c->graphs[graph], c->stream));
+    return ZCU_OK;
+}
+static void fill_args(zcu_context* c, LaunchArgs& a) {
+    memset(&a, 0, sizeof(a));
+    a.stream = c->stream;
+    a.sm_count = c->dry ? 148 : c->prop.multiProcessorCount;
+    a.status = c->status;
+    a.err = c->err;
+    a.err_cap = sizeof(c->err);
+}
+
+ZCU_EXPORT zcu_result zcu_program_begin(zcu_context* c) {
+    LIVE(c);
+    if (c->dry) return fail(c, ZCU_E_INVALID, "a step program needs a device");
+    if (c->recording || c->capturing) return fail(c, ZCU_E_INVALID, "a recording or capture is already open");
+    c->recording = program_new();
+    return ZCU_OK;
+}
+ZCU_EXPORT zcu_result zcu_program_end(zcu_context* c, uint32_t* out_program) {
+    LIVE(c);
+    if (!c->recording || !out_program) return fail(c, ZCU_E_INVALID, "no step program is being recorded");
+    zcu_program* pr = c->recording;
+    c->recording = nullptr;
+    LaunchArgs a;
+    fill_args(c, a);
+    cudaSetDevice(c->device);
+    const zcu_result r = program_finish(pr, a);
+    if (r != ZCU_OK) {
+        program_free(pr);
+        return r;
+    }
+    c->programs.push_back(pr);
+    *out_program = (uint32_t)c->programs.size() - 1;
+    return ZCU_OK;
+}
+ZCU_EXPORT zcu_result zcu_program_abandon(zcu_context* c) {
+    if (!c) return ZCU_E_INVALID;
+    program_free(c->recording);
+    c->recording = nullptr;
+    return ZCU_OK;
+}
+ZCU_EXPORT zcu_result zcu_program_launch(zcu_context* c, uint32_t program) {
+    LIVE(c);
+    if (program >= c->programs.size() || !c->programs[program]) return fail(c, ZCU_E_BAD_ID, "no step program %u", program);
+    LaunchArgs a;
+    fill_args(c, a);
+    c->launches += 1;
+    return program_launch(c->programs[program], a);
+}
+ZCU_EXPORT zcu_result zcu_program_destroy(zcu_context* c, uint32_t program) {
+    if (!c) return ZCU_E_INVALID;
+    if (program >= c->programs.size() || !c->programs[program]) return fail(c, ZCU_E_BAD_ID, "no step program %u", program);
+    program_free(c->programs[program]);
+    c->programs[program] = nullptr;
     return ZCU_OK;
 }
 ZCU_EXPORT zcu_result zcu_graph_destroy(zcu_context* c, uint32_t graph) {

@@ -123,6 +123,15 @@ zcu_result launch_delta_chunked(const LaunchArgs& a);          // 64-token chunk
 zcu_result launch_gated_norm(const LaunchArgs& a);
 zcu_result launch_attn_static(const LaunchArgs& a, uint32_t max_keys, uint32_t rows);
 
+// The step program (k_program.cu): a recorded list of dispatches run by one persistent kernel.
+struct zcu_program;
+zcu_program* program_new();
+void program_free(zcu_program* pr);
+uint64_t program_dispatches(const zcu_program* pr);
+zcu_result program_record(zcu_program* pr, uint32_t kernel, const LaunchArgs& a);
+zcu_result program_finish(zcu_program* pr, const LaunchArgs& a);
+zcu_result program_launch(zcu_program* pr, const LaunchArgs& a);
+
 // Whether (kernel, variant) exists, and its artifact name.
 bool matvec_variant_ok(uint32_t kernel, uint32_t variant);
 
