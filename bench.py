@@ -294,7 +294,7 @@ class DecodeStep:
     name = "decode"
     context = 8192
 
-    def __init__(self, dist: Dist, batch: int = 1, variant: int = 0, layers: int = 32):
+    def __init__(self, dist: Dist, batch: int = 1, variant: int = 0, layers: int = 32, replay: str = "auto"):
         import torch
 
         from zllm_b200 import abi
@@ -339,6 +339,10 @@ class DecodeStep:
         self.graph = None
         self.tgraph = None
         self.mv_graph = None
+        self.program = None
+        # how a step is replayed on one GPU: "program" = one persistent kernel (batch 1), "graph" = a CUDA graph
+        # of the step's launches
+        self.replay = replay if replay != "auto" else ("program" if (not dist.on and batch == 1) else "graph")
         self.bytes = self.prog.algorithmic_bytes(self.positions)
 
     def _record(self):
@@ -346,6 +350,13 @@ class DecodeStep:
 
     def step(self):
         torch = self.torch
+        if not self.dist.on and self.replay == "program":
+            if self.program is None:
+                self.ctx.program_begin()
+                self._record()
+                self.program = self.ctx.program_end()
+            self.ctx.program_launch(self.program)
+            return
         if not self.dist.on:
             if self.graph is None:
                 self.ctx.capture_begin()
@@ -376,6 +387,8 @@ class DecodeStep:
         return self.tokens.nbytes, self.pinned_logits.numel() * 4
 
     def launches_per_step(self) -> int:
+        if self.program is not None:
+            return 1  # one persistent kernel runs the step's whole dispatch list
         return self.prog.launches_per_step or (2 + 7 * self.cfg.layers)
 
     def metric(self):
@@ -390,6 +403,8 @@ class DecodeStep:
                             f"{c.heads}/{c.kv_heads} heads of {c.head_dim}, FFN {c.ff}, vocab {c.vocab} Q8_0 head), "
                             f"f16 KV cache at {self.context} positions, batch {self.batch}",
                 "batch": self.batch, "context": self.context,
+                "replay": ("one persistent kernel per step (step program)" if self.program is not None
+                           else "CUDA graph of the step's launches"),
                 "l2": f"inputs larger than L2: a step reads {self.bytes['total'] / 1e9:.2f} GB per rank "
                       f"({self.bytes['weights'] / 1e9:.2f} GB weights + {self.bytes['kv'] / 1e9:.2f} GB KV)",
                 "parallelism": (f"tp{self.dist.world} (rows and KV heads sharded, NCCL all-gather of output slices)"
@@ -727,8 +742,10 @@ def run_cuda(args):
 
     dist = Dist(args.gpus)
     kw = {"batch": args.batch, "variant": int(args.variant, 0)}
-    if args.workload == "decode" and args.layers:
-        kw["layers"] = args.layers
+    if args.workload == "decode":
+        kw["replay"] = args.replay
+        if args.layers:
+            kw["layers"] = args.layers
     wl = WORKLOADS[args.workload](dist, **kw)
     torch.cuda.set_device(dist.local)
     warmup = max(args.warmup, 3)
@@ -879,6 +896,8 @@ def main():
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--variant", default="0", help="matvec variant word (see include/zllm_cuda.h)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
+    ap.add_argument("--replay", default="auto", choices=["auto", "program", "graph"],
+                    help="decode: replay a step as one persistent kernel or as a CUDA graph of its launches")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

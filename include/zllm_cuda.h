@@ -250,6 +250,11 @@ zcu_result zcu_program_end(zcu_context *context, uint32_t *out_program);
 zcu_result zcu_program_abandon(zcu_context *context);
 zcu_result zcu_program_launch(zcu_context *context, uint32_t program);
 zcu_result zcu_program_destroy(zcu_context *context, uint32_t program);
+/* Per-operation GPU times of the program's last launch (the counterpart of the per-dispatch timestamps of
+ * startProfile/timings, src/gpu/timings.zig): waits for the stream, then fills out[3 i] = kernel family of
+ * operation i, out[3 i + 1] = nanoseconds CTA 0 spent in it, out[3 i + 2] = nanoseconds it then waited at the
+ * barrier. *out_ops = operations in the program. */
+zcu_result zcu_program_timings(zcu_context *context, uint32_t program, uint64_t *out, size_t capacity, size_t *out_ops);
 
 #ifdef __cplusplus
 }

@@ -36,7 +36,7 @@ EXPORTS = [
     "zcu_download", "zcu_memset", "zcu_launch", "zcu_sync", "zcu_launch_count", "zcu_capture_begin",
     "zcu_capture_end", "zcu_graph_launch", "zcu_graph_destroy", "zcu_rope_table",
     "zcu_attention_decode_static", "zcu_program_begin", "zcu_program_end", "zcu_program_abandon", "zcu_program_launch",
-    "zcu_program_destroy",
+    "zcu_program_destroy", "zcu_program_timings",
 ]
 
 
@@ -121,6 +121,7 @@ def lib() -> C.CDLL:
         "zcu_program_abandon": (C.c_int32, [vp]),
         "zcu_program_launch": (C.c_int32, [vp, u32]),
         "zcu_program_destroy": (C.c_int32, [vp, u32]),
+        "zcu_program_timings": (C.c_int32, [vp, u32, vp, C.c_size_t, C.POINTER(C.c_size_t)]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(L, name)
@@ -327,6 +328,13 @@ class Context:
 
     def program_launch(self, program: int):
         self._check(lib().zcu_program_launch(self.h, program))
+
+    def program_timings(self, program: int, cap_ops: int = 4096) -> np.ndarray:
+        """[ops, 3] of (operation family, ns in the operation, ns at the barrier after it) for the last launch."""
+        out = np.zeros(3 * cap_ops, dtype=np.uint64)
+        n = C.c_size_t()
+        self._check(lib().zcu_program_timings(self.h, program, out.ctypes.data, out.size, C.byref(n)))
+        return out[: 3 * min(n.value, cap_ops)].reshape(-1, 3)
 
     def close(self):
         if self.h:

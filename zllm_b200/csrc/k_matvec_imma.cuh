@@ -195,12 +195,12 @@ __device__ __forceinline__ void im_issue_setup(ImIssue& s, const PMatvec& p, con
     s.nparts = (p.flags & MV_SILU_PAIR) ? 2 : 1;
     s.units = Q4 ? k / 256 : (k / 32 + Q8_UNIT - 1) / Q8_UNIT;
     const int row_tiles = (n + 15) / 16;
-    s.rt_lo = (int)(((long long)cta * row_tiles) / ncta);
-    const int rt_hi = (int)(((long long)(cta + 1) * row_tiles) / ncta);
+    s.rt_lo = (int)((unsigned)cta * (unsigned)row_tiles / (unsigned)ncta);   // cta * row_tiles < 2^31
+    const int rt_hi = (int)((unsigned)(cta + 1) * (unsigned)row_tiles / (unsigned)ncta);
     const int per_rt = s.nparts * s.units;
     const int nt = (rt_hi - s.rt_lo) * per_rt;
-    s.lo = (int)(((long long)warp * nt) / IM_WARPS);
-    s.hi = (int)(((long long)(warp + 1) * nt) / IM_WARPS);
+    s.lo = (int)(((unsigned)warp * (unsigned)nt) / IM_WARPS);
+    s.hi = (int)(((unsigned)(warp + 1) * (unsigned)nt) / IM_WARPS);
     s.is_rtl = s.lo / per_rt;
     s.is_part = (s.lo % per_rt) / s.units;
     s.is_unit = s.lo % s.units;
@@ -289,13 +289,19 @@ __device__ __forceinline__ void im_multiply(uint8_t* smem, ImRing& rg, ImIssue& 
     const int units = Q4 ? k / 256 : (k / 32 + Q8_UNIT - 1) / Q8_UNIT;  // tiles along k
     const int nblk = k / 32;
     const int row_tiles = (n + 15) / 16;
-    const int rt_lo = (int)(((long long)cta * row_tiles) / ncta);
-    const int rt_hi = (int)(((long long)(cta + 1) * row_tiles) / ncta);
+    const int rt_lo = (int)((unsigned)cta * (unsigned)row_tiles / (unsigned)ncta);
+    const int rt_hi = (int)((unsigned)(cta + 1) * (unsigned)row_tiles / (unsigned)ncta);
     const int per_rt = nparts * units;
     const int lo = iss.lo, hi = iss.hi;
 
     for (int i = tid; i < IM_WARPS * seg_max; i += IM_THREADS) segkey[i] = -1;
     wait_inputs();
+    // the value this thread's first output accumulates onto: asked for now, needed after the tile stream
+    float first_old = 0.f;
+    if ((p.flags & MV_ACCUMULATE) && tid < (rt_hi - rt_lo) * 16 * mt) {
+        const int j0 = (rt_lo + tid / (mt * 16)) * 16 + (tid / mt) % 16;
+        if (j0 < n) first_old = __ldcg(out + (size_t)(t0 + tid % mt) * p.out_stride + p.col0 + j0);
+    }
 
     // ---- activations -> fixed point. Per token: sum of squares (RMSNorm) and largest magnitude over
     //      the CTA, a power-of-two scale s with |x * s| <= 2^25, then four balanced signed byte digits of
@@ -579,7 +585,7 @@ __device__ __forceinline__ void im_multiply(uint8_t* smem, ImRing& rg, ImIssue& 
         }
         if (pair) v = silu_f(v) * u;
         const size_t o = (size_t)(t0 + tk) * p.out_stride + p.col0 + j;
-        if (p.flags & MV_ACCUMULATE) v += __ldcg(out + o);
+        if (p.flags & MV_ACCUMULATE) v += i == tid ? first_old : __ldcg(out + o);
         out[o] = v;
     }
 }

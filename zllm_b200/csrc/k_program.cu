@@ -87,6 +87,21 @@ __device__ __forceinline__ bool grid_sync(unsigned* bar, unsigned target, int* s
     return __syncthreads_or(bad) == 0;
 }
 
+__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];\n" ::"l"(p)); }
+__device__ __forceinline__ void prefetch_l1(const void* p) { asm volatile("prefetch.global.L1 [%0];\n" ::"l"(p)); }
+
+// The constant inputs a multiply reads right after its barrier (the norm weights) are asked into L2 one
+// multiply ahead, by one CTA.
+__device__ __forceinline__ void prefetch_constants(const ProgOp* ops, int index) {
+    if (index < 0) return;
+    const ProgOp& op = ops[index];
+    PMatvec p;
+    memcpy(&p, op.params, sizeof(p));
+    if (!(p.flags & MV_NORM) || op.b[3] == nullptr) return;
+    const char* nw = static_cast<const char*>(op.b[3]);
+    for (uint32_t off = threadIdx.x * 128u; off < p.k * 4u; off += PROG_THREADS * 128u) prefetch_l2(nw + off);
+}
+
 template <int TYPE>
 __device__ __forceinline__ void prime_op(ImRing& rg, ImIssue& iss, const ProgOp& op, int index, int cta, int warp, int lane) {
     PMatvec p;
@@ -123,6 +138,7 @@ __device__ __noinline__ void run_multiply(uint8_t* smem, ImRing& rg_io, ImIssue&
     } else {
         prime_ahead(rg, iss, ops, op.next_mv, cta, warp, lane);
     }
+    if (cta == index % (int)gridDim.x) prefetch_constants(ops, op.next_mv);
     rg_io = rg;
     iss_io = iss;
 }
@@ -198,8 +214,16 @@ __device__ __noinline__ void run_combine(const ProgOp& op, uint8_t* scratch) {
     });
 }
 
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;\n" : "=l"(t));
+    return t;
+}
+
+// trace[2 i], trace[2 i + 1]: when CTA 0 entered operation i and when it finished its share of it (nanoseconds
+// of the GPU's global timer). The gap to the next entry is the barrier.
 __global__ void __launch_bounds__(PROG_THREADS, 1) program_kernel(const ProgOp* __restrict__ ops, int n_ops, unsigned* bar,
-                                                                 int* __restrict__ status) {
+                                                                 int* __restrict__ status, unsigned long long* __restrict__ trace) {
     extern __shared__ __align__(128) uint8_t smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, cta = (int)blockIdx.x;
     uint8_t* scratch = smem + prog_scratch_offset();
@@ -208,10 +232,20 @@ __global__ void __launch_bounds__(PROG_THREADS, 1) program_kernel(const ProgOp* 
     iss.op = -1;
     iss.issued = iss.hi = iss.lo = 0;
     im_ring_init<PROG_STAGES>(rg, smem, im_layout(4, 256, true, 2, 1, PROG_STAGES), warp, lane);
+    // the operation list is read once per launch: ask all of it into L2 now, and each operation's lines into
+    // L1 one operation ahead
+    for (size_t off = ((size_t)cta * PROG_THREADS + threadIdx.x) * 128; off < (size_t)n_ops * sizeof(ProgOp); off += (size_t)gridDim.x * PROG_THREADS * 128)
+        prefetch_l2(reinterpret_cast<const char*>(ops) + off);
     __syncthreads();
     unsigned epoch = 0;
     for (int i = 0; i < n_ops; i++) {
         const ProgOp& op = ops[i];
+        if (threadIdx.x < 4) {
+            if (i + 1 < n_ops) prefetch_l1(reinterpret_cast<const char*>(&ops[i + 1]) + 128 * (threadIdx.x & 1));
+            if (op.next_mv >= 0 && threadIdx.x >= 2) prefetch_l1(reinterpret_cast<const char*>(&ops[op.next_mv]) + 128 * (threadIdx.x & 1));
+        }
+        const bool tracer = trace != nullptr && cta == 0 && threadIdx.x == 0;
+        if (tracer) trace[2 * i] = global_ns();
         switch (op.kind) {
             case PK_MV_Q4_K: run_multiply<W_Q4_K>(smem, rg, iss, ops, i, cta, status); break;
             case PK_MV_Q8_0: run_multiply<W_Q8_0>(smem, rg, iss, ops, i, cta, status); break;
@@ -224,6 +258,7 @@ __global__ void __launch_bounds__(PROG_THREADS, 1) program_kernel(const ProgOp* 
             case PK_ATTN_COMBINE: run_combine(op, scratch); break;
             default: break;
         }
+        if (tracer) trace[2 * i + 1] = global_ns();
         if (i + 1 < n_ops && !grid_sync(bar, ++epoch * gridDim.x, status)) break;
     }
 }
@@ -235,6 +270,7 @@ struct zcu_program {
     std::vector<ProgOp> ops;
     ProgOp* d_ops = nullptr;
     unsigned* d_bar = nullptr;
+    unsigned long long* d_trace = nullptr;
     int grid = 0;
     int smem = 0;
     uint64_t launches_equiv = 0;  // dispatches the program stands for
@@ -246,6 +282,7 @@ void program_free(zcu_program* pr) {
     if (!pr) return;
     if (pr->d_ops) cudaFree(pr->d_ops);
     if (pr->d_bar) cudaFree(pr->d_bar);
+    if (pr->d_trace) cudaFree(pr->d_trace);
     delete pr;
 }
 
@@ -372,7 +409,8 @@ zcu_result program_finish(zcu_program* pr, const LaunchArgs& a) {
     }
     pr->grid = a.sm_count;
     const size_t bytes = pr->ops.size() * sizeof(ProgOp);
-    if (cudaMalloc((void**)&pr->d_ops, bytes) != cudaSuccess || cudaMalloc((void**)&pr->d_bar, 64) != cudaSuccess) {
+    if (cudaMalloc((void**)&pr->d_ops, bytes) != cudaSuccess || cudaMalloc((void**)&pr->d_bar, 64) != cudaSuccess ||
+        cudaMalloc((void**)&pr->d_trace, pr->ops.size() * 16) != cudaSuccess) {
         cudaGetLastError();
         return zcu_fail(a, ZCU_E_OUT_OF_MEMORY, "step program: no memory for %zu bytes of operations", bytes);
     }
@@ -393,11 +431,31 @@ zcu_result program_launch(zcu_program* pr, const LaunchArgs& a) {
     int n = (int)pr->ops.size();
     unsigned* bar = pr->d_bar;
     int* status = a.status;
-    void* args[] = {(void*)&ops, (void*)&n, (void*)&bar, (void*)&status};
+    unsigned long long* trace = pr->d_trace;
+    void* args[] = {(void*)&ops, (void*)&n, (void*)&bar, (void*)&status, (void*)&trace};
     const cudaError_t e = cudaLaunchCooperativeKernel((const void*)program_kernel, dim3(pr->grid), dim3(PROG_THREADS), args, (size_t)pr->smem, a.stream);
     if (e != cudaSuccess) {
         cudaGetLastError();
         return zcu_fail(a, ZCU_E_GPU, "step program: cooperative launch failed: %s", cudaGetErrorString(e));
+    }
+    return ZCU_OK;
+}
+
+// Per-operation times of the program's last completed launch, as CTA 0 saw them: out[3 i] = kind of operation i,
+// out[3 i + 1] = nanoseconds in the operation, out[3 i + 2] = nanoseconds at the barrier after it.
+zcu_result program_timings(zcu_program* pr, const LaunchArgs& a, uint64_t* out, size_t cap, size_t* n_out) {
+    ZCU_NEED(a, pr && pr->d_trace, "step program: not finished");
+    const size_t n = pr->ops.size();
+    std::vector<unsigned long long> t(2 * n);
+    if (cudaMemcpy(t.data(), pr->d_trace, 16 * n, cudaMemcpyDeviceToHost) != cudaSuccess) {
+        cudaGetLastError();
+        return zcu_fail(a, ZCU_E_GPU, "step program: reading the trace failed");
+    }
+    if (n_out) *n_out = n;
+    for (size_t i = 0; i < n && 3 * i + 2 < cap; i++) {
+        out[3 * i] = pr->ops[i].kind;
+        out[3 * i + 1] = t[2 * i + 1] - t[2 * i];
+        out[3 * i + 2] = i + 1 < n ? t[2 * i + 2] - t[2 * i + 1] : 0;
     }
     return ZCU_OK;
 }

@@ -1048,6 +1048,15 @@ ZCU_EXPORT zcu_result zcu_program_launch(zcu_context* c, uint32_t program) {
     c->launches += 1;
     return program_launch(c->programs[program], a);
 }
+ZCU_EXPORT zcu_result zcu_program_timings(zcu_context* c, uint32_t program, uint64_t* out, size_t capacity, size_t* out_ops) {
+    LIVE(c);
+    if (program >= c->programs.size() || !c->programs[program] || !out) return fail(c, ZCU_E_BAD_ID, "no step program %u", program);
+    zcu_result r = wait_stream(c, 60000u);
+    if (r != ZCU_OK) return r;
+    LaunchArgs a;
+    fill_args(c, a);
+    return program_timings(c->programs[program], a, out, capacity, out_ops);
+}
 ZCU_EXPORT zcu_result zcu_program_destroy(zcu_context* c, uint32_t program) {
     if (!c) return ZCU_E_INVALID;
     if (program >= c->programs.size() || !c->programs[program]) return fail(c, ZCU_E_BAD_ID, "no step program %u", program);

@@ -131,6 +131,7 @@ uint64_t program_dispatches(const zcu_program* pr);
 zcu_result program_record(zcu_program* pr, uint32_t kernel, const LaunchArgs& a);
 zcu_result program_finish(zcu_program* pr, const LaunchArgs& a);
 zcu_result program_launch(zcu_program* pr, const LaunchArgs& a);
+zcu_result program_timings(zcu_program* pr, const LaunchArgs& a, uint64_t* out, size_t cap, size_t* n_out);
 
 // Whether (kernel, variant) exists, and its artifact name.
 bool matvec_variant_ok(uint32_t kernel, uint32_t variant);
