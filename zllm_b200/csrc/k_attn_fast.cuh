@@ -20,9 +20,12 @@ namespace attn {
 constexpr int AF_KEYS = 128;
 constexpr int AF_THREADS = 256;
 
-// Shared memory of one virtual block: scores [GROUP_CAP][128], statistics, then [8 warps][group][HD] partial sums.
+// Shared memory of one virtual block: scores [GROUP_CAP][128], statistics, then one region that first holds the
+// block's values (128 keys x hd halves, each thread's own 16-byte pieces, brought in by cp.async while the
+// scores are computed) and afterwards the [8 warps][group][HD] partial sums.
 __host__ __device__ constexpr size_t attn_fast_smem(int group_cap, int group, int hd) {
-    return ((size_t)group_cap * AF_KEYS + 2 * group_cap + 8 + (size_t)(AF_THREADS / 32) * group * hd) * sizeof(float);
+    const size_t pv = (size_t)(AF_THREADS / 32) * group * hd * sizeof(float), vals = (size_t)AF_KEYS * hd * 2;
+    return ((size_t)group_cap * AF_KEYS + 2 * group_cap + 8) * sizeof(float) + (pv > vals ? pv : vals);
 }
 
 template <int HD, int GROUP_CAP>
@@ -67,6 +70,20 @@ __device__ __forceinline__ void attn_split_fast_body(const VBlock& vb, const PAt
 #pragma unroll
         for (int c = 0; c < DPT / 8; c++) kraw[ps][c] = __ldcg(reinterpret_cast<const uint4*>(kp) + c);
     }
+    // the values do not depend on the scores: their loads are in flight while the scores are computed
+    constexpr int TPK = HD / 8;            // threads per key in the value phase
+    constexpr int KG = AF_THREADS / TPK;   // key groups
+    constexpr int KPT = AF_KEYS / KG;      // keys per thread
+    const int kg = tid / TPK, dl = tid % TPK;
+    // piece i of this thread sits at (i * 256 + tid) * 16 bytes: only the thread that copied a piece reads it
+    const uint32_t vslot = (uint32_t)__cvta_generic_to_shared(pv) + (uint32_t)tid * 16u;
+#pragma unroll
+    for (int i = 0; i < KPT; i++) {
+        const int key = k0 + kg + KG * i;
+        const __half* src = vc + seq_off + (size_t)min(key, keys - 1) * kv_stride + (size_t)g * HD + 8 * dl;
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(vslot + (uint32_t)i * AF_THREADS * 16u), "l"(src) : "memory");
+    }
+    asm volatile("cp.async.commit_group;\n" ::: "memory");
 #pragma unroll
     for (int ps = 0; ps < PASSES; ps++) {
         const int key = k0 + ps * KPP + kl;
@@ -124,26 +141,21 @@ __device__ __forceinline__ void attn_split_fast_body(const VBlock& vb, const PAt
     vb.sync();
 
     // ---- sum exp * v: thread (key group kg of 16, dims 8 dl .. 8 dl + 7)
-    constexpr int TPK = HD / 8;            // threads per key
-    constexpr int KG = AF_THREADS / TPK;   // key groups
-    constexpr int KPT = AF_KEYS / KG;      // keys per thread
-    const int kg = tid / TPK, dl = tid % TPK;
     float acc[GROUP_CAP][8];
 #pragma unroll
     for (int h = 0; h < GROUP_CAP; h++)
 #pragma unroll
         for (int d = 0; d < 8; d++) acc[h][d] = 0.f;
-    uint4 vraw[KPT];
-#pragma unroll
-    for (int i = 0; i < KPT; i++) {
-        const int key = k0 + kg + KG * i;
-        vraw[i] = __ldcg(reinterpret_cast<const uint4*>(vc + seq_off + (size_t)min(key, keys - 1) * kv_stride + (size_t)g * HD + 8 * dl));
-    }
+    asm volatile("cp.async.wait_group 0;\n" ::: "memory");
 #pragma unroll
     for (int i = 0; i < KPT; i++) {
         const int ki = kg + KG * i;
         if (ki < n) {
-            const __half2* hp = reinterpret_cast<const __half2*>(&vraw[i]);
+            uint4 vpiece;
+            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+                         : "=r"(vpiece.x), "=r"(vpiece.y), "=r"(vpiece.z), "=r"(vpiece.w)
+                         : "r"(vslot + (uint32_t)i * AF_THREADS * 16u));
+            const __half2* hp = reinterpret_cast<const __half2*>(&vpiece);
             float vv[8];
 #pragma unroll
             for (int e = 0; e < 4; e++) {
@@ -170,6 +182,7 @@ __device__ __forceinline__ void attn_split_fast_body(const VBlock& vb, const PAt
             for (int o = TPK; o < 32; o <<= 1) v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, o));
             acc[h][d] = v;
         }
+    vb.sync();  // every thread is done with its values: the region now takes the warps' partial sums
     if (lane < TPK) {
 #pragma unroll
         for (int h = 0; h < GROUP_CAP; h++)

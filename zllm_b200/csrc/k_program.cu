@@ -28,11 +28,11 @@ namespace {
 
 using namespace imma;
 
-constexpr int PROG_STAGES = 4;       // tiles per warp ring
+constexpr int PROG_STAGES = 3;       // tiles per warp ring
 constexpr int PROG_THREADS = IM_THREADS;
 constexpr int VB_THREADS = 256;      // threads of a virtual block
 constexpr int VB_PER_CTA = PROG_THREADS / VB_THREADS;
-constexpr int VB_SMEM = 24 * 1024;   // shared memory of a virtual block
+constexpr int VB_SMEM = 36 * 1024;   // shared memory of a virtual block
 constexpr int PROG_SMEM_MAX = 227 * 1024;
 
 enum : uint32_t { PK_MV_Q4_K = 1, PK_MV_Q8_0, PK_EMBED_Q4_K, PK_EMBED_Q8_0, PK_EMBED_BF16, PK_EMBED_F16, PK_ROPE_APPEND, PK_ATTN_SPLIT, PK_ATTN_COMBINE };
