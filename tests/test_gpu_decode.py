@@ -59,7 +59,7 @@ def test_decode_step_matches_oracle(ref, gpu, batch):
     gpu.sync()
     logits = prog.logits.download(np.float32).reshape(batch, cfg.vocab)
     hidden = prog.x.download(np.float32).reshape(batch, cfg.hidden)
-    assert prog.launches_per_step == 1 + 7 * cfg.layers + 1
+    assert prog.launches_per_step == 1 + (6 if prog.fuse_rope else 7) * cfg.layers + 1
     for b in range(batch):
         kc = [np.ascontiguousarray(kc_host[il][b]).view(np.uint16).copy() for il in range(cfg.layers)]
         vc = [np.ascontiguousarray(vc_host[il][b]).view(np.uint16).copy() for il in range(cfg.layers)]
@@ -172,3 +172,32 @@ def test_step_program_refuses_what_it_cannot_run(gpu, launcher):
             launcher.rmsnorm(x, w, y, 1, 64, 1e-5)
     finally:
         gpu.program_abandon()
+
+
+@pytest.mark.parametrize("batch", [1, 2, 4])
+def test_rope_append_in_the_multiply_epilogue_equals_its_own_launch(gpu, batch):
+    # rope_append fused into the Q|K|V multiply (one launch fewer per layer) gives the same rotated queries,
+    # the same cache rows and the same logits as the separate kernel, bit for bit.
+    cfg = CFG
+    host = M.host_model(cfg, "tiny")
+    weights = M.upload(host, cfg, gpu.put)
+    rng = np.random.default_rng(23 + batch)
+    positions = np.array([150, 7, 299, 64][:batch], dtype=np.uint32)
+    tokens = rng.integers(0, cfg.vocab, size=batch).astype(np.uint32)
+    kv_shape = (batch, cfg.max_ctx, cfg.kv_heads, cfg.head_dim)
+    kc_host = [rng.normal(size=kv_shape).astype(np.float16) for _ in range(cfg.layers)]
+    vc_host = [rng.normal(size=kv_shape).astype(np.float16) for _ in range(cfg.layers)]
+    got = {}
+    for fuse in (False, True):
+        prog = DenseProgram(gpu, cfg, weights, batch, gpu.zeros, fuse_rope=fuse)
+        prog.set_rope_table(gpu.put(DenseProgram.rope_table(cfg)))
+        for il in range(cfg.layers):
+            prog.kc[il].upload(kc_host[il].view(np.uint16))
+            prog.vc[il].upload(vc_host[il].view(np.uint16))
+        prog.write_step(tokens, positions)
+        prog.record_step(int(positions.max()) + 1)
+        gpu.sync()
+        got[fuse] = ([prog.logits.download(np.uint32), prog.qkv.download(np.uint32), prog.x.download(np.uint32)]
+                     + [c.download(np.uint16) for c in prog.kc + prog.vc])
+    for a, b in zip(got[False], got[True]):
+        assert np.array_equal(a, b)

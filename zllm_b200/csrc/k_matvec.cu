@@ -281,6 +281,23 @@ zcu_result parse_matvec(const LaunchArgs& a, MvArgs& v, uint32_t elem_block, boo
     ZCU_NEED(a, ((uintptr_t)v.x & 15) == 0 && ((uintptr_t)v.w & 15) == 0, "matvec: x and w must be 16-byte aligned");
     ZCU_NEED(a, v.p.x_stride == 0 || v.p.x_stride * 4 >= v.p.k, "matvec: x_stride shorter than k");
     (void)needs_256;
+    v.has_rope = (v.p.flags & MV_ROPE_APPEND) != 0;
+    if (v.has_rope) {
+        // an extension: rope_append fused into the multiply that produces the Q|K|V row. The parameter block is
+        // PMatvec followed by params.RopeAppend; bindings 4.. are rope_append's table, kc, vc, step[, positions].
+        ZCU_NEED(a, a.params_bytes >= sizeof(PMatvec) + sizeof(PRopeAppend) && a.nb >= 8, "matvec + rope_append: parameter block or bindings too short");
+        memcpy(&v.rope.p, static_cast<const char*>(a.params) + sizeof(PMatvec), sizeof(PRopeAppend));
+        const PRopeAppend& r = v.rope.p;
+        ZCU_NEED(a, r.normal == 1 && r.qk_norm == 0, "matvec + rope_append: only adjacent-pair RoPE without q/k norms is fused");
+        ZCU_NEED(a, r.head_dim % 2 == 0 && r.n_rot % 2 == 0 && r.n_rot <= r.head_dim && (r.kv == KV_F32 || r.kv == KV_F16), "matvec + rope_append: head_dim %u n_rot %u cache %u", r.head_dim, r.n_rot, r.kv);
+        ZCU_NEED(a, v.m == 1 || v.m == 2 || v.m == 4, "matvec + rope_append: %d tokens (1, 2 or 4)", v.m);
+        ZCU_NEED(a, v.p.col0 % 2 == 0 && v.p.n % 2 == 0 && !(v.p.flags & (MV_SILU_PAIR | MV_ACCUMULATE)), "matvec + rope_append: odd column range or conflicting flags");
+        v.rope.table = static_cast<const float2*>(a.b[4].ptr);
+        v.rope.kc = a.b[5].ptr;
+        v.rope.vc = a.b[6].ptr;
+        v.rope.step = static_cast<const PStep*>(a.b[7].ptr);
+        v.rope.seq_pos = (a.nb >= 9 && r._pad[0] != 0) ? static_cast<const uint32_t*>(a.b[8].ptr) : nullptr;
+    }
     return ZCU_OK;
 }
 
@@ -295,6 +312,7 @@ zcu_result launch_quant(const LaunchArgs& a, uint32_t block) {
     const bool imma_ok = TYPE != W_Q8_0 || v.p.k % 256 == 0;
     if ((a.variant == 0 && imma_ok) || family == ZCU_FAMILY_MMA)
         return launch_matvec_imma(a, v, TYPE, (int)(a.variant & 0xffu), 0);
+    if (v.has_rope) return zcu_fail(a, ZCU_E_UNSUPPORTED_KERNEL, "matvec + rope_append: only the tensor-core family fuses it");
     if (a.variant == 0) return launch_scalar<TYPE>(a, v);
     if (family == ZCU_FAMILY_SCALAR) return launch_scalar<TYPE>(a, v);
     return zcu_fail(a, ZCU_E_UNSUPPORTED_KERNEL, "matvec: variant 0x%x is not built", a.variant);

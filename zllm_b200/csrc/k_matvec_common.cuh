@@ -68,6 +68,8 @@ struct MvArgs {
     float* out;
     const float* nw;
     int m;
+    bool has_rope;   // MV_ROPE_APPEND: the outputs are a Q|K|V row that is rotated and appended to the cache
+    MvRope rope;
 };
 
 }  // namespace mv

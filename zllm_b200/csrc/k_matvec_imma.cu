@@ -12,7 +12,7 @@ template <int TYPE, int NB, int STAGES>
 __global__ void __launch_bounds__(IM_THREADS, 1) matvec_imma(PMatvec p, const float* __restrict__ x,
                                                             const uint8_t* __restrict__ w, float* __restrict__ out,
                                                             const float* __restrict__ norm_w, int t0, int mt,
-                                                            int seg_max, int* __restrict__ status) {
+                                                            int seg_max, int* __restrict__ status, const __grid_constant__ MvRope rope) {
     extern __shared__ __align__(16) uint8_t smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const ImLayout L = im_layout(4 * mt, (int)p.k, TYPE == W_Q4_K, 2 * NB, seg_max, STAGES);
@@ -22,6 +22,7 @@ __global__ void __launch_bounds__(IM_THREADS, 1) matvec_imma(PMatvec p, const fl
     im_prime<TYPE, STAGES>(rg, iss, p, w, (int)blockIdx.x, (int)gridDim.x, warp, lane, 0);
     im_multiply<TYPE, NB, STAGES>(
         smem, rg, iss, (int)blockIdx.x, (int)gridDim.x, p, x, out, norm_w, t0, mt, seg_max, status,
+        (p.flags & MV_ROPE_APPEND) ? &rope : nullptr,
         [] {
             // everything before touched only the weights, which no kernel writes; from here on the
             // activations are read, so the kernels before this one must have finished
@@ -57,7 +58,7 @@ zcu_result launch_staged(const LaunchArgs& a, const MvArgs& v, int t0, int mt, i
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, v.p, v.x, v.w, v.out, v.nw, t0, mt, seg_max, a.status);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, v.p, v.x, v.w, v.out, v.nw, t0, mt, seg_max, a.status, v.rope);
     if (e != cudaSuccess) return zcu_fail(a, ZCU_E_GPU, "matvec_imma: launch failed: %s", cudaGetErrorString(e));
     return ZCU_OK;
 }

@@ -268,7 +268,7 @@ template <int TYPE, int NB, int STAGES, class WaitInputs, class Between>
 __device__ __forceinline__ void im_multiply(uint8_t* smem, ImRing& rg, ImIssue& iss, int cta, int ncta, const PMatvec& p,
                                             const float* __restrict__ x, float* __restrict__ out,
                                             const float* __restrict__ norm_w, int t0, int mt, int seg_max,
-                                            int* __restrict__ status, WaitInputs wait_inputs, Between between) {
+                                            int* __restrict__ status, const MvRope* __restrict__ rope, WaitInputs wait_inputs, Between between) {
     constexpr bool Q4 = TYPE == W_Q4_K;
     constexpr int SLOTS = 2 * NB;  // token slots of a pass
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -571,20 +571,53 @@ __device__ __forceinline__ void im_multiply(uint8_t* smem, ImRing& rg, ImIssue& 
     between();
     __syncthreads();
 
-    // ---- add each row's segments in (warp, segment) order and write it
+    // ---- add each row's segments in (warp, segment) order and write it. With MV_ROPE_APPEND the row is
+    //      Q|K|V: adjacent outputs (2i, 2i+1) of a q or k head are a RoPE pair held by lanes `mt` apart; q is
+    //      written rotated, k and v go to the cache at the token's position (rope_append's arithmetic,
+    //      src/kernels/rope_append.wgsl; every product rounded, src/ref/ops.zig:64-86).
     const int local_rts = rt_hi - rt_lo;
-    for (int i = tid; i < local_rts * 16 * mt; i += IM_THREADS) {
+    const bool fused_rope = rope != nullptr && (p.flags & MV_ROPE_APPEND);
+    const int total = local_rts * 16 * mt;
+    for (int i0 = 0; i0 < total; i0 += IM_THREADS) {
+        const int i = i0 + tid;
         const int tk = i % mt, row = (i / mt) % 16, rtl = i / (mt * 16);
         const int j = (rt_lo + rtl) * 16 + row;
-        if (j >= n) continue;
+        const bool valid = i < total && j < n;
         float v = 0.f, u = 0.f;
-        for (int sgi = 0; sgi < IM_WARPS * seg_max; sgi++) {
-            const int key = segkey[sgi];
-            if (key == rtl * 2) v = __fadd_rn(v, red[((size_t)sgi * 16 + row) * SLOTS + tk]);
-            else if (key == rtl * 2 + 1) u = __fadd_rn(u, red[((size_t)sgi * 16 + row) * SLOTS + tk]);
+        if (valid) {
+            for (int sgi = 0; sgi < IM_WARPS * seg_max; sgi++) {
+                const int key = segkey[sgi];
+                if (key == rtl * 2) v = __fadd_rn(v, red[((size_t)sgi * 16 + row) * SLOTS + tk]);
+                else if (key == rtl * 2 + 1) u = __fadd_rn(u, red[((size_t)sgi * 16 + row) * SLOTS + tk]);
+            }
         }
         if (pair) v = silu_f(v) * u;
         const size_t o = (size_t)(t0 + tk) * p.out_stride + p.col0 + j;
+        if (fused_rope) {
+            const float other = __shfl_xor_sync(0xffffffffu, v, mt);  // the pair's other element (whole warps run this loop)
+            if (!valid) continue;
+            const PRopeAppend& r = rope->p;
+            const int tok = t0 + tk;
+            const uint32_t pos = rope->seq_pos ? rope->seq_pos[tok] : rope->step->pos0 + (uint32_t)tok;
+            const uint32_t col = p.col0 + (uint32_t)j, hd = r.head_dim, q_head = r.gated ? 2 * hd : hd;
+            const bool is_q = col < r.k_off, is_k = !is_q && col < r.v_off;
+            const uint32_t d = is_q ? col % q_head : (col - (is_k ? r.k_off : r.v_off)) % hd;
+            float val = v;
+            if ((is_q || is_k) && d < r.n_rot) {
+                const float2 cs = rope->table[(size_t)pos * (r.n_rot / 2) + d / 2];
+                val = (d & 1) ? __fadd_rn(__fmul_rn(other, cs.y), __fmul_rn(v, cs.x)) : __fsub_rn(__fmul_rn(v, cs.x), __fmul_rn(other, cs.y));
+            }
+            out[o] = is_q ? val : v;  // the row keeps rotated q and, like rope_append, unrotated k and v
+            if (!is_q) {
+                const uint32_t gh = (col - (is_k ? r.k_off : r.v_off)) / hd;
+                const size_t e = (size_t)tok * r._pad[0] + (size_t)pos * r.kv_heads * hd + (size_t)gh * hd + d;
+                void* cache = is_k ? rope->kc : rope->vc;
+                if (r.kv == KV_F16) reinterpret_cast<__half*>(cache)[e] = __float2half_rn(val);
+                else reinterpret_cast<float*>(cache)[e] = val;
+            }
+            continue;
+        }
+        if (!valid) continue;
         if (p.flags & MV_ACCUMULATE) v += i == tid ? first_old : __ldcg(out + o);
         out[o] = v;
     }

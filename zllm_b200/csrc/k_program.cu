@@ -46,7 +46,7 @@ struct ProgOp {
     uint32_t kb;             // attn_combine: cache positions per partial block
     uint32_t hd;             // attn_split: head_dim (64 or 128)
     uint32_t _pad;
-    uint32_t params[16];     // the dispatch's parameter block
+    uint32_t params[24];     // the dispatch's parameter block (a multiply's may carry rope_append's after its own)
     const void* b[9];        // its bindings
 };
 
@@ -131,9 +131,19 @@ __device__ __noinline__ void run_multiply(uint8_t* smem, ImRing& rg_io, ImIssue&
         PMatvec p;
         memcpy(&p, op.params, sizeof(p));
         prime_ahead(rg, iss, ops, index, cta, warp, lane);  // normally done one multiply ago
+        MvRope rope;
+        if (p.flags & MV_ROPE_APPEND) {
+            memcpy(&rope.p, op.params + sizeof(PMatvec) / 4, sizeof(PRopeAppend));
+            rope.table = static_cast<const float2*>(op.b[4]);
+            rope.kc = const_cast<void*>(op.b[5]);
+            rope.vc = const_cast<void*>(op.b[6]);
+            rope.step = static_cast<const PStep*>(op.b[7]);
+            rope.seq_pos = static_cast<const uint32_t*>(op.b[8]);
+        }
         im_multiply<TYPE, 1, PROG_STAGES>(
             smem, rg, iss, cta, (int)op.ncta, p, static_cast<const float*>(op.b[0]), static_cast<float*>(const_cast<void*>(op.b[2])),
-            static_cast<const float*>(op.b[3]), (int)op.t0, (int)op.mt, (int)op.seg_max, status, [] {},
+            static_cast<const float*>(op.b[3]), (int)op.t0, (int)op.mt, (int)op.seg_max, status,
+            (p.flags & MV_ROPE_APPEND) ? &rope : nullptr, [] {},
             [&] { prime_ahead(rg, iss, ops, op.next_mv, cta, warp, lane); });
     } else {
         prime_ahead(rg, iss, ops, op.next_mv, cta, warp, lane);
@@ -316,6 +326,15 @@ zcu_result program_record(zcu_program* pr, uint32_t kernel, const LaunchArgs& a)
             if (m > 2) return zcu_fail(a, ZCU_E_UNSUPPORTED_KERNEL, "step program: %d tokens per multiply (at most 2)", m);
             if (p.k % 256 != 0 || p.k == 0) return zcu_fail(a, ZCU_E_UNSUPPORTED_KERNEL, "step program: k = %u is not a multiple of 256", p.k);
             ZCU_NEED(a, !(p.flags & MV_NORM) || a.nb >= 4, "step program: NORM without a norm weight binding");
+            if (p.flags & MV_ROPE_APPEND) {
+                PRopeAppend r;
+                ZCU_NEED(a, a.params_bytes >= sizeof(PMatvec) + sizeof(PRopeAppend) && a.nb >= 8, "step program: matvec + rope_append with a short parameter block or bindings");
+                memcpy(&r, static_cast<const char*>(a.params) + sizeof(PMatvec), sizeof(r));
+                ZCU_NEED(a, r.normal == 1 && r.qk_norm == 0 && r.head_dim % 2 == 0 && r.n_rot % 2 == 0 && r.n_rot <= r.head_dim && (r.kv == KV_F32 || r.kv == KV_F16) &&
+                                p.col0 % 2 == 0 && p.n % 2 == 0 && !(p.flags & (MV_SILU_PAIR | MV_ACCUMULATE)),
+                         "step program: this matvec + rope_append is not fused (adjacent pairs, no q/k norm, f16 or f32 cache)");
+                if (!(a.nb >= 9 && r._pad[0] != 0)) op.b[8] = nullptr;
+            }
             ZCU_NEED(a, ((uintptr_t)a.b[0].ptr & 15) == 0 && ((uintptr_t)a.b[1].ptr & 15) == 0, "step program: x and w must be 16-byte aligned");
             const int row_tiles = ((int)p.n + 15) / 16;
             op.kind = q4 ? PK_MV_Q4_K : PK_MV_Q8_0;

@@ -33,7 +33,7 @@ struct PMatvec {  // kernels.zig:472-494 (MatvecBf16, shared by every matvec ide
     float eps;
     uint32_t flags, half, x_stride;
 };
-enum : uint32_t { MV_NORM = 1u, MV_ACCUMULATE = 2u, MV_SILU_PAIR = 4u };
+enum : uint32_t { MV_NORM = 1u, MV_ACCUMULATE = 2u, MV_SILU_PAIR = 4u, MV_ROPE_APPEND = 8u };
 struct PQuantizeQ8 {  // kernels.zig:495-501
     uint32_t k, block, mode;
     float eps;
@@ -69,6 +69,17 @@ struct PGatedNorm {  // kernels.zig:624-633
     uint32_t v_heads, dim;
     float eps;
     uint32_t z_row, z_off, sigmoid, _pad[2];
+};
+
+// What a multiply with MV_ROPE_APPEND needs beyond its own block: the rope_append parameters (they follow
+// PMatvec in the parameter block) and that kernel's other bindings.
+struct MvRope {
+    PRopeAppend p;
+    const float2* table;
+    void* kc;
+    void* vc;
+    const PStep* step;
+    const uint32_t* seq_pos;
 };
 
 static_assert(sizeof(PStep) == 16, "Step");

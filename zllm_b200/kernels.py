@@ -22,6 +22,9 @@ KERNEL_COUNT = 57
 
 # MatvecBf16.Flags (kernels.zig:485-493)
 NORM, ACCUMULATE, SILU_PAIR = 1, 2, 4
+# an extension of this backend: the multiply's outputs are a Q|K|V row, rotated and appended to the cache in its
+# epilogue (rope_append without its own launch); the parameter block is Matvec followed by RopeAppend
+ROPE_APPEND_FUSED = 8
 
 # plan.common.KvFormat
 KV_F32, KV_F16 = 0, 1
@@ -63,6 +66,7 @@ Embed = _struct("EmbedBf16", [("dim", u32), ("row0", u32), ("chunk_rows", u32), 
 RopeAppend = _struct("RopeAppend", [("heads", u32), ("kv_heads", u32), ("head_dim", u32), ("n_rot", u32), ("row", u32),
                                     ("k_off", u32), ("v_off", u32), ("kv", u32), ("eps", f32), ("gated", u32),
                                     ("qk_norm", u32), ("normal", u32), ("scales", u32), ("_pad", u32 * 3)])
+MatvecRope = _struct("MatvecRope", [("mv", Matvec), ("rope", RopeAppend)])
 Attention = _struct("Attention", [("heads", u32), ("kv_heads", u32), ("head_dim", u32), ("kv", u32), ("scale", f32),
                                   ("max_blocks", u32), ("q_row", u32), ("row0", u32), ("gated", u32), ("scales", u32),
                                   ("_pad", u32 * 2)])
@@ -120,9 +124,16 @@ class Launcher:
 
     # -- the decode multiply: grid (ceil(n / groupRows), m, 1) in the reference; only m matters here
     def matvec(self, ttype, x, w, out, n, k, m=1, col0=0, out_stride=None, flags=0, eps=0.0, half=0, x_stride=0,
-               norm_w=None, variant=0):
+               norm_w=None, variant=0, rope=None):
+        """`rope` = (RopeAppend, [table, kc, vc, step(, positions)]) fuses rope_append into the multiply that
+        produces the Q|K|V row (ROPE_APPEND_FUSED; needs norm_w as binding 3)."""
         p = Matvec(n, k, col0, out_stride if out_stride is not None else n, eps, flags, half, x_stride)
         args = [x, w, out] + ([norm_w] if norm_w is not None else [])
+        if rope is not None:
+            assert norm_w is not None and len(args) == 4
+            p.flags |= ROPE_APPEND_FUSED
+            p = MatvecRope(p, rope[0])
+            args += list(rope[1])
         self.launch(MATVEC_KERNEL[ttype], p, args, (-(-n // 8), m, 1), variant)
 
     def matmul(self, ttype, x, w, out, rows, n, k, col0=0, out_stride=None, accumulate=False, variant=0, layout=0):

@@ -123,12 +123,15 @@ class DenseProgram:
     """
 
     def __init__(self, ctx, cfg: DenseConfig, weights, batch: int, alloc, shard: Shard | None = None, gather=None,
-                 variants: dict | None = None):
+                 variants: dict | None = None, fuse_rope: bool | None = None):
         self.ctx, self.cfg, self.w, self.B = ctx, cfg, weights, batch
         self.sh = shard or Shard()
         self.gather = gather
         self.L = K.Launcher(ctx)
         self.variants = variants or {}
+        # rope_append inside the Q|K|V multiply's epilogue (one launch fewer per layer) where that is built:
+        # 1, 2 or 4 sequences
+        self.fuse_rope = (batch in (1, 2, 4)) if fuse_rope is None else fuse_rope
         self.launches_per_step = 0
         sh, hd = self.sh, cfg.head_dim
         h0, h1 = sh.heads(cfg)
@@ -204,12 +207,17 @@ class DenseProgram:
         att_cols = self.att.at(self.h0 * hd * 4)                # this rank's head columns of att
         for il in range(cfg.layers):
             lw = self.w["layers"][il]
-            # 1. fused attn_norm + Q|K|V projection (local heads)
-            self._matvec(cfg.body_type, self.x, lw["wqkv"], self.qkv, self.qkv_row, e, flags=K.NORM, eps=cfg.eps,
-                         norm_w=lw["attn_norm"])
-            # 2. RoPE (normal pairs) and the cache append at each sequence's position
-            self.L.launch(K.ROPE_APPEND, rp, [self.qkv, self.dummy, self.dummy, self.rope, self.kc[il], self.vc[il],
-                                              self.step, self.positions], (self.lh + self.lg, B, 1))
+            # 1. fused attn_norm + Q|K|V projection (local heads); 2. RoPE (normal pairs) and the cache append at
+            #    each sequence's position, in the multiply's epilogue or as rope_append's own launch
+            if self.fuse_rope:
+                self._matvec(cfg.body_type, self.x, lw["wqkv"], self.qkv, self.qkv_row, e, flags=K.NORM, eps=cfg.eps,
+                             norm_w=lw["attn_norm"], rope=(rp, [self.rope, self.kc[il], self.vc[il], self.step, self.positions]))
+                self.launches_per_step -= 1
+            else:
+                self._matvec(cfg.body_type, self.x, lw["wqkv"], self.qkv, self.qkv_row, e, flags=K.NORM, eps=cfg.eps,
+                             norm_w=lw["attn_norm"])
+                self.L.launch(K.ROPE_APPEND, rp, [self.qkv, self.dummy, self.dummy, self.rope, self.kc[il], self.vc[il],
+                                                  self.step, self.positions], (self.lh + self.lg, B, 1))
             # 3-4. split attention over each sequence's cache, merged into this rank's head columns of att
             self.L.launch(K.ATTN_SPLIT, ap, [self.qkv, self.kc[il], self.vc[il], self.part, self.step, self.positions],
                           (self.lg, blocks, B))
