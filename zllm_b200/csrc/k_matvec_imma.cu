@@ -10,16 +10,17 @@ using namespace imma;
 // (griddepcontrol.wait) only before it reads activations.
 template <int TYPE, int NB, int STAGES>
 __global__ void __launch_bounds__(IM_THREADS, 1) matvec_imma(PMatvec p, const float* __restrict__ x,
-                                                            const uint8_t* __restrict__ w, float* __restrict__ out,
+                                                            const __grid_constant__ CUtensorMap wmap,
+                                                            const __grid_constant__ CUtensorMap smap, float* __restrict__ out,
                                                             const float* __restrict__ norm_w, int t0, int mt,
                                                             int seg_max, int* __restrict__ status, const __grid_constant__ MvRope rope) {
-    extern __shared__ __align__(16) uint8_t smem[];
+    extern __shared__ __align__(128) uint8_t smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const ImLayout L = im_layout(4 * mt, (int)p.k, TYPE == W_Q4_K, 2 * NB, seg_max, STAGES);
     ImRing rg;
     ImIssue iss;
     im_ring_init<STAGES>(rg, smem, L, warp, lane);
-    im_prime<TYPE, STAGES>(rg, iss, p, w, (int)blockIdx.x, (int)gridDim.x, warp, lane, 0);
+    im_prime<TYPE, STAGES>(rg, iss, p, &wmap, &smap, (int)blockIdx.x, (int)gridDim.x, warp, lane, 0);
     im_multiply<TYPE, NB, STAGES>(
         smem, rg, iss, (int)blockIdx.x, (int)gridDim.x, p, x, out, norm_w, t0, mt, seg_max, status,
         (p.flags & MV_ROPE_APPEND) ? &rope : nullptr,
@@ -58,7 +59,13 @@ zcu_result launch_staged(const LaunchArgs& a, const MvArgs& v, int t0, int mt, i
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, v.p, v.x, v.w, v.out, v.nw, t0, mt, seg_max, a.status, v.rope);
+    // the weights as a byte matrix of 16-row boxes (both halves of a SILU_PAIR matrix are rows of one matrix)
+    const size_t rows = (size_t)v.p.n + ((v.p.flags & MV_SILU_PAIR) ? v.p.half : 0);
+    CUtensorMap wmap, smap;
+    if (!im_weight_map(&wmap, v.w, TYPE == W_Q4_K, (int)v.p.k, rows, false) ||
+        !im_weight_map(&smap, v.w, TYPE == W_Q4_K, (int)v.p.k, rows, TYPE != W_Q4_K))
+        return zcu_fail(a, ZCU_E_GPU, "matvec_imma: the driver refused a tensor map (n %u, k %u)", v.p.n, v.p.k);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, v.p, v.x, wmap, smap, v.out, v.nw, t0, mt, seg_max, a.status, v.rope);
     if (e != cudaSuccess) return zcu_fail(a, ZCU_E_GPU, "matvec_imma: launch failed: %s", cudaGetErrorString(e));
     return ZCU_OK;
 }

@@ -28,6 +28,7 @@
 #pragma once
 
 #include "k_matvec_common.cuh"
+#include "tma_util.cuh"
 
 namespace imma {
 
@@ -94,15 +95,32 @@ __device__ __forceinline__ int stage_pos(int e) {
     return e;
 }
 
-// One warp's tile of weights: 16 rows x one super-block (Q4_K, 144 bytes a row) or x four blocks
-// (Q8_0: 128 value bytes a row, then its 4 f16 scales). Each row of a tile is one bulk copy
-// (cp.async.bulk, global -> shared, completing on an mbarrier) into a ring of stages per warp, several
-// tiles ahead of the one being multiplied. Rows sit 160 bytes apart in shared memory, so the 8-byte
-// fragment loads of a half-warp (four rows) cover 128 distinct bytes.
+// One warp's tile of weights: 16 rows x one super-block (Q4_K, 144 bytes a row) or x four blocks (Q8_0: 128
+// value bytes a row, and the 16 bytes that hold the rows' scales). A tile is ONE TMA copy of a 16-row x 160-byte
+// box of the weight matrix (seen as a byte matrix through a tensor map), completing on an mbarrier, into a ring
+// of stages per warp, several tiles ahead of the one being multiplied; Q8_0 adds a 16 x 16-byte box for the
+// scales. One request per tile matters: the TMA unit takes requests at a limited rate, and 16 row copies per
+// tile made that rate the bound. The box is 160 bytes wide so that rows sit 160 bytes apart in shared memory
+// and the 8-byte fragment loads of a half-warp (four rows) cover 128 distinct bytes; the 16 (Q4_K) or 32
+// (Q8_0) extra bytes of a row are the start of the next tile's (sectors that are fetched anyway) or zeros past
+// the row's end.
 constexpr int Q8_UNIT = 4;        // blocks per Q8_0 tile
 constexpr int TILE_ROW = 160;
-constexpr int TILE_BYTES = 16 * TILE_ROW;
+constexpr int TILE_SCALES = 16 * TILE_ROW;         // where a Q8_0 tile's [16 rows][16 bytes] of scales sit
+constexpr int TILE_BYTES = 16 * TILE_ROW + 256;    // a stage: a multiple of 128 bytes
 
+// Tensor map of a weight matrix for these tiles. `rows`: every row the multiply may touch (both halves of a
+// SILU_PAIR matrix).
+inline bool im_weight_map(CUtensorMap* map, const void* w, bool q4, int k, size_t rows, bool scales) {
+    const uint64_t rb = q4 ? (uint64_t)(k / 256) * 144 : (((uint64_t)k + k / 16 + 15) & ~(uint64_t)15);
+    return tma::bytes_2d(map, w, rows, rb, scales ? 16u : (uint32_t)TILE_ROW, 16u);
+}
+
+__device__ __forceinline__ void tma_tile(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t mbar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n" ::"r"(dst),
+                 "l"((uint64_t)map), "r"(mbar), "r"(x), "r"(y)
+                 : "memory");
+}
 
 struct ImLayout {
     int ring, mbar, xd, sxd, red, segkey, meta, total;
@@ -167,31 +185,25 @@ __device__ __forceinline__ void im_ring_init(ImRing& rg, uint8_t* smem, const Im
 
 // The copy side of one multiply for one warp: which tile comes next and where its rows start.
 struct ImIssue {
-    const uint8_t* w;
-    const uint8_t* is_row;
-    size_t rb;
+    const CUtensorMap* map;   // the weight matrix as 160-byte-wide boxes
+    const CUtensorMap* smap;  // Q8_0: its scales as 16-byte-wide boxes
     int n, half, k, units, nparts, rt_lo;
     int is_rtl, is_part, is_unit, issued, lo, hi;
     int op;                // which operation of a program this iterator belongs to (-1: none)
 };
 
-__device__ __forceinline__ void im_issue_row(ImIssue& s, int lane) {
-    const int j = (s.is_part ? s.half : 0) + (s.rt_lo + s.is_rtl) * 16 + (lane & 15);
-    const int lim = (s.is_part ? s.half : 0) + s.n - 1;
-    s.is_row = s.w + (size_t)min(j, lim) * s.rb;
-}
-
 // CTA `cta` of `ncta` owns the contiguous row tiles [cta*RT/ncta, (cta+1)*RT/ncta); its tiles, ordered (row
 // tile, part, k), are cut into 16 contiguous ranges, one per warp.
 template <int TYPE>
-__device__ __forceinline__ void im_issue_setup(ImIssue& s, const PMatvec& p, const uint8_t* w, int cta, int ncta, int warp, int lane) {
+__device__ __forceinline__ void im_issue_setup(ImIssue& s, const PMatvec& p, const CUtensorMap* map, const CUtensorMap* smap, int cta,
+                                               int ncta, int warp) {
     constexpr bool Q4 = TYPE == W_Q4_K;
     const int k = (int)p.k, n = (int)p.n;
-    s.w = w;
+    s.map = map;
+    s.smap = smap;
     s.k = k;
     s.n = n;
     s.half = (int)p.half;
-    s.rb = Q4 ? (size_t)(k / 256) * 144 : (((size_t)k + k / 16 + 15) & ~(size_t)15);
     s.nparts = (p.flags & MV_SILU_PAIR) ? 2 : 1;
     s.units = Q4 ? k / 256 : (k / 32 + Q8_UNIT - 1) / Q8_UNIT;
     const int row_tiles = (n + 15) / 16;
@@ -205,31 +217,31 @@ __device__ __forceinline__ void im_issue_setup(ImIssue& s, const PMatvec& p, con
     s.is_part = (s.lo % per_rt) / s.units;
     s.is_unit = s.lo % s.units;
     s.issued = s.lo;
-    im_issue_row(s, lane);
 }
 
-// Copies tile `issued` into the ring's next stage (lane l < 16 copies row l with one bulk copy), then steps
-// the iterator. Does nothing once the warp's range is exhausted.
+// Copies tile `issued` into the ring's next stage (one lane asks the TMA unit for the whole box), then steps the
+// iterator. Does nothing once the warp's range is exhausted.
 template <int TYPE, int STAGES>
 __device__ __forceinline__ void im_issue(ImRing& rg, ImIssue& s, int lane) {
     constexpr bool Q4 = TYPE == W_Q4_K;
-    constexpr uint32_t ROW_COPY = Q4 ? 144u : 128u;
     if (s.issued >= s.hi) return;
     const uint32_t mb = rg.mbar + 8 * rg.is_stage;
-    // the stage was read with ordinary loads; the bulk copy writes it through the async proxy
+    // the stage was read with ordinary loads; the copy writes it through the async proxy
     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-    if (lane == 0) mbar_expect_tx(mb, Q4 ? 16u * 144u : 16u * (128u + 16u));
     __syncwarp();
-    if (lane < 16) {
-        const uint32_t dst = rg.base + (uint32_t)rg.is_stage * TILE_BYTES + (uint32_t)lane * TILE_ROW;
+    if (lane == 0) {
+        const uint32_t dst = rg.base + (uint32_t)rg.is_stage * TILE_BYTES;
+        const int y = (s.is_part ? s.half : 0) + (s.rt_lo + s.is_rtl) * 16;
         if constexpr (Q4) {
-            bulk_g2s(dst, s.is_row + (size_t)s.is_unit * 144, ROW_COPY, mb);
+            mbar_expect_tx(mb, 16u * TILE_ROW);
+            tma_tile(dst, s.map, s.is_unit * 144, y, mb);
         } else {
-            // four blocks of values, and the 16 bytes that hold their four scales (k is a multiple of
-            // 256 here, so both copies are 16-byte aligned and never run past the row)
+            // four blocks of values, and the 16 bytes that hold the scales of blocks (b0 & ~7) .. +7 (k is a
+            // multiple of 256 here, so both boxes start on 16-byte boundaries)
             const int b0 = s.is_unit * Q8_UNIT;
-            bulk_g2s(dst, s.is_row + (size_t)b0 * 32, ROW_COPY, mb);
-            bulk_g2s(dst + 128, s.is_row + s.k + 2 * (b0 & ~7), 16u, mb);
+            mbar_expect_tx(mb, 16u * TILE_ROW + 256u);
+            tma_tile(dst, s.map, b0 * 32, y, mb);
+            tma_tile(dst + TILE_SCALES, s.smap, s.k + 2 * (b0 & ~7), y, mb);
         }
     }
     s.issued++;
@@ -242,16 +254,15 @@ __device__ __forceinline__ void im_issue(ImRing& rg, ImIssue& s, int lane) {
             s.is_part = 0;
             s.is_rtl++;
         }
-        if (s.issued < s.hi) im_issue_row(s, lane);
     }
 }
 
 // Starts a multiply's copies: the first STAGES - 1 tiles of this warp's range. Weights do not depend on
 // the activations, so this may run long before the multiply itself.
 template <int TYPE, int STAGES>
-__device__ __forceinline__ void im_prime(ImRing& rg, ImIssue& s, const PMatvec& p, const uint8_t* w, int cta, int ncta, int warp,
-                                         int lane, int op) {
-    im_issue_setup<TYPE>(s, p, w, cta, ncta, warp, lane);
+__device__ __forceinline__ void im_prime(ImRing& rg, ImIssue& s, const PMatvec& p, const CUtensorMap* map, const CUtensorMap* smap,
+                                         int cta, int ncta, int warp, int lane, int op) {
+    im_issue_setup<TYPE>(s, p, map, smap, cta, ncta, warp);
     s.op = op;
 #pragma unroll
     for (int i = 0; i < STAGES - 1; i++) im_issue<TYPE, STAGES>(rg, s, lane);
@@ -526,7 +537,7 @@ __device__ __forceinline__ void im_multiply(uint8_t* smem, ImRing& rg, ImIssue& 
         } else {
             const int b0 = unit * Q8_UNIT;
             // the 16 bytes copied hold the scales of blocks (b0 & ~7) .. +7: this tile's four are its low or high half
-            const uint2 sc0 = lds64(tile + hoff + 128 + 8 * (unit & 1)), sc1 = lds64(tile + hoff + 8 * TILE_ROW + 128 + 8 * (unit & 1));
+            const uint2 sc0 = lds64(tile + TILE_SCALES + 16 * g + 8 * (unit & 1)), sc1 = lds64(tile + TILE_SCALES + 16 * (g + 8) + 8 * (unit & 1));
             const uint32_t scw0[2] = {sc0.x, sc0.y}, scw1[2] = {sc1.x, sc1.y};
 #pragma unroll
             for (int i = 0; i < Q8_UNIT; i++) {

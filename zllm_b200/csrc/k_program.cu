@@ -37,7 +37,9 @@ constexpr int PROG_SMEM_MAX = 227 * 1024;
 
 enum : uint32_t { PK_MV_Q4_K = 1, PK_MV_Q8_0, PK_EMBED_Q4_K, PK_EMBED_Q8_0, PK_EMBED_BF16, PK_EMBED_F16, PK_ROPE_APPEND, PK_ATTN_SPLIT, PK_ATTN_COMBINE };
 
-struct ProgOp {
+struct alignas(64) ProgOp {
+    CUtensorMap map;         // multiply: the weight matrix as 16-row x 160-byte boxes (64-byte aligned)
+    CUtensorMap smap;        // Q8_0 multiply: its scales as 16-row x 16-byte boxes
     uint32_t kind;
     uint32_t gx, gy, gz;     // grid of virtual blocks (the small kernels)
     uint32_t ncta;           // multiply: CTAs that take part (the standalone kernel's grid)
@@ -106,7 +108,7 @@ template <int TYPE>
 __device__ __forceinline__ void prime_op(ImRing& rg, ImIssue& iss, const ProgOp& op, int index, int cta, int warp, int lane) {
     PMatvec p;
     memcpy(&p, op.params, sizeof(p));
-    im_prime<TYPE, PROG_STAGES>(rg, iss, p, static_cast<const uint8_t*>(op.b[1]), cta, (int)op.ncta, warp, lane, index);
+    im_prime<TYPE, PROG_STAGES>(rg, iss, p, &op.map, &op.smap, cta, (int)op.ncta, warp, lane, index);
 }
 
 // Starts the copies of the multiply at `index` (if this CTA takes part in it) unless they were started already.
@@ -250,9 +252,9 @@ __global__ void __launch_bounds__(PROG_THREADS, 1) program_kernel(const ProgOp* 
     unsigned epoch = 0;
     for (int i = 0; i < n_ops; i++) {
         const ProgOp& op = ops[i];
-        if (threadIdx.x < 4) {
-            if (i + 1 < n_ops) prefetch_l1(reinterpret_cast<const char*>(&ops[i + 1]) + 128 * (threadIdx.x & 1));
-            if (op.next_mv >= 0 && threadIdx.x >= 2) prefetch_l1(reinterpret_cast<const char*>(&ops[op.next_mv]) + 128 * (threadIdx.x & 1));
+        if (threadIdx.x < 8) {
+            if (i + 1 < n_ops && threadIdx.x < 4) prefetch_l1(reinterpret_cast<const char*>(&ops[i + 1]) + 128 * (threadIdx.x & 3));
+            if (op.next_mv >= 0 && threadIdx.x >= 4) prefetch_l1(reinterpret_cast<const char*>(&ops[op.next_mv]) + 128 * (threadIdx.x & 3));
         }
         const bool tracer = trace != nullptr && cta == 0 && threadIdx.x == 0;
         if (tracer) trace[2 * i] = global_ns();
@@ -346,6 +348,9 @@ zcu_result program_record(zcu_program* pr, uint32_t kernel, const LaunchArgs& a)
             if (need > PROG_SMEM_MAX)
                 return zcu_fail(a, ZCU_E_UNSUPPORTED_KERNEL, "step program: k = %u with %d tokens needs %d bytes of shared memory", p.k, m, need);
             if (need > pr->smem) pr->smem = need;
+            const size_t rows = (size_t)p.n + ((p.flags & MV_SILU_PAIR) ? p.half : 0);
+            if (!im_weight_map(&op.map, a.b[1].ptr, q4, (int)p.k, rows, false) || !im_weight_map(&op.smap, a.b[1].ptr, q4, (int)p.k, rows, !q4))
+                return zcu_fail(a, ZCU_E_GPU, "step program: the driver refused a tensor map (n %u, k %u)", p.n, p.k);
             break;
         }
         case ZCU_K_EMBED_Q4_K:
