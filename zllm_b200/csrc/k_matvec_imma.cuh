@@ -366,7 +366,8 @@ __device__ __forceinline__ void im_multiply(uint8_t* smem, ImRing& rg, ImIssue& 
             }
             float nscale = 1.0f;
             if (norm) {
-                const float mean = (float)(tot / (double)k);
+                // (a power-of-two k divides exactly either way; the multiply skips the slow f64 division)
+                const float mean = (k & (k - 1)) == 0 ? (float)(tot * (1.0 / (double)k)) : (float)(tot / (double)k);
                 nscale = 1.0f / sqrtf(mean + p.eps);
             }
             am = am * nscale * 1.0001f;  // the staged products round separately
@@ -596,10 +597,15 @@ __device__ __forceinline__ void im_multiply(uint8_t* smem, ImRing& rg, ImIssue& 
         const bool valid = i < total && j < n;
         float v = 0.f, u = 0.f;
         if (valid) {
+            // every segment is loaded (eight at a time, no dependent branches) and added only where its key
+            // matches, in (warp, segment) order
+            const float* rbase = red + (size_t)row * SLOTS + tk;
+#pragma unroll 8
             for (int sgi = 0; sgi < IM_WARPS * seg_max; sgi++) {
                 const int key = segkey[sgi];
-                if (key == rtl * 2) v = __fadd_rn(v, red[((size_t)sgi * 16 + row) * SLOTS + tk]);
-                else if (key == rtl * 2 + 1) u = __fadd_rn(u, red[((size_t)sgi * 16 + row) * SLOTS + tk]);
+                const float r = rbase[(size_t)sgi * 16 * SLOTS];
+                v = __fadd_rn(v, key == rtl * 2 ? r : 0.f);
+                u = __fadd_rn(u, key == rtl * 2 + 1 ? r : 0.f);
             }
         }
         if (pair) v = silu_f(v) * u;
