@@ -193,7 +193,7 @@ __global__ void __launch_bounds__(AT_THREADS) attn_split_kernel(PAttention p, co
 }
 
 template <int HD, int GROUP_CAP>
-__global__ void __launch_bounds__(attn::AF_THREADS) attn_split_fast(PAttention p, const float* __restrict__ qg,
+__global__ void __launch_bounds__(attn::AF_THREADS, 3) attn_split_fast(PAttention p, const float* __restrict__ qg,
                                                                    const __half* __restrict__ kc,
                                                                    const __half* __restrict__ vc, float* __restrict__ part,
                                                                    const PStep* __restrict__ step,
