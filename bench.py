@@ -342,7 +342,7 @@ class DecodeStep:
         self.program = None
         # how a step is replayed on one GPU: "program" = one persistent kernel (batch 1), "graph" = a CUDA graph
         # of the step's launches
-        self.replay = replay if replay != "auto" else ("program" if (not dist.on and batch == 1) else "graph")
+        self.replay = replay if replay != "auto" else "graph"  # the graph is the faster of the two today
         self.bytes = self.prog.algorithmic_bytes(self.positions)
 
     def _record(self):
