@@ -201,3 +201,44 @@ def test_rope_append_in_the_multiply_epilogue_equals_its_own_launch(gpu, batch):
                      + [c.download(np.uint16) for c in prog.kc + prog.vc])
     for a, b in zip(got[False], got[True]):
         assert np.array_equal(a, b)
+
+
+def test_peer_exchange_with_one_rank_equals_the_plain_step(gpu):
+    # The tensor-parallel path with a world of one: outputs go through the arena, every producer publishes its
+    # exchange slot and every consumer waits for it (its own count). Same bits as the plain step, also when the
+    # step is captured once and replayed (the counters keep growing).
+    from zllm_b200 import abi
+
+    cfg = CFG
+    host = M.host_model(cfg, "tiny")
+    weights = M.upload(host, cfg, gpu.put)
+    rng = np.random.default_rng(77)
+    kv_shape = (1, cfg.max_ctx, cfg.kv_heads, cfg.head_dim)
+    kc_host = [rng.normal(size=kv_shape).astype(np.float16) for _ in range(cfg.layers)]
+    vc_host = [rng.normal(size=kv_shape).astype(np.float16) for _ in range(cfg.layers)]
+    arena = abi.PeerArena(gpu, 0, 1, DenseProgram.arena_bytes(cfg, 1), DenseProgram.arena_slots(cfg))
+
+    def fresh(**kw):
+        prog = DenseProgram(gpu, cfg, weights, 1, gpu.zeros, **kw)
+        prog.set_rope_table(gpu.put(DenseProgram.rope_table(cfg)))
+        for il in range(cfg.layers):
+            prog.kc[il].upload(kc_host[il].view(np.uint16))
+            prog.vc[il].upload(vc_host[il].view(np.uint16))
+        return prog
+
+    plain, peer = fresh(), fresh(arena=arena)
+    graph = None
+    for token, pos in [(5, 100), (900, 101), (31, 102)]:
+        tok, ps = np.array([token], dtype=np.uint32), np.array([pos], dtype=np.uint32)
+        plain.write_step(tok, ps)
+        plain.record_step(cfg.max_ctx)
+        peer.write_step(tok, ps)
+        if graph is None:
+            gpu.sync()
+            gpu.capture_begin()
+            peer.record_step(cfg.max_ctx)
+            graph = gpu.capture_end()
+        gpu.graph_launch(graph)
+        gpu.sync()
+        for name in ("logits", "x", "att", "act"):
+            assert np.array_equal(getattr(plain, name).download(np.uint32), getattr(peer, name).download(np.uint32)), (name, pos)

@@ -73,6 +73,98 @@ def _rank(rank: int, world: int, port: int, out_dir: str):
     os._exit(0)  # no NCCL teardown: see bench.py
 
 
+def _rank_peer(rank: int, world: int, port: int, out_dir: str):
+    """The same comparison with the library's own exchange: arenas mapped over CUDA IPC, outputs pushed by the
+    kernels' epilogues, counters instead of collectives. torch.distributed (gloo) only carries the IPC handles."""
+    import torch.distributed as dist
+
+    from zllm_b200 import abi
+    from zllm_b200 import model as M
+    from zllm_b200.plan import DenseConfig, DenseProgram, Shard
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    cfg = DenseConfig(layers=2, hidden=512, heads=8, kv_heads=2, head_dim=64, ff=1024, vocab=1536, max_ctx=320)
+    host = M.host_model(cfg, "tp-test")
+    rng = np.random.default_rng(17)
+    batch = 2
+    kv_shape = (batch, cfg.max_ctx, cfg.kv_heads, cfg.head_dim)
+    kc_host = [rng.normal(size=kv_shape).astype(np.float16) for _ in range(cfg.layers)]
+    vc_host = [rng.normal(size=kv_shape).astype(np.float16) for _ in range(cfg.layers)]
+    steps = [(rng.integers(0, cfg.vocab, size=batch).astype(np.uint32), np.array(p, dtype=np.uint32)) for p in ([100, 37], [101, 38], [102, 39])]
+    ctx = abi.Context(rank)
+
+    def exchange(handle: bytes):
+        got = [None] * world
+        dist.all_gather_object(got, handle)
+        return got
+
+    def build(sh, arena):
+        weights = M.upload(host, cfg, ctx.put, sh)
+        prog = DenseProgram(ctx, cfg, weights, batch, ctx.zeros, sh, arena=arena)
+        prog.set_rope_table(ctx.put(DenseProgram.rope_table(cfg)))
+        g0, g1 = sh.kv_heads(cfg)
+        for il in range(cfg.layers):
+            prog.kc[il].upload(np.ascontiguousarray(kc_host[il][:, :, g0:g1]).view(np.uint16))
+            prog.vc[il].upload(np.ascontiguousarray(vc_host[il][:, :, g0:g1]).view(np.uint16))
+        return prog
+
+    arena = abi.PeerArena(ctx, rank, world, DenseProgram.arena_bytes(cfg, batch), DenseProgram.arena_slots(cfg), exchange)
+    sharded = build(Shard(rank, world), arena)
+    whole = build(Shard(0, 1), None) if rank == 0 else None
+    dist.barrier()
+    graph, got, want = None, [], []
+    for tokens, positions in steps:
+        sharded.write_step(tokens, positions)
+        if graph is None:
+            ctx.sync()
+            ctx.capture_begin()
+            sharded.record_step(cfg.max_ctx)
+            graph = ctx.capture_end()
+        ctx.graph_launch(graph)
+        ctx.sync()
+        got.append(sharded.logits.download(np.float32).reshape(batch, cfg.vocab).copy())
+        if whole is not None:
+            whole.write_step(tokens, positions)
+            whole.record_step(cfg.max_ctx)
+            ctx.sync()
+            want.append(whole.logits.download(np.float32).reshape(batch, cfg.vocab).copy())
+        dist.barrier()  # a rank leaves a step only when every rank has read its logits
+    if rank == 0:
+        np.save(os.path.join(out_dir, "one.npy"), np.stack(want))
+    np.save(os.path.join(out_dir, f"peer{rank}.npy"), np.stack(got))
+    dist.barrier()
+    os._exit(0)
+
+
+def _spawn(fn, tmp):
+    import torch.multiprocessing as mp
+
+    port = 29700 + os.getpid() % 200
+    ctx = mp.spawn(fn, args=(2, port, tmp), nprocs=2, join=False)
+    deadline = time.monotonic() + 240
+    while not ctx.join(timeout=5):  # join() returns as soon as one rank ends; True once all have
+        if time.monotonic() > deadline:
+            for p in ctx.processes:
+                p.kill()  # the two PIDs this test started
+            pytest.fail("the two ranks did not finish in 240 s")
+
+
+def test_two_gpus_with_peer_pushes_give_the_single_gpu_logits():
+    import torch
+
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    with tempfile.TemporaryDirectory() as tmp:
+        _spawn(_rank_peer, tmp)
+        one = np.load(os.path.join(tmp, "one.npy"))
+        peers = [np.load(os.path.join(tmp, f"peer{r}.npy")) for r in range(2)]
+    assert np.isfinite(one).all() and np.abs(one).max() > 0
+    for r in range(2):  # every rank holds the whole logits, and they are the single-GPU bits
+        assert np.array_equal(one.view(np.uint32), peers[r].view(np.uint32)), r
+
+
 def test_two_gpus_give_the_single_gpu_logits():
     import torch
 

@@ -36,7 +36,7 @@ EXPORTS = [
     "zcu_download", "zcu_memset", "zcu_launch", "zcu_sync", "zcu_launch_count", "zcu_capture_begin",
     "zcu_capture_end", "zcu_graph_launch", "zcu_graph_destroy", "zcu_rope_table",
     "zcu_attention_decode_static", "zcu_program_begin", "zcu_program_end", "zcu_program_abandon", "zcu_program_launch",
-    "zcu_program_destroy", "zcu_program_timings",
+    "zcu_program_destroy", "zcu_program_timings", "zcu_ipc_export", "zcu_ipc_open", "zcu_peer_config",
 ]
 
 
@@ -122,6 +122,9 @@ def lib() -> C.CDLL:
         "zcu_program_launch": (C.c_int32, [vp, u32]),
         "zcu_program_destroy": (C.c_int32, [vp, u32]),
         "zcu_program_timings": (C.c_int32, [vp, u32, vp, C.c_size_t, C.POINTER(C.c_size_t)]),
+        "zcu_ipc_export": (C.c_int32, [vp, vp, vp]),
+        "zcu_ipc_open": (C.c_int32, [vp, vp, C.POINTER(vp)]),
+        "zcu_peer_config": (C.c_int32, [vp, u32, u32, C.POINTER(u64), u64, u64, u32]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(L, name)
@@ -186,6 +189,51 @@ class DevBuf:
         if self.ptr:
             lib().zcu_free(self.ctx.h, self.ptr)
             self.ptr = None
+
+
+class SubBuf(DevBuf):
+    """A range of a larger device allocation (an arena), with DevBuf's interface."""
+
+    def __init__(self, ctx: "Context", ptr: int, nbytes: int):  # no allocation of its own
+        self.ctx, self.ptr, self.nbytes = ctx, int(ptr), int(nbytes)
+
+    def free(self):
+        self.ptr = None
+
+
+class PeerArena:
+    """One rank's arena for the tensor-parallel exchange over peer memory (include/zllm_cuda.h): the vectors
+    every rank reads whole, then the exchange counters. `exchange(handle_bytes) -> [handle_bytes per rank]` is the
+    caller's all-gather of the 64-byte IPC handles (torch.distributed.all_gather_object, or anything else);
+    with world == 1 nothing is exchanged."""
+
+    def __init__(self, ctx: "Context", rank: int, world: int, data_bytes: int, slots: int, exchange=None):
+        self.ctx, self.rank, self.world, self.slots = ctx, rank, world, slots
+        self.data_bytes = (int(data_bytes) + 255) & ~255
+        self.nbytes = self.data_bytes + slots * 8 * 4
+        self.buf = ctx.alloc(self.nbytes).zero()
+        ctx.sync()
+        bases = [0] * world
+        bases[rank] = self.buf.ptr
+        if world > 1:
+            handle = C.create_string_buffer(64)
+            ctx._check(lib().zcu_ipc_export(ctx.h, self.buf.ptr, handle))
+            handles = exchange(handle.raw)
+            for r in range(world):
+                if r != rank:
+                    p = C.c_void_p()
+                    ctx._check(lib().zcu_ipc_open(ctx.h, C.create_string_buffer(handles[r], 64), C.byref(p)))
+                    bases[r] = p.value
+        arr = (C.c_uint64 * world)(*bases)
+        ctx._check(lib().zcu_peer_config(ctx.h, rank, world, arr, self.nbytes, self.data_bytes, slots))
+        self.bases, self.used = bases, 0
+
+    def alloc(self, nbytes: int) -> SubBuf:
+        size = (int(nbytes) + 255) & ~255
+        assert self.used + size <= self.data_bytes, "the arena is full"
+        b = SubBuf(self.ctx, self.buf.ptr + self.used, nbytes)
+        self.used += size
+        return b
 
 
 class Context:

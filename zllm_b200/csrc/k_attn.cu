@@ -205,9 +205,17 @@ __global__ void __launch_bounds__(attn::AF_THREADS, 3) attn_split_fast(PAttentio
 __global__ void __launch_bounds__(256) attn_combine_kernel(PAttention p, const float* __restrict__ qg,
                                                           const float* __restrict__ part, float* __restrict__ out,
                                                           const PStep* __restrict__ step,
-                                                          const uint32_t* __restrict__ seq_pos, int kb) {
+                                                          const uint32_t* __restrict__ seq_pos, int kb,
+                                                          const __grid_constant__ PeerUse pu) {
     extern __shared__ __align__(16) unsigned char dyn_smem[];
-    attn::attn_combine_body(vblock_of_cta(dyn_smem), p, qg, part, out, step, seq_pos, kb);
+    attn::attn_combine_body(vblock_of_cta(dyn_smem), p, qg, part, out, step, seq_pos, kb, &pu);
+    peer::publish(pu, gridDim.x * gridDim.y);
+}
+
+// Waits for one tensor-parallel exchange (ZCU_K_EXT_PEER_WAIT): what a host that is about to read a gathered
+// vector puts at the end of its step.
+__global__ void __launch_bounds__(32) peer_wait_kernel(const __grid_constant__ PeerUse pu, int* __restrict__ status) {
+    peer::wait_slot(pu, status);
 }
 
 using attn::AF_KEYS;
@@ -284,9 +292,18 @@ zcu_result launch_attn_combine(const LaunchArgs& a) {
     if (a.grid[0] == 0 || a.grid[1] == 0) return ZCU_OK;
     const uint32_t* seq_pos = (a.nb >= 5 && p._pad[0] != 0) ? (const uint32_t*)a.b[4].ptr : nullptr;
     const size_t smem = attn::attn_combine_smem((int)p.max_blocks);
+    PeerUse pu;
+    {
+        // the columns this launch writes: heads * head_dim floats of each of its rows
+        const size_t orow = p._pad[1] ? (size_t)p._pad[1] : (size_t)p.heads * p.head_dim;
+        const float* lo = (const float*)a.b[2].ptr + (size_t)p.row0 * orow;
+        const float* hi = lo + (size_t)(a.grid[1] - 1) * orow + (size_t)p.heads * p.head_dim;
+        zcu_result pr = parse_peer(a, pu, lo, hi);
+        if (pr != ZCU_OK) return pr;
+    }
     attn_combine_kernel<<<dim3(p.heads, a.grid[1]), 256, smem, a.stream>>>(p, (const float*)a.b[0].ptr, (const float*)a.b[1].ptr,
                                                                            (float*)a.b[2].ptr, (const PStep*)a.b[3].ptr, seq_pos,
-                                                                           attn_keys_per_block(p));
+                                                                           attn_keys_per_block(p), pu);
     ZCU_CHECK_LAUNCH(a);
     return ZCU_OK;
 }
@@ -362,4 +379,14 @@ zcu_result launch_attn_static(const LaunchArgs& a, uint32_t max_keys, uint32_t r
     c.grid[1] = rows;
     c.grid[2] = 1;
     return launch_attn_combine(c);
+}
+
+zcu_result launch_peer_wait(const LaunchArgs& a) {
+    PeerUse pu;
+    zcu_result pr = parse_peer(a, pu, nullptr, nullptr);
+    if (pr != ZCU_OK) return pr;
+    ZCU_NEED(a, pu.wait_slot != PEER_NONE && pu.push_slot == PEER_NONE, "peer_wait: the parameter block must name a slot to wait for, and only that");
+    peer_wait_kernel<<<1, 32, 0, a.stream>>>(pu, a.status);
+    ZCU_CHECK_LAUNCH(a);
+    return ZCU_OK;
 }

@@ -220,7 +220,7 @@ __host__ __device__ constexpr size_t attn_combine_smem(int max_blocks) { return 
 __device__ __forceinline__ void attn_combine_body(const VBlock& vb, const PAttention& p, const float* __restrict__ qg,
                                                   const float* __restrict__ part, float* __restrict__ out,
                                                   const PStep* __restrict__ step, const uint32_t* __restrict__ seq_pos,
-                                                  int kb) {
+                                                  int kb, const PeerUse* __restrict__ pu = nullptr) {
     float* wsm = reinterpret_cast<float*>(vb.smem);  // [blocks] weights, [32] scratch, [128] float2 of the upper half
     const int tid = vb.tid, lane = tid & 31, warp = tid >> 5, h = vb.x, t = vb.y;
     const int hd = (int)p.head_dim;
@@ -273,12 +273,16 @@ __device__ __forceinline__ void attn_combine_body(const VBlock& vb, const PAtten
     // _pad[1] != 0 (extension): floats between output rows, for writing a rank's head columns of a wider row.
     const size_t orow = p._pad[1] ? (size_t)p._pad[1] : (size_t)p.heads * hd;
     const size_t oi = (size_t)row * orow + (size_t)h * hd + tid_d;
-    if (!p.gated) {
-        out[oi] = o / l;
-        return;
+    float res = o / l;
+    if (p.gated) {
+        const float gate = __ldcg(qg + (size_t)row * p.q_row + (size_t)2 * h * hd + hd + tid_d);
+        res = o / l / (1.0f + expf(-gate));
     }
-    const float gate = __ldcg(qg + (size_t)row * p.q_row + (size_t)2 * h * hd + hd + tid_d);
-    out[oi] = o / l / (1.0f + expf(-gate));
+    if (pu != nullptr && pu->push_slot != PEER_NONE) {
+        for (int r = 0; r < pu->t.world; r++) *peer::remote(*pu, out + oi, r) = res;  // this rank's heads, to every rank
+    } else {
+        out[oi] = res;
+    }
 }
 
 

@@ -281,6 +281,13 @@ zcu_result parse_matvec(const LaunchArgs& a, MvArgs& v, uint32_t elem_block, boo
     ZCU_NEED(a, ((uintptr_t)v.x & 15) == 0 && ((uintptr_t)v.w & 15) == 0, "matvec: x and w must be 16-byte aligned");
     ZCU_NEED(a, v.p.x_stride == 0 || v.p.x_stride * 4 >= v.p.k, "matvec: x_stride shorter than k");
     (void)needs_256;
+    {
+        // the rows this launch writes: [col0, col0 + n) of m output rows
+        const float* lo = v.out + v.p.col0;
+        const float* hi = v.out + (size_t)(v.m - 1) * v.p.out_stride + v.p.col0 + v.p.n;
+        zcu_result pr = parse_peer(a, v.peer, lo, hi);
+        if (pr != ZCU_OK) return pr;
+    }
     v.has_rope = (v.p.flags & MV_ROPE_APPEND) != 0;
     if (v.has_rope) {
         // an extension: rope_append fused into the multiply that produces the Q|K|V row. The parameter block is
@@ -313,6 +320,8 @@ zcu_result launch_quant(const LaunchArgs& a, uint32_t block) {
     if ((a.variant == 0 && imma_ok) || family == ZCU_FAMILY_MMA)
         return launch_matvec_imma(a, v, TYPE, (int)(a.variant & 0xffu), 0);
     if (v.has_rope) return zcu_fail(a, ZCU_E_UNSUPPORTED_KERNEL, "matvec + rope_append: only the tensor-core family fuses it");
+    if (v.peer.wait_slot != PEER_NONE || v.peer.push_slot != PEER_NONE)
+        return zcu_fail(a, ZCU_E_UNSUPPORTED_KERNEL, "matvec in a peer exchange: only the tensor-core family takes part");
     if (a.variant == 0) return launch_scalar<TYPE>(a, v);
     if (family == ZCU_FAMILY_SCALAR) return launch_scalar<TYPE>(a, v);
     return zcu_fail(a, ZCU_E_UNSUPPORTED_KERNEL, "matvec: variant 0x%x is not built", a.variant);

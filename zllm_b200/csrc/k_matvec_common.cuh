@@ -68,6 +68,7 @@ struct MvArgs {
     float* out;
     const float* nw;
     int m;
+    PeerUse peer;    // tensor-parallel exchange this launch waits for / publishes (slots PEER_NONE: none)
     bool has_rope;   // MV_ROPE_APPEND: the outputs are a Q|K|V row that is rotated and appended to the cache
     MvRope rope;
 };

@@ -13,7 +13,8 @@ __global__ void __launch_bounds__(IM_THREADS, 1) matvec_imma(PMatvec p, const fl
                                                             const __grid_constant__ CUtensorMap wmap,
                                                             const __grid_constant__ CUtensorMap smap, float* __restrict__ out,
                                                             const float* __restrict__ norm_w, int t0, int mt,
-                                                            int seg_max, int* __restrict__ status, const __grid_constant__ MvRope rope) {
+                                                            int seg_max, int* __restrict__ status, const __grid_constant__ MvRope rope,
+                                                            const __grid_constant__ PeerUse pu) {
     extern __shared__ __align__(128) uint8_t smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const ImLayout L = im_layout(4 * mt, (int)p.k, TYPE == W_Q4_K, 2 * NB, seg_max, STAGES);
@@ -23,12 +24,14 @@ __global__ void __launch_bounds__(IM_THREADS, 1) matvec_imma(PMatvec p, const fl
     im_prime<TYPE, STAGES>(rg, iss, p, &wmap, &smap, (int)blockIdx.x, (int)gridDim.x, warp, lane, 0);
     im_multiply<TYPE, NB, STAGES>(
         smem, rg, iss, (int)blockIdx.x, (int)gridDim.x, p, x, out, norm_w, t0, mt, seg_max, status,
-        (p.flags & MV_ROPE_APPEND) ? &rope : nullptr,
-        [] {
+        (p.flags & MV_ROPE_APPEND) ? &rope : nullptr, &pu,
+        [&] {
             // everything before touched only the weights, which no kernel writes; from here on the
-            // activations are read, so the kernels before this one must have finished
+            // activations are read, so the kernels before this one must have finished - on this GPU, and,
+            // in a tensor-parallel exchange, the producers of the activations on every rank
             asm volatile("griddepcontrol.wait;\n" ::: "memory");
             asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+            peer::wait_slot(pu, status);
         },
         [] {});
 }
@@ -65,7 +68,7 @@ zcu_result launch_staged(const LaunchArgs& a, const MvArgs& v, int t0, int mt, i
     if (!im_weight_map(&wmap, v.w, TYPE == W_Q4_K, (int)v.p.k, rows, false) ||
         !im_weight_map(&smap, v.w, TYPE == W_Q4_K, (int)v.p.k, rows, TYPE != W_Q4_K))
         return zcu_fail(a, ZCU_E_GPU, "matvec_imma: the driver refused a tensor map (n %u, k %u)", v.p.n, v.p.k);
-    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, v.p, v.x, wmap, smap, v.out, v.nw, t0, mt, seg_max, a.status, v.rope);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, v.p, v.x, wmap, smap, v.out, v.nw, t0, mt, seg_max, a.status, v.rope, v.peer);
     if (e != cudaSuccess) return zcu_fail(a, ZCU_E_GPU, "matvec_imma: launch failed: %s", cudaGetErrorString(e));
     return ZCU_OK;
 }

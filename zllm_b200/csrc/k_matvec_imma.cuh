@@ -279,7 +279,8 @@ template <int TYPE, int NB, int STAGES, class WaitInputs, class Between>
 __device__ __forceinline__ void im_multiply(uint8_t* smem, ImRing& rg, ImIssue& iss, int cta, int ncta, const PMatvec& p,
                                             const float* __restrict__ x, float* __restrict__ out,
                                             const float* __restrict__ norm_w, int t0, int mt, int seg_max,
-                                            int* __restrict__ status, const MvRope* __restrict__ rope, WaitInputs wait_inputs, Between between) {
+                                            int* __restrict__ status, const MvRope* __restrict__ rope, const PeerUse* __restrict__ pu, WaitInputs wait_inputs,
+                                            Between between) {
     constexpr bool Q4 = TYPE == W_Q4_K;
     constexpr int SLOTS = 2 * NB;  // token slots of a pass
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -636,8 +637,13 @@ __device__ __forceinline__ void im_multiply(uint8_t* smem, ImRing& rg, ImIssue& 
         }
         if (!valid) continue;
         if (p.flags & MV_ACCUMULATE) v += i == tid ? first_old : __ldcg(out + o);
-        out[o] = v;
+        if (pu != nullptr && pu->push_slot != PEER_NONE) {
+            for (int r = 0; r < pu->t.world; r++) *peer::remote(*pu, out + o, r) = v;  // this rank's slice, to every rank
+        } else {
+            out[o] = v;
+        }
     }
+    if (pu != nullptr) peer::publish(*pu, (unsigned)ncta);
 }
 
 }  // namespace imma

@@ -145,7 +145,7 @@ __device__ __noinline__ void run_multiply(uint8_t* smem, ImRing& rg_io, ImIssue&
         im_multiply<TYPE, 1, PROG_STAGES>(
             smem, rg, iss, cta, (int)op.ncta, p, static_cast<const float*>(op.b[0]), static_cast<float*>(const_cast<void*>(op.b[2])),
             static_cast<const float*>(op.b[3]), (int)op.t0, (int)op.mt, (int)op.seg_max, status,
-            (p.flags & MV_ROPE_APPEND) ? &rope : nullptr, [] {},
+            (p.flags & MV_ROPE_APPEND) ? &rope : nullptr, nullptr, [] {},
             [&] { prime_ahead(rg, iss, ops, op.next_mv, cta, warp, lane); });
     } else {
         prime_ahead(rg, iss, ops, op.next_mv, cta, warp, lane);

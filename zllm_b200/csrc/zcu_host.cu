@@ -98,6 +98,8 @@ struct zcu_context {
     bool capturing = false;
     std::vector<cudaGraphExec_t> graphs;
     zcu_program* recording = nullptr;     // dispatches go into this step program instead of running
+    PeerTable peers = {};                 // tensor-parallel exchange (world == 0: not configured)
+    std::vector<void*> ipc_open;          // peer arenas this context mapped
     std::vector<zcu_program*> programs;
     uint8_t* pinned = nullptr;  // staging for uploads and readbacks
     int* status = nullptr;      // mapped host word kernels set when a bounded wait gives up
@@ -202,6 +204,7 @@ zcu_result dispatch_kernel(zcu_context* c, uint32_t kernel, uint32_t variant, co
     a.variant = variant;
     a.sm_count = c->dry ? 148 : c->prop.multiProcessorCount;
     a.status = c->status;
+    a.peers = c->peers.world > 0 ? &c->peers : nullptr;
     a.err = c->err;
     a.err_cap = sizeof(c->err);
     char name[64];
@@ -227,6 +230,7 @@ zcu_result dispatch_kernel(zcu_context* c, uint32_t kernel, uint32_t variant, co
         case ZCU_K_ATTN_COMBINE: return launch_attn_combine(a);
         case ZCU_K_DELTA_PREP: return launch_delta_prep(a);
         case ZCU_K_DELTA_RULE: return launch_delta_rule(a);
+        case ZCU_K_EXT_PEER_WAIT: return launch_peer_wait(a);
         case ZCU_K_GATED_NORM: return launch_gated_norm(a);
         case ZCU_K_REPACK_Q8_0: return launch_repack_q8_0(a);
         case ZCU_K_MATVEC_Q8_0: return launch_matvec_q8_0(a);
@@ -622,6 +626,7 @@ const char* kernel_name(uint32_t k) {
         case ZCU_K_ATTN_COMBINE: return "attn_combine";
         case ZCU_K_DELTA_PREP: return "delta_prep";
         case ZCU_K_DELTA_RULE: return "delta_rule";
+        case ZCU_K_EXT_PEER_WAIT: return "ext_peer_wait";
         case ZCU_K_GATED_NORM: return "gated_norm";
         case ZCU_K_REPACK_Q8_0: return "repack_q8_0";
         case ZCU_K_MATVEC_Q8_0: return "matvec_q8_0";
@@ -642,6 +647,26 @@ zcu_result zcu_fail(const LaunchArgs& a, zcu_result r, const char* fmt, ...) {
         va_end(ap);
     }
     return r;
+}
+
+zcu_result parse_peer(const LaunchArgs& a, PeerUse& u, const void* out_lo, const void* out_hi) {
+    memset(&u, 0, sizeof(u));
+    u.wait_slot = u.push_slot = PEER_NONE;
+    if (a.params_bytes < sizeof(PPeer)) return ZCU_OK;
+    PPeer pp;
+    memcpy(&pp, static_cast<const char*>(a.params) + a.params_bytes - sizeof(PPeer), sizeof(pp));
+    if (pp.magic != PEER_MAGIC) return ZCU_OK;
+    ZCU_NEED(a, a.peers != nullptr, "this dispatch takes part in a peer exchange, but zcu_peer_config was not called");
+    u.t = *a.peers;
+    ZCU_NEED(a, (pp.wait_slot == PEER_NONE || pp.wait_slot < u.t.slots) && (pp.push_slot == PEER_NONE || pp.push_slot < u.t.slots),
+             "peer exchange: slot out of range (%u, %u of %u)", pp.wait_slot, pp.push_slot, u.t.slots);
+    u.wait_slot = pp.wait_slot;
+    u.push_slot = pp.push_slot;
+    if (u.push_slot != PEER_NONE) {
+        const uint64_t lo = reinterpret_cast<uint64_t>(out_lo), hi = reinterpret_cast<uint64_t>(out_hi), base = u.t.base[u.t.rank];
+        ZCU_NEED(a, lo >= base && hi <= base + u.t.flags_off && lo <= hi, "peer exchange: the output is not inside the local arena");
+    }
+    return ZCU_OK;
 }
 
 // ------------------------------------------------------------------ exports
@@ -723,6 +748,8 @@ ZCU_EXPORT zcu_result zcu_destroy(zcu_context* c, uint32_t timeout_ms) {
         zcu_result r = wait_stream(c, timeout_ms);
         if (r == ZCU_E_TIMEOUT) return r;  // the handle stays valid for a retry
     }
+    for (void* m : c->ipc_open) cudaIpcCloseMemHandle(m);
+    if (c->peers.counts) cudaFree(c->peers.counts);
     for (zcu_program* pr : c->programs) program_free(pr);
     program_free(c->recording);
     for (cudaGraphExec_t g : c->graphs)
@@ -961,6 +988,7 @@ ZCU_EXPORT zcu_result zcu_attention_decode_static(zcu_context* c, const void* pa
     a.variant = 0;
     a.sm_count = c->prop.multiProcessorCount;
     a.status = c->status;
+    a.peers = nullptr;
     a.err = c->err;
     a.err_cap = sizeof(c->err);
     c->launches += 2;
@@ -1006,8 +1034,52 @@ static void fill_args(zcu_context* c, LaunchArgs& a) {
     a.stream = c->stream;
     a.sm_count = c->dry ? 148 : c->prop.multiProcessorCount;
     a.status = c->status;
+    a.peers = c->peers.world > 0 ? &c->peers : nullptr;
     a.err = c->err;
     a.err_cap = sizeof(c->err);
+}
+
+// ---- tensor-parallel exchange over peer memory (peer.cuh)
+ZCU_EXPORT zcu_result zcu_ipc_export(zcu_context* c, void* ptr, void* out_handle64) {
+    LIVE(c);
+    if (c->dry || !ptr || !out_handle64) return fail(c, ZCU_E_INVALID, "ipc_export: needs a device allocation");
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+    CU(c, cudaIpcGetMemHandle(static_cast<cudaIpcMemHandle_t*>(out_handle64), ptr));
+    return ZCU_OK;
+}
+ZCU_EXPORT zcu_result zcu_ipc_open(zcu_context* c, const void* handle64, void** out_ptr) {
+    LIVE(c);
+    if (c->dry || !handle64 || !out_ptr) return fail(c, ZCU_E_INVALID, "ipc_open: needs a device and a handle");
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle64, sizeof(h));
+    CU(c, cudaIpcOpenMemHandle(out_ptr, h, cudaIpcMemLazyEnablePeerAccess));
+    c->ipc_open.push_back(*out_ptr);
+    return ZCU_OK;
+}
+ZCU_EXPORT zcu_result zcu_peer_config(zcu_context* c, uint32_t rank, uint32_t world, const uint64_t* bases, uint64_t arena_bytes,
+                                      uint64_t flags_offset, uint32_t slots) {
+    LIVE(c);
+    if (c->dry) return fail(c, ZCU_E_INVALID, "peer_config: needs a device");
+    if (!bases || world == 0 || world > PEER_MAX || rank >= world || slots == 0)
+        return fail(c, ZCU_E_INVALID, "peer_config: rank %u of %u, %u slots", rank, world, slots);
+    if (flags_offset % 4 != 0 || flags_offset + (uint64_t)slots * PEER_MAX * 4 > arena_bytes)
+        return fail(c, ZCU_E_INVALID, "peer_config: the flags do not fit the arena");
+    PeerTable t = {};
+    t.rank = (int32_t)rank;
+    t.world = (int32_t)world;
+    t.slots = slots;
+    for (uint32_t r = 0; r < world; r++) t.base[r] = bases[r];
+    t.arena_bytes = arena_bytes;
+    t.flags_off = flags_offset;
+    uint32_t* words = nullptr;
+    CU(c, cudaMalloc((void**)&words, (size_t)slots * 2 * sizeof(uint32_t)));
+    CU(c, cudaMemset(words, 0, (size_t)slots * 2 * sizeof(uint32_t)));
+    CU(c, cudaMemset(reinterpret_cast<void*>(t.base[rank] + flags_offset), 0, (size_t)slots * PEER_MAX * 4));
+    t.counts = words;
+    t.tickets = words + slots;
+    if (c->peers.counts) cudaFree(c->peers.counts);
+    c->peers = t;
+    return ZCU_OK;
 }
 
 ZCU_EXPORT zcu_result zcu_program_begin(zcu_context* c) {

@@ -1,6 +1,7 @@
 // Shared between the host (zcu_host.cu) and the kernel translation units.
 #pragma once
 
+#include "peer.cuh"
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -108,6 +109,7 @@ struct LaunchArgs {
     uint32_t variant;
     int sm_count;
     int* status;                   // device-visible word a kernel sets when a bounded wait gives up
+    const PeerTable* peers;        // the context's tensor-parallel exchange table (null: none configured)
     char* err;                     // message buffer on failure
     size_t err_cap;
 };
@@ -133,6 +135,11 @@ zcu_result launch_delta_recurrent(const LaunchArgs& a, uint32_t t_first, uint32_
 zcu_result launch_delta_chunked(const LaunchArgs& a);          // 64-token chunks, then the recurrent tail
 zcu_result launch_gated_norm(const LaunchArgs& a);
 zcu_result launch_attn_static(const LaunchArgs& a, uint32_t max_keys, uint32_t rows);
+zcu_result launch_peer_wait(const LaunchArgs& a);
+
+// The exchange a dispatch takes part in: a PPeer block trailing its parameter block (see peer.cuh). `outs`: the
+// ranges it stores to, which must lie in the local arena when it pushes. Fills `u` (both slots PEER_NONE without one).
+zcu_result parse_peer(const LaunchArgs& a, PeerUse& u, const void* out_lo, const void* out_hi);
 
 // The step program (k_program.cu): a recorded list of dispatches run by one persistent kernel.
 struct zcu_program;

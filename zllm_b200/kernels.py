@@ -113,6 +113,20 @@ X_HALF, OUT_HALF = 1, 2
 VARIANT_DELTA_CHUNK64 = 0xFFFD0000
 
 
+# The tensor-parallel exchange a dispatch takes part in (zcu_peer_ext): appended to its parameter block.
+PEER_MAGIC, PEER_NONE, EXT_PEER_WAIT = 0x52454550, 0xFFFFFFFF, 64
+PeerExt = _struct("PeerExt", [("magic", u32), ("wait_slot", u32), ("push_slot", u32), ("reserved", u32)])
+
+
+def with_peer(params, wait=None, push=None):
+    """`params` followed by a PeerExt (or `params` itself when the dispatch takes no part in an exchange)."""
+    if wait is None and push is None:
+        return params
+    ext = PeerExt(PEER_MAGIC, PEER_NONE if wait is None else wait, PEER_NONE if push is None else push, 0)
+    raw = bytes(params) + bytes(ext)
+    return (C.c_uint8 * len(raw)).from_buffer_copy(raw)
+
+
 class Launcher:
     """Immediate launches on a context (kernels.Launcher, kernels.zig:925-960)."""
 
@@ -124,7 +138,7 @@ class Launcher:
 
     # -- the decode multiply: grid (ceil(n / groupRows), m, 1) in the reference; only m matters here
     def matvec(self, ttype, x, w, out, n, k, m=1, col0=0, out_stride=None, flags=0, eps=0.0, half=0, x_stride=0,
-               norm_w=None, variant=0, rope=None):
+               norm_w=None, variant=0, rope=None, wait=None, push=None):
         """`rope` = (RopeAppend, [table, kc, vc, step(, positions)]) fuses rope_append into the multiply that
         produces the Q|K|V row (ROPE_APPEND_FUSED; needs norm_w as binding 3)."""
         p = Matvec(n, k, col0, out_stride if out_stride is not None else n, eps, flags, half, x_stride)
@@ -134,7 +148,11 @@ class Launcher:
             p.flags |= ROPE_APPEND_FUSED
             p = MatvecRope(p, rope[0])
             args += list(rope[1])
-        self.launch(MATVEC_KERNEL[ttype], p, args, (-(-n // 8), m, 1), variant)
+        self.launch(MATVEC_KERNEL[ttype], with_peer(p, wait, push), args, (-(-n // 8), m, 1), variant)
+
+    def peer_wait(self, slot: int):
+        """Waits (on the device, in stream order) until every rank has published exchange `slot`."""
+        self.launch(EXT_PEER_WAIT, PeerExt(PEER_MAGIC, slot, PEER_NONE, 0), [], (1, 1, 1))
 
     def matmul(self, ttype, x, w, out, rows, n, k, col0=0, out_stride=None, accumulate=False, variant=0, layout=0):
         """The prefill multiply on half-precision weights. `variant` 0 is the exact f32 identity;

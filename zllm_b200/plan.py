@@ -123,10 +123,15 @@ class DenseProgram:
     """
 
     def __init__(self, ctx, cfg: DenseConfig, weights, batch: int, alloc, shard: Shard | None = None, gather=None,
-                 variants: dict | None = None, fuse_rope: bool | None = None):
+                 variants: dict | None = None, fuse_rope: bool | None = None, arena=None):
         self.ctx, self.cfg, self.w, self.B = ctx, cfg, weights, batch
         self.sh = shard or Shard()
         self.gather = gather
+        # Tensor parallelism without a collective library: `arena` (abi.PeerArena) holds the vectors every rank
+        # reads whole; their producers store into every rank's arena and publish an exchange slot, their
+        # consumers wait for it. Slots: 4 per layer (att, x after wo, act, x after down), then the logits.
+        self.arena = arena
+        assert arena is None or gather is None
         self.L = K.Launcher(ctx)
         self.variants = variants or {}
         # rope_append inside the Q|K|V multiply's epilogue (one launch fewer per layer) where that is built:
@@ -147,11 +152,12 @@ class DenseProgram:
         self.tokens = alloc(B * 4)
         self.positions = alloc(B * 4)
         self.step = alloc(16)
-        self.x = alloc(B * e * f4)
+        shared = arena.alloc if arena is not None else alloc
+        self.x = shared(B * e * f4)
         self.qkv = alloc(B * self.qkv_row * f4)
-        self.att = alloc(B * cfg.q_dim * f4)          # full width: column slices are gathered
-        self.act = alloc(B * cfg.ff * f4)
-        self.logits = alloc(B * cfg.vocab * f4)
+        self.att = shared(B * cfg.q_dim * f4)         # full width: column slices are gathered
+        self.act = shared(B * cfg.ff * f4)
+        self.logits = shared(B * cfg.vocab * f4)
         self.max_blocks = -(-cfg.max_ctx // K.ATTN_BLOCK)
         self.part = alloc(B * self.lh * self.max_blocks * (hd + 2) * f4)
         self.seq_stride = cfg.max_ctx * self.lg * hd          # cache elements per sequence
@@ -188,6 +194,15 @@ class DenseProgram:
         if self.gather is not None:
             self.gather(buf, self.B, width)
 
+    @staticmethod
+    def arena_bytes(cfg: DenseConfig, batch: int) -> int:
+        """Bytes of the vectors a peer arena must hold for `batch` sequences (each rounded up to 256)."""
+        return sum(((batch * w * 4 + 255) & ~255) for w in (cfg.hidden, cfg.q_dim, cfg.ff, cfg.vocab))
+
+    @staticmethod
+    def arena_slots(cfg: DenseConfig) -> int:
+        return 4 * cfg.layers + 1
+
     def record_step(self, max_keys: int):
         """Issues the step's launches on the context's stream (inside a graph capture they are captured).
         `max_keys`: the largest position + 1 of the batch (sizes the attention grid)."""
@@ -205,42 +220,52 @@ class DenseProgram:
         ap._pad[1] = cfg.q_dim                                  # att rows are full width on every rank
         blocks = -(-max_keys // K.ATTN_BLOCK)
         att_cols = self.att.at(self.h0 * hd * 4)                # this rank's head columns of att
+        peer = self.arena is not None
         for il in range(cfg.layers):
             lw = self.w["layers"][il]
+            s_att, s_xwo, s_act, s_xdown = (4 * il, 4 * il + 1, 4 * il + 2, 4 * il + 3) if peer else (None,) * 4
+            s_prev = (4 * il - 1) if (peer and il > 0) else None  # the x this layer starts from
             # 1. fused attn_norm + Q|K|V projection (local heads); 2. RoPE (normal pairs) and the cache append at
             #    each sequence's position, in the multiply's epilogue or as rope_append's own launch
             if self.fuse_rope:
                 self._matvec(cfg.body_type, self.x, lw["wqkv"], self.qkv, self.qkv_row, e, flags=K.NORM, eps=cfg.eps,
-                             norm_w=lw["attn_norm"], rope=(rp, [self.rope, self.kc[il], self.vc[il], self.step, self.positions]))
+                             norm_w=lw["attn_norm"], rope=(rp, [self.rope, self.kc[il], self.vc[il], self.step, self.positions]),
+                             wait=s_prev)
                 self.launches_per_step -= 1
             else:
                 self._matvec(cfg.body_type, self.x, lw["wqkv"], self.qkv, self.qkv_row, e, flags=K.NORM, eps=cfg.eps,
-                             norm_w=lw["attn_norm"])
+                             norm_w=lw["attn_norm"], wait=s_prev)
                 self.L.launch(K.ROPE_APPEND, rp, [self.qkv, self.dummy, self.dummy, self.rope, self.kc[il], self.vc[il],
                                                   self.step, self.positions], (self.lh + self.lg, B, 1))
             # 3-4. split attention over each sequence's cache, merged into this rank's head columns of att
             self.L.launch(K.ATTN_SPLIT, ap, [self.qkv, self.kc[il], self.vc[il], self.part, self.step, self.positions],
                           (self.lg, blocks, B))
-            self.L.launch(K.ATTN_COMBINE, ap, [self.qkv, self.part, att_cols, self.step, self.positions], (self.lh, B, 1))
+            self.L.launch(K.ATTN_COMBINE, K.with_peer(ap, push=s_att), [self.qkv, self.part, att_cols, self.step, self.positions],
+                          (self.lh, B, 1))
             self.launches_per_step += 3
             self._gather(self.att, cfg.q_dim)
             # 5. Wo rows of this rank, accumulated into the residual stream's slice
             self._matvec(cfg.body_type, self.att, lw["wo"], self.x, self.le, cfg.q_dim, col0=sh.rank * self.le,
-                         out_stride=e, flags=K.ACCUMULATE)
+                         out_stride=e, flags=K.ACCUMULATE, wait=s_att, push=s_xwo)
             self._gather(self.x, e)
             # 6. fused ffn_norm + gate|up + SwiGLU (local ff rows)
             self._matvec(cfg.body_type, self.x, lw["wgu"], self.act, self.lff, e, col0=sh.rank * self.lff,
                          out_stride=cfg.ff, flags=K.NORM | K.SILU_PAIR, eps=cfg.eps, half=self.lff,
-                         norm_w=lw["ffn_norm"])
+                         norm_w=lw["ffn_norm"], wait=s_xwo, push=s_act)
             self._gather(self.act, cfg.ff)
             # 7. Wdown rows of this rank, accumulated
             self._matvec(cfg.body_type, self.act, lw["wdown"], self.x, self.le, cfg.ff, col0=sh.rank * self.le,
-                         out_stride=e, flags=K.ACCUMULATE)
+                         out_stride=e, flags=K.ACCUMULATE, wait=s_act, push=s_xdown)
             self._gather(self.x, e)
         # output norm fused into the LM head
+        s_logits = 4 * cfg.layers if peer else None
         self._matvec(cfg.head_type, self.x, self.w["head"], self.logits, self.lv, e, col0=sh.rank * self.lv,
-                     out_stride=cfg.vocab, flags=K.NORM, eps=cfg.eps, norm_w=self.w["out_norm"])
+                     out_stride=cfg.vocab, flags=K.NORM, eps=cfg.eps, norm_w=self.w["out_norm"],
+                     wait=(4 * cfg.layers - 1) if peer else None, push=s_logits)
         self._gather(self.logits, cfg.vocab)
+        if peer:
+            self.L.peer_wait(s_logits)  # the host may read the logits once this has run
+            self.launches_per_step += 1
 
     def algorithmic_bytes(self, positions: np.ndarray) -> dict:
         """Bytes one step must move on this rank: every weight once, K and V of every cached position."""
