@@ -294,7 +294,8 @@ class DecodeStep:
     name = "decode"
     context = 8192
 
-    def __init__(self, dist: Dist, batch: int = 1, variant: int = 0, layers: int = 32, replay: str = "auto"):
+    def __init__(self, dist: Dist, batch: int = 1, variant: int = 0, layers: int = 32, replay: str = "auto",
+                 exchange: str = "peer"):
         import torch
 
         from zllm_b200 import abi
@@ -318,8 +319,28 @@ class DecodeStep:
             self.bufs.append(b)
             return b
 
-        self.prog = DenseProgram(self.ctx, self.cfg, self.weights, batch, alloc, self.shard,
-                                 gather=nccl_gather(dist.dist, dist.rank, dist.world) if dist.on else None)
+        # N ranks exchange output slices either by the kernels themselves (stores into every rank's arena over
+        # NVLink, counters instead of collectives) or by NCCL all-gathers between the kernels
+        self.exchange = exchange if dist.on else "none"
+        arena = None
+        if self.exchange == "peer":
+            def handles(h: bytes):
+                got = [None] * dist.world
+                dist.dist.all_gather_object(got, h)
+                return got
+
+            arena = abi.PeerArena(self.ctx, dist.rank, dist.world, DenseProgram.arena_bytes(self.cfg, batch),
+                                  DenseProgram.arena_slots(self.cfg), handles)
+        self.prog = DenseProgram(self.ctx, self.cfg, self.weights, batch, alloc, self.shard, arena=arena,
+                                 gather=nccl_gather(dist.dist, dist.rank, dist.world) if self.exchange == "nccl" else None)
+        if arena is not None:
+            class _View:  # the arena's logits as a torch tensor (zero copy), for the read-back of the e2e leg
+                __cuda_array_interface__ = {"shape": (batch * self.cfg.vocab,), "typestr": "<f4",
+                                            "data": (self.prog.logits.ptr, False), "version": 2}
+
+            self.logits_view = torch.as_tensor(_View(), device=self.dev)
+        else:
+            self.logits_view = self.prog.logits.f32()
         table = alloc(self.cfg.max_ctx * self.cfg.head_dim * 4)
         table.upload(DenseProgram.rope_table(self.cfg))
         self.prog.set_rope_table(table)
@@ -357,7 +378,7 @@ class DecodeStep:
                 self.program = self.ctx.program_end()
             self.ctx.program_launch(self.program)
             return
-        if not self.dist.on:
+        if self.exchange != "nccl":
             if self.graph is None:
                 self.ctx.capture_begin()
                 self._record()
@@ -380,7 +401,7 @@ class DecodeStep:
             self.prog.tokens.t[: 4 * self.batch].view(torch.int32).copy_(self.pinned_tokens, non_blocking=True)
         self.step()
         with torch.cuda.stream(self.stream):
-            self.pinned_logits.copy_(self.prog.logits.f32().view(self.batch, self.cfg.vocab), non_blocking=True)
+            self.pinned_logits.copy_(self.logits_view.view(self.batch, self.cfg.vocab), non_blocking=True)
         self.stream.synchronize()
 
     def e2e_bytes(self):
@@ -407,8 +428,10 @@ class DecodeStep:
                            else "CUDA graph of the step's launches"),
                 "l2": f"inputs larger than L2: a step reads {self.bytes['total'] / 1e9:.2f} GB per rank "
                       f"({self.bytes['weights'] / 1e9:.2f} GB weights + {self.bytes['kv'] / 1e9:.2f} GB KV)",
-                "parallelism": (f"tp{self.dist.world} (rows and KV heads sharded, NCCL all-gather of output slices)"
-                                if self.dist.on else "1 GPU"),
+                "parallelism": ("1 GPU" if not self.dist.on else
+                                f"tp{self.dist.world} (rows and KV heads sharded; output slices " +
+                                ("pushed into every rank's arena by the kernels' epilogues over NVLink, counters for collectives)"
+                                 if self.exchange == "peer" else "all-gathered by NCCL)")),
                 "step_bytes": self.bytes["total"]}
 
     def roofline(self, ms_per_step: float):
@@ -744,6 +767,7 @@ def run_cuda(args):
     kw = {"batch": args.batch, "variant": int(args.variant, 0)}
     if args.workload == "decode":
         kw["replay"] = args.replay
+        kw["exchange"] = args.exchange
         if args.layers:
             kw["layers"] = args.layers
     wl = WORKLOADS[args.workload](dist, **kw)
@@ -896,6 +920,8 @@ def main():
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--variant", default="0", help="matvec variant word (see include/zllm_cuda.h)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
+    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
+                    help="decode on N > 1 GPUs: slices pushed by the kernels over peer memory, or NCCL all-gathers")
     ap.add_argument("--replay", default="auto", choices=["auto", "program", "graph"],
                     help="decode: replay a step as one persistent kernel or as a CUDA graph of its launches")
     args = ap.parse_args()

@@ -30,7 +30,8 @@ struct PeerTable {
     uint64_t arena_bytes;
     uint64_t flags_off;        // arena offset of flags[slots][PEER_MAX] (u32): flags[s][r] = rank r's count
     uint32_t* counts;          // local: this rank's count per slot
-    uint32_t* tickets;         // local: CTAs of the producing kernel that have finished, per slot
+    uint32_t* tickets;         // local: CTAs of the producing kernel that have finished, per slot; tickets[slots] is
+                               // the abort word: set by the first wait that gives up, it ends every later wait at once
 };
 
 struct PeerUse {  // what one launch does with the table
@@ -56,6 +57,7 @@ __device__ __forceinline__ bool wait_slot(const PeerUse& u, int* status) {
         const uint32_t want = __ldcg(u.t.counts + u.wait_slot);  // this rank's own count: its producer ran before us
         const uint32_t* flags = reinterpret_cast<const uint32_t*>(u.t.base[u.t.rank] + u.t.flags_off) + (size_t)u.wait_slot * PEER_MAX;
         const unsigned long long t0 = now_ns();
+        if (__ldcg(u.t.tickets + u.t.slots) != 0) ok = 0;  // an earlier wait of this context gave up
         for (int r = 0; r < u.t.world && ok; r++) {
             for (unsigned spins = 0;; spins++) {
                 uint32_t seen;
@@ -63,6 +65,7 @@ __device__ __forceinline__ bool wait_slot(const PeerUse& u, int* status) {
                 if ((int32_t)(seen - want) >= 0) break;
                 if ((spins & 1023u) == 1023u && now_ns() - t0 > 2000000000ull) {
                     if (status) atomicExch(status, 5);
+                    atomicExch(u.t.tickets + u.t.slots, 1u);
                     ok = 0;
                     break;
                 }
@@ -82,9 +85,9 @@ __device__ __forceinline__ float* remote(const PeerUse& u, const float* local, i
 // Every thread of the CTA calls it after its last store of the exchange. The last CTA of the grid publishes.
 __device__ __forceinline__ void publish(const PeerUse& u, unsigned ncta) {
     if (u.push_slot == PEER_NONE) return;
-    __threadfence_system();  // this thread's peer stores are ordered before the ticket
-    __syncthreads();
+    __syncthreads();  // the CTA's peer stores happen before thread 0's fence (cumulative), which precedes the ticket
     if (threadIdx.x == 0) {
+        __threadfence_system();
         const unsigned t = atomicAdd(u.t.tickets + u.push_slot, 1u);
         if (t == ncta - 1) {
             u.t.tickets[u.push_slot] = 0;

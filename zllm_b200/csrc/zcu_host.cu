@@ -185,6 +185,9 @@ zcu_result wait_stream(zcu_context* c, uint32_t timeout_ms) {
         if (what == 3)
             return fail(c, ZCU_E_GPU, "delta_rule (chunked): the token count in the parameter block is not the step's, or a kept row "
                                       "lies inside the chunked part; the step was not applied past its whole chunks");
+        if (what == 5)
+            return fail(c, ZCU_E_GPU, "a rank did not publish a tensor-parallel exchange within 2 s; every later wait of this context "
+                                      "gives up at once (configure the peers again to clear it)");
         return fail(c, ZCU_E_GPU, "a kernel gave up a bounded wait (a copy or a peer never arrived); its results are invalid");
     }
     return ZCU_OK;
@@ -1072,8 +1075,8 @@ ZCU_EXPORT zcu_result zcu_peer_config(zcu_context* c, uint32_t rank, uint32_t wo
     t.arena_bytes = arena_bytes;
     t.flags_off = flags_offset;
     uint32_t* words = nullptr;
-    CU(c, cudaMalloc((void**)&words, (size_t)slots * 2 * sizeof(uint32_t)));
-    CU(c, cudaMemset(words, 0, (size_t)slots * 2 * sizeof(uint32_t)));
+    CU(c, cudaMalloc((void**)&words, ((size_t)slots * 2 + 1) * sizeof(uint32_t)));
+    CU(c, cudaMemset(words, 0, ((size_t)slots * 2 + 1) * sizeof(uint32_t)));
     CU(c, cudaMemset(reinterpret_cast<void*>(t.base[rank] + flags_offset), 0, (size_t)slots * PEER_MAX * 4));
     t.counts = words;
     t.tickets = words + slots;
