@@ -136,3 +136,36 @@ def test_rope_append_writes_rounded_cache(ref, gpu, launcher, normal, qk_norm, g
                     assert rel_err(kcache[pos, g_], wk) < 1e-6
         # positions outside the step stay zero
         assert not kcache[:pos0].any() and not kcache[pos0 + m:].any()
+
+
+def test_both_forms_of_the_split_give_the_same_partials(gpu, launcher):
+    # One CTA per key block (variant 1) and the persistent walk with pipelined tiles (variant 2) keep the same
+    # order in every sum: identical partials and outputs, for rows with different key counts (batched
+    # sequences: 700, 1 and 333 keys; blocks past a row's keys are skipped by both).
+    rng = np.random.default_rng(91)
+    heads, kv_heads, hd, rows, ctx = 8, 2, 128, 3, 768
+    positions = np.array([699, 0, 332], dtype=np.uint32)
+    kc = rng.normal(size=(rows, ctx, kv_heads, hd)).astype(np.float16)
+    vc = rng.normal(size=(rows, ctx, kv_heads, hd)).astype(np.float16)
+    q = uniform(rng, (rows, heads * hd), 1.0)
+    max_blocks = -(-ctx // K.ATTN_BLOCK)
+    p = K.Attention(heads, kv_heads, hd, K.KV_F16, K.attention_scale(hd), max_blocks, heads * hd, 0, 0, 0)
+    p._pad[0] = ctx * kv_heads * hd
+    dq, dk, dv = gpu.put(q), gpu.put(kc.view(np.uint16)), gpu.put(vc.view(np.uint16))
+    step, dpos = gpu.put(np.array([rows, 0, 0, 0], dtype=np.uint32)), gpu.put(positions)
+    got = []
+    for variant in (1, 2):
+        part = gpu.zeros(rows * heads * max_blocks * (hd + 2) * 4)
+        out = gpu.zeros(rows * heads * hd * 4)
+        launcher.launch(K.ATTN_SPLIT, p, [dq, dk, dv, part, step, dpos], (kv_heads, max_blocks, rows), variant)
+        launcher.launch(K.ATTN_COMBINE, p, [dq, part, out, step, dpos], (heads, rows, 1))
+        gpu.sync()
+        got.append((part.download(np.uint32), out.download(np.uint32)))
+    assert np.array_equal(got[0][1], got[1][1])
+    assert np.abs(got[0][1].view(np.float32)).max() > 0
+    # the partials of every block that holds keys (128 per block on this path); the one-CTA-per-block form also
+    # writes the unused slots past a row's keys, the walk skips them
+    pa, pb = (g[0].reshape(rows, heads, max_blocks, hd + 2) for g in got)
+    for t in range(rows):
+        used = -(-(int(positions[t]) + 1) // 128)
+        assert np.array_equal(pa[t, :, :used], pb[t, :, :used]), t

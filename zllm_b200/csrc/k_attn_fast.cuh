@@ -209,6 +209,216 @@ __device__ __forceinline__ void attn_split_fast_body(const VBlock& vb, const PAt
     }
 }
 
+// ---- the same block arithmetic as a persistent kernel: one CTA per SM walks a contiguous range of the
+// (row, KV head, key block) space with its K and V tiles (128 keys x head_dim halves each) arriving through a
+// 3-stage cp.async pipeline, so the loads of the next two blocks are in flight while a block is computed. With
+// one block per CTA (the kernel above) each CTA pays an HBM round trip before its first multiply and a wave and a
+// bit of CTAs pay it twice; here it is paid once per CTA. Every sum keeps the order of attn_split_fast_body, so
+// the partials are the same bits.
+constexpr int AP_STAGES = 3;
+__host__ __device__ constexpr size_t attn_persist_smem(int group_cap, int group, int hd) {
+    return (size_t)AP_STAGES * 2 * AF_KEYS * hd * 2 + ((size_t)group_cap * AF_KEYS + 2 * group_cap + 8) * sizeof(float) +
+           (size_t)(AF_THREADS / 32) * group * hd * sizeof(float);
+}
+
+template <int HD, int GROUP_CAP>
+__device__ __forceinline__ void attn_split_persistent_body(unsigned char* smem, const PAttention& p, const float* __restrict__ qg,
+                                                           const __half* __restrict__ kc, const __half* __restrict__ vc,
+                                                           float* __restrict__ part, const PStep* __restrict__ step,
+                                                           const uint32_t* __restrict__ seq_pos, int by, int rows) {
+    constexpr int DPT = HD / 8, KPP = AF_THREADS / 8, PASSES = AF_KEYS / KPP;
+    constexpr int TPK = HD / 8, KG = AF_THREADS / TPK, KPT = AF_KEYS / KG;
+    constexpr int TILE = AF_KEYS * HD * 2;        // bytes of one K (or V) tile
+    constexpr int PIECES = TILE / 16 / AF_THREADS; // 16-byte pieces of a tile per thread
+    float (*sc)[AF_KEYS] = reinterpret_cast<float (*)[AF_KEYS]>(smem + (size_t)AP_STAGES * 2 * TILE);
+    float* stat = reinterpret_cast<float*>(sc) + GROUP_CAP * AF_KEYS;
+    float* pv = stat + 2 * GROUP_CAP + 8;
+    const uint32_t stage0 = (uint32_t)__cvta_generic_to_shared(smem);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int kvh = (int)p.kv_heads, group = (int)(p.heads / p.kv_heads);
+    const size_t kv_stride = (size_t)kvh * HD;
+    const int q_head = p.gated ? 2 * HD : HD;
+    const int total = kvh * by * rows;
+    const int lo = (int)((long long)blockIdx.x * total / gridDim.x), hi = (int)((long long)(blockIdx.x + 1) * total / gridDim.x);
+    const int kl = tid >> 3, sl = tid & 7, kg = tid / TPK, dl = tid % TPK;
+
+    auto keys_of = [&](int t) {
+        const int row = (int)p.row0 + t;
+        return (seq_pos ? (int)seq_pos[row] : (int)step->pos0 + row) + 1;
+    };
+    // asks for block idx's tiles into `stage` (nothing for a block past its row's keys or past this CTA's range)
+    auto issue = [&](int idx, int stage) {
+        if (idx < hi) {
+            const int b = idx % by, g = (idx / by) % kvh, t = idx / (by * kvh);
+            const int keys = keys_of(t), k0 = b * AF_KEYS;
+            if (k0 < keys) {
+                const size_t seq_off = (size_t)((int)p.row0 + t) * p._pad[0];
+#pragma unroll
+                for (int i = 0; i < PIECES; i++) {
+                    const int j = tid + AF_THREADS * i, key = j / (HD / 8), piece = j % (HD / 8);
+                    const size_t src = seq_off + (size_t)min(k0 + key, keys - 1) * kv_stride + (size_t)g * HD + 8 * piece;
+                    const uint32_t dst = stage0 + (uint32_t)stage * 2 * TILE + (uint32_t)j * 16u;
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(kc + src) : "memory");
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst + TILE), "l"(vc + src) : "memory");
+                }
+            }
+        }
+        asm volatile("cp.async.commit_group;\n" ::: "memory");  // one group per call, empty or not
+    };
+#pragma unroll
+    for (int s = 0; s < AP_STAGES - 1; s++) issue(lo + s, s);
+
+    float q[GROUP_CAP][DPT];
+    int q_g = -1, q_t = -1;
+    int stage = 0;
+    for (int idx = lo; idx < hi; idx++) {
+        issue(idx + AP_STAGES - 1, stage == 0 ? AP_STAGES - 1 : stage - 1);
+        asm volatile("cp.async.wait_group %0;\n" ::"n"(AP_STAGES - 1) : "memory");
+        __syncthreads();  // every thread's pieces of this block have landed; the last block's scratch is free
+        const int b = idx % by, g = (idx / by) % kvh, t = idx / (by * kvh);
+        const int keys = keys_of(t), k0 = b * AF_KEYS;
+        const uint32_t ktile = stage0 + (uint32_t)stage * 2 * TILE, vtile = ktile + TILE;
+        stage = stage + 1 == AP_STAGES ? 0 : stage + 1;
+        if (k0 >= keys) continue;
+        const int n = min(AF_KEYS, keys - k0);
+        const int row = (int)p.row0 + t;
+        if (g != q_g || t != q_t) {  // consecutive blocks of a CTA mostly share their queries
+            q_g = g, q_t = t;
+#pragma unroll
+            for (int h = 0; h < GROUP_CAP; h++) {
+                const float* qp = qg + (size_t)row * p.q_row + (size_t)(g * group + min(h, group - 1)) * q_head + sl * DPT;
+#pragma unroll
+                for (int d = 0; d < DPT; d += 4) {
+                    const float4 v = __ldcg(reinterpret_cast<const float4*>(qp + d));
+                    q[h][d] = v.x; q[h][d + 1] = v.y; q[h][d + 2] = v.z; q[h][d + 3] = v.w;
+                }
+            }
+        }
+        // ---- scores: 8 threads per key, K from the tile
+#pragma unroll
+        for (int ps = 0; ps < PASSES; ps++) {
+            const int key = k0 + ps * KPP + kl;
+            float dot[GROUP_CAP];
+#pragma unroll
+            for (int h = 0; h < GROUP_CAP; h++) dot[h] = 0.f;
+#pragma unroll
+            for (int c = 0; c < DPT / 8; c++) {
+                uint4 kraw;
+                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+                             : "=r"(kraw.x), "=r"(kraw.y), "=r"(kraw.z), "=r"(kraw.w)
+                             : "r"(ktile + (uint32_t)(ps * KPP + kl) * (HD * 2) + (uint32_t)sl * (DPT * 2) + 16u * c));
+                const __half2* hp = reinterpret_cast<const __half2*>(&kraw);
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const float2 kk = __half22float2(hp[e]);
+#pragma unroll
+                    for (int h = 0; h < GROUP_CAP; h++) {
+                        dot[h] = __fmaf_rn(q[h][8 * c + 2 * e], kk.x, dot[h]);
+                        dot[h] = __fmaf_rn(q[h][8 * c + 2 * e + 1], kk.y, dot[h]);
+                    }
+                }
+            }
+#pragma unroll
+            for (int h = 0; h < GROUP_CAP; h++) {
+                float v = dot[h];
+                v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 1));
+                v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 2));
+                v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 4));
+                if (sl == 0 && h < group) sc[h][ps * KPP + kl] = key < keys ? v * p.scale : -FLT_MAX;
+            }
+        }
+        __syncthreads();
+        // ---- block softmax: warp h takes head h, four keys per lane
+        if (warp < group) {
+            float s[4], mx = -FLT_MAX;
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                s[i] = lane + 32 * i < n ? sc[warp][lane + 32 * i] : -FLT_MAX;
+                mx = fmaxf(mx, s[i]);
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+            float sum = 0.f;
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const float e = (lane + 32 * i < n && s[i] != -FLT_MAX) ? expf(s[i] - mx) : 0.f;
+                sc[warp][lane + 32 * i] = e;
+                sum = __fadd_rn(sum, e);
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) sum = __fadd_rn(sum, __shfl_xor_sync(0xffffffffu, sum, o));
+            if (lane == 0) {
+                stat[2 * warp] = mx;
+                stat[2 * warp + 1] = sum;
+            }
+        }
+        __syncthreads();
+        // ---- sum exp * v: thread (key group kg, dims 8 dl .. 8 dl + 7), V from the tile
+        float acc[GROUP_CAP][8];
+#pragma unroll
+        for (int h = 0; h < GROUP_CAP; h++)
+#pragma unroll
+            for (int d = 0; d < 8; d++) acc[h][d] = 0.f;
+#pragma unroll
+        for (int i = 0; i < KPT; i++) {
+            const int ki = kg + KG * i;
+            if (ki < n) {
+                uint4 vpiece;
+                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+                             : "=r"(vpiece.x), "=r"(vpiece.y), "=r"(vpiece.z), "=r"(vpiece.w)
+                             : "r"(vtile + (uint32_t)ki * (HD * 2) + 16u * dl));
+                const __half2* hp = reinterpret_cast<const __half2*>(&vpiece);
+                float vv[8];
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const float2 f = __half22float2(hp[e]);
+                    vv[2 * e] = f.x;
+                    vv[2 * e + 1] = f.y;
+                }
+#pragma unroll
+                for (int h = 0; h < GROUP_CAP; h++) {
+                    const float w = sc[h < group ? h : 0][ki];
+#pragma unroll
+                    for (int d = 0; d < 8; d++) acc[h][d] = __fmaf_rn(w, vv[d], acc[h][d]);
+                }
+            }
+        }
+#pragma unroll
+        for (int h = 0; h < GROUP_CAP; h++)
+#pragma unroll
+            for (int d = 0; d < 8; d++) {
+                float v = acc[h][d];
+#pragma unroll
+                for (int o = TPK; o < 32; o <<= 1) v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, o));
+                acc[h][d] = v;
+            }
+        if (lane < TPK) {
+#pragma unroll
+            for (int h = 0; h < GROUP_CAP; h++)
+                if (h < group) {
+                    float* dst = pv + ((size_t)warp * group + h) * HD + 8 * lane;
+                    *reinterpret_cast<float4*>(dst) = make_float4(acc[h][0], acc[h][1], acc[h][2], acc[h][3]);
+                    *reinterpret_cast<float4*>(dst + 4) = make_float4(acc[h][4], acc[h][5], acc[h][6], acc[h][7]);
+                }
+        }
+        __syncthreads();
+        for (int i = tid; i < group * HD; i += AF_THREADS) {
+            const int h = i / HD, d = i % HD;
+            float o = 0.f;
+#pragma unroll
+            for (int wv = 0; wv < AF_THREADS / 32; wv++) o = __fadd_rn(o, pv[((size_t)wv * group + h) * HD + d]);
+            const int head = g * group + h;
+            const size_t base = (((size_t)t * p.heads + head) * p.max_blocks + b) * (HD + 2);
+            part[base + 2 + d] = o;
+            if (d == 0) {
+                part[base] = stat[2 * h];
+                part[base + 1] = stat[2 * h + 1];
+            }
+        }
+    }
+    asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+}
+
 // grid (heads, rows). Merges the blocks' partials (src/kernels/attn_combine.wgsl):
 //   M = max m_b,  L = sum l_b e^(m_b - M),  o = sum o_b e^(m_b - M) / L,  times sigmoid(gate) when gated.
 // Bindings: qg, part, out, step (+ per-row positions for batched sequences). `kb`: cache positions per block.
