@@ -239,16 +239,18 @@ zcu_result zcu_capture_end(zcu_context *context, uint32_t *out_graph);
 zcu_result zcu_graph_launch(zcu_context *context, uint32_t graph);
 zcu_result zcu_graph_destroy(zcu_context *context, uint32_t graph);
 
-/* Tensor-parallel exchange over peer memory, one process per GPU (no collective library, no multicast). Every rank
- * allocates one arena (zcu_alloc), exports it (zcu_ipc_export: a 64-byte handle for the other processes), opens
- * its peers' (zcu_ipc_open) and calls zcu_peer_config with all bases as mapped locally. The last
- * slots * 8 * 4 bytes region at flags_offset holds the exchange counters; vectors that every rank reads whole
- * live below it. A dispatch takes part by appending a zcu_peer_ext to its parameter block: matvec_q4_k/q8_0
- * (tensor-core family) and attn_combine store their output slice into every rank's arena and publish
- * `push_slot`; matvec_* wait for `wait_slot` before they read their activations; ZCU_K_EXT_PEER_WAIT only waits.
- * The reference has no multi-GPU path; this is the row/head sharding its kernels allow (every output row, head
- * and state column is computed by one rank with unchanged arithmetic, so results are bitwise those of one GPU).
- * Waits give up after 2 s with ZCU_E_GPU at the next sync. */
+/* Tensor-parallel exchange over peer memory, one process per GPU (no collective library, no multicast, no
+ * fences). Every rank allocates one arena (zcu_alloc), exports it (zcu_ipc_export: a 64-byte handle for the other
+ * processes), opens its peers' (zcu_ipc_open) and calls zcu_peer_config with all bases as mapped locally. The
+ * first `exchange_offset` bytes hold the vectors that every rank reads whole; the 2 * exchange_offset bytes after
+ * them are their exchange slots: 8 bytes {value, tag} per float. A dispatch takes part by appending a zcu_peer_ext
+ * to its parameter block: matvec_q4_k/q8_0 (tensor-core family) and attn_combine with `push_slot` also store each
+ * output, tagged, into the slot of every rank; matvec_* with `wait_slot` read their activations from the slots
+ * and wait, element by element, for the tag of the exchange; ZCU_K_EXT_PEER_WAIT (binding: the vector) waits the
+ * same way and fills in the plain floats, for a host about to read them. The reference has no multi-GPU path;
+ * this is the row/head sharding its kernels allow (every output row, head and state column is computed by one
+ * rank with unchanged arithmetic, so results are bitwise those of one GPU). A wait gives up after 2 s with
+ * ZCU_E_GPU at the next sync. */
 #define ZCU_PEER_MAGIC 0x52454550u
 #define ZCU_PEER_NONE 0xffffffffu
 typedef struct zcu_peer_ext {
@@ -260,7 +262,7 @@ typedef struct zcu_peer_ext {
 zcu_result zcu_ipc_export(zcu_context *context, void *ptr, void *out_handle64);
 zcu_result zcu_ipc_open(zcu_context *context, const void *handle64, void **out_ptr);
 zcu_result zcu_peer_config(zcu_context *context, uint32_t rank, uint32_t world, const uint64_t *bases, uint64_t arena_bytes,
-                           uint64_t flags_offset, uint32_t slots);
+                           uint64_t exchange_offset, uint32_t slots);
 
 /* A step program: the dispatches issued between begin and end are recorded (not run) and later replayed by ONE
  * persistent kernel, one CTA per SM, with grid-wide barriers where the reference has dispatch boundaries and

@@ -203,14 +203,14 @@ class SubBuf(DevBuf):
 
 class PeerArena:
     """One rank's arena for the tensor-parallel exchange over peer memory (include/zllm_cuda.h): the vectors
-    every rank reads whole, then the exchange counters. `exchange(handle_bytes) -> [handle_bytes per rank]` is the
+    every rank reads whole, then their tagged exchange slots. `exchange(handle_bytes) -> [handle_bytes per rank]` is the
     caller's all-gather of the 64-byte IPC handles (torch.distributed.all_gather_object, or anything else);
     with world == 1 nothing is exchanged."""
 
     def __init__(self, ctx: "Context", rank: int, world: int, data_bytes: int, slots: int, exchange=None):
         self.ctx, self.rank, self.world, self.slots = ctx, rank, world, slots
         self.data_bytes = (int(data_bytes) + 255) & ~255
-        self.nbytes = self.data_bytes + slots * 8 * 4
+        self.nbytes = 3 * self.data_bytes  # the vectors, then 8 bytes {value, tag} per float of them
         self.buf = ctx.alloc(self.nbytes).zero()
         ctx.sync()
         bases = [0] * world

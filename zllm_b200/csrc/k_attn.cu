@@ -219,13 +219,16 @@ __global__ void __launch_bounds__(256) attn_combine_kernel(PAttention p, const f
                                                           const __grid_constant__ PeerUse pu) {
     extern __shared__ __align__(16) unsigned char dyn_smem[];
     attn::attn_combine_body(vblock_of_cta(dyn_smem), p, qg, part, out, step, seq_pos, kb, &pu);
-    peer::publish(pu, gridDim.x * gridDim.y);
+    peer::finish(pu, gridDim.x * gridDim.y);
 }
 
-// Waits for one tensor-parallel exchange (ZCU_K_EXT_PEER_WAIT): what a host that is about to read a gathered
-// vector puts at the end of its step.
-__global__ void __launch_bounds__(32) peer_wait_kernel(const __grid_constant__ PeerUse pu, int* __restrict__ status) {
-    peer::wait_slot(pu, status);
+// Copies an exchanged vector out of its exchange slots into the plain floats beside them, waiting for every
+// slice (ZCU_K_EXT_PEER_WAIT): what a host that is about to read a gathered vector puts at the end of its step.
+__global__ void __launch_bounds__(256) peer_unpack_kernel(const __grid_constant__ PeerUse pu, float* __restrict__ v, uint32_t count,
+                                                          int* __restrict__ status) {
+    const uint32_t tag = peer::want_tag(pu);
+    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < count; i += gridDim.x * blockDim.x)
+        v[i] = peer::read1(pu, v + i, tag, status);
 }
 
 using attn::AF_KEYS;
@@ -407,12 +410,18 @@ zcu_result launch_attn_static(const LaunchArgs& a, uint32_t max_keys, uint32_t r
     return launch_attn_combine(c);
 }
 
+// Parameter block: a PPeer naming the slot to wait for. Binding: the vector (inside the local arena).
 zcu_result launch_peer_wait(const LaunchArgs& a) {
     PeerUse pu;
     zcu_result pr = parse_peer(a, pu, nullptr, nullptr);
     if (pr != ZCU_OK) return pr;
-    ZCU_NEED(a, pu.wait_slot != PEER_NONE && pu.push_slot == PEER_NONE, "peer_wait: the parameter block must name a slot to wait for, and only that");
-    peer_wait_kernel<<<1, 32, 0, a.stream>>>(pu, a.status);
+    ZCU_NEED(a, pu.wait_slot != PEER_NONE && pu.push_slot == PEER_NONE && a.nb >= 1, "peer_wait: needs a slot to wait for and the vector");
+    const uint64_t lo = reinterpret_cast<uint64_t>(a.b[0].ptr), base = pu.t.base[pu.t.rank];
+    ZCU_NEED(a, lo >= base && lo + a.b[0].size <= base + pu.t.ll_off && a.b[0].size % 4 == 0, "peer_wait: the vector is not inside the local arena");
+    const uint32_t count = (uint32_t)(a.b[0].size / 4);
+    if (count == 0) return ZCU_OK;
+    const int blocks = (int)((count + 255) / 256 < (uint32_t)(a.sm_count * 4) ? (count + 255) / 256 : (uint32_t)(a.sm_count * 4));
+    peer_unpack_kernel<<<blocks, 256, 0, a.stream>>>(pu, (float*)a.b[0].ptr, count, a.status);
     ZCU_CHECK_LAUNCH(a);
     return ZCU_OK;
 }

@@ -488,11 +488,8 @@ __device__ __forceinline__ void attn_combine_body(const VBlock& vb, const PAtten
         const float gate = __ldcg(qg + (size_t)row * p.q_row + (size_t)2 * h * hd + hd + tid_d);
         res = o / l / (1.0f + expf(-gate));
     }
-    if (pu != nullptr && pu->push_slot != PEER_NONE) {
-        for (int r = 0; r < pu->t.world; r++) *peer::remote(*pu, out + oi, r) = res;  // this rank's heads, to every rank
-    } else {
-        out[oi] = res;
-    }
+    out[oi] = res;
+    if (pu != nullptr && pu->push_slot != PEER_NONE) peer::push(*pu, out + oi, res, peer::push_tag(*pu));  // this rank's heads, to every rank
 }
 
 

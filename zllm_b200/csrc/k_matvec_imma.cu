@@ -27,11 +27,10 @@ __global__ void __launch_bounds__(IM_THREADS, 1) matvec_imma(PMatvec p, const fl
         (p.flags & MV_ROPE_APPEND) ? &rope : nullptr, &pu,
         [&] {
             // everything before touched only the weights, which no kernel writes; from here on the
-            // activations are read, so the kernels before this one must have finished - on this GPU, and,
-            // in a tensor-parallel exchange, the producers of the activations on every rank
+            // activations are read, so the kernels before this one must have finished on this GPU (in a
+            // tensor-parallel exchange the reads themselves wait for the other ranks' slices)
             asm volatile("griddepcontrol.wait;\n" ::: "memory");
             asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
-            peer::wait_slot(pu, status);
         },
         [] {});
 }

@@ -315,6 +315,12 @@ __device__ __forceinline__ void im_multiply(uint8_t* smem, ImRing& rg, ImIssue& 
         if (j0 < n) first_old = __ldcg(out + (size_t)(t0 + tid % mt) * p.out_stride + p.col0 + j0);
     }
 
+    // the activations: local memory, or the slots of a tensor-parallel exchange (each read waits for its tag)
+    const bool x_exchanged = pu != nullptr && pu->wait_slot != PEER_NONE;
+    const uint32_t x_tag = x_exchanged ? peer::want_tag(*pu) : 0u;
+    auto ldx = [&](const float* row, int i) {
+        return x_exchanged ? peer::read4(*pu, row + 4 * i, x_tag, status) : __ldcg(reinterpret_cast<const float4*>(row) + i);
+    };
     // ---- activations -> fixed point. Per token: sum of squares (RMSNorm) and largest magnitude over
     //      the CTA, a power-of-two scale s with |x * s| <= 2^25, then four balanced signed byte digits of
     //      X = rint(x * s):  X = D0 + 2^8 D1 + 2^16 D2 + 2^24 D3, each D in [-128, 127].
@@ -344,11 +350,11 @@ __device__ __forceinline__ void im_multiply(uint8_t* smem, ImRing& rg, ImIssue& 
                 const int i = tid + c * IM_THREADS;
                 keep[c] = make_float4(0.f, 0.f, 0.f, 0.f);
                 if (i < vecs) {
-                    keep[c] = __ldcg(reinterpret_cast<const float4*>(xt) + i);
+                    keep[c] = ldx(xt, i);
                     stat(keep[c], i);
                 }
             }
-            for (int i = tid + KEEP * IM_THREADS; i < vecs; i += IM_THREADS) stat(__ldcg(reinterpret_cast<const float4*>(xt) + i), i);
+            for (int i = tid + KEEP * IM_THREADS; i < vecs; i += IM_THREADS) stat(ldx(xt, i), i);
             if (norm) ss = warp_sum_d(ss);
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
@@ -427,7 +433,7 @@ __device__ __forceinline__ void im_multiply(uint8_t* smem, ImRing& rg, ImIssue& 
                 const int i = tid + c * IM_THREADS;
                 if (i < vecs) stage(keep[c], i);
             }
-            for (int i = tid + KEEP * IM_THREADS; i < vecs; i += IM_THREADS) stage(__ldcg(reinterpret_cast<const float4*>(xt) + i), i);
+            for (int i = tid + KEEP * IM_THREADS; i < vecs; i += IM_THREADS) stage(ldx(xt, i), i);
             __syncthreads();  // dred is reused by the next token; xd is read after the last one
         }
     }
@@ -590,6 +596,8 @@ __device__ __forceinline__ void im_multiply(uint8_t* smem, ImRing& rg, ImIssue& 
     //      src/kernels/rope_append.wgsl; every product rounded, src/ref/ops.zig:64-86).
     const int local_rts = rt_hi - rt_lo;
     const bool fused_rope = rope != nullptr && (p.flags & MV_ROPE_APPEND);
+    const bool pushing = pu != nullptr && pu->push_slot != PEER_NONE;
+    const uint32_t out_tag = pushing ? peer::push_tag(*pu) : 0u;
     const int total = local_rts * 16 * mt;
     for (int i0 = 0; i0 < total; i0 += IM_THREADS) {
         const int i = i0 + tid;
@@ -637,13 +645,10 @@ __device__ __forceinline__ void im_multiply(uint8_t* smem, ImRing& rg, ImIssue& 
         }
         if (!valid) continue;
         if (p.flags & MV_ACCUMULATE) v += i == tid ? first_old : __ldcg(out + o);
-        if (pu != nullptr && pu->push_slot != PEER_NONE) {
-            for (int r = 0; r < pu->t.world; r++) *peer::remote(*pu, out + o, r) = v;  // this rank's slice, to every rank
-        } else {
-            out[o] = v;
-        }
+        out[o] = v;
+        if (pushing) peer::push(*pu, out + o, v, out_tag);  // this rank's slice, to every rank's exchange slots
     }
-    if (pu != nullptr) peer::publish(*pu, (unsigned)ncta);
+    if (pu != nullptr) peer::finish(*pu, (unsigned)ncta);
 }
 
 }  // namespace imma

@@ -1,12 +1,20 @@
-// Tensor-parallel exchange without a collective library: every rank keeps the vectors that all ranks read
-// whole (the residual stream, the attention output, the FFN activations, the logits) in one "arena" that its
-// peers have mapped (CUDA IPC over NVLink). A kernel that produces a slice of such a vector stores it into the
-// arena of EVERY rank (its own included), and the last CTA of that kernel then publishes, on every rank, that
-// rank's count for the exchange ("slot"). A kernel that reads the vector first waits until every rank's count for
-// the slot has reached its own. No multicast: plain stores and loads on peer memory.
+// Tensor-parallel exchange without a collective library and without fences: every rank keeps the vectors that
+// all ranks read whole (the residual stream, the attention output, the FFN activations, the logits) in one
+// "arena" that its peers have mapped (CUDA IPC over NVLink). Beside each float of the arena's data region there is
+// an 8-byte slot {value bits, tag} in its exchange region (at ll_off + 2 * offset). A kernel that produces a slice
+// of such a vector stores {value, tag} into the slot of EVERY rank (its own included) with one 8-byte store; a
+// kernel that reads the vector reads the slots and waits, element by element, until the tag is the one it
+// expects. An 8-byte store arrives whole, so a matching tag proves its value: no flag, no fence, no round trip -
+// the data is its own signal (the idea of NCCL's low-latency protocol). No multicast: plain stores and loads.
 //
-// Counts only grow (one per execution of the slot's producer on each rank, and all ranks run the same list),
-// so nothing is reset between steps. Every wait is bounded in time; a rank that gives up sets the status word.
+// Tags: exchange `slot` of a step list, executed for the c-th time, uses tag c * slots + slot + 1. A buffer that
+// several exchanges of a step write in turn (the residual stream) therefore never shows the same tag twice, and
+// tags are never 0 (the arena starts zeroed). Every rank runs the same list, so a consumer computes the expected
+// tag from its own count of the slot, which its own producer advanced before (stream order).
+// A fast rank cannot overwrite a slot that a slow rank still has to read: to reach the next write of a buffer it
+// must have read, through the exchanges in between, data that the slow rank produces only after that read.
+// Every wait is bounded in time (2 s); a rank that gives up sets the context's status word and an abort word that
+// ends every later wait at once.
 #pragma once
 
 #include <cstdint>
@@ -18,8 +26,8 @@ constexpr uint32_t PEER_NONE = 0xffffffffu;
 // Trails a kernel's own parameter block when the dispatch takes part in an exchange.
 struct PPeer {
     uint32_t magic;      // PEER_MAGIC
-    uint32_t wait_slot;  // wait for this exchange before reading inputs (PEER_NONE: none)
-    uint32_t push_slot;  // store outputs to every rank and publish this exchange (PEER_NONE: none)
+    uint32_t wait_slot;  // the input vector comes from this exchange (PEER_NONE: it is local)
+    uint32_t push_slot;  // outputs go to every rank as this exchange (PEER_NONE: local only)
     uint32_t _pad;
 };
 
@@ -28,10 +36,10 @@ struct PeerTable {
     uint32_t slots, _pad;
     uint64_t base[PEER_MAX];   // every rank's arena as mapped here (base[rank] is the local one)
     uint64_t arena_bytes;
-    uint64_t flags_off;        // arena offset of flags[slots][PEER_MAX] (u32): flags[s][r] = rank r's count
-    uint32_t* counts;          // local: this rank's count per slot
+    uint64_t ll_off;           // arena offset of the exchange region: the float at offset q has its slot at ll_off + 2 q
+    uint32_t* counts;          // local: executions of each slot's producer on this rank
     uint32_t* tickets;         // local: CTAs of the producing kernel that have finished, per slot; tickets[slots] is
-                               // the abort word: set by the first wait that gives up, it ends every later wait at once
+                               // the abort word
 };
 
 struct PeerUse {  // what one launch does with the table
@@ -48,56 +56,72 @@ __device__ __forceinline__ unsigned long long now_ns() {
     return t;
 }
 
-// Every thread of the CTA calls it. Returns false (and sets *status) if a rank did not publish within 2 s.
-__device__ __forceinline__ bool wait_slot(const PeerUse& u, int* status) {
-    __shared__ int ok_flag;
-    if (u.wait_slot == PEER_NONE) return true;
-    if (threadIdx.x == 0) {
-        int ok = 1;
-        const uint32_t want = __ldcg(u.t.counts + u.wait_slot);  // this rank's own count: its producer ran before us
-        const uint32_t* flags = reinterpret_cast<const uint32_t*>(u.t.base[u.t.rank] + u.t.flags_off) + (size_t)u.wait_slot * PEER_MAX;
-        const unsigned long long t0 = now_ns();
-        if (__ldcg(u.t.tickets + u.t.slots) != 0) ok = 0;  // an earlier wait of this context gave up
-        for (int r = 0; r < u.t.world && ok; r++) {
-            for (unsigned spins = 0;; spins++) {
-                uint32_t seen;
-                asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(seen) : "l"(flags + r) : "memory");
-                if ((int32_t)(seen - want) >= 0) break;
-                if ((spins & 1023u) == 1023u && now_ns() - t0 > 2000000000ull) {
-                    if (status) atomicExch(status, 5);
-                    atomicExch(u.t.tickets + u.t.slots, 1u);
-                    ok = 0;
-                    break;
-                }
-            }
-        }
-        ok_flag = ok;
+// The tag the consumer of `slot` expects (its own producer has run: the count is already advanced) and the tag a
+// producer of `slot` writes (the count advances when its kernel ends).
+__device__ __forceinline__ uint32_t want_tag(const PeerUse& u) { return __ldcg(u.t.counts + u.wait_slot) * u.t.slots + u.wait_slot + 1; }
+__device__ __forceinline__ uint32_t push_tag(const PeerUse& u) { return (__ldcg(u.t.counts + u.push_slot) + 1) * u.t.slots + u.push_slot + 1; }
+
+// The exchange slot of the float at `local` (an address inside the local arena's data region), in rank r's arena.
+__device__ __forceinline__ uint2* slot_of(const PeerUse& u, const float* local, int r) {
+    const uint64_t q = reinterpret_cast<uint64_t>(local) - u.t.base[u.t.rank];
+    return reinterpret_cast<uint2*>(u.t.base[r] + u.t.ll_off + 2 * q);
+}
+
+// One output of an exchange: its slot on every rank.
+__device__ __forceinline__ void push(const PeerUse& u, const float* local, float v, uint32_t tag) {
+    for (int r = 0; r < u.t.world; r++) {
+        uint2* s = slot_of(u, local, r);
+        asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};\n" ::"l"(s), "r"(__float_as_uint(v)), "r"(tag) : "memory");
     }
-    __syncthreads();
-    return ok_flag != 0;
 }
 
-// Where element `offset_bytes` of the local arena lives in rank r's arena.
-__device__ __forceinline__ float* remote(const PeerUse& u, const float* local, int r) {
-    return reinterpret_cast<float*>(u.t.base[r] + (reinterpret_cast<uint64_t>(local) - u.t.base[u.t.rank]));
+__device__ __forceinline__ bool gave_up(const PeerUse& u, unsigned long long t0, unsigned spins, int* status) {
+    if ((spins & 1023u) != 1023u) return false;
+    if (__ldcg(u.t.tickets + u.t.slots) != 0) return true;  // another wait of this context gave up
+    if (now_ns() - t0 > 2000000000ull) {
+        if (status) atomicExch(status, 5);
+        atomicExch(u.t.tickets + u.t.slots, 1u);
+        return true;
+    }
+    return false;
 }
 
-// Every thread of the CTA calls it after its last store of the exchange. The last CTA of the grid publishes.
-__device__ __forceinline__ void publish(const PeerUse& u, unsigned ncta) {
+// Four consecutive floats of an exchanged vector (`local` is 16-byte aligned): waits until all four slots carry `tag`.
+__device__ __forceinline__ float4 read4(const PeerUse& u, const float* local, uint32_t tag, int* status) {
+    const uint2* s = slot_of(u, local, u.t.rank);
+    uint4 a, b;
+    const unsigned long long t0 = now_ns();
+    for (unsigned spins = 0;; spins++) {
+        asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(a.x), "=r"(a.y), "=r"(a.z), "=r"(a.w) : "l"(s) : "memory");
+        asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(b.x), "=r"(b.y), "=r"(b.z), "=r"(b.w) : "l"(s + 2) : "memory");
+        if (a.y == tag && a.w == tag && b.y == tag && b.w == tag) break;
+        if (gave_up(u, t0, spins, status)) break;
+    }
+    return make_float4(__uint_as_float(a.x), __uint_as_float(a.z), __uint_as_float(b.x), __uint_as_float(b.z));
+}
+
+__device__ __forceinline__ float read1(const PeerUse& u, const float* local, uint32_t tag, int* status) {
+    const uint2* s = slot_of(u, local, u.t.rank);
+    uint2 a;
+    const unsigned long long t0 = now_ns();
+    for (unsigned spins = 0;; spins++) {
+        asm volatile("ld.volatile.global.v2.u32 {%0,%1}, [%2];\n" : "=r"(a.x), "=r"(a.y) : "l"(s) : "memory");
+        if (a.y == tag) break;
+        if (gave_up(u, t0, spins, status)) break;
+    }
+    return __uint_as_float(a.x);
+}
+
+// Every thread of a producing CTA calls it after its last push. The last CTA of the grid advances the slot's count
+// (local memory only: the consumers on this rank run after this kernel).
+__device__ __forceinline__ void finish(const PeerUse& u, unsigned ncta) {
     if (u.push_slot == PEER_NONE) return;
-    __syncthreads();  // the CTA's peer stores happen before thread 0's fence (cumulative), which precedes the ticket
+    __syncthreads();
     if (threadIdx.x == 0) {
-        __threadfence_system();
-        const unsigned t = atomicAdd(u.t.tickets + u.push_slot, 1u);
-        if (t == ncta - 1) {
+        __threadfence();
+        if (atomicAdd(u.t.tickets + u.push_slot, 1u) == ncta - 1) {
             u.t.tickets[u.push_slot] = 0;
-            __threadfence_system();
-            const uint32_t count = u.t.counts[u.push_slot] + 1;
-            u.t.counts[u.push_slot] = count;
-            for (int r = 0; r < u.t.world; r++) {
-                uint32_t* flag = reinterpret_cast<uint32_t*>(u.t.base[r] + u.t.flags_off) + (size_t)u.push_slot * PEER_MAX + u.t.rank;
-                asm volatile("st.release.sys.global.u32 [%0], %1;\n" ::"l"(flag), "r"(count) : "memory");
-            }
+            u.t.counts[u.push_slot] += 1;
         }
     }
 }

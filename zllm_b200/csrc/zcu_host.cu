@@ -186,7 +186,7 @@ zcu_result wait_stream(zcu_context* c, uint32_t timeout_ms) {
             return fail(c, ZCU_E_GPU, "delta_rule (chunked): the token count in the parameter block is not the step's, or a kept row "
                                       "lies inside the chunked part; the step was not applied past its whole chunks");
         if (what == 5)
-            return fail(c, ZCU_E_GPU, "a rank did not publish a tensor-parallel exchange within 2 s; every later wait of this context "
+            return fail(c, ZCU_E_GPU, "a slice of a tensor-parallel exchange did not arrive within 2 s; every later wait of this context "
                                       "gives up at once (configure the peers again to clear it)");
         return fail(c, ZCU_E_GPU, "a kernel gave up a bounded wait (a copy or a peer never arrived); its results are invalid");
     }
@@ -667,7 +667,7 @@ zcu_result parse_peer(const LaunchArgs& a, PeerUse& u, const void* out_lo, const
     u.push_slot = pp.push_slot;
     if (u.push_slot != PEER_NONE) {
         const uint64_t lo = reinterpret_cast<uint64_t>(out_lo), hi = reinterpret_cast<uint64_t>(out_hi), base = u.t.base[u.t.rank];
-        ZCU_NEED(a, lo >= base && hi <= base + u.t.flags_off && lo <= hi, "peer exchange: the output is not inside the local arena");
+        ZCU_NEED(a, lo >= base && hi <= base + u.t.ll_off && lo <= hi, "peer exchange: the output is not inside the local arena");
     }
     return ZCU_OK;
 }
@@ -1061,24 +1061,24 @@ ZCU_EXPORT zcu_result zcu_ipc_open(zcu_context* c, const void* handle64, void** 
     return ZCU_OK;
 }
 ZCU_EXPORT zcu_result zcu_peer_config(zcu_context* c, uint32_t rank, uint32_t world, const uint64_t* bases, uint64_t arena_bytes,
-                                      uint64_t flags_offset, uint32_t slots) {
+                                      uint64_t exchange_offset, uint32_t slots) {
     LIVE(c);
     if (c->dry) return fail(c, ZCU_E_INVALID, "peer_config: needs a device");
     if (!bases || world == 0 || world > PEER_MAX || rank >= world || slots == 0)
         return fail(c, ZCU_E_INVALID, "peer_config: rank %u of %u, %u slots", rank, world, slots);
-    if (flags_offset % 4 != 0 || flags_offset + (uint64_t)slots * PEER_MAX * 4 > arena_bytes)
-        return fail(c, ZCU_E_INVALID, "peer_config: the flags do not fit the arena");
+    if (exchange_offset % 16 != 0 || exchange_offset * 3 > arena_bytes)
+        return fail(c, ZCU_E_INVALID, "peer_config: the exchange region (twice the data region) does not fit the arena");
     PeerTable t = {};
     t.rank = (int32_t)rank;
     t.world = (int32_t)world;
     t.slots = slots;
     for (uint32_t r = 0; r < world; r++) t.base[r] = bases[r];
     t.arena_bytes = arena_bytes;
-    t.flags_off = flags_offset;
+    t.ll_off = exchange_offset;
     uint32_t* words = nullptr;
     CU(c, cudaMalloc((void**)&words, ((size_t)slots * 2 + 1) * sizeof(uint32_t)));
     CU(c, cudaMemset(words, 0, ((size_t)slots * 2 + 1) * sizeof(uint32_t)));
-    CU(c, cudaMemset(reinterpret_cast<void*>(t.base[rank] + flags_offset), 0, (size_t)slots * PEER_MAX * 4));
+    CU(c, cudaMemset(reinterpret_cast<void*>(t.base[rank] + exchange_offset), 0, (size_t)exchange_offset * 2));  // tag 0: nothing yet
     t.counts = words;
     t.tickets = words + slots;
     if (c->peers.counts) cudaFree(c->peers.counts);

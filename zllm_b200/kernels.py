@@ -150,9 +150,10 @@ class Launcher:
             args += list(rope[1])
         self.launch(MATVEC_KERNEL[ttype], with_peer(p, wait, push), args, (-(-n // 8), m, 1), variant)
 
-    def peer_wait(self, slot: int):
-        """Waits (on the device, in stream order) until every rank has published exchange `slot`."""
-        self.launch(EXT_PEER_WAIT, PeerExt(PEER_MAGIC, slot, PEER_NONE, 0), [], (1, 1, 1))
+    def peer_wait(self, slot: int, vector):
+        """Waits (on the device, in stream order) for every rank's slice of exchange `slot` and fills in the plain
+        floats of `vector` (a buffer inside the arena) for the host to read."""
+        self.launch(EXT_PEER_WAIT, PeerExt(PEER_MAGIC, slot, PEER_NONE, 0), [vector], (1, 1, 1))
 
     def matmul(self, ttype, x, w, out, rows, n, k, col0=0, out_stride=None, accumulate=False, variant=0, layout=0):
         """The prefill multiply on half-precision weights. `variant` 0 is the exact f32 identity;

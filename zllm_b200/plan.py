@@ -264,7 +264,7 @@ class DenseProgram:
                      wait=(4 * cfg.layers - 1) if peer else None, push=s_logits)
         self._gather(self.logits, cfg.vocab)
         if peer:
-            self.L.peer_wait(s_logits)  # the host may read the logits once this has run
+            self.L.peer_wait(s_logits, self.logits)  # the host may read the logits once this has run
             self.launches_per_step += 1
 
     def algorithmic_bytes(self, positions: np.ndarray) -> dict:
