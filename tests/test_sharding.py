@@ -138,3 +138,52 @@ def test_two_gloo_ranks_reproduce_the_unsharded_layer(ref):
                                   cfg.rope_base, K.attention_scale(hd))
     # every output row, head and column is computed by exactly one rank with the same arithmetic: same bits
     assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
+def test_exchange_slots_chain_through_the_sharded_launch_list():
+    # The sharded plan on a dry-run context (no device): every multiply that reads a gathered vector waits for the
+    # exchange that the vector's producer pushes, slots are used once per step, and the list ends with the wait
+    # that hands the logits to the host.
+    import ctypes as C
+
+    from zllm_b200 import abi
+    from zllm_b200.plan import DenseProgram
+
+    ctx = abi.Context(dry_run=True)
+
+    class FakeArena:
+        def alloc(self, n):
+            return ctx.alloc(n)
+
+    cfg = DenseConfig(layers=3, hidden=512, heads=8, kv_heads=4, head_dim=64, ff=1024, vocab=1024, max_ctx=64)
+    weights = {"embed": ctx.alloc(256), "head": ctx.alloc(256), "out_norm": ctx.alloc(256),
+               "layers": [{k: ctx.alloc(256) for k in ("wqkv", "wo", "wgu", "wdown", "attn_norm", "ffn_norm")} for _ in range(cfg.layers)]}
+    prog = DenseProgram(ctx, cfg, weights, 1, ctx.alloc, Shard(1, 2), arena=FakeArena())
+    prog.set_rope_table(ctx.alloc(256))
+    seen = []
+    real = prog.L.launch
+
+    def spy(kernel, params, args, groups, variant=0):
+        raw = bytes(params)
+        ext = K.PeerExt.from_buffer_copy(raw[-16:]) if len(raw) >= 16 else None
+        seen.append((kernel, (ext.wait_slot, ext.push_slot) if ext is not None and ext.magic == K.PEER_MAGIC else None))
+        real(kernel, params, args, groups, variant)
+
+    prog.L.launch = spy
+    before = ctx.launch_count()
+    prog.record_step(17)
+    assert ctx.launch_count() - before == len(seen) == 2 + 6 * cfg.layers + 1 == prog.launches_per_step
+    none = K.PEER_NONE
+    exts = [e for _, e in seen]
+    assert exts[0] is None                                    # embed: every rank decodes the row itself
+    for il in range(cfg.layers):
+        qkv, split, combine, wo, gu, down = exts[1 + 6 * il: 7 + 6 * il]
+        assert qkv == (None if il == 0 else (4 * il - 1, none))  # the residual stream of the layer before
+        assert split is None and combine == (none, 4 * il)
+        assert wo == (4 * il, 4 * il + 1) and gu == (4 * il + 1, 4 * il + 2) and down == (4 * il + 2, 4 * il + 3)
+    assert exts[-2] == (4 * cfg.layers - 1, 4 * cfg.layers)       # the head
+    assert seen[-1] == (K.EXT_PEER_WAIT, (4 * cfg.layers, none))  # the host's wait for the logits
+    pushed = [e[1] for e in exts if e is not None and e[1] != none]
+    assert sorted(pushed) == list(range(DenseProgram.arena_slots(cfg)))
+    assert len(bytes(K.with_peer(K.Matvec(1, 2, 3, 4, 0.0, 0, 0, 0), wait=3))) == C.sizeof(K.Matvec) + 16
+    ctx.close()
