@@ -307,6 +307,11 @@ __device__ __forceinline__ void im_multiply(uint8_t* smem, ImRing& rg, ImIssue& 
     const int lo = iss.lo, hi = iss.hi;
 
     for (int i = tid; i < IM_WARPS * seg_max; i += IM_THREADS) segkey[i] = -1;
+    // the norm weights are constants read once per step: ask for them now, while the kernel before this one
+    // is still running, so the staging below finds them on chip
+    if (norm)
+        for (int off = tid * 128; off < k * 4; off += IM_THREADS * 128)
+            asm volatile("prefetch.global.L1 [%0];\n" ::"l"(reinterpret_cast<const char*>(norm_w) + off));
     wait_inputs();
     // the value this thread's first output accumulates onto: asked for now, needed after the tile stream
     float first_old = 0.f;
@@ -364,13 +369,19 @@ __device__ __forceinline__ void im_multiply(uint8_t* smem, ImRing& rg, ImIssue& 
             }
             __syncthreads();
             // every thread finishes the reduction itself (fixed order), so no second barrier is needed
-            double tot = 0.0;
+            // (a pairwise tree: four dependent f64 additions instead of sixteen)
+            double part[IM_WARPS];
             float am = 0.f;
 #pragma unroll
             for (int wv = 0; wv < IM_WARPS; wv++) {
-                tot += dred[wv];
+                part[wv] = dred[wv];
                 am = fmaxf(am, (float)dred[32 + wv]);
             }
+#pragma unroll
+            for (int span = 1; span < IM_WARPS; span *= 2)
+#pragma unroll
+                for (int wv = 0; wv < IM_WARPS; wv += 2 * span) part[wv] += part[wv + span];
+            const double tot = part[0];
             float nscale = 1.0f;
             if (norm) {
                 // (a power-of-two k divides exactly either way; the multiply skips the slow f64 division)
