@@ -474,7 +474,12 @@ class DecodeStep:
         peak, kind = measured_hbm_peak()
         return {"bound": "hbm", "kernel": "matvec_imma<Q4_K> (the 4 body multiplies of each layer, mean over a step)",
                 "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": f"of {kind}",
-                "frac_of_8000_nominal": achieved / 8000.0, "traffic": None, "bytes_per_launch": per_launch,
+                "frac_of_8000_nominal": achieved / 8000.0,
+                # dram__bytes_read + write per launch of the same four multiplies from an ncu capture of this workload
+                # on one GPU (14.26, 9.54, 66.16 and 33.17 MB: profiles/matvec_imma_decode_traffic.md); not captured
+                # for sharded or batched runs
+                "traffic": 30.78e6 if (self.dist.world == 1 and self.batch == 1) else None,
+                "bytes_per_launch": per_launch,
                 "us_per_launch": us, "launches_per_step": launches,
                 "step_hbm_gbs": self.bytes["total"] / (ms_per_step * 1e-3) / 1e9,
                 "step_frac": self.bytes["total"] / (ms_per_step * 1e-3) / 1e9 / peak}
