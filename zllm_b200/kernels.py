@@ -47,6 +47,15 @@ def variant(tiles: int = 0, splitk: int = 0, family: int = 0) -> int:
 # Tensor-core family: tiles in flight per warp (byte 0); scalar family: one shape.
 MATVEC_CANDIDATES = [variant(st, 0, FAMILY_MMA) for st in (2, 4, 6)] + [variant(0, 0, FAMILY_SCALAR)]
 
+
+def matvec_variant_exists(ttype: str, k: int, v: int) -> bool:
+    """Whether variant word `v` can run a (ttype, k) multiply: the tensor-core family needs Q8_0 rows of whole
+    256-weight pieces (the default falls back to the scalar family there)."""
+    family = (v >> 16) & 0xFF
+    if ttype == "q8_0" and k % 256 != 0:
+        return v == 0 or family == FAMILY_SCALAR
+    return True
+
 u32, f32 = C.c_uint32, C.c_float
 
 

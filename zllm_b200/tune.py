@@ -1,0 +1,84 @@
+"""Load-time tuning of the quantised decode multiplies: the counterpart of the reference's tune.Sweep
+(src/tune/tune.zig:1-27, 77-106). For each shape (type, n, k) every candidate variant of this backend
+(kernels.MATVEC_CANDIDATES: tiles in flight per warp 2/4/6 of the tensor-core family, and the scalar family) runs on
+the shape's real weights: it is first checked against the default variant (relative L2 error above `TOLERANCE`
+drops it: candidates differ only in the order of each row's sums), then timed - `WARMUP` batches, then the median
+of `TIMED` batches, each batch repeating the dispatch so that it lasts about a millisecond. The fastest per shape
+goes into the table a plan passes as `variants`.
+
+The inputs are the reference's: x[i] = sin(0.7 i), of RMS about 1 like normed activations."""
+from __future__ import annotations
+
+import time
+
+import numpy as np
+
+from . import kernels as K
+
+TIMED, WARMUP, TOLERANCE = 7, 3, 1e-5  # src/tune/tune.zig:24-30
+
+
+def _rel_l2(got: np.ndarray, want: np.ndarray) -> float:
+    den = float(np.sqrt((want.astype(np.float64) ** 2).sum()))
+    return float(np.sqrt(((got.astype(np.float64) - want.astype(np.float64)) ** 2).sum())) / (den if den > 0 else 1.0)
+
+
+class Sweep:
+    """sweep = Sweep(ctx, tokens=1); sweep.add("q4_k", weights_buffer, n, k); table = sweep.run()"""
+
+    def __init__(self, ctx, tokens: int = 1, candidates=None):
+        assert 1 <= tokens <= 4  # kernels.decode_max_rows
+        self.ctx, self.tokens = ctx, tokens
+        self.candidates = list(candidates if candidates is not None else [0] + K.MATVEC_CANDIDATES)
+        assert self.candidates[0] == 0, "the default first: it is the reference the others must match"
+        self.shapes, self.dropped, self.report = [], 0, []
+        self.L = K.Launcher(ctx)
+
+    def add(self, ttype: str, weights, n: int, k: int):
+        if ttype not in ("q4_k", "q8_0") or any(s[0] == ttype and s[2] == n and s[3] == k for s in self.shapes):
+            return
+        row_bytes = K.row_bytes(ttype, k)
+        reps = int(np.clip((256 << 20) // max(n * row_bytes, 1), 2, 64))
+        self.shapes.append((ttype, weights, n, k, reps))
+
+    def _batch(self, shape, variant, x, out) -> float:
+        ttype, w, n, k, reps = shape
+        self.ctx.sync()
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            self.L.matvec(ttype, x, w, out, n, k, m=self.tokens, variant=variant)
+        self.ctx.sync()
+        return (time.perf_counter() - t0) / reps
+
+    def run(self) -> dict:
+        """{(type, n, k): variant word} with the fastest agreeing candidate of every shape."""
+        table = {}
+        if not self.shapes:
+            return table
+        k_max = max(s[3] for s in self.shapes)
+        n_max = max(s[2] for s in self.shapes)
+        xs = np.sin(np.arange(self.tokens * k_max, dtype=np.float32) * np.float32(0.7)).astype(np.float32)
+        out = self.ctx.zeros(self.tokens * n_max * 4)
+        for shape in self.shapes:
+            ttype, w, n, k, reps = shape
+            x = self.ctx.put(xs[: self.tokens * k])
+            reference, best = None, None
+            for variant in self.candidates:
+                if not K.matvec_variant_exists(ttype, k, variant):
+                    continue
+                self._batch(shape, variant, x, out)  # the correctness run is the first warm-up batch
+                got = out.download(np.float32, self.tokens * n)
+                if reference is None:
+                    reference = got.copy()
+                elif _rel_l2(got, reference) > TOLERANCE or not np.isfinite(got).all():
+                    self.dropped += 1
+                    self.report.append((ttype, n, k, variant, None))
+                    continue
+                for _ in range(WARMUP - 1):
+                    self._batch(shape, variant, x, out)
+                ns = float(np.median([self._batch(shape, variant, x, out) for _ in range(TIMED)])) * 1e9
+                self.report.append((ttype, n, k, variant, ns))
+                if best is None or ns < best[1]:
+                    best = (variant, ns)
+            table[(ttype, n, k)] = best[0]
+        return table
