@@ -132,7 +132,8 @@ def test_step_program_equals_launch_by_launch(ref, gpu):
     vc_host = [rng.normal(size=kv_shape).astype(np.float16) for _ in range(cfg.layers)]
 
     def fresh():
-        prog = DenseProgram(gpu, cfg, weights, 1, gpu.zeros)
+        # the program runs attention's CUDA-core form (variant 1); the launch-by-launch side is told to as well
+        prog = DenseProgram(gpu, cfg, weights, 1, gpu.zeros, variants={"attn_split": 1})
         prog.set_rope_table(gpu.put(DenseProgram.rope_table(cfg)))
         for il in range(cfg.layers):
             prog.kc[il].upload(kc_host[il].view(np.uint16))

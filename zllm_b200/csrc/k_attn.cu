@@ -202,6 +202,16 @@ __global__ void __launch_bounds__(attn::AF_THREADS, 3) attn_split_fast(PAttentio
     attn::attn_split_fast_body<HD, GROUP_CAP>(vblock_of_cta(dyn_smem), p, qg, kc, vc, part, step, seq_pos);
 }
 
+template <int HD>
+__global__ void __launch_bounds__(attn::AM_THREADS, 3) attn_split_mma(PAttention p, const float* __restrict__ qg,
+                                                                     const __half* __restrict__ kc,
+                                                                     const __half* __restrict__ vc, float* __restrict__ part,
+                                                                     const PStep* __restrict__ step,
+                                                                     const uint32_t* __restrict__ seq_pos) {
+    extern __shared__ __align__(128) unsigned char dyn_smem[];
+    attn::attn_split_mma_body<HD>(dyn_smem, p, qg, kc, vc, part, step, seq_pos, (int)blockIdx.x, (int)blockIdx.y, (int)blockIdx.z);
+}
+
 template <int HD, int GROUP_CAP>
 __global__ void __launch_bounds__(attn::AF_THREADS, 1) attn_split_persistent(PAttention p, const float* __restrict__ qg,
                                                                             const __half* __restrict__ kc,
@@ -283,11 +293,23 @@ zcu_result launch_attn_split(const LaunchArgs& a) {
         float* part = (float*)a.b[3].ptr;
         const PStep* step = (const PStep*)a.b[4].ptr;
         const uint32_t* seq_pos = (a.nb >= 6 && p._pad[0] != 0) ? (const uint32_t*)a.b[5].ptr : nullptr;
-        // Few blocks (one or two sequences): one CTA per block, three of them resident per SM, hides the phases of
-        // a block best. Many blocks: one persistent CTA per SM with the tiles of the next blocks in flight
-        // (batch 8 at 8192 keys: 12.9 -> 11.3 ms per step). Variant 1 / 2 force the first / second form.
+        // Variants: 0 (default) / 3 = one CTA per block on the tensor cores; 1 = one CTA per block on the CUDA cores
+        // (exact f32 products; the form the step program runs); 2 = the CUDA-core arithmetic as a persistent walk
+        // with pipelined tiles.
         const int total_blocks = (int)(grid.x * grid.y * grid.z);
-        if (a.variant == 1 || (a.variant == 0 && total_blocks < 1024)) {
+        if (a.variant == 0 || a.variant == 3) {
+            // the default: one CTA per block on the f16 tensor cores (queries and probabilities as two f16 terms)
+            const size_t msmem = attn::attn_mma_smem(hd);
+            auto mk = hd == 128 ? attn_split_mma<128> : attn_split_mma<64>;
+            if (cudaFuncSetAttribute(mk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)msmem) != cudaSuccess) {
+                cudaGetLastError();
+                return zcu_fail(a, ZCU_E_GPU, "attn_split: %zu bytes of shared memory refused", msmem);
+            }
+            mk<<<grid, attn::AM_THREADS, msmem, a.stream>>>(p, qg, kc, vc, part, step, seq_pos);
+            ZCU_CHECK_LAUNCH(a);
+            return ZCU_OK;
+        }
+        if (a.variant == 1) {
             if (hd == 128) attn_split_fast<128, 4><<<grid, AF_THREADS, smem, a.stream>>>(p, qg, kc, vc, part, step, seq_pos);
             else attn_split_fast<64, 4><<<grid, AF_THREADS, smem, a.stream>>>(p, qg, kc, vc, part, step, seq_pos);
             ZCU_CHECK_LAUNCH(a);

@@ -209,6 +209,185 @@ __device__ __forceinline__ void attn_split_fast_body(const VBlock& vb, const PAt
     }
 }
 
+// ---- the block on the f16 tensor cores (mma.sync.m16n8k16, f32 accumulate). The cache holds f16 values, which the
+// tensor cores multiply exactly; the f32 queries and probabilities are split into two f16 terms each
+// (x = hi + lo, |x - hi - lo| <= 2^-22 |x|), which occupy rows 0-3 (hi of the group's heads) and 4-7 (lo) of the
+// 16-row A operand; the two partial results are added afterwards. Scores: A = Q [16 x dims], B = K^T [dims x keys]
+// read straight out of the staged K tile; sum exp * v: A = P [16 x keys], B = V [keys x dims] through
+// ldmatrix.trans, each warp owning head_dim / 8 output dims over all 128 keys, so no cross-warp reduction is
+// left. About 350 warp instructions per warp and block instead of 1600 on the CUDA cores. K and V tiles (rows
+// padded to head_dim * 2 + 16 bytes: conflict-free fragment reads) arrive by cp.async while the queries are split.
+constexpr int AM_THREADS = 256;
+__host__ __device__ constexpr size_t attn_mma_smem(int hd) {
+    return (size_t)2 * AF_KEYS * (hd * 2 + 16) + (size_t)(4 * AF_KEYS + 8 + 4 * hd) * sizeof(float);
+}
+
+__device__ __forceinline__ void mma_f16_16816(float* c, uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+    // rows 8-15 of A are zero (a1 = a3 = 0)
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
+}
+// (hi, hi) or (lo, lo) halves of two floats, as one A-operand register
+__device__ __forceinline__ uint32_t split_pair(float x0, float x1, bool low) {
+    __half h0 = __float2half_rn(x0), h1 = __float2half_rn(x1);
+    if (low) {
+        h0 = __float2half_rn(x0 - __half2float(h0));
+        h1 = __float2half_rn(x1 - __half2float(h1));
+    }
+    return (uint32_t)__half_as_ushort(h0) | ((uint32_t)__half_as_ushort(h1) << 16);
+}
+
+template <int HD>
+__device__ __forceinline__ void attn_split_mma_body(unsigned char* smem, const PAttention& p, const float* __restrict__ qg,
+                                                    const __half* __restrict__ kc, const __half* __restrict__ vc,
+                                                    float* __restrict__ part, const PStep* __restrict__ step,
+                                                    const uint32_t* __restrict__ seq_pos, int g_kv, int b, int t) {
+    constexpr int RS = HD * 2 + 16;              // bytes between the rows of a staged tile
+    constexpr int PIECES = AF_KEYS * (HD / 8) / AM_THREADS;
+    constexpr int KSTEPS = HD / 16;              // k-steps of the score product
+    constexpr int NBLK = HD / 64;                // 8-dim output blocks per warp in the value product
+    unsigned char* Kt = smem;
+    unsigned char* Vt = smem + (size_t)AF_KEYS * RS;
+    float (*sc)[AF_KEYS] = reinterpret_cast<float (*)[AF_KEYS]>(Vt + (size_t)AF_KEYS * RS);
+    float* stat = reinterpret_cast<float*>(sc) + 4 * AF_KEYS;
+    float* qs = stat + 8;                        // [4][HD]
+    const uint32_t kt_s = (uint32_t)__cvta_generic_to_shared(Kt), vt_s = (uint32_t)__cvta_generic_to_shared(Vt);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, tq = lane & 3;      // fragment coordinates
+    const int group = (int)(p.heads / p.kv_heads);
+    const int row = (int)p.row0 + t;
+    const size_t seq_off = (size_t)row * p._pad[0];
+    const int keys = (seq_pos ? (int)seq_pos[row] : (int)step->pos0 + row) + 1;
+    const int k0 = b * AF_KEYS;
+    const size_t kv_stride = (size_t)p.kv_heads * HD;
+    const int q_head = p.gated ? 2 * HD : HD;
+    const int n = min(AF_KEYS, keys - min(keys, k0));
+
+    // ---- tiles on their way
+#pragma unroll
+    for (int i = 0; i < PIECES; i++) {
+        const int j = tid + AM_THREADS * i, key = j / (HD / 8), piece = j % (HD / 8);
+        const size_t src = seq_off + (size_t)min(k0 + key, keys - 1) * kv_stride + (size_t)g_kv * HD + 8 * piece;
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(kt_s + (uint32_t)key * RS + 16u * piece), "l"(kc + src) : "memory");
+    }
+    asm volatile("cp.async.commit_group;\n" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < PIECES; i++) {
+        const int j = tid + AM_THREADS * i, key = j / (HD / 8), piece = j % (HD / 8);
+        const size_t src = seq_off + (size_t)min(k0 + key, keys - 1) * kv_stride + (size_t)g_kv * HD + 8 * piece;
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(vt_s + (uint32_t)key * RS + 16u * piece), "l"(vc + src) : "memory");
+    }
+    asm volatile("cp.async.commit_group;\n" ::: "memory");
+    // ---- the group's queries
+    for (int i = tid; i < 4 * HD / 4; i += AM_THREADS) {
+        const int h = i / (HD / 4), d4 = i % (HD / 4);
+        const float* qp = qg + (size_t)row * p.q_row + (size_t)(g_kv * group + min(h, group - 1)) * q_head;
+        reinterpret_cast<float4*>(qs)[i] = __ldcg(reinterpret_cast<const float4*>(qp) + d4);
+    }
+    asm volatile("cp.async.wait_group 1;\n" ::: "memory");
+    __syncthreads();
+
+    // ---- scores: warp w takes keys 16 w .. 16 w + 15
+    {
+        const float* qrow = qs + (size_t)(g & 3) * HD;
+        const bool low = g >= 4;
+        float c[2][4];
+#pragma unroll
+        for (int nb = 0; nb < 2; nb++) c[nb][0] = c[nb][1] = c[nb][2] = c[nb][3] = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ks++) {
+            const float2 qa = *reinterpret_cast<const float2*>(qrow + 16 * ks + 2 * tq);
+            const float2 qb = *reinterpret_cast<const float2*>(qrow + 16 * ks + 8 + 2 * tq);
+            const uint32_t a0 = split_pair(qa.x, qa.y, low), a2 = split_pair(qb.x, qb.y, low);
+#pragma unroll
+            for (int nb = 0; nb < 2; nb++) {
+                const uint32_t kaddr = kt_s + (uint32_t)(16 * warp + 8 * nb + g) * RS + (uint32_t)(16 * ks + 2 * tq) * 2u;
+                uint32_t b0, b1;
+                asm volatile("ld.shared.u32 %0, [%1];\n" : "=r"(b0) : "r"(kaddr));
+                asm volatile("ld.shared.u32 %0, [%1];\n" : "=r"(b1) : "r"(kaddr + 16u));
+                mma_f16_16816(c[nb], a0, a2, b0, b1);
+            }
+        }
+#pragma unroll
+        for (int nb = 0; nb < 2; nb++) {
+            // hi rows (lanes g < 4) + lo rows (lanes g + 4 = lane + 16)
+            const float s0 = __fadd_rn(c[nb][0], __shfl_xor_sync(0xffffffffu, c[nb][0], 16));
+            const float s1 = __fadd_rn(c[nb][1], __shfl_xor_sync(0xffffffffu, c[nb][1], 16));
+            if (g < group) {
+                const int kl = 16 * warp + 8 * nb + 2 * tq;
+                sc[g][kl] = k0 + kl < keys ? s0 * p.scale : -FLT_MAX;
+                sc[g][kl + 1] = k0 + kl + 1 < keys ? s1 * p.scale : -FLT_MAX;
+            }
+        }
+    }
+    __syncthreads();
+    // ---- block softmax: warp h takes head h, four keys per lane
+    if (warp < group) {
+        float s[4], mx = -FLT_MAX;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            s[i] = lane + 32 * i < n ? sc[warp][lane + 32 * i] : -FLT_MAX;
+            mx = fmaxf(mx, s[i]);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        float sum = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const float e = (lane + 32 * i < n && s[i] != -FLT_MAX) ? expf(s[i] - mx) : 0.f;
+            sc[warp][lane + 32 * i] = e;
+            sum = __fadd_rn(sum, e);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sum = __fadd_rn(sum, __shfl_xor_sync(0xffffffffu, sum, o));
+        if (lane == 0) {
+            stat[2 * warp] = mx;
+            stat[2 * warp + 1] = sum;
+        }
+    }
+    asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+    __syncthreads();
+    // ---- sum exp * v: warp w takes dims (HD / 8) w .. over all 128 keys
+    {
+        const float* prow = sc[min(g & 3, group - 1)];
+        const bool low = g >= 4;
+        float c[NBLK][4];
+#pragma unroll
+        for (int nb = 0; nb < NBLK; nb++) c[nb][0] = c[nb][1] = c[nb][2] = c[nb][3] = 0.f;
+        const int d0 = (HD / 8) * warp;
+#pragma unroll
+        for (int ks = 0; ks < AF_KEYS / 16; ks++) {
+            const float2 pa = *reinterpret_cast<const float2*>(prow + 16 * ks + 2 * tq);
+            const float2 pb = *reinterpret_cast<const float2*>(prow + 16 * ks + 8 + 2 * tq);
+            const uint32_t a0 = split_pair(pa.x, pa.y, low), a2 = split_pair(pb.x, pb.y, low);
+#pragma unroll
+            for (int nb = 0; nb < NBLK; nb++) {
+                // two 8 x 8 matrices of V (keys 16 ks .. +7 and +8 .. +15, dims d0 + 8 nb .. +7), transposed on the way
+                const uint32_t vaddr = vt_s + (uint32_t)(16 * ks + (lane & 15)) * RS + (uint32_t)(d0 + 8 * nb) * 2u;
+                uint32_t b0, b1;
+                asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];\n" : "=r"(b0), "=r"(b1) : "r"(vaddr));
+                mma_f16_16816(c[nb], a0, a2, b0, b1);
+            }
+        }
+#pragma unroll
+        for (int nb = 0; nb < NBLK; nb++) {
+            const float o0 = __fadd_rn(c[nb][0], __shfl_xor_sync(0xffffffffu, c[nb][0], 16));
+            const float o1 = __fadd_rn(c[nb][1], __shfl_xor_sync(0xffffffffu, c[nb][1], 16));
+            if (g < group) {
+                const int head = g_kv * group + g, d = d0 + 8 * nb + 2 * tq;
+                const size_t base = (((size_t)t * p.heads + head) * p.max_blocks + b) * (HD + 2);
+                part[base + 2 + d] = o0;
+                part[base + 2 + d + 1] = o1;
+                if (d == 0) {
+                    part[base] = stat[2 * g];
+                    part[base + 1] = stat[2 * g + 1];
+                }
+            }
+        }
+    }
+}
+
 // ---- the same block arithmetic as a persistent kernel: one CTA per SM walks a contiguous range of the
 // (row, KV head, key block) space with its K and V tiles (128 keys x head_dim halves each) arriving through a
 // 3-stage cp.async pipeline, so the loads of the next two blocks are in flight while a block is computed. With

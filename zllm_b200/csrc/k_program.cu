@@ -381,6 +381,7 @@ zcu_result program_record(zcu_program* pr, uint32_t kernel, const LaunchArgs& a)
             const uint32_t group = p.kv_heads ? p.heads / p.kv_heads : 0;
             const bool fast = p.kv == KV_F16 && p.kv_heads > 0 && p.heads % p.kv_heads == 0 && group >= 1 && group <= 4 && (p.head_dim == 64 || p.head_dim == 128);
             if (!fast) return zcu_fail(a, ZCU_E_UNSUPPORTED_KERNEL, "step program: attention needs the f16 cache, a GQA group of at most 4 and head_dim 64 or 128");
+            if (a.variant != 1) return zcu_fail(a, ZCU_E_UNSUPPORTED_KERNEL, "step program: only attn_split's CUDA-core form (variant 1) runs inside it");
             ZCU_NEED(a, a.grid[1] <= p.max_blocks, "step program: %u key blocks above max_blocks %u", a.grid[1], p.max_blocks);
             if (a.grid[1] == 0 || a.grid[2] == 0) return ZCU_OK;
             if (!(a.nb >= 6 && p._pad[0] != 0)) op.b[5] = nullptr;

@@ -239,7 +239,7 @@ class DenseProgram:
                                                   self.step, self.positions], (self.lh + self.lg, B, 1))
             # 3-4. split attention over each sequence's cache, merged into this rank's head columns of att
             self.L.launch(K.ATTN_SPLIT, ap, [self.qkv, self.kc[il], self.vc[il], self.part, self.step, self.positions],
-                          (self.lg, blocks, B))
+                          (self.lg, blocks, B), self.variants.get("attn_split", 0))
             self.L.launch(K.ATTN_COMBINE, K.with_peer(ap, push=s_att), [self.qkv, self.part, att_cols, self.step, self.positions],
                           (self.lh, B, 1))
             self.launches_per_step += 3
