@@ -295,7 +295,7 @@ class DecodeStep:
     context = 8192
 
     def __init__(self, dist: Dist, batch: int = 1, variant: int = 0, layers: int = 32, replay: str = "auto",
-                 exchange: str = "peer"):
+                 exchange: str = "peer", attn_variant: int = 0):
         import torch
 
         from zllm_b200 import abi
@@ -332,6 +332,7 @@ class DecodeStep:
             arena = abi.PeerArena(self.ctx, dist.rank, dist.world, DenseProgram.arena_bytes(self.cfg, batch),
                                   DenseProgram.arena_slots(self.cfg), handles)
         self.prog = DenseProgram(self.ctx, self.cfg, self.weights, batch, alloc, self.shard, arena=arena,
+                                 variants={"attn_split": attn_variant},
                                  gather=nccl_gather(dist.dist, dist.rank, dist.world) if self.exchange == "nccl" else None)
         if arena is not None:
             class _View:  # the arena's logits as a torch tensor (zero copy), for the read-back of the e2e leg
@@ -773,6 +774,7 @@ def run_cuda(args):
     if args.workload == "decode":
         kw["replay"] = args.replay
         kw["exchange"] = args.exchange
+        kw["attn_variant"] = args.attn_variant
         if args.layers:
             kw["layers"] = args.layers
     wl = WORKLOADS[args.workload](dist, **kw)
@@ -925,6 +927,7 @@ def main():
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--variant", default="0", help="matvec variant word (see include/zllm_cuda.h)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
+    ap.add_argument("--attn-variant", type=int, default=0, help="decode: form of attn_split's fast path (0 default, 1-4: k_attn.cu)")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                     help="decode on N > 1 GPUs: slices pushed by the kernels over peer memory, or NCCL all-gathers")
     ap.add_argument("--replay", default="auto", choices=["auto", "program", "graph"],

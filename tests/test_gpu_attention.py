@@ -13,7 +13,7 @@ pytestmark = pytest.mark.gpu
 TOL = 1e-5
 
 
-def run_attention(gpu, launcher, q_rows, kc, vc, pos0, heads, kv_heads, hd, gated, kv_fmt, max_keys):
+def run_attention(gpu, launcher, q_rows, kc, vc, pos0, heads, kv_heads, hd, gated, kv_fmt, max_keys, variant=0):
     """q_rows: [m, q_row] f32 (heads interleaved with gates when gated). Returns out [m, heads, hd]."""
     m, q_row = q_rows.shape
     max_blocks = -(-max_keys // K.ATTN_BLOCK)
@@ -22,7 +22,7 @@ def run_attention(gpu, launcher, q_rows, kc, vc, pos0, heads, kv_heads, hd, gate
     out = gpu.zeros(m * heads * hd * 4)
     step = gpu.put(np.array([m, pos0, 0, 0], dtype=np.uint32))
     dq, dk, dv = gpu.put(q_rows), gpu.put(kc), gpu.put(vc)
-    launcher.attn_split(p, dq, dk, dv, part, step, pos0 + m, m)
+    launcher.attn_split(p, dq, dk, dv, part, step, pos0 + m, m, variant=variant)
     launcher.attn_combine(p, dq, part, out, step, m)
     return out.download(np.float32).reshape(m, heads, hd)
 
@@ -38,8 +38,14 @@ def test_attn_decode_f16_cache(ref, gpu, launcher, heads, kv_heads, hd, gated):
     vcf = uniform(rng, (keys_max, kv_heads, hd), 1.0).astype(np.float16)
     q_head = 2 * hd if gated else hd
     q_rows = uniform(rng, (m, heads * q_head), 1.0)
-    got = run_attention(gpu, launcher, q_rows, kcf.view(np.uint16), vcf.view(np.uint16), pos0, heads, kv_heads, hd,
-                        gated, K.KV_F16, 256)
+    fast = heads // kv_heads <= 4 and hd in (64, 128)
+    for variant in ((0, 1, 2, 3, 4) if fast else (0,)):  # every form of the fast path; the generic path otherwise
+        got = run_attention(gpu, launcher, q_rows, kcf.view(np.uint16), vcf.view(np.uint16), pos0, heads, kv_heads, hd,
+                            gated, K.KV_F16, 256, variant=variant)
+        _check_rows(ref, got, q_rows, kcf, vcf, pos0, m, heads, kv_heads, hd, gated, q_head)
+
+
+def _check_rows(ref, got, q_rows, kcf, vcf, pos0, m, heads, kv_heads, hd, gated, q_head):
     for t in range(m):
         qv = q_rows[t].reshape(heads, q_head)
         gate = qv[:, hd:] if gated else None
@@ -154,18 +160,20 @@ def test_both_forms_of_the_split_give_the_same_partials(gpu, launcher):
     dq, dk, dv = gpu.put(q), gpu.put(kc.view(np.uint16)), gpu.put(vc.view(np.uint16))
     step, dpos = gpu.put(np.array([rows, 0, 0, 0], dtype=np.uint32)), gpu.put(positions)
     got = []
-    for variant in (1, 2):
+    for variant in (1, 2, 3, 4):
         part = gpu.zeros(rows * heads * max_blocks * (hd + 2) * 4)
         out = gpu.zeros(rows * heads * hd * 4)
         launcher.launch(K.ATTN_SPLIT, p, [dq, dk, dv, part, step, dpos], (kv_heads, max_blocks, rows), variant)
         launcher.launch(K.ATTN_COMBINE, p, [dq, part, out, step, dpos], (heads, rows, 1))
         gpu.sync()
         got.append((part.download(np.uint32), out.download(np.uint32)))
-    assert np.array_equal(got[0][1], got[1][1])
+    assert np.array_equal(got[0][1], got[1][1])   # CUDA cores: per block == walk
+    assert np.array_equal(got[2][1], got[3][1])   # tensor cores: per block == walk
+    assert rel_err(got[2][1].view(np.float32), got[0][1].view(np.float32)) < TOL  # the two arithmetics agree
     assert np.abs(got[0][1].view(np.float32)).max() > 0
     # the partials of every block that holds keys (128 per block on this path); the one-CTA-per-block form also
     # writes the unused slots past a row's keys, the walk skips them
-    pa, pb = (g[0].reshape(rows, heads, max_blocks, hd + 2) for g in got)
+    pa, pb = (g[0].reshape(rows, heads, max_blocks, hd + 2) for g in got[:2])
     for t in range(rows):
         used = -(-(int(positions[t]) + 1) // 128)
         assert np.array_equal(pa[t, :, :used], pb[t, :, :used]), t

@@ -5,6 +5,7 @@
 #include <cfloat>
 #include <cuda_fp16.h>
 
+#include "tma_util.cuh"
 #include "vblock.cuh"
 #include "zcu_internal.h"
 
@@ -238,56 +239,28 @@ __device__ __forceinline__ uint32_t split_pair(float x0, float x1, bool low) {
     return (uint32_t)__half_as_ushort(h0) | ((uint32_t)__half_as_ushort(h1) << 16);
 }
 
-template <int HD>
-__device__ __forceinline__ void attn_split_mma_body(unsigned char* smem, const PAttention& p, const float* __restrict__ qg,
-                                                    const __half* __restrict__ kc, const __half* __restrict__ vc,
-                                                    float* __restrict__ part, const PStep* __restrict__ step,
-                                                    const uint32_t* __restrict__ seq_pos, int g_kv, int b, int t) {
-    constexpr int RS = HD * 2 + 16;              // bytes between the rows of a staged tile
-    constexpr int PIECES = AF_KEYS * (HD / 8) / AM_THREADS;
+// One block's arithmetic once its K and V tiles (rows RS bytes apart) and the group's queries (qs) are in shared
+// memory. Every thread of the 256 calls it; it ends with the partial written.
+// Where 16 bytes (8 dims starting at `dim`, a multiple of 8) of key/value row r sit in a staged tile.
+// SWZ = false: rows HD * 2 + 16 bytes apart (cp.async fills them). SWZ = true: the tile as TMA leaves it with the
+// 128-byte swizzle: one 128-row x 128-byte panel per 64 dims, 16-byte chunks XORed with the row's low three bits.
+template <int HD, bool SWZ>
+__device__ __forceinline__ uint32_t tile_addr(uint32_t tile, int r, int dim) {
+    if (!SWZ) return tile + (uint32_t)r * (HD * 2 + 16) + (uint32_t)dim * 2u;
+    const int panel = dim >> 6, chunk = (dim & 63) >> 3;
+    return tile + (uint32_t)panel * (AF_KEYS * 128) + (uint32_t)r * 128u + (uint32_t)((chunk ^ (r & 7)) << 4);
+}
+
+template <int HD, bool SWZ = false>
+__device__ __forceinline__ void mma_block_compute(uint32_t kt_s, uint32_t vt_s, float (*sc)[AF_KEYS], float* stat, const float* qs,
+                                                  const PAttention& p, float* __restrict__ part, int g_kv, int b, int t, int keys,
+                                                  int k0, bool wait_values) {
     constexpr int KSTEPS = HD / 16;              // k-steps of the score product
     constexpr int NBLK = HD / 64;                // 8-dim output blocks per warp in the value product
-    unsigned char* Kt = smem;
-    unsigned char* Vt = smem + (size_t)AF_KEYS * RS;
-    float (*sc)[AF_KEYS] = reinterpret_cast<float (*)[AF_KEYS]>(Vt + (size_t)AF_KEYS * RS);
-    float* stat = reinterpret_cast<float*>(sc) + 4 * AF_KEYS;
-    float* qs = stat + 8;                        // [4][HD]
-    const uint32_t kt_s = (uint32_t)__cvta_generic_to_shared(Kt), vt_s = (uint32_t)__cvta_generic_to_shared(Vt);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, tq = lane & 3;      // fragment coordinates
     const int group = (int)(p.heads / p.kv_heads);
-    const int row = (int)p.row0 + t;
-    const size_t seq_off = (size_t)row * p._pad[0];
-    const int keys = (seq_pos ? (int)seq_pos[row] : (int)step->pos0 + row) + 1;
-    const int k0 = b * AF_KEYS;
-    const size_t kv_stride = (size_t)p.kv_heads * HD;
-    const int q_head = p.gated ? 2 * HD : HD;
     const int n = min(AF_KEYS, keys - min(keys, k0));
-
-    // ---- tiles on their way
-#pragma unroll
-    for (int i = 0; i < PIECES; i++) {
-        const int j = tid + AM_THREADS * i, key = j / (HD / 8), piece = j % (HD / 8);
-        const size_t src = seq_off + (size_t)min(k0 + key, keys - 1) * kv_stride + (size_t)g_kv * HD + 8 * piece;
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(kt_s + (uint32_t)key * RS + 16u * piece), "l"(kc + src) : "memory");
-    }
-    asm volatile("cp.async.commit_group;\n" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < PIECES; i++) {
-        const int j = tid + AM_THREADS * i, key = j / (HD / 8), piece = j % (HD / 8);
-        const size_t src = seq_off + (size_t)min(k0 + key, keys - 1) * kv_stride + (size_t)g_kv * HD + 8 * piece;
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(vt_s + (uint32_t)key * RS + 16u * piece), "l"(vc + src) : "memory");
-    }
-    asm volatile("cp.async.commit_group;\n" ::: "memory");
-    // ---- the group's queries
-    for (int i = tid; i < 4 * HD / 4; i += AM_THREADS) {
-        const int h = i / (HD / 4), d4 = i % (HD / 4);
-        const float* qp = qg + (size_t)row * p.q_row + (size_t)(g_kv * group + min(h, group - 1)) * q_head;
-        reinterpret_cast<float4*>(qs)[i] = __ldcg(reinterpret_cast<const float4*>(qp) + d4);
-    }
-    asm volatile("cp.async.wait_group 1;\n" ::: "memory");
-    __syncthreads();
-
     // ---- scores: warp w takes keys 16 w .. 16 w + 15
     {
         const float* qrow = qs + (size_t)(g & 3) * HD;
@@ -302,10 +275,10 @@ __device__ __forceinline__ void attn_split_mma_body(unsigned char* smem, const P
             const uint32_t a0 = split_pair(qa.x, qa.y, low), a2 = split_pair(qb.x, qb.y, low);
 #pragma unroll
             for (int nb = 0; nb < 2; nb++) {
-                const uint32_t kaddr = kt_s + (uint32_t)(16 * warp + 8 * nb + g) * RS + (uint32_t)(16 * ks + 2 * tq) * 2u;
+                const int kr = 16 * warp + 8 * nb + g;
                 uint32_t b0, b1;
-                asm volatile("ld.shared.u32 %0, [%1];\n" : "=r"(b0) : "r"(kaddr));
-                asm volatile("ld.shared.u32 %0, [%1];\n" : "=r"(b1) : "r"(kaddr + 16u));
+                asm volatile("ld.shared.u32 %0, [%1];\n" : "=r"(b0) : "r"(tile_addr<HD, SWZ>(kt_s, kr, 16 * ks) + 4u * tq));
+                asm volatile("ld.shared.u32 %0, [%1];\n" : "=r"(b1) : "r"(tile_addr<HD, SWZ>(kt_s, kr, 16 * ks + 8) + 4u * tq));
                 mma_f16_16816(c[nb], a0, a2, b0, b1);
             }
         }
@@ -346,7 +319,7 @@ __device__ __forceinline__ void attn_split_mma_body(unsigned char* smem, const P
             stat[2 * warp + 1] = sum;
         }
     }
-    asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+    if (wait_values) asm volatile("cp.async.wait_group 0;\n" ::: "memory");
     __syncthreads();
     // ---- sum exp * v: warp w takes dims (HD / 8) w .. over all 128 keys
     {
@@ -364,7 +337,7 @@ __device__ __forceinline__ void attn_split_mma_body(unsigned char* smem, const P
 #pragma unroll
             for (int nb = 0; nb < NBLK; nb++) {
                 // two 8 x 8 matrices of V (keys 16 ks .. +7 and +8 .. +15, dims d0 + 8 nb .. +7), transposed on the way
-                const uint32_t vaddr = vt_s + (uint32_t)(16 * ks + (lane & 15)) * RS + (uint32_t)(d0 + 8 * nb) * 2u;
+                const uint32_t vaddr = tile_addr<HD, SWZ>(vt_s, 16 * ks + (lane & 15), d0 + 8 * nb);
                 uint32_t b0, b1;
                 asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];\n" : "=r"(b0), "=r"(b1) : "r"(vaddr));
                 mma_f16_16816(c[nb], a0, a2, b0, b1);
@@ -388,6 +361,55 @@ __device__ __forceinline__ void attn_split_mma_body(unsigned char* smem, const P
     }
 }
 
+template <int HD>
+__device__ __forceinline__ void attn_split_mma_body(unsigned char* smem, const PAttention& p, const float* __restrict__ qg,
+                                                    const __half* __restrict__ kc, const __half* __restrict__ vc,
+                                                    float* __restrict__ part, const PStep* __restrict__ step,
+                                                    const uint32_t* __restrict__ seq_pos, int g_kv, int b, int t) {
+    constexpr int RS = HD * 2 + 16;              // bytes between the rows of a staged tile
+    constexpr int PIECES = AF_KEYS * (HD / 8) / AM_THREADS;
+    unsigned char* Kt = smem;
+    unsigned char* Vt = smem + (size_t)AF_KEYS * RS;
+    float (*sc)[AF_KEYS] = reinterpret_cast<float (*)[AF_KEYS]>(Vt + (size_t)AF_KEYS * RS);
+    float* stat = reinterpret_cast<float*>(sc) + 4 * AF_KEYS;
+    float* qs = stat + 8;                        // [4][HD]
+    const uint32_t kt_s = (uint32_t)__cvta_generic_to_shared(Kt), vt_s = (uint32_t)__cvta_generic_to_shared(Vt);
+    const int tid = threadIdx.x;
+    const int group = (int)(p.heads / p.kv_heads);
+    const int row = (int)p.row0 + t;
+    const size_t seq_off = (size_t)row * p._pad[0];
+    const int keys = (seq_pos ? (int)seq_pos[row] : (int)step->pos0 + row) + 1;
+    const int k0 = b * AF_KEYS;
+    const size_t kv_stride = (size_t)p.kv_heads * HD;
+    const int q_head = p.gated ? 2 * HD : HD;
+
+    // ---- tiles on their way
+#pragma unroll
+    for (int i = 0; i < PIECES; i++) {
+        const int j = tid + AM_THREADS * i, key = j / (HD / 8), piece = j % (HD / 8);
+        const size_t src = seq_off + (size_t)min(k0 + key, keys - 1) * kv_stride + (size_t)g_kv * HD + 8 * piece;
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(kt_s + (uint32_t)key * RS + 16u * piece), "l"(kc + src) : "memory");
+    }
+    asm volatile("cp.async.commit_group;\n" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < PIECES; i++) {
+        const int j = tid + AM_THREADS * i, key = j / (HD / 8), piece = j % (HD / 8);
+        const size_t src = seq_off + (size_t)min(k0 + key, keys - 1) * kv_stride + (size_t)g_kv * HD + 8 * piece;
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(vt_s + (uint32_t)key * RS + 16u * piece), "l"(vc + src) : "memory");
+    }
+    asm volatile("cp.async.commit_group;\n" ::: "memory");
+    // ---- the group's queries
+    for (int i = tid; i < 4 * HD / 4; i += AM_THREADS) {
+        const int h = i / (HD / 4), d4 = i % (HD / 4);
+        const float* qp = qg + (size_t)row * p.q_row + (size_t)(g_kv * group + min(h, group - 1)) * q_head;
+        reinterpret_cast<float4*>(qs)[i] = __ldcg(reinterpret_cast<const float4*>(qp) + d4);
+    }
+    asm volatile("cp.async.wait_group 1;\n" ::: "memory");
+    __syncthreads();
+
+    mma_block_compute<HD>(kt_s, vt_s, sc, stat, qs, p, part, g_kv, b, t, keys, k0, true);
+}
+
 // ---- the same block arithmetic as a persistent kernel: one CTA per SM walks a contiguous range of the
 // (row, KV head, key block) space with its K and V tiles (128 keys x head_dim halves each) arriving through a
 // 3-stage cp.async pipeline, so the loads of the next two blocks are in flight while a block is computed. With
@@ -398,6 +420,102 @@ constexpr int AP_STAGES = 3;
 __host__ __device__ constexpr size_t attn_persist_smem(int group_cap, int group, int hd) {
     return (size_t)AP_STAGES * 2 * AF_KEYS * hd * 2 + ((size_t)group_cap * AF_KEYS + 2 * group_cap + 8) * sizeof(float) +
            (size_t)(AF_THREADS / 32) * group * hd * sizeof(float);
+}
+
+// The tensor-core block arithmetic as a persistent walk: one CTA per SM, the K/V tiles of the next two blocks in
+// flight. A tile is TMA box copies (one per 64 dims: 128 rows x 128 bytes, 128-byte swizzle) issued by one thread
+// and completing on the stage's mbarrier, so the arithmetic warps spend no instructions on loading. A block costs
+// about a microsecond of arithmetic, so the walk is bound by the tiles' arrival, i.e. by HBM. Waits are bounded.
+__host__ __device__ constexpr size_t attn_mma_persist_smem(int hd) {
+    return 1024 + (size_t)AP_STAGES * 2 * AF_KEYS * hd * 2 + (size_t)(4 * AF_KEYS + 8 + 4 * hd) * sizeof(float) + 64;
+}
+
+template <int HD>
+__device__ __forceinline__ void attn_split_mma_persistent_body(unsigned char* smem_raw, const PAttention& p, const float* __restrict__ qg,
+                                                               const CUtensorMap* kmap, const CUtensorMap* vmap,
+                                                               float* __restrict__ part, const PStep* __restrict__ step,
+                                                               const uint32_t* __restrict__ seq_pos, int by, int rows,
+                                                               int* __restrict__ status) {
+    constexpr int TILE = AF_KEYS * HD * 2;       // bytes of a K (or V) tile: HD / 64 panels of 128 rows x 128 bytes
+    constexpr int PANELS = HD / 64;
+    unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);  // swizzled tiles
+    float (*sc)[AF_KEYS] = reinterpret_cast<float (*)[AF_KEYS]>(smem + (size_t)AP_STAGES * 2 * TILE);
+    float* stat = reinterpret_cast<float*>(sc) + 4 * AF_KEYS;
+    float* qs = stat + 8;
+    const uint32_t stage0 = (uint32_t)__cvta_generic_to_shared(smem);
+    const uint32_t bar0 = (uint32_t)__cvta_generic_to_shared(qs + 4 * HD);
+    const int tid = threadIdx.x;
+    const int kvh = (int)p.kv_heads, group = (int)(p.heads / p.kv_heads);
+    const int q_head = p.gated ? 2 * HD : HD;
+    const int total = kvh * by * rows;
+    const int lo = (int)((long long)blockIdx.x * total / gridDim.x), hi = (int)((long long)(blockIdx.x + 1) * total / gridDim.x);
+    if (tid == 0) {
+        for (int s = 0; s < AP_STAGES; s++) asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar0 + 8 * s), "r"(1) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    __syncthreads();
+    auto keys_of = [&](int t) {
+        const int row = (int)p.row0 + t;
+        return (seq_pos ? (int)seq_pos[row] : (int)step->pos0 + row) + 1;
+    };
+    // thread 0 asks for block idx's tiles into `stage` (nothing for a block past its row's keys or this CTA's range)
+    auto issue = [&](int idx, int stage) {
+        if (tid != 0 || idx >= hi) return;
+        const int b = idx % by, g = (idx / by) % kvh, t = idx / (by * kvh);
+        if (b * AF_KEYS >= keys_of(t)) return;
+        const uint32_t bar = bar0 + 8 * stage, kt = stage0 + (uint32_t)stage * 2 * TILE;
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // the stage was read with ordinary loads
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(2 * TILE) : "memory");
+#pragma unroll
+        for (int pn = 0; pn < PANELS; pn++) {
+            const int x = g * HD * 2 + 128 * pn, y = b * AF_KEYS, z = p._pad[0] ? (int)p.row0 + t : 0;  // one cache unless rows are sequences
+            asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];\n" ::"r"(kt + pn * (AF_KEYS * 128)),
+                         "l"((uint64_t)kmap), "r"(bar), "r"(x), "r"(y), "r"(z)
+                         : "memory");
+            asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];\n" ::"r"(kt + TILE + pn * (AF_KEYS * 128)),
+                         "l"((uint64_t)vmap), "r"(bar), "r"(x), "r"(y), "r"(z)
+                         : "memory");
+        }
+    };
+#pragma unroll
+    for (int s = 0; s < AP_STAGES - 1; s++) issue(lo + s, s);
+    int q_g = -1, q_t = -1, stage = 0;
+    uint32_t phase_bits = 0;
+    bool timed_out = false;
+    for (int idx = lo; idx < hi; idx++) {
+        issue(idx + AP_STAGES - 1, stage == 0 ? AP_STAGES - 1 : stage - 1);
+        const int b = idx % by, g = (idx / by) % kvh, t = idx / (by * kvh);
+        const int keys = keys_of(t), k0 = b * AF_KEYS;
+        const uint32_t kt = stage0 + (uint32_t)stage * 2 * TILE, bar = bar0 + 8 * stage;
+        const int this_stage = stage;
+        stage = stage + 1 == AP_STAGES ? 0 : stage + 1;
+        if (k0 >= keys) continue;  // nothing was asked for: the stage's barrier is untouched
+        if (g != q_g || t != q_t) {  // consecutive blocks of a CTA mostly share their queries
+            q_g = g, q_t = t;
+            const int row = (int)p.row0 + t;
+            for (int i = tid; i < 4 * HD / 4; i += AM_THREADS) {
+                const int h = i / (HD / 4), d4 = i % (HD / 4);
+                const float* qp = qg + (size_t)row * p.q_row + (size_t)(g * group + min(h, group - 1)) * q_head;
+                reinterpret_cast<float4*>(qs)[i] = __ldcg(reinterpret_cast<const float4*>(qp) + d4);
+            }
+        }
+        {   // the tiles of this block (at most 2^20 polls)
+            bool ok = false;
+            const uint32_t parity = (phase_bits >> this_stage) & 1u;
+            for (int spin = 0; spin < (1 << 20) && !ok; spin++) {
+                uint32_t done;
+                asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+                             : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+                ok = done != 0;
+            }
+            if (!ok) timed_out = true;
+            phase_bits ^= 1u << this_stage;
+        }
+        __syncthreads();  // the queries are in place
+        mma_block_compute<HD, true>(kt, kt + TILE, sc, stat, qs, p, part, g, b, t, keys, k0, false);
+        __syncthreads();  // every warp is done with this block's tiles, probabilities and queries
+    }
+    if (timed_out && (tid & 31) == 0 && status) atomicExch(status, 1);
 }
 
 template <int HD, int GROUP_CAP>

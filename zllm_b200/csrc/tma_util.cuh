@@ -34,4 +34,16 @@ inline bool bytes_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t
                CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// [seqs][rows][row_bytes] bytes: boxes of 128 bytes x box_rows rows of one sequence, 128-byte swizzle (16-byte chunks
+// of a box row XORed with the row's low three bits). Rows and sequences outside the tensor read as zero.
+inline bool bytes_3d_swizzled(CUtensorMap* map, const void* base, uint64_t seqs, uint64_t rows, uint64_t row_bytes, uint64_t seq_bytes,
+                              uint32_t box_rows) {
+    EncodeTiledFn enc = encode_tiled();
+    if (!enc) return false;
+    const cuuint64_t dims[3] = {row_bytes, rows, seqs}, strides[2] = {row_bytes, seq_bytes};
+    const cuuint32_t box[3] = {128, box_rows, 1}, elem[3] = {1, 1, 1};
+    return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 }  // namespace tma

@@ -187,10 +187,10 @@ class Launcher:
     def rope_append(self, p: "RopeAppend", qkv, q_norm, k_norm, rope, kc, vc, step, m):
         self.launch(ROPE_APPEND, p, [qkv, q_norm, k_norm, rope, kc, vc, step], (p.heads + p.kv_heads, m, 1))
 
-    def attn_split(self, p: "Attention", qg, kc, vc, part, step, keys, rows):
+    def attn_split(self, p: "Attention", qg, kc, vc, part, step, keys, rows, variant=0):
         group = p.heads // p.kv_heads
         kern = ATTN_SPLIT if group <= ATTN_MAX_GROUP else ATTN_SPLIT_WIDE
-        self.launch(kern, p, [qg, kc, vc, part, step], (p.kv_heads, -(-keys // ATTN_BLOCK), rows))
+        self.launch(kern, p, [qg, kc, vc, part, step], (p.kv_heads, -(-keys // ATTN_BLOCK), rows), variant)
 
     def attn_combine(self, p: "Attention", qg, part, out, step, rows):
         self.launch(ATTN_COMBINE, p, [qg, part, out, step], (p.heads, rows, 1))
