@@ -332,7 +332,7 @@ class DecodeStep:
             arena = abi.PeerArena(self.ctx, dist.rank, dist.world, DenseProgram.arena_bytes(self.cfg, batch),
                                   DenseProgram.arena_slots(self.cfg), handles)
         self.prog = DenseProgram(self.ctx, self.cfg, self.weights, batch, alloc, self.shard, arena=arena,
-                                 variants={"attn_split": attn_variant},
+                                 variants={"attn_split": attn_variant} if attn_variant else None,
                                  gather=nccl_gather(dist.dist, dist.rank, dist.world) if self.exchange == "nccl" else None)
         if arena is not None:
             class _View:  # the arena's logits as a torch tensor (zero copy), for the read-back of the e2e leg

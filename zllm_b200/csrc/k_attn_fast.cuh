@@ -422,6 +422,115 @@ __host__ __device__ constexpr size_t attn_persist_smem(int group_cap, int group,
            (size_t)(AF_THREADS / 32) * group * hd * sizeof(float);
 }
 
+// The merge of a KV head's partials by the CTA that finished last (attn_combine's arithmetic in attn_combine's order:
+// the same bits), so a decode step needs no combine launch. 256 threads: two warps per head of the group; the
+// block weights go through `wsm` ([4][128] floats), the halves' sums through `hsm` ([4][HD] float + [4] l).
+// Needs at most 128 blocks.
+template <int HD>
+__device__ __forceinline__ void combine_group_tail(const PAttention& p, const float* __restrict__ qg, const float* __restrict__ part,
+                                                   float* __restrict__ out, float (*wsm)[AF_KEYS], float* hsm, int g_kv, int t,
+                                                   int blocks, const PeerUse* __restrict__ pu) {
+    constexpr int DPL = HD / 32;  // dims per lane
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int group = (int)(p.heads / p.kv_heads);
+    const int hh = warp >> 1, sub = warp & 1;  // head of the group, half of the blocks
+    const int h = g_kv * group + min(hh, group - 1);
+    const int row = (int)p.row0 + t;
+    const size_t bs = (size_t)HD + 2, base0 = ((size_t)t * p.heads + h) * p.max_blocks * bs;
+    // the largest block maximum, then the block weights
+    float mb[4], mx = -FLT_MAX;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const int b = lane + 32 * i;
+        mb[i] = b < blocks ? __ldcg(part + base0 + b * bs) : -FLT_MAX;
+        mx = fmaxf(mx, mb[i]);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    if (sub == 0) {
+#pragma unroll
+        for (int i = 0; i < 4; i++)
+            if (lane + 32 * i < blocks) wsm[hh][lane + 32 * i] = expf(mb[i] - mx);
+    }
+    __syncthreads();
+    // each half of the blocks in block order (attn_combine's two halves), then low + high
+    const int per = (blocks + 1) / 2, b0 = sub * per, b1 = min(blocks, b0 + per);
+    float l = 0.f, o[DPL];
+#pragma unroll
+    for (int d = 0; d < DPL; d++) o[d] = 0.f;
+#pragma unroll 4
+    for (int b = b0; b < b1; b++) {
+        const float w = wsm[hh][b];
+        const float* pb = part + base0 + b * bs;
+        l = __fmaf_rn(__ldcg(pb + 1), w, l);
+#pragma unroll
+        for (int d = 0; d < DPL; d += 2) {
+            const float2 v = __ldcg(reinterpret_cast<const float2*>(pb + 2 + DPL * lane + d));
+            o[d] = __fmaf_rn(v.x, w, o[d]);
+            o[d + 1] = __fmaf_rn(v.y, w, o[d + 1]);
+        }
+    }
+    if (sub == 1) {
+#pragma unroll
+        for (int d = 0; d < DPL; d++) hsm[hh * HD + DPL * lane + d] = o[d];
+        if (lane == 0) hsm[4 * HD + hh] = l;
+    }
+    __syncthreads();
+    if (sub == 1 || hh >= group) return;
+    l = __fadd_rn(l, hsm[4 * HD + hh]);
+    const size_t orow = p._pad[1] ? (size_t)p._pad[1] : (size_t)p.heads * HD;
+    const bool pushing = pu != nullptr && pu->push_slot != PEER_NONE;
+    const uint32_t tag = pushing ? peer::push_tag(*pu) : 0u;
+#pragma unroll
+    for (int d = 0; d < DPL; d++) {
+        const int dim = DPL * lane + d;
+        const float ov = __fadd_rn(o[d], hsm[hh * HD + dim]);
+        float res = ov / l;
+        if (p.gated) {
+            const float gate = __ldcg(qg + (size_t)row * p.q_row + (size_t)2 * h * HD + HD + dim);
+            res = ov / l / (1.0f + expf(-gate));
+        }
+        const size_t oi = (size_t)row * orow + (size_t)h * HD + dim;
+        out[oi] = res;
+        if (pushing) peer::push(*pu, out + oi, res, tag);
+    }
+}
+
+// attn_split_mma_body followed by the merge when this CTA is the last of its (row, KV head) to finish.
+// tickets[row * kv_heads + g]: blocks of that pair that have finished (zero before the first use; the last block
+// puts the zero back).
+template <int HD>
+__device__ __forceinline__ void attn_split_mma_fused_body(unsigned char* smem, const PAttention& p, const float* __restrict__ qg,
+                                                          const __half* __restrict__ kc, const __half* __restrict__ vc,
+                                                          float* __restrict__ part, const PStep* __restrict__ step,
+                                                          const uint32_t* __restrict__ seq_pos, float* __restrict__ out,
+                                                          uint32_t* __restrict__ tickets, int g_kv, int b, int t,
+                                                          const PeerUse* __restrict__ pu) {
+    __shared__ int is_last;
+    const int row = (int)p.row0 + t;
+    const int keys = (seq_pos ? (int)seq_pos[row] : (int)step->pos0 + row) + 1;
+    if (b * AF_KEYS >= keys) return;  // no keys here: neither a partial nor a ticket
+    const int blocks = (keys + AF_KEYS - 1) / AF_KEYS;
+    attn_split_mma_body<HD>(smem, p, qg, kc, vc, part, step, seq_pos, g_kv, b, t);
+    __threadfence();  // this thread's part of the partial before the ticket
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        uint32_t* tk = tickets + (size_t)t * p.kv_heads + g_kv;
+        const bool last = atomicAdd(tk, 1u) == (uint32_t)blocks - 1;
+        if (last) {
+            *tk = 0;
+            __threadfence();  // the others' partials (published before their tickets) before this CTA reads them
+        }
+        is_last = last;
+    }
+    __syncthreads();
+    if (!is_last) return;
+    constexpr int RS = HD * 2 + 16;
+    float (*wsm)[AF_KEYS] = reinterpret_cast<float (*)[AF_KEYS]>(smem + (size_t)2 * AF_KEYS * RS);  // the block's score scratch
+    float* hsm = reinterpret_cast<float*>(smem);                                                 // the K tile's place
+    combine_group_tail<HD>(p, qg, part, out, wsm, hsm, g_kv, t, blocks, pu);
+}
+
 // The tensor-core block arithmetic as a persistent walk: one CTA per SM, the K/V tiles of the next two blocks in
 // flight. A tile is TMA box copies (one per 64 dims: 128 rows x 128 bytes, 128-byte swizzle) issued by one thread
 // and completing on the stage's mbarrier, so the arithmetic warps spend no instructions on loading. A block costs
