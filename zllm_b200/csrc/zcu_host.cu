@@ -234,6 +234,10 @@ zcu_result dispatch_kernel(zcu_context* c, uint32_t kernel, uint32_t variant, co
         case ZCU_K_DELTA_PREP: return launch_delta_prep(a);
         case ZCU_K_DELTA_RULE: return launch_delta_rule(a);
         case ZCU_K_EXT_PEER_WAIT: return launch_peer_wait(a);
+        case ZCU_K_QUANTIZE_Q8: return launch_quantize_q8(a);
+        case ZCU_K_MATMUL_Q4_K: return launch_matmul_q4_k(a);
+        case ZCU_K_MATMUL_Q8_0: return launch_matmul_q8_0(a);
+        case ZCU_K_MATMUL_REDUCE: return launch_matmul_reduce(a);
         case ZCU_K_GATED_NORM: return launch_gated_norm(a);
         case ZCU_K_REPACK_Q8_0: return launch_repack_q8_0(a);
         case ZCU_K_MATVEC_Q8_0: return launch_matvec_q8_0(a);
@@ -618,6 +622,10 @@ const char* kernel_name(uint32_t k) {
         case ZCU_K_RMSNORM: return "rmsnorm";
         case ZCU_K_MATMUL_BF16: return "matmul_bf16";
         case ZCU_K_MATMUL_F16: return "matmul_f16";
+        case ZCU_K_MATMUL_REDUCE: return "matmul_reduce";
+        case ZCU_K_QUANTIZE_Q8: return "quantize_q8";
+        case ZCU_K_MATMUL_Q8_0: return "matmul_q8_0";
+        case ZCU_K_MATMUL_Q4_K: return "matmul_q4_k";
         case ZCU_K_MATVEC_BF16: return "matvec_bf16";
         case ZCU_K_MATVEC_F16: return "matvec_f16";
         case ZCU_K_SILU_MUL: return "silu_mul";

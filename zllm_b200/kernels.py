@@ -75,6 +75,11 @@ Embed = _struct("EmbedBf16", [("dim", u32), ("row0", u32), ("chunk_rows", u32), 
 RopeAppend = _struct("RopeAppend", [("heads", u32), ("kv_heads", u32), ("head_dim", u32), ("n_rot", u32), ("row", u32),
                                     ("k_off", u32), ("v_off", u32), ("kv", u32), ("eps", f32), ("gated", u32),
                                     ("qk_norm", u32), ("normal", u32), ("scales", u32), ("_pad", u32 * 3)])
+QuantizeQ8 = _struct("QuantizeQ8", [("k", u32), ("block", u32), ("mode", u32), ("eps", f32)])
+MatmulQuant = _struct("MatmulQuant", [("rows", u32), ("n", u32), ("k", u32), ("col0", u32), ("out_stride", u32),
+                                      ("accumulate", u32), ("k_slice", u32), ("slice_stride", u32)])
+MatmulReduce = _struct("MatmulReduce", [("rows", u32), ("n", u32), ("slices", u32), ("col0", u32), ("out_stride", u32),
+                                        ("accumulate", u32), ("slice_stride", u32), ("_pad", u32)])
 MatvecRope = _struct("MatvecRope", [("mv", Matvec), ("rope", RopeAppend)])
 Attention = _struct("Attention", [("heads", u32), ("kv_heads", u32), ("head_dim", u32), ("kv", u32), ("scale", f32),
                                   ("max_blocks", u32), ("q_row", u32), ("row0", u32), ("gated", u32), ("scales", u32),
@@ -175,6 +180,23 @@ class Launcher:
         p = MatmulBf16(rows, n, k, col0, out_stride if out_stride is not None else n, int(accumulate))
         p._pad[0] = layout
         self.launch(MATMUL_BF16 if ttype == "bf16" else MATMUL_F16, p, [x, w, out], (-(-n // 64), -(-rows // 16), 1), variant)
+
+    # -- the quantised prefill family (src/plan/common.zig:389-477)
+    def quantize_q8(self, x, qx, dx, rows, k, block, mode=0, eps=0.0, nw=None):
+        """Rounds rows of activations to 8-bit blocks (block 256: Q8_K for the K-quants; 32: Q8_0). mode 1 rounds
+        RMSNorm(x) * nw, mode 2 silu(gate) * up of rows gate | up."""
+        self.launch(QUANTIZE_Q8, QuantizeQ8(k, block, mode, eps), [x, qx, dx, nw if nw is not None else x], (k // 256, rows, 1))
+
+    def matmul_quant(self, ttype, qx, w, out, dx, rows, n, k, col0=0, out_stride=None, accumulate=False, k_slice=None,
+                     slice_stride=0):
+        k_slice = k if k_slice is None else k_slice
+        p = MatmulQuant(rows, n, k, col0, out_stride if out_stride is not None else n, int(accumulate), k_slice, slice_stride)
+        self.launch(MATMUL_Q4_K if ttype == "q4_k" else MATMUL_Q8_0, p, [qx, w, out, dx],
+                    (-(-n // 128), -(-rows // 32), -(-k // k_slice)))
+
+    def matmul_reduce(self, partials, out, rows, n, slices, slice_stride, col0=0, out_stride=None, accumulate=False):
+        p = MatmulReduce(rows, n, slices, col0, out_stride if out_stride is not None else n, int(accumulate), slice_stride, 0)
+        self.launch(MATMUL_REDUCE, p, [partials, out], elementwise(rows * n))
 
     def rmsnorm(self, x, w, y, rows, dim, eps, w_rows=0):
         self.launch(RMSNORM, RmsNorm(rows, dim, eps, w_rows), [x, w, y], (rows, 1, 1))
