@@ -79,6 +79,7 @@ enum {
     ZCU_K_MATVEC_Q8_0 = 40,
     ZCU_K_MATVEC_Q4_K = 42,
     ZCU_K_MATMUL_Q8_0 = 45,
+    ZCU_K_MATMUL_Q8_0_FLOAT = 46,
     ZCU_K_MATMUL_Q4_K = 48,
     ZCU_K_EMBED_Q8_0 = 51,
     ZCU_K_EMBED_Q4_K = 53,

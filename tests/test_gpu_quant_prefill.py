@@ -115,3 +115,27 @@ def test_matmul_q4_k_prefill_shape(ref, gpu, launcher):
     out = gpu.zeros(rows * n * 4)
     launcher.matmul_quant("q4_k", qx, gpu.put(raw), out, dx, rows, n, k)
     assert rel_err(out.download(np.float32).reshape(rows, n), want) < TOL
+
+
+def test_matmul_q8_0_float_keeps_the_activations(ref, gpu, launcher):
+    # Q8_0 weights against unrounded f32 activations: the oracle's exact matmul, every output summed in k order (so
+    # a 3-token step equals the first rows of the 33-token step bit for bit), whole and split over k.
+    rng = synth.rng_for("quant-prefill", "q8f")
+    rows, n, k = 33, 150, 1024
+    raw = synth.q8_0_weights(rng, n, k)
+    dw = gpu.put(M.split_q8_0_rows(raw, k))
+    x = uniform(rng, (rows, k), 1.0)
+    want = ref.matmul(x, ref.Matrix(ref.Q8_0, raw, n, k))
+    dxv = gpu.put(x)
+    out = gpu.zeros(rows * n * 4)
+    launcher.matmul_q8_0_float(dxv, dw, out, rows, n, k)
+    got = out.download(np.float32).reshape(rows, n)
+    assert rel_err(got, want) < TOL
+    o3 = gpu.zeros(3 * n * 4)
+    launcher.matmul_q8_0_float(gpu.put(x[:3]), dw, o3, 3, n, k)
+    assert np.array_equal(o3.download(np.uint32).reshape(3, n), got[:3].view(np.uint32))
+    partials = gpu.zeros(2 * rows * n * 4)
+    launcher.matmul_q8_0_float(dxv, dw, partials, rows, n, k, k_slice=512, slice_stride=rows * n)
+    out2 = gpu.put(np.ones((rows, n), dtype=np.float32))
+    launcher.matmul_reduce(partials, out2, rows, n, 2, rows * n, accumulate=True)
+    assert rel_err(out2.download(np.float32).reshape(rows, n), 1.0 + want) < TOL

@@ -238,6 +238,7 @@ zcu_result dispatch_kernel(zcu_context* c, uint32_t kernel, uint32_t variant, co
         case ZCU_K_MATMUL_Q4_K: return launch_matmul_q4_k(a);
         case ZCU_K_MATMUL_Q8_0: return launch_matmul_q8_0(a);
         case ZCU_K_MATMUL_REDUCE: return launch_matmul_reduce(a);
+        case ZCU_K_MATMUL_Q8_0_FLOAT: return launch_matmul_q8_0_float(a);
         case ZCU_K_GATED_NORM: return launch_gated_norm(a);
         case ZCU_K_REPACK_Q8_0: return launch_repack_q8_0(a);
         case ZCU_K_MATVEC_Q8_0: return launch_matvec_q8_0(a);
@@ -626,6 +627,7 @@ const char* kernel_name(uint32_t k) {
         case ZCU_K_QUANTIZE_Q8: return "quantize_q8";
         case ZCU_K_MATMUL_Q8_0: return "matmul_q8_0";
         case ZCU_K_MATMUL_Q4_K: return "matmul_q4_k";
+        case ZCU_K_MATMUL_Q8_0_FLOAT: return "matmul_q8_0_float";
         case ZCU_K_MATVEC_BF16: return "matvec_bf16";
         case ZCU_K_MATVEC_F16: return "matvec_f16";
         case ZCU_K_SILU_MUL: return "silu_mul";

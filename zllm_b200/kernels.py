@@ -18,6 +18,7 @@ EMBED_BF16, EMBED_F16, ROPE_APPEND, ATTN_SPLIT, ATTN_SPLIT_WIDE, ATTN_SPLIT_SPAR
 DELTA_PREP, DELTA_RULE, GATED_NORM = 18, 19, 20
 REPACK_Q8_0, QUANTIZE_Q8, MATVEC_Q8_0, MATVEC_Q4_K = 38, 39, 40, 42
 MATMUL_Q8_0, MATMUL_Q4_K, EMBED_Q8_0, EMBED_Q4_K = 45, 48, 51, 53
+MATMUL_Q8_0_FLOAT = 46
 KERNEL_COUNT = 57
 
 # MatvecBf16.Flags (kernels.zig:485-493)
@@ -193,6 +194,12 @@ class Launcher:
         p = MatmulQuant(rows, n, k, col0, out_stride if out_stride is not None else n, int(accumulate), k_slice, slice_stride)
         self.launch(MATMUL_Q4_K if ttype == "q4_k" else MATMUL_Q8_0, p, [qx, w, out, dx],
                     (-(-n // 128), -(-rows // 32), -(-k // k_slice)))
+
+    def matmul_q8_0_float(self, x, w, out, rows, n, k, col0=0, out_stride=None, accumulate=False, k_slice=None, slice_stride=0):
+        """Q8_0 weights against f32 activations as they are (no rounding): exact f32, k-ordered."""
+        k_slice = k if k_slice is None else k_slice
+        p = MatmulQuant(rows, n, k, col0, out_stride if out_stride is not None else n, int(accumulate), k_slice, slice_stride)
+        self.launch(MATMUL_Q8_0_FLOAT, p, [x, w, out], (-(-n // 64), -(-rows // 16), -(-k // k_slice)))
 
     def matmul_reduce(self, partials, out, rows, n, slices, slice_stride, col0=0, out_stride=None, accumulate=False):
         p = MatmulReduce(rows, n, slices, col0, out_stride if out_stride is not None else n, int(accumulate), slice_stride, 0)
