@@ -295,7 +295,7 @@ class DecodeStep:
     context = 8192
 
     def __init__(self, dist: Dist, batch: int = 1, variant: int = 0, layers: int = 32, replay: str = "auto",
-                 exchange: str = "peer", attn_variant: int = 0):
+                 exchange: str = "peer", attn_variant: int = 0, batched: str = "auto"):
         import torch
 
         from zllm_b200 import abi
@@ -333,6 +333,7 @@ class DecodeStep:
                                   DenseProgram.arena_slots(self.cfg), handles)
         self.prog = DenseProgram(self.ctx, self.cfg, self.weights, batch, alloc, self.shard, arena=arena,
                                  variants={"attn_split": attn_variant} if attn_variant else None,
+                                 batched=None if batched == "auto" else batched == "on",
                                  gather=nccl_gather(dist.dist, dist.rank, dist.world) if self.exchange == "nccl" else None)
         if arena is not None:
             class _View:  # the arena's logits as a torch tensor (zero copy), for the read-back of the e2e leg
@@ -760,7 +761,124 @@ class DeltaPrefill:
                           "(C++ restatement of the reference's src/ref recurHead, one head per task)"}
 
 
-WORKLOADS = {"matvec_q4_k": MatvecQ4K, "decode": DecodeStep, "prefill_matmul": PrefillMatmul, "deltanet_prefill": DeltaPrefill}
+class QuantPrefill:
+    """The quantised prefill multiply (the reference's prefill path for K-quant models: quantize_q8 + matmul_q4_k):
+    2048 tokens x the Llama-3-8B FFN-up matrix (14336 x 4096, Q4_K); activations f32 ~ N(0,1) rounded to Q8_K blocks
+    inside the timed step. With N ranks the weight rows are sharded (no collective in the step)."""
+
+    rows, n, k = 2048, 14336, 4096
+    name = "prefill_q4_k"
+    dtype = "u4 x s8 integer products (exact), f32 sums and scales"
+
+    def __init__(self, dist: Dist, batch: int = 1, variant: int = 0, **_):
+        import torch
+
+        from zllm_b200 import abi, synth
+        from zllm_b200 import kernels as K
+
+        self.torch, self.K, self.dist = torch, K, dist
+        self.dev = torch.device("cuda", dist.local)
+        torch.cuda.set_device(self.dev)
+        self.stream = torch.cuda.Stream(self.dev)
+        self.ctx = abi.Context(dist.local, stream=self.stream.cuda_stream)
+        self.launcher = K.Launcher(self.ctx)
+        # --variant 0: the tcgen05 rung (0xfffc0000); --variant 1: the integer-dot identity on mma.sync
+        self.rung = 0 if variant == 1 else K.VARIANT_PREFILL_TC
+        self.copies = 4                                  # 4 distinct matrices: 132 MB of weights + 235 MB of outputs per step
+        self.ln = self.n // dist.world
+        rb = K.row_bytes("q4_k", self.k)
+        one = torch.from_numpy(synth.q4_k_weights(synth.rng_for("cfg2", f"w-rank{dist.rank}"), self.ln, self.k).reshape(-1)).to(self.dev)
+        self.w = torch.stack([torch.roll(one.view(self.ln, rb), shifts=c, dims=0).reshape(-1) for c in range(self.copies)])
+        self.pinned_x = torch.randn((self.rows, self.k), generator=torch.Generator().manual_seed(11)).pin_memory()
+        self.x = self.pinned_x.to(self.dev)
+        self.qx = torch.zeros((self.rows, self.k), dtype=torch.int8, device=self.dev)
+        self.dx = torch.zeros((self.rows, self.k // 256), dtype=torch.float32, device=self.dev)
+        self.out = torch.zeros((self.copies, self.rows, self.ln), dtype=torch.float32, device=self.dev)
+        self.pinned_out = torch.empty((self.rows, self.ln), dtype=torch.float32).pin_memory()
+        self.graph = None
+        torch.cuda.synchronize()
+
+    def _buf(self, t):
+        return (t.data_ptr(), t.numel() * t.element_size())
+
+    def flops_per_launch(self) -> float:
+        return 2.0 * self.rows * self.ln * self.k
+
+    def launches_per_step(self) -> int:
+        return 1 + self.copies * (3 if self.rung else 1)  # the rung: columns, scale-table clear, multiply
+
+    def _launch_all(self):
+        self.launcher.quantize_q8(self._buf(self.x), self._buf(self.qx), self._buf(self.dx), self.rows, self.k, 256)
+        for c in range(self.copies):
+            self.launcher.matmul_quant("q4_k", self._buf(self.qx), self._buf(self.w[c]), self._buf(self.out[c]), self._buf(self.dx),
+                                       self.rows, self.ln, self.k, variant=self.rung)
+
+    def step(self):
+        if self.graph is None:
+            self.ctx.capture_begin()
+            self._launch_all()
+            self.graph = self.ctx.capture_end()
+        self.ctx.graph_launch(self.graph)
+
+    def e2e_step(self):
+        torch = self.torch
+        with torch.cuda.stream(self.stream):
+            self.x.copy_(self.pinned_x, non_blocking=True)
+        self.step()
+        with torch.cuda.stream(self.stream):
+            self.pinned_out.copy_(self.out[self.copies - 1], non_blocking=True)
+        self.stream.synchronize()
+
+    def e2e_bytes(self):
+        return self.pinned_x.numel() * 4, self.pinned_out.numel() * 4
+
+    def roofline(self, ms_per_step: float):
+        peak, kind = measured_tensor_peak()
+        us = ms_per_step * 1e3 / self.copies  # the one quantize_q8 of a step is counted into its multiplies
+        achieved = self.flops_per_launch() / us / 1e6
+        kernel = ("qgemm_q4k_kernel<128> (tcgen05 kind::f16 on f16 integers, accumulators in tensor memory)" if self.rung
+                  else "matmul_quant_kernel<Q4_K> (mma.sync s8, unit scales on the CUDA cores)")
+        return {"bound": "tensor", "kernel": kernel, "achieved": achieved,
+                "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                "peak_kind": f"of {kind} (the dense bf16 cuBLAS figure)", "traffic": None,
+                "flops_per_launch": self.flops_per_launch(), "us_per_launch": us}
+
+    def metric(self):
+        return "prefill_q4_k_matmul_tflops", "TFLOP/s"
+
+    def value(self, seconds_per_step: float) -> float:
+        return self.flops_per_launch() * self.copies * self.dist.world / seconds_per_step / 1e12
+
+    def config(self):
+        return {"workload": f"Q4_K prefill matmul, {self.rows} tokens x {self.n} x {self.k}, Q8_K-rounded activations (quantize_q8 in the step)",
+                "rung": "tcgen05 (variant 0xfffc0000)" if self.rung else "integer dot on mma.sync (variant 0)",
+                "matrices_per_step": self.copies,
+                "l2": f"inputs larger than L2: {self.copies} weight matrices and outputs, {self.copies * (self.ln * self.k * 9 // 16 + self.rows * self.ln * 4) / 1e6:.0f} MB per step per rank",
+                "parallelism": f"tp{self.dist.world} (weight rows sharded, no collective in the step)" if self.dist.on else "1 GPU"}
+
+    def cpu_baseline(self, budget_s: float = 12.0):
+        from oracle import ref
+        from zllm_b200 import synth
+
+        ref.build()
+        pool = ref.Pool()
+        rng = synth.rng_for("cfg2", "cpu-prefill")
+        rows, n = 32, 2048                                  # a bounded sample: 32 tokens x 2048 of the 14336 rows
+        mat = ref.Matrix(ref.Q4_K, synth.q4_k_weights(rng, n, self.k), n, self.k, pool)
+        x = synth.normal_f32(rng, rows, self.k)
+        ref.matmul(x, mat, act=True, pool=pool)
+        t0, reps = time.perf_counter(), 0
+        while time.perf_counter() - t0 < budget_s and reps < 200:
+            ref.matmul(x, mat, act=True, pool=pool)
+            reps += 1
+        dt = (time.perf_counter() - t0) / reps
+        return {"value": 2.0 * rows * n * self.k / dt / 1e12, "unit": "TFLOP/s", "cores": pool.threads, "kind": "port", "isa": ref.build_info(),
+                "sample": f"{reps} multiplies of {rows} tokens x {n} x {self.k} (roundLikeLlama + panel matmul), {dt * 1e3:.1f} ms each "
+                          "(C++ restatement of the reference's src/ref)"}
+
+
+WORKLOADS = {"matvec_q4_k": MatvecQ4K, "decode": DecodeStep, "prefill_matmul": PrefillMatmul, "deltanet_prefill": DeltaPrefill,
+             "prefill_q4_k": QuantPrefill}
 
 
 
@@ -775,6 +893,7 @@ def run_cuda(args):
         kw["replay"] = args.replay
         kw["exchange"] = args.exchange
         kw["attn_variant"] = args.attn_variant
+        kw["batched"] = args.batched
         if args.layers:
             kw["layers"] = args.layers
     wl = WORKLOADS[args.workload](dist, **kw)
@@ -927,6 +1046,8 @@ def main():
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--variant", default="0", help="matvec variant word (see include/zllm_cuda.h)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
+    ap.add_argument("--batched", default="auto", choices=["auto", "on", "off"],
+                    help="decode: Q4_K multiplies in one pass for all sequences (tcgen05 family; auto = for 5..64 sequences on one GPU)")
     ap.add_argument("--attn-variant", type=int, default=0, help="decode: form of attn_split's fast path (0 default, 1-4: k_attn.cu)")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                     help="decode on N > 1 GPUs: slices pushed by the kernels over peer memory, or NCCL all-gathers")

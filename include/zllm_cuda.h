@@ -93,11 +93,14 @@ enum {
  * (src/kernels/kernels.zig:330-333); this backend reads the same word as
  * weight tiles in flight per warp (byte 0: 2, 4 or 6; 0 = as deep as fits),
  * byte 1 reserved (0), and kernel family (byte 2: 1 = scalar f32 FMA,
- * 2 = integer tensor-core fragments). Reserved
+ * 2 = integer tensor-core fragments, 3 = matvec_q4_k for up to 64 tokens in
+ * one pass over the weights: tcgen05 with accumulators in tensor memory, the
+ * tokens as two f16 terms; bytes 0 and 1 zero). Reserved
  * prefill rungs keep the reference's ids (src/kernels/kernels.zig:798-822). */
 #define ZCU_VARIANT(tiles, splitk, family) ((uint32_t)(tiles) | ((uint32_t)(splitk) << 8) | ((uint32_t)(family) << 16))
 #define ZCU_FAMILY_SCALAR 1u
 #define ZCU_FAMILY_MMA 2u
+#define ZCU_FAMILY_TCGEN05 3u
 #define ZCU_VARIANT_PREFILL_BF16_TC 0xfffc0000u
 /* delta_rule in its chunked form (64-token chunks, the remainder by the recurrent kernel). No reference
  * counterpart: the reference runs every token serially. DeltaRule._pad must hold the step's token count. */

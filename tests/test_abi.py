@@ -45,11 +45,16 @@ def test_artifacts_and_missing_kernels():
     assert abi.artifact(K.RMSNORM, 5) == b""
     # the reserved prefill-rung id exists for the half-precision multiplies only, and mutated ids do not
     # (src/agility/kernels.zig:200-232)
-    for k in (K.MATMUL_BF16, K.MATMUL_F16):
+    for k in (K.MATMUL_BF16, K.MATMUL_F16, K.MATMUL_Q4_K):
         assert abi.artifact(k, K.VARIANT_PREFILL_TC)
         for bit in range(32):
             assert abi.artifact(k, K.VARIANT_PREFILL_TC ^ (1 << bit)) == b""
     assert abi.artifact(K.RMSNORM, K.VARIANT_PREFILL_TC) == b"" and abi.artifact(K.MATMUL_BF16, 0xFFFF0000) == b""
+    assert abi.artifact(K.MATMUL_Q8_0, K.VARIANT_PREFILL_TC) == b""
+    # the batched tcgen05 family of the decode multiply: Q4_K only, no tile or split bytes
+    assert abi.artifact(K.MATVEC_Q4_K, K.MATVEC_BATCHED) == b"cuda:matvec_q4_k:30000"
+    assert abi.artifact(K.MATVEC_Q8_0, K.MATVEC_BATCHED) == b"" and abi.artifact(K.MATVEC_Q4_K, K.MATVEC_BATCHED | 4) == b""
+    assert K.matvec_variant_exists("q4_k", 4096, K.MATVEC_BATCHED) and not K.matvec_variant_exists("q8_0", 4096, K.MATVEC_BATCHED)
     assert "sm_100a" in abi.backend_source()
 
 

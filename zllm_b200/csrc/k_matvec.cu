@@ -315,6 +315,10 @@ zcu_result launch_quant(const LaunchArgs& a, uint32_t block) {
     if (r != ZCU_OK) return r;
     if (v.p.n == 0) return ZCU_OK;
     const uint32_t family = (a.variant >> 16) & 0xffu;
+    if (family == ZCU_FAMILY_TCGEN05) {
+        if (TYPE != W_Q4_K) return zcu_fail(a, ZCU_E_UNSUPPORTED_KERNEL, "matvec: the tcgen05 family is built for Q4_K only");
+        return launch_matvec_q4_k_tc(a, v);
+    }
     // Q8_0 rows that are not whole 256-weight pieces have ragged tiles: the scalar family takes them.
     const bool imma_ok = TYPE != W_Q8_0 || v.p.k % 256 == 0;
     if ((a.variant == 0 && imma_ok) || family == ZCU_FAMILY_MMA)
@@ -339,6 +343,7 @@ bool matvec_variant_ok(uint32_t kernel, uint32_t variant) {
         const uint32_t stages = variant & 0xffu;
         return ks == 0 && (stages == 0 || (stages >= 2 && stages <= 6));
     }
+    if (family == ZCU_FAMILY_TCGEN05) return kernel == ZCU_K_MATVEC_Q4_K && (variant & 0xffffu) == 0;
     return false;
 }
 

@@ -77,3 +77,5 @@ struct MvArgs {
 
 // The tensor-core family (k_matvec_imma.cu). stages = 0 picks the deepest ring that fits.
 zcu_result launch_matvec_imma(const LaunchArgs& a, const mv::MvArgs& v, int type, int stages, int reserved);
+// The batched tcgen05 family of matvec_q4_k (k_quant_tc.cu): up to 64 tokens in one pass over the weights.
+zcu_result launch_matvec_q4_k_tc(const LaunchArgs& a, const mv::MvArgs& v);

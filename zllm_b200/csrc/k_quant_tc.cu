@@ -1,0 +1,687 @@
+// Q4_K multiplies on the 5th-generation tensor cores (tcgen05, accumulators in tensor memory), for steps with
+// enough columns to share a weight tile: the prefill rung of matmul_q4_k (variant 0xfffc0000) and the batched
+// form of matvec_q4_k (family 3: 1..64 tokens in ONE pass over the weights).
+//
+// The arithmetic stays the reference's integer one (src/kernels/matmul_quant.wgsl:1-16, quant/q4_k.wgsl:1-35):
+//   out[c][j] = sum over 256-weight super-blocks b of
+//               s[c][b] * ( d[j][b] * sum_i (sc_u(i) q_i) X[c][i]  -  dmin[j][b] * sum_u m_u S[c][u] )
+// with q the 4-bit codes, sc_u / m_u the 6-bit scale and min of 32-weight unit u, X the column's values and
+// S[c][u] the sum of X over unit u. What changes is where the products run: the CUDA cores only turn a weight
+// tile into the f16 INTEGERS sc_u q_i (at most 63 * 15 = 945, exact in f16: one mask, one fused multiply-add per
+// two weights), written to shared memory in the tensor cores' K-major 128-byte-swizzled layout; tcgen05.mma
+// (kind::f16, M 128 weight rows, N columns, K 16) accumulates them against the columns in f32 tensor memory. The
+// min term is one more K = 16 instruction per super-block (each m_u twice, against S[c][u] as two f16 terms).
+// Once per super-block the two sums leave tensor memory and meet the f16 super-scales and the column's scale in
+// registers. A column is
+//   prefill: a token's Q8_K block values (integers, exact in f16), s = the block's f32 scale (quantize_q8's dx);
+//   decode:  one of the TWO f16 terms of a token's f32 activations (x 2^e per block = hi + lo, 22 bits), s = 2^-e;
+//            the token's result is the sum of its two columns.
+// Products are exact (10 x 11 bits), sums are f32 over at most 256 terms per drain: within 1e-6 of the integer
+// arithmetic, against the 1e-5 bar of the reference's kernel checks.
+//
+// One CTA owns 128 weight rows x BN columns x a slice of k. Roles (16 warps):
+//   warp 0      TMA: the raw weight tiles (128 rows x 144 bytes per super-block), several super-blocks ahead
+//   warp 1      TMA: the columns' tiles (BN x 64 values, 128-byte swizzle), the unit sums, the column scales
+//   warp 2      allocates tensor memory; one lane issues the MMAs and commits stages / accumulators
+//   warps 4-7   decode the raw tile: thread r owns weight row r
+//   warps 8-15  drain: thread (quadrant, lane) owns a weight row's accumulators for half of the columns
+// Two accumulator sets alternate, so a super-block's products run while the one before it drains. Every wait is
+// bounded; one that gives up raises the CTA's abort flag, every role leaves, tensor memory is freed and the
+// context's status word reports it.
+
+#include <cuda.h>
+#include <cuda_fp16.h>
+
+#include "k_matvec_common.cuh"
+#include "tma_util.cuh"
+
+namespace {
+
+constexpr int QT_ROWS = 128, QT_CHUNK = 64, QT_STAGES = 4, QT_THREADS = 512;
+constexpr int RAW_ROW = 144, RAW_BYTES = QT_ROWS * RAW_ROW;   // a super-block of 128 rows as stored
+constexpr int A_BYTES = QT_ROWS * 128;                        // 128 rows x 64 f16
+constexpr int HDR_SLOTS = 4;
+constexpr int MODE_PREFILL = 0, MODE_DECODE = 1;
+
+__host__ __device__ constexpr int raw_stages(int bn) { return bn > 64 ? 3 : 5; }
+__host__ __device__ constexpr int qt_smem(int bn) {
+    return 1024 + QT_STAGES * A_BYTES + QT_STAGES * bn * 128 + raw_stages(bn) * RAW_BYTES + HDR_SLOTS * QT_ROWS * 8 + HDR_SLOTS * bn * 4 + 256;
+}
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t mbar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(mbar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t mbar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(mbar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t mbar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(mbar) : "memory");
+}
+// Waits for phase `parity`, at most 2^20 polls; gives up early when another role raised the abort flag.
+__device__ __forceinline__ bool mbar_wait(uint32_t mbar, uint32_t parity, volatile uint32_t* abort_flag) {
+    for (int spin = 0; spin < (1 << 20); spin++) {
+        uint32_t ok;
+        asm volatile(
+            "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+            : "=r"(ok)
+            : "r"(mbar), "r"(parity)
+            : "memory");
+        if (ok) return true;
+        if ((spin & 63) == 63 && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t mbar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n" ::"r"(dst),
+                 "l"((uint64_t)map), "r"(mbar), "r"(x), "r"(y)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t mbar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(dst), "l"(src),
+                 "r"(bytes), "r"(mbar)
+                 : "memory");
+}
+// K-major rows of 128 bytes, 128-byte swizzle, groups of 8 rows 1024 bytes apart.
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t saddr) {
+    uint64_t d = (uint64_t)((saddr >> 4) & 0x3FFFu);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(d_tmem),
+                 "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
+                 : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t mbar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(mbar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t* r) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
+
+struct QtArgs {
+    int seg_rows, nseg, seg1_y, tiles_per_seg;   // weight-row segments (two for a SILU_PAIR matrix: gate rows, up rows)
+    int cols, cols_pad;                          // columns, and the padded width of the scale table
+    int nsb, sb_per_slice;                       // super-blocks of a row, and per k slice
+    float* out;                                  // out[z * slice_stride + c * out_stride + col0 + seg * seg_out + row]
+    size_t slice_stride;
+    uint32_t out_stride, col0, seg_out, accumulate;
+    const float* scales;                         // [nsb][cols_pad]
+    int* status;
+};
+
+// Two f16 in one register from an int pair held in 16-bit lanes: 0x6400 | v is the f16 1024 + v.
+__device__ __forceinline__ uint32_t scaled_pair(uint32_t bits, __half2 sc, __half2 off) {
+    const uint32_t h = bits | 0x64006400u;
+    const __half2 r = __hfma2(*reinterpret_cast<const __half2*>(&h), sc, off);
+    return *reinterpret_cast<const uint32_t*>(&r);
+}
+
+template <int BN>
+__global__ void __launch_bounds__(QT_THREADS, 1)
+    qgemm_q4k_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap bmap,
+                     const __grid_constant__ CUtensorMap smap, QtArgs q) {
+    constexpr int RS = raw_stages(BN), B_BYTES = BN * 128, CPT = BN / 2, TCOLS = 4 * BN < 32 ? 32 : 4 * BN;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    unsigned char* a_ring = smem;
+    unsigned char* b_ring = a_ring + QT_STAGES * A_BYTES;
+    unsigned char* raw_ring = b_ring + QT_STAGES * B_BYTES;
+    float2* hdr = reinterpret_cast<float2*>(raw_ring + RS * RAW_BYTES);          // [slot][row]: d, dmin
+    float* csc = reinterpret_cast<float*>(hdr + HDR_SLOTS * QT_ROWS);            // [slot][BN]: the columns' scales
+    uint64_t* bars = reinterpret_cast<uint64_t*>(csc + HDR_SLOTS * BN);
+    const uint32_t full_a0 = smem_u32(bars), full_b0 = full_a0 + 8 * QT_STAGES, empty0 = full_b0 + 8 * QT_STAGES,
+                   raw_full0 = empty0 + 8 * QT_STAGES, raw_empty0 = raw_full0 + 8 * RS, tfull0 = raw_empty0 + 8 * RS,
+                   tempty0 = tfull0 + 16;
+    uint32_t* holder = reinterpret_cast<uint32_t*>(bars + 3 * QT_STAGES + 2 * RS + 4);
+    volatile uint32_t* abort_flag = holder + 1;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < QT_STAGES; s++) {
+            mbar_init(full_a0 + 8 * s, 128);
+            mbar_init(full_b0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, 1);
+        }
+        for (int s = 0; s < RS; s++) {
+            mbar_init(raw_full0 + 8 * s, 1);
+            mbar_init(raw_empty0 + 8 * s, 128);
+        }
+        for (int a = 0; a < 2; a++) {
+            mbar_init(tfull0 + 8 * a, 1);
+            mbar_init(tempty0 + 8 * a, 256);
+        }
+        holder[1] = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 2) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(holder)), "r"(TCOLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = holder[0];
+
+    const int seg = (int)blockIdx.x / q.tiles_per_seg, tile = (int)blockIdx.x % q.tiles_per_seg;
+    const int row0 = tile * QT_ROWS;                          // within the segment
+    const int y0 = (seg ? q.seg1_y : 0) + row0;               // in the weight matrix
+    const int c0 = (int)blockIdx.y * BN, z = (int)blockIdx.z;
+    const int sb_lo = min(q.nsb, z * q.sb_per_slice), sb_hi = min(q.nsb, sb_lo + q.sb_per_slice);
+    bool gave_up = false;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int rs = 0;
+            uint32_t rphase = 0;
+            for (int sb = sb_lo; sb < sb_hi; sb++) {
+                if (!mbar_wait(raw_empty0 + 8 * rs, rphase ^ 1u, abort_flag)) {
+                    gave_up = true;
+                    break;
+                }
+                mbar_expect_tx(raw_full0 + 8 * rs, RAW_BYTES);
+                tma_load_2d(smem_u32(raw_ring + rs * RAW_BYTES), &wmap, sb * RAW_ROW, y0, raw_full0 + 8 * rs);
+                if (++rs == RS) rs = 0, rphase ^= 1u;
+            }
+            if (gave_up)
+                for (int i = 0; i < 200; i++) __nanosleep(1000);
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            int s = 0;
+            uint32_t phase = 0;
+            for (int sb = sb_lo; sb < sb_hi && !gave_up; sb++) {
+                for (int c = 0; c < 5; c++) {
+                    if (!mbar_wait(empty0 + 8 * s, phase ^ 1u, abort_flag)) {
+                        gave_up = true;
+                        break;
+                    }
+                    const uint32_t dst = smem_u32(b_ring + s * B_BYTES), fb = full_b0 + 8 * s;
+                    if (c < 4) {
+                        mbar_expect_tx(fb, B_BYTES);
+                        tma_load_2d(dst, &bmap, (sb * 256 + c * QT_CHUNK) * 2, c0, fb);
+                    } else {
+                        // the unit sums of this super-block, and the columns' scales for it
+                        mbar_expect_tx(fb, B_BYTES + BN * 4);
+                        tma_load_2d(dst, &smap, sb * 128, c0, fb);
+                        bulk_load(smem_u32(csc + ((sb - sb_lo) & (HDR_SLOTS - 1)) * BN), q.scales + (size_t)sb * q.cols_pad + c0, BN * 4, fb);
+                    }
+                    if (++s == QT_STAGES) s = 0, phase ^= 1u;
+                }
+            }
+            if (gave_up)
+                for (int i = 0; i < 200; i++) __nanosleep(1000);
+        }
+    } else if (warp == 2) {
+        if (lane == 0) {
+            const uint32_t idesc = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(QT_ROWS >> 4) << 24);
+            int s = 0, acc = 0;
+            uint32_t phase = 0, acc_phase = 0;
+            for (int sb = sb_lo; sb < sb_hi && !gave_up; sb++) {
+                if (!mbar_wait(tempty0 + 8 * acc, acc_phase ^ 1u, abort_flag)) {
+                    gave_up = true;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t d1 = tmem_base + (uint32_t)acc * 2 * BN, d2 = d1 + BN;
+                for (int c = 0; c < 5; c++) {
+                    if (!mbar_wait(full_a0 + 8 * s, phase, abort_flag) || !mbar_wait(full_b0 + 8 * s, phase, abort_flag)) {
+                        gave_up = true;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint64_t da = umma_desc_sw128(smem_u32(a_ring + s * A_BYTES)), db = umma_desc_sw128(smem_u32(b_ring + s * B_BYTES));
+                    if (c < 4) {
+#pragma unroll
+                        for (int kk = 0; kk < 4; kk++) umma_f16(d1, da + (uint64_t)(2 * kk), db + (uint64_t)(2 * kk), idesc, (c | kk) != 0);
+                    } else {
+                        umma_f16(d2, da, db, idesc, 0u);
+                    }
+                    umma_commit(empty0 + 8 * s);
+                    if (++s == QT_STAGES) s = 0, phase ^= 1u;
+                }
+                if (gave_up) break;
+                umma_commit(tfull0 + 8 * acc);
+                if (++acc == 2) acc = 0, acc_phase ^= 1u;
+            }
+        }
+    } else if (warp >= 4 && warp < 8) {
+        // ---- raw tile -> the tensor cores' operand. Thread r owns weight row r.
+        const int r = (int)threadIdx.x - 128;
+        const uint32_t swz = (uint32_t)(r & 7);
+        int s = 0, rs = 0;
+        uint32_t phase = 0, rphase = 0;
+        for (int sb = sb_lo; sb < sb_hi && !gave_up; sb++) {
+            if (!mbar_wait(raw_full0 + 8 * rs, rphase, abort_flag)) {
+                gave_up = true;
+                break;
+            }
+            const unsigned char* raw = raw_ring + rs * RAW_BYTES + r * RAW_ROW;
+            const uint4 h = *reinterpret_cast<const uint4*>(raw);
+            // 6-bit scales and mins of the eight units (src/ref/tensor.zig:95-104)
+            const uint32_t scw[2] = {h.y & 0x3f3f3f3fu, (h.w & 0x0f0f0f0fu) | ((h.y >> 2) & 0x30303030u)};
+            const uint32_t mnw[2] = {h.z & 0x3f3f3f3fu, ((h.w >> 4) & 0x0f0f0f0fu) | ((h.z >> 2) & 0x30303030u)};
+            hdr[((sb - sb_lo) & (HDR_SLOTS - 1)) * QT_ROWS + r] =
+                make_float2(__half2float(__ushort_as_half((unsigned short)(h.x & 0xffffu))), __half2float(__ushort_as_half((unsigned short)(h.x >> 16))));
+            for (int c = 0; c < 5; c++) {
+                if (!mbar_wait(empty0 + 8 * s, phase ^ 1u, abort_flag)) {
+                    gave_up = true;
+                    break;
+                }
+                unsigned char* arow = a_ring + s * A_BYTES + r * 128;
+                if (c < 4) {
+                    const uint4 qa = *reinterpret_cast<const uint4*>(raw + 16 + 32 * c), qb = *reinterpret_cast<const uint4*>(raw + 32 + 32 * c);
+                    const uint32_t qw[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+                    const int u = 2 * c;  // units 2c (low nibbles) and 2c + 1 (high nibbles)
+                    const float sl = (float)((scw[u >> 2] >> (8 * (u & 3))) & 0xffu), sh = (float)((scw[(u + 1) >> 2] >> (8 * ((u + 1) & 3))) & 0xffu);
+                    const __half2 scl = __float2half2_rn(sl), offl = __float2half2_rn(-1024.0f * sl);
+                    const __half2 sch = __float2half2_rn(sh), offh = __float2half2_rn(-1024.0f * sh);
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        // 16 bytes = positions 8i .. 8i+7 of the unit: values (0,2,1,3 | 4,6,5,7) of two code words
+                        const uint32_t w0 = qw[2 * i], w1 = qw[2 * i + 1];
+                        uint4 lo, hi;
+                        lo.x = scaled_pair(w0 & 0x000f000fu, scl, offl);
+                        lo.y = scaled_pair((w0 >> 8) & 0x000f000fu, scl, offl);
+                        lo.z = scaled_pair(w1 & 0x000f000fu, scl, offl);
+                        lo.w = scaled_pair((w1 >> 8) & 0x000f000fu, scl, offl);
+                        hi.x = scaled_pair((w0 >> 4) & 0x000f000fu, sch, offh);
+                        hi.y = scaled_pair((w0 >> 12) & 0x000f000fu, sch, offh);
+                        hi.z = scaled_pair((w1 >> 4) & 0x000f000fu, sch, offh);
+                        hi.w = scaled_pair((w1 >> 12) & 0x000f000fu, sch, offh);
+                        *reinterpret_cast<uint4*>(arow + (((uint32_t)i ^ swz) << 4)) = lo;
+                        *reinterpret_cast<uint4*>(arow + (((uint32_t)(i + 4) ^ swz) << 4)) = hi;
+                    }
+                } else {
+                    // the mins, each twice: K positions 2u, 2u + 1 meet the two terms of unit u's column sum
+                    uint4 m0, m1;
+                    auto dup = [](uint32_t byte) {
+                        const __half2 v = __float2half2_rn((float)byte);
+                        return *reinterpret_cast<const uint32_t*>(&v);
+                    };
+                    m0.x = dup(mnw[0] & 0xffu), m0.y = dup((mnw[0] >> 8) & 0xffu), m0.z = dup((mnw[0] >> 16) & 0xffu), m0.w = dup(mnw[0] >> 24);
+                    m1.x = dup(mnw[1] & 0xffu), m1.y = dup((mnw[1] >> 8) & 0xffu), m1.z = dup((mnw[1] >> 16) & 0xffu), m1.w = dup(mnw[1] >> 24);
+                    *reinterpret_cast<uint4*>(arow + ((0u ^ swz) << 4)) = m0;
+                    *reinterpret_cast<uint4*>(arow + ((1u ^ swz) << 4)) = m1;
+                }
+                // these stores are read through the async proxy (the tensor cores)
+                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+                mbar_arrive(full_a0 + 8 * s);
+                if (++s == QT_STAGES) s = 0, phase ^= 1u;
+            }
+            mbar_arrive(raw_empty0 + 8 * rs);
+            if (++rs == RS) rs = 0, rphase ^= 1u;
+        }
+    } else if (warp >= 8) {
+        // ---- drain. Thread (quad, lane) owns weight row quad * 32 + lane and CPT of the CTA's columns.
+        const int quad = warp & 3, chalf = (warp - 8) >> 2;
+        const int r = quad * 32 + lane;
+        float accv[CPT];
+#pragma unroll
+        for (int i = 0; i < CPT; i++) accv[i] = 0.f;
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        for (int sb = sb_lo; sb < sb_hi; sb++) {
+            if (!__all_sync(0xffffffffu, mbar_wait(tfull0 + 8 * acc, acc_phase, abort_flag))) {
+                gave_up = true;
+                break;
+            }
+            tc_fence_after();
+            const int slot = (sb - sb_lo) & (HDR_SLOTS - 1);
+            const float2 dd = hdr[slot * QT_ROWS + r];
+            const float* cs = csc + slot * BN + chalf * CPT;
+            const uint32_t t1 = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)acc * 2 * BN + (uint32_t)(chalf * CPT), t2 = t1 + BN;
+#pragma unroll
+            for (int i0 = 0; i0 < CPT; i0 += 8) {
+                uint32_t v1[8], v2[8];
+                tmem_ld8(t1 + i0, v1);
+                tmem_ld8(t2 + i0, v2);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 8; i++)
+                    accv[i0 + i] = __fmaf_rn(cs[i0 + i], __fmaf_rn(dd.x, __uint_as_float(v1[i]), -(dd.y * __uint_as_float(v2[i]))), accv[i0 + i]);
+            }
+            tc_fence_before();
+            mbar_arrive(tempty0 + 8 * acc);
+            if (++acc == 2) acc = 0, acc_phase ^= 1u;
+        }
+        if (!gave_up && row0 + r < q.seg_rows) {
+            float* dst = q.out + (size_t)z * q.slice_stride + q.col0 + (size_t)seg * q.seg_out + row0 + r;
+#pragma unroll
+            for (int i = 0; i < CPT; i++) {
+                const int c = c0 + chalf * CPT + i;
+                if (c < q.cols) {
+                    float* o = dst + (size_t)c * q.out_stride;
+                    *o = q.accumulate ? *o + accv[i] : accv[i];
+                }
+            }
+        }
+    }
+    if (gave_up && q.status) atomicExch(q.status, 2);
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 2) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(TCOLS) : "memory");
+    }
+}
+
+
+// ---------------------------------------------------------------------------------------------- the columns
+// Position of value e inside its group of four: the decoder leaves a code word's values as (0, 2, 1, 3).
+__device__ __forceinline__ uint2 perm_pack(__half a, __half b, __half c, __half d) {
+    const __half2 lo = __halves2half2(a, c), hi = __halves2half2(b, d);
+    return make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+}
+
+// Prefill: the Q8_K values of quantize_q8 -> f16 columns, their unit sums as two exact f16 terms (even part, low
+// bit), and the block scales transposed. grid (k / 256, tokens), 64 threads, thread = four values.
+__global__ void __launch_bounds__(64) cols_from_q8_kernel(const int8_t* __restrict__ qx, const float* __restrict__ dx, __half* __restrict__ bcol,
+                                                         __half* __restrict__ bsum, float* __restrict__ scales, int k, int cols_pad) {
+    const int li = threadIdx.x, sb = blockIdx.x, tok = blockIdx.y, nsb = k / 256;
+    const char4 v = reinterpret_cast<const char4*>(qx + (size_t)tok * k + (size_t)sb * 256)[li];
+    reinterpret_cast<uint2*>(bcol + (size_t)tok * k + (size_t)sb * 256)[li] =
+        perm_pack(__int2half_rn(v.x), __int2half_rn(v.y), __int2half_rn(v.z), __int2half_rn(v.w));
+    int s = (int)v.x + v.y + v.z + v.w;
+    s += __shfl_xor_sync(0xffffffffu, s, 1);
+    s += __shfl_xor_sync(0xffffffffu, s, 2);
+    s += __shfl_xor_sync(0xffffffffu, s, 4);
+    if ((li & 7) == 0) {
+        const __half2 two = __halves2half2(__int2half_rn(s & ~1), __int2half_rn(s & 1));  // |s| <= 4064: both exact
+        reinterpret_cast<__half2*>(bsum + (size_t)tok * nsb * 64 + (size_t)sb * 64)[li >> 3] = two;
+    }
+    if (li == 0) scales[(size_t)sb * cols_pad + tok] = dx[(size_t)tok * nsb + sb];
+}
+
+// Decode: f32 activations (RMSNorm or SiLU-pair fused, as quantize_q8 fuses them) -> two f16 columns per token.
+// Per 256-value block: e with amax * 2^e in [2^9, 2^10); hi = f16(x 2^e), lo = f16(x 2^e - hi); the block's
+// scale is 2^-e for both columns. grid (k / 256, tokens), 64 threads.
+__global__ void __launch_bounds__(64) cols_from_f32_kernel(const float* __restrict__ x, const float* __restrict__ nw, __half* __restrict__ bcol,
+                                                          __half* __restrict__ bsum, float* __restrict__ scales, int k, int x_stride, int mode,
+                                                          float eps, int cols_pad) {
+    __shared__ double red[2];
+    __shared__ float amax_s[2];
+    const int li = threadIdx.x, sb = blockIdx.x, tok = blockIdx.y, nsb = k / 256;
+    const float* xt = x + (size_t)tok * x_stride;
+    float4 v;
+    if (mode == 2) {  // silu(gate) * up over rows of gate | up (src/kernels/quantize_q8.wgsl)
+        const float4 g = reinterpret_cast<const float4*>(xt)[sb * 64 + li], u = reinterpret_cast<const float4*>(xt + k)[sb * 64 + li];
+        v = make_float4(mv::silu_f(g.x) * u.x, mv::silu_f(g.y) * u.y, mv::silu_f(g.z) * u.z, mv::silu_f(g.w) * u.w);
+    } else {
+        v = reinterpret_cast<const float4*>(xt)[sb * 64 + li];
+    }
+    if (mode == 1) {  // RMSNorm(x) * w: f32 squares summed in f64 (src/ref/ops.zig:30-41)
+        double ss = 0.0;
+        for (int i = li; i < k / 4; i += 64) {
+            const float4 r = reinterpret_cast<const float4*>(xt)[i];
+            ss += (double)__fmul_rn(r.x, r.x);
+            ss += (double)__fmul_rn(r.y, r.y);
+            ss += (double)__fmul_rn(r.z, r.z);
+            ss += (double)__fmul_rn(r.w, r.w);
+        }
+        ss = mv::warp_sum_d(ss);
+        if ((li & 31) == 0) red[li >> 5] = ss;
+        __syncthreads();
+        const float mean = (float)((red[0] + red[1]) / (double)k);
+        const float scale = 1.0f / sqrtf(mean + eps);
+        const float4 w = reinterpret_cast<const float4*>(nw)[sb * 64 + li];
+        v.x = __fmul_rn(__fmul_rn(v.x, scale), w.x);
+        v.y = __fmul_rn(__fmul_rn(v.y, scale), w.y);
+        v.z = __fmul_rn(__fmul_rn(v.z, scale), w.z);
+        v.w = __fmul_rn(__fmul_rn(v.w, scale), w.w);
+    }
+    float am = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
+    if ((li & 31) == 0) amax_s[li >> 5] = am;
+    __syncthreads();
+    am = fmaxf(amax_s[0], amax_s[1]);
+    float up = 1.0f, down = 1.0f;
+    if (am > 0.f && am < 3.0e38f) {
+        const int e = (int)((__float_as_uint(am) >> 23) & 0xffu) - 127;   // am = f 2^e, f in [1, 2)
+        const int sh = max(-110, min(110, 9 - e));
+        up = __uint_as_float((uint32_t)(sh + 127) << 23);
+        down = __uint_as_float((uint32_t)(127 - sh) << 23);
+    }
+    const float y[4] = {v.x * up, v.y * up, v.z * up, v.w * up};
+    __half hi[4], lo[4];
+    float sh_ = 0.f, sl_ = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        hi[i] = __float2half_rn(y[i]);
+        lo[i] = __float2half_rn(y[i] - __half2float(hi[i]));
+        sh_ += __half2float(hi[i]);
+        sl_ += __half2float(lo[i]);
+    }
+    __half* b0 = bcol + (size_t)(2 * tok) * k + (size_t)sb * 256;
+    reinterpret_cast<uint2*>(b0)[li] = perm_pack(hi[0], hi[1], hi[2], hi[3]);
+    reinterpret_cast<uint2*>(b0 + k)[li] = perm_pack(lo[0], lo[1], lo[2], lo[3]);
+#pragma unroll
+    for (int o = 1; o < 8; o <<= 1) {
+        sh_ += __shfl_xor_sync(0xffffffffu, sh_, o);
+        sl_ += __shfl_xor_sync(0xffffffffu, sl_, o);
+    }
+    if ((li & 7) == 0) {
+        const __half a = __float2half_rn(sh_), c = __float2half_rn(sl_);
+        __half* s0 = bsum + (size_t)(2 * tok) * nsb * 64 + (size_t)sb * 64 + 2 * (li >> 3);
+        *reinterpret_cast<__half2*>(s0) = __halves2half2(a, __float2half_rn(sh_ - __half2float(a)));
+        *reinterpret_cast<__half2*>(s0 + (size_t)nsb * 64) = __halves2half2(c, __float2half_rn(sl_ - __half2float(c)));
+    }
+    if (li == 0) {
+        scales[(size_t)sb * cols_pad + 2 * tok] = down;
+        scales[(size_t)sb * cols_pad + 2 * tok + 1] = down;
+    }
+}
+
+// Decode: the k slices and the two columns of a token, added in a fixed order; SILU_PAIR and ACCUMULATE as the
+// multiply's epilogue applies them. part[z][column][seg * n + j].
+__global__ void __launch_bounds__(256) cols_reduce_kernel(const float* __restrict__ part, float* __restrict__ out, int n, int m, int slices,
+                                                         int cols, int pair, int accumulate, uint32_t out_stride, uint32_t col0) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (size_t)n * m) return;
+    const int tok = (int)(i / n), j = (int)(i % n);
+    const size_t width = (size_t)n * (pair ? 2 : 1), zs = (size_t)cols * width;
+    float v = 0.f, u = 0.f;
+    for (int z = 0; z < slices; z++) {
+        const float* p = part + z * zs + (size_t)(2 * tok) * width + j;
+        v = __fadd_rn(v, __fadd_rn(p[0], p[width]));
+        if (pair) u = __fadd_rn(u, __fadd_rn(p[n], p[width + n]));
+    }
+    if (pair) v = mv::silu_f(v) * u;
+    const size_t o = (size_t)tok * out_stride + col0 + j;
+    out[o] = accumulate ? out[o] + v : v;
+}
+
+// ---------------------------------------------------------------------------------------------- host side
+inline bool cols_map(CUtensorMap* map, const void* base, uint64_t cols, uint64_t row_bytes, uint32_t bn) {
+    tma::EncodeTiledFn enc = tma::encode_tiled();
+    if (!enc) return false;
+    const cuuint64_t dims[2] = {row_bytes, cols}, strides[1] = {row_bytes};
+    const cuuint32_t box[2] = {128, bn}, elem[2] = {1, 1};
+    return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+struct QtPlan {
+    const void* w;
+    uint64_t w_rows;     // every row the weight map may touch
+    int k, cols, bn;
+    const void* bcol;
+    const void* bsum;
+    QtArgs q;
+    int slices;
+};
+
+template <int BN>
+zcu_result launch_qgemm_bn(const LaunchArgs& a, const QtPlan& pl) {
+    CUtensorMap wmap, bmap, smap;
+    const uint64_t rb = (uint64_t)(pl.k / 256) * 144;
+    const bool ok = tma::bytes_2d(&wmap, pl.w, pl.w_rows, rb, RAW_ROW, QT_ROWS) && cols_map(&bmap, pl.bcol, (uint64_t)pl.cols, (uint64_t)pl.k * 2, BN) &&
+                    cols_map(&smap, pl.bsum, (uint64_t)pl.cols, (uint64_t)(pl.k / 256) * 128, BN);
+    if (!ok) return zcu_fail(a, ZCU_E_GPU, "q4_k multiply (tcgen05): the driver refused a tensor map (k %d, columns %d)", pl.k, pl.cols);
+    auto kern = qgemm_q4k_kernel<BN>;
+    constexpr int SMEM = qt_smem(BN);
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) {
+        cudaGetLastError();
+        return zcu_fail(a, ZCU_E_GPU, "q4_k multiply (tcgen05): %d bytes of shared memory refused", SMEM);
+    }
+    const dim3 grid((unsigned)(pl.q.tiles_per_seg * pl.q.nseg), (unsigned)((pl.cols + BN - 1) / BN), (unsigned)pl.slices);
+    kern<<<grid, QT_THREADS, SMEM, a.stream>>>(wmap, bmap, smap, pl.q);
+    ZCU_CHECK_LAUNCH(a);
+    return ZCU_OK;
+}
+
+zcu_result launch_qgemm(const LaunchArgs& a, const QtPlan& pl) {
+    switch (pl.bn) {
+        case 16: return launch_qgemm_bn<16>(a, pl);
+        case 32: return launch_qgemm_bn<32>(a, pl);
+        case 64: return launch_qgemm_bn<64>(a, pl);
+        default: return launch_qgemm_bn<128>(a, pl);
+    }
+}
+
+inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+}  // namespace
+
+// matmul_q4_k, the tensor-core rung: params.MatmulQuant and the bindings qx, w, out, dx of the integer-dot identity.
+zcu_result launch_matmul_q4_k_tc(const LaunchArgs& a) {
+    PMatmulQuant p;
+    ZCU_NEED(a, a.params_bytes >= sizeof(p) && a.nb >= 4, "matmul_q4_k (tcgen05): bad parameter block or bindings");
+    memcpy(&p, a.params, sizeof(p));
+    const uint32_t cap = a.grid[1] * 32u;   // the reference dispatches token tiles of 32 (grid y)
+    const int tokens = (int)(p.rows < cap ? p.rows : cap);
+    if (tokens == 0 || p.n == 0) return ZCU_OK;
+    ZCU_NEED(a, p.k % 256 == 0 && p.k > 0, "matmul_q4_k (tcgen05): k = %u is not a multiple of 256", p.k);
+    ZCU_NEED(a, p.k_slice > 0 && p.k_slice % 256 == 0, "matmul_q4_k (tcgen05): k_slice = %u is not a multiple of 256", p.k_slice);
+    const uint32_t slices = (p.k + p.k_slice - 1) / p.k_slice;
+    ZCU_NEED(a, a.grid[2] <= 1 || a.grid[2] == slices, "matmul_q4_k (tcgen05): %u slices in the grid, %u by k_slice", a.grid[2], slices);
+    ZCU_NEED(a, ((uintptr_t)a.b[0].ptr & 15) == 0 && ((uintptr_t)a.b[1].ptr & 15) == 0, "matmul_q4_k (tcgen05): qx and w must be 16-byte aligned");
+    const int k = (int)p.k, nsb = k / 256;
+    const int bn = tokens > 64 ? 128 : tokens > 32 ? 64 : tokens > 16 ? 32 : 16;
+    const int cols_pad = (int)align_up((size_t)tokens, (size_t)bn);
+    const size_t b_bytes = align_up((size_t)tokens * k * 2, 1024), s_bytes = align_up((size_t)tokens * nsb * 128, 1024),
+                 c_bytes = align_up((size_t)nsb * cols_pad * 4, 1024);
+    unsigned char* scratch = nullptr;
+    if (cudaMallocAsync((void**)&scratch, b_bytes + s_bytes + c_bytes, a.stream) != cudaSuccess) {
+        cudaGetLastError();
+        return zcu_fail(a, ZCU_E_GPU, "matmul_q4_k (tcgen05): no memory for %zu bytes of columns", b_bytes + s_bytes + c_bytes);
+    }
+    __half* bcol = reinterpret_cast<__half*>(scratch);
+    __half* bsum = reinterpret_cast<__half*>(scratch + b_bytes);
+    float* scales = reinterpret_cast<float*>(scratch + b_bytes + s_bytes);
+    cudaMemsetAsync(scales, 0, c_bytes, a.stream);
+    cols_from_q8_kernel<<<dim3((unsigned)nsb, (unsigned)tokens), 64, 0, a.stream>>>((const int8_t*)a.b[0].ptr, (const float*)a.b[3].ptr, bcol, bsum, scales,
+                                                                                 k, cols_pad);
+    QtPlan pl{};
+    pl.w = a.b[1].ptr;
+    pl.w_rows = p.n;
+    pl.k = k;
+    pl.cols = tokens;
+    pl.bn = bn;
+    pl.bcol = bcol;
+    pl.bsum = bsum;
+    pl.slices = (int)slices;
+    pl.q.seg_rows = (int)p.n;
+    pl.q.nseg = 1;
+    pl.q.seg1_y = 0;
+    pl.q.tiles_per_seg = ((int)p.n + QT_ROWS - 1) / QT_ROWS;
+    pl.q.cols = tokens;
+    pl.q.cols_pad = cols_pad;
+    pl.q.nsb = nsb;
+    pl.q.sb_per_slice = (int)p.k_slice / 256;
+    pl.q.out = (float*)a.b[2].ptr;
+    pl.q.slice_stride = p.slice_stride;
+    pl.q.out_stride = p.out_stride;
+    pl.q.col0 = p.col0;
+    pl.q.seg_out = 0;
+    pl.q.accumulate = p.accumulate;
+    pl.q.scales = scales;
+    pl.q.status = a.status;
+    const zcu_result r = launch_qgemm(a, pl);
+    cudaFreeAsync(scratch, a.stream);
+    return r;
+}
+
+// matvec_q4_k, the batched family: one pass over the weights for up to 64 tokens.
+zcu_result launch_matvec_q4_k_tc(const LaunchArgs& a, const mv::MvArgs& v) {
+    const PMatvec& p = v.p;
+    const int m = v.m, k = (int)p.k, n = (int)p.n, nsb = k / 256;
+    ZCU_NEED(a, m <= 64, "matvec_q4_k (tcgen05): %d tokens in one step (at most 64)", m);
+    ZCU_NEED(a, k % 256 == 0, "matvec_q4_k (tcgen05): k = %d is not a multiple of 256", k);
+    if (v.has_rope) return zcu_fail(a, ZCU_E_UNSUPPORTED_KERNEL, "matvec + rope_append: only the mma.sync family fuses it");
+    if (v.peer.wait_slot != PEER_NONE || v.peer.push_slot != PEER_NONE)
+        return zcu_fail(a, ZCU_E_UNSUPPORTED_KERNEL, "matvec in a peer exchange: only the mma.sync family takes part");
+    const bool pair = (p.flags & MV_SILU_PAIR) != 0, norm = (p.flags & MV_NORM) != 0;
+    const int cols = 2 * m;
+    const int bn = cols > 64 ? 128 : cols > 32 ? 64 : cols > 16 ? 32 : 16;
+    const int cols_pad = (int)align_up((size_t)cols, (size_t)bn);
+    const int tiles_per_seg = (n + QT_ROWS - 1) / QT_ROWS, nseg = pair ? 2 : 1;
+    const int tiles = tiles_per_seg * nseg, sms = a.sm_count > 0 ? a.sm_count : 148;
+    // k slices: fill the SMs once, but keep at least four super-blocks per CTA
+    int slices = sms / tiles;
+    if (slices < 1) slices = 1;
+    if (slices > nsb / 4) slices = nsb / 4 > 0 ? nsb / 4 : 1;
+    const int sb_per_slice = (nsb + slices - 1) / slices;
+    slices = (nsb + sb_per_slice - 1) / sb_per_slice;
+    const size_t width = (size_t)n * nseg;
+    const size_t b_bytes = align_up((size_t)cols * k * 2, 1024), s_bytes = align_up((size_t)cols * nsb * 128, 1024),
+                 c_bytes = align_up((size_t)nsb * cols_pad * 4, 1024), p_bytes = align_up((size_t)slices * cols * width * 4, 1024);
+    unsigned char* scratch = nullptr;
+    if (cudaMallocAsync((void**)&scratch, b_bytes + s_bytes + c_bytes + p_bytes, a.stream) != cudaSuccess) {
+        cudaGetLastError();
+        return zcu_fail(a, ZCU_E_GPU, "matvec_q4_k (tcgen05): no memory for %zu bytes of scratch", b_bytes + s_bytes + c_bytes + p_bytes);
+    }
+    __half* bcol = reinterpret_cast<__half*>(scratch);
+    __half* bsum = reinterpret_cast<__half*>(scratch + b_bytes);
+    float* scales = reinterpret_cast<float*>(scratch + b_bytes + s_bytes);
+    float* part = reinterpret_cast<float*>(scratch + b_bytes + s_bytes + c_bytes);
+    if (cols_pad != cols) cudaMemsetAsync(scales, 0, c_bytes, a.stream);
+    const int xr = p.x_stride ? (int)p.x_stride * 4 : k;
+    cols_from_f32_kernel<<<dim3((unsigned)nsb, (unsigned)m), 64, 0, a.stream>>>(v.x, v.nw, bcol, bsum, scales, k, xr, norm ? 1 : 0, p.eps, cols_pad);
+    QtPlan pl{};
+    pl.w = v.w;
+    pl.w_rows = pair ? (uint64_t)p.half + n : (uint64_t)n;
+    pl.k = k;
+    pl.cols = cols;
+    pl.bn = bn;
+    pl.bcol = bcol;
+    pl.bsum = bsum;
+    pl.slices = slices;
+    pl.q.seg_rows = n;
+    pl.q.nseg = nseg;
+    pl.q.seg1_y = (int)p.half;
+    pl.q.tiles_per_seg = tiles_per_seg;
+    pl.q.cols = cols;
+    pl.q.cols_pad = cols_pad;
+    pl.q.nsb = nsb;
+    pl.q.sb_per_slice = sb_per_slice;
+    pl.q.out = part;
+    pl.q.slice_stride = (size_t)cols * width;
+    pl.q.out_stride = (uint32_t)width;
+    pl.q.col0 = 0;
+    pl.q.seg_out = (uint32_t)n;
+    pl.q.accumulate = 0;
+    pl.q.scales = scales;
+    pl.q.status = a.status;
+    zcu_result r = launch_qgemm(a, pl);
+    if (r == ZCU_OK) {
+        const size_t elems = (size_t)n * m;
+        cols_reduce_kernel<<<(unsigned)((elems + 255) / 256), 256, 0, a.stream>>>(part, v.out, n, m, slices, cols, pair ? 1 : 0,
+                                                                                (p.flags & MV_ACCUMULATE) ? 1 : 0, p.out_stride, p.col0);
+        const cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) r = zcu_fail(a, ZCU_E_GPU, "matvec_q4_k (tcgen05): launch failed: %s", cudaGetErrorString(e));
+    }
+    cudaFreeAsync(scratch, a.stream);
+    return r;
+}

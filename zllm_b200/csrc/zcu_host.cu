@@ -235,7 +235,7 @@ zcu_result dispatch_kernel(zcu_context* c, uint32_t kernel, uint32_t variant, co
         case ZCU_K_DELTA_RULE: return launch_delta_rule(a);
         case ZCU_K_EXT_PEER_WAIT: return launch_peer_wait(a);
         case ZCU_K_QUANTIZE_Q8: return launch_quantize_q8(a);
-        case ZCU_K_MATMUL_Q4_K: return launch_matmul_q4_k(a);
+        case ZCU_K_MATMUL_Q4_K: return variant == ZCU_VARIANT_PREFILL_BF16_TC ? launch_matmul_q4_k_tc(a) : launch_matmul_q4_k(a);
         case ZCU_K_MATMUL_Q8_0: return launch_matmul_q8_0(a);
         case ZCU_K_MATMUL_REDUCE: return launch_matmul_reduce(a);
         case ZCU_K_MATMUL_Q8_0_FLOAT: return launch_matmul_q8_0_float(a);
@@ -694,7 +694,7 @@ ZCU_EXPORT size_t zcu_artifact(uint32_t kernel, uint32_t variant, char* out, siz
     bool ok = name != nullptr;
     if (ok) {
         const bool is_matvec = kernel == ZCU_K_MATVEC_Q4_K || kernel == ZCU_K_MATVEC_Q8_0 || kernel == ZCU_K_MATVEC_BF16 || kernel == ZCU_K_MATVEC_F16;
-        const bool has_rung = kernel == ZCU_K_MATMUL_BF16 || kernel == ZCU_K_MATMUL_F16;  // tensor-core prefill rung
+        const bool has_rung = kernel == ZCU_K_MATMUL_BF16 || kernel == ZCU_K_MATMUL_F16 || kernel == ZCU_K_MATMUL_Q4_K;  // tensor-core prefill rung
         if (is_matvec) ok = matvec_variant_ok(kernel, variant);
         else ok = variant == 0 || (has_rung && variant == ZCU_VARIANT_PREFILL_BF16_TC) ||
                   (kernel == ZCU_K_DELTA_RULE && variant == ZCU_VARIANT_DELTA_CHUNK64) ||

@@ -141,6 +141,7 @@ zcu_result launch_matmul_q4_k(const LaunchArgs& a);
 zcu_result launch_matmul_q8_0(const LaunchArgs& a);
 zcu_result launch_matmul_reduce(const LaunchArgs& a);
 zcu_result launch_matmul_q8_0_float(const LaunchArgs& a);
+zcu_result launch_matmul_q4_k_tc(const LaunchArgs& a);       // the tcgen05 prefill rung of matmul_q4_k
 
 // The exchange a dispatch takes part in: a PPeer block trailing its parameter block (see peer.cuh). `outs`: the
 // ranges it stores to, which must lie in the local arena when it pushes. Fills `u` (both slots PEER_NONE without one).

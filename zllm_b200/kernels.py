@@ -36,7 +36,7 @@ DECODE_MAX_ROWS = 4    # kernels.decode_max_rows
 ATTN_MAX_GROUP = 8     # kernels.attn_max_group
 ATTN_MAX_GROUP_WIDE = 12
 
-FAMILY_SCALAR, FAMILY_MMA = 1, 2
+FAMILY_SCALAR, FAMILY_MMA, FAMILY_TCGEN05 = 1, 2, 3
 
 
 def variant(tiles: int = 0, splitk: int = 0, family: int = 0) -> int:
@@ -47,12 +47,17 @@ def variant(tiles: int = 0, splitk: int = 0, family: int = 0) -> int:
 # Candidates the tuning sweep tries (the cuda arm of MatvecVariant.candidates).
 # Tensor-core family: tiles in flight per warp (byte 0); scalar family: one shape.
 MATVEC_CANDIDATES = [variant(st, 0, FAMILY_MMA) for st in (2, 4, 6)] + [variant(0, 0, FAMILY_SCALAR)]
+# matvec_q4_k for up to 64 tokens in one pass over the weights (tcgen05, accumulators in tensor memory).
+MATVEC_BATCHED = variant(0, 0, FAMILY_TCGEN05)
+MATVEC_BATCHED_MAX_TOKENS = 64
 
 
 def matvec_variant_exists(ttype: str, k: int, v: int) -> bool:
     """Whether variant word `v` can run a (ttype, k) multiply: the tensor-core family needs Q8_0 rows of whole
     256-weight pieces (the default falls back to the scalar family there)."""
     family = (v >> 16) & 0xFF
+    if family == FAMILY_TCGEN05:
+        return ttype == "q4_k" and k % 256 == 0 and (v & 0xFFFF) == 0
     if ttype == "q8_0" and k % 256 != 0:
         return v == 0 or family == FAMILY_SCALAR
     return True
@@ -189,11 +194,12 @@ class Launcher:
         self.launch(QUANTIZE_Q8, QuantizeQ8(k, block, mode, eps), [x, qx, dx, nw if nw is not None else x], (k // 256, rows, 1))
 
     def matmul_quant(self, ttype, qx, w, out, dx, rows, n, k, col0=0, out_stride=None, accumulate=False, k_slice=None,
-                     slice_stride=0):
+                     slice_stride=0, variant=0):
+        """`variant` VARIANT_PREFILL_TC (Q4_K only): the same integer arithmetic on tcgen05, sums in f32."""
         k_slice = k if k_slice is None else k_slice
         p = MatmulQuant(rows, n, k, col0, out_stride if out_stride is not None else n, int(accumulate), k_slice, slice_stride)
         self.launch(MATMUL_Q4_K if ttype == "q4_k" else MATMUL_Q8_0, p, [qx, w, out, dx],
-                    (-(-n // 128), -(-rows // 32), -(-k // k_slice)))
+                    (-(-n // 128), -(-rows // 32), -(-k // k_slice)), variant)
 
     def matmul_q8_0_float(self, x, w, out, rows, n, k, col0=0, out_stride=None, accumulate=False, k_slice=None, slice_stride=0):
         """Q8_0 weights against f32 activations as they are (no rounding): exact f32, k-ordered."""

@@ -123,7 +123,8 @@ class DenseProgram:
     """
 
     def __init__(self, ctx, cfg: DenseConfig, weights, batch: int, alloc, shard: Shard | None = None, gather=None,
-                 variants: dict | None = None, fuse_rope: bool | None = None, arena=None, fuse_combine: bool | None = None):
+                 variants: dict | None = None, fuse_rope: bool | None = None, arena=None, fuse_combine: bool | None = None,
+                 batched: bool | None = None):
         self.ctx, self.cfg, self.w, self.B = ctx, cfg, weights, batch
         self.sh = shard or Shard()
         self.gather = gather
@@ -137,6 +138,10 @@ class DenseProgram:
         # rope_append inside the Q|K|V multiply's epilogue (one launch fewer per layer) where that is built:
         # 1, 2 or 4 sequences
         self.fuse_rope = (batch in (1, 2, 4)) if fuse_rope is None else fuse_rope
+        # Q4_K multiplies of 5..64 sequences in ONE pass over the weights (the tcgen05 family) instead of a pass per
+        # 2-4 sequences; one GPU (that family takes no part in a peer exchange)
+        can_batch = 4 < batch <= K.MATVEC_BATCHED_MAX_TOKENS and arena is None
+        self.batched = can_batch if batched is None else (bool(batched) and batch <= K.MATVEC_BATCHED_MAX_TOKENS and arena is None)
         # attn_combine by the last key block of each (sequence, KV head) inside attn_split (one launch fewer per
         # layer): the tensor-core fast path (f16 cache, GQA group <= 4, head_dim 64 or 128) with at most 128 blocks
         # of 128 keys, unless a form of attn_split was asked for
@@ -196,8 +201,11 @@ class DenseProgram:
 
     # ---- the launch list
     def _matvec(self, ttype, x, w, out, n, k, **kw):
-        self.L.matvec(ttype, x, w, out, n, k, m=self.B, variant=self.variants.get((ttype, n, k), 0), **kw)
-        self.launches_per_step += 1
+        v = self.variants.get((ttype, n, k), 0)
+        if v == 0 and self.batched and ttype == "q4_k" and k % 256 == 0 and "rope" not in kw:
+            v = K.MATVEC_BATCHED
+        self.L.matvec(ttype, x, w, out, n, k, m=self.B, variant=v, **kw)
+        self.launches_per_step += 3 if v == K.MATVEC_BATCHED else 1  # columns, multiply, reduction
 
     def _gather(self, buf, width):
         if self.gather is not None:
