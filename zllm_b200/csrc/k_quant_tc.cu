@@ -19,12 +19,12 @@
 // Products are exact (10 x 11 bits), sums are f32 over at most 256 terms per drain: within 1e-6 of the integer
 // arithmetic, against the 1e-5 bar of the reference's kernel checks.
 //
-// One CTA owns 128 weight rows x BN columns x a slice of k. Roles (16 warps):
-//   warp 0      TMA: the raw weight tiles (128 rows x 144 bytes per super-block), several super-blocks ahead
-//   warp 1      TMA: the columns' tiles (BN x 64 values, 128-byte swizzle), the unit sums, the column scales
-//   warp 2      allocates tensor memory; one lane issues the MMAs and commits stages / accumulators
-//   warps 4-7   decode the raw tile: thread r owns weight row r
-//   warps 8-15  drain: thread (quadrant, lane) owns a weight row's accumulators for half of the columns
+// One CTA owns 128 weight rows x BN columns x a slice of k. Roles (20 warps):
+//   warp 0       TMA: the raw weight tiles (128 rows x 144 bytes per super-block), several super-blocks ahead
+//   warp 1       TMA: the columns' tiles (BN x 64 values, 128-byte swizzle), the unit sums, the column scales
+//   warp 2       allocates tensor memory; one lane issues the MMAs and commits stages / accumulators
+//   warps 4-11   decode the raw tile: two groups of four warps take alternate 64-weight chunks, thread = weight row
+//   warps 12-19  drain: thread (quadrant, lane) owns a weight row's accumulators for half of the columns
 // Two accumulator sets alternate, so a super-block's products run while the one before it drains. Every wait is
 // bounded; one that gives up raises the CTA's abort flag, every role leaves, tensor memory is freed and the
 // context's status word reports it.
@@ -37,15 +37,25 @@
 
 namespace {
 
-constexpr int QT_ROWS = 128, QT_CHUNK = 64, QT_STAGES = 4, QT_THREADS = 512;
+constexpr int QT_ROWS = 128, QT_CHUNK = 64, QT_THREADS = 640;
 constexpr int RAW_ROW = 144, RAW_BYTES = QT_ROWS * RAW_ROW;   // a super-block of 128 rows as stored
 constexpr int A_BYTES = QT_ROWS * 128;                        // 128 rows x 64 f16
-constexpr int HDR_SLOTS = 4;
+constexpr int HDR_SLOTS = 4, CSC_SLOTS = 8;   // super-blocks whose row scales / column scales are in flight
 constexpr int MODE_PREFILL = 0, MODE_DECODE = 1;
 
-__host__ __device__ constexpr int raw_stages(int bn) { return bn > 64 ? 3 : 5; }
+// Ring depths. The decoded tiles are made on the SM (short latency: few stages); the columns' tiles and the raw
+// weights cross the chip (about a microsecond each): their rings must hold what the SM consumes in that time.
+// Up to 64 columns the decoded tiles live in TENSOR memory (the accumulators leave room: 4 BN <= 256 of the 512
+// columns), written there by tcgen05.st and read by the MMA as its A operand: the tile then crosses shared memory
+// neither on its way in nor out (16 KB each way per 64 weights of 128 rows, which bounded the narrow multiplies).
+__host__ __device__ constexpr bool a_in_tmem(int bn) { return bn <= 64; }
+constexpr int A_COL0 = 256, A_COLS = 32;   // tensor-memory columns of the A ring: 8 stages x 32 (64 f16 per row)
+__host__ __device__ constexpr int a_stages(int bn) { return bn > 64 ? 3 : 8; }
+__host__ __device__ constexpr int b_stages(int bn) { return bn > 64 ? 8 : bn > 32 ? 10 : bn > 16 ? 15 : 20; }
+__host__ __device__ constexpr int raw_stages(int bn) { return bn > 64 ? 2 : 6; }
 __host__ __device__ constexpr int qt_smem(int bn) {
-    return 1024 + QT_STAGES * A_BYTES + QT_STAGES * bn * 128 + raw_stages(bn) * RAW_BYTES + HDR_SLOTS * QT_ROWS * 8 + HDR_SLOTS * bn * 4 + 256;
+    return 1024 + (a_in_tmem(bn) ? 0 : a_stages(bn) * A_BYTES) + b_stages(bn) * bn * 128 + raw_stages(bn) * RAW_BYTES + HDR_SLOTS * QT_ROWS * 8 +
+           CSC_SLOTS * bn * 4 + 1024;
 }
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -58,17 +68,31 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t mbar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint32_t mbar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(mbar) : "memory");
 }
-// Waits for phase `parity`, at most 2^20 polls; gives up early when another role raised the abort flag.
+// Waits for phase `parity`. A waiting thread is SUSPENDED by the hardware (try_wait with a time hint) and resumes
+// when the phase completes, so the many waiting warps of this kernel leave the issue slots to the working ones; a
+// plain polling loop here took about half of them. The wait is bounded in time (about two seconds of SM clocks)
+// and ends early when another role raised the abort flag. Returns false (flag raised) when it gave up.
 __device__ __forceinline__ bool mbar_wait(uint32_t mbar, uint32_t parity, volatile uint32_t* abort_flag) {
-    for (int spin = 0; spin < (1 << 20); spin++) {
+    {   // the phase is usually complete already: test_wait answers at once
         uint32_t ok;
         asm volatile(
-            "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+            "{\n.reg .pred p;\nmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
             : "=r"(ok)
             : "r"(mbar), "r"(parity)
             : "memory");
         if (ok) return true;
-        if ((spin & 63) == 63 && *abort_flag) return false;
+    }
+    const long long t0 = clock64();
+    for (;;) {
+        uint32_t ok;
+        asm volatile(
+            "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\nselp.u32 %0, 1, 0, p;\n}\n"
+            : "=r"(ok)
+            : "r"(mbar), "r"(parity), "r"(100000u)   // suspend for up to 100 microseconds at a time
+            : "memory");
+        if (ok) return true;
+        if (*abort_flag) return false;
+        if (clock64() - t0 > 4000000000ll) break;
     }
     *abort_flag = 1;
     return false;
@@ -97,8 +121,27 @@ __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a, uint64_t b
                  "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
                  : "memory");
 }
+// The same with A read from tensor memory (lane = row, one 32-bit column = two consecutive K values).
+__device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n" ::"r"(d_tmem),
+                 "r"(a_tmem), "l"(b), "r"(idesc), "r"(accumulate)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, uint32_t r0, uint32_t r1, uint32_t r2, uint32_t r3, uint32_t r4, uint32_t r5, uint32_t r6,
+                                         uint32_t r7) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};\n" ::"r"(taddr), "r"(r0), "r"(r1), "r"(r2), "r"(r3),
+                 "r"(r4), "r"(r5), "r"(r6), "r"(r7)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
 __device__ __forceinline__ void umma_commit(uint32_t mbar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(mbar) : "memory");
+}
+// One lane of the (converged) warp.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile("{\n.reg .pred p;\nelect.sync _|p, 0xffffffff;\nselp.u32 %0, 1, 0, p;\n}\n" : "=r"(pred));
+    return pred != 0;
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
@@ -108,6 +151,26 @@ __device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t* r) {
                  : "r"(taddr));
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
+
+// Build with -DQT_TRACE to collect, for CTA (0, 0, 0), the clocks each role spends in its waits and in its work
+// (a profiling aid for this file alone; nothing reads it otherwise).
+#ifdef QT_TRACE
+__device__ unsigned long long qt_trace[32];
+#define QT_DECL() long long trace_acc__[20] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0}
+#define QT_MARK(slot, tprev) do { const long long now__ = clock64(); trace_acc__[slot] += now__ - tprev; tprev = now__; } while (0)
+#define QT_T0() const long long t0__ = clock64()
+#define QT_ADD(slot, cond) trace_acc__[slot] += clock64() - t0__
+#define QT_FLUSH(slot, cond)                                                                                      \
+    do {                                                                                                          \
+        if ((cond) && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) qt_trace[slot] += (unsigned long long)trace_acc__[slot]; \
+    } while (0)
+#else
+#define QT_DECL()
+#define QT_MARK(slot, tprev)
+#define QT_T0()
+#define QT_ADD(slot, cond)
+#define QT_FLUSH(slot, cond)
+#endif
 
 struct QtArgs {
     int seg_rows, nseg, seg1_y, tiles_per_seg;   // weight-row segments (two for a SILU_PAIR matrix: gate rows, up rows)
@@ -131,31 +194,45 @@ template <int BN>
 __global__ void __launch_bounds__(QT_THREADS, 1)
     qgemm_q4k_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap bmap,
                      const __grid_constant__ CUtensorMap smap, QtArgs q) {
-    constexpr int RS = raw_stages(BN), B_BYTES = BN * 128, CPT = BN / 2, TCOLS = 4 * BN < 32 ? 32 : 4 * BN;
+    constexpr int RS = raw_stages(BN), NA = a_stages(BN), NB = b_stages(BN), B_BYTES = BN * 128, CPT = BN / 2, TCOLS = 512;
+    constexpr bool ATM = a_in_tmem(BN);
+    static_assert(!ATM || (4 * BN <= A_COL0 && A_COL0 + NA * A_COLS <= TCOLS), "accumulators and the A ring share tensor memory");
+    // The columns' tiles of a super-block share one barrier pair where the ring holds whole super-blocks (narrow
+    // tiles): the issuing thread then waits and commits once per super-block instead of once per tile.
+    constexpr int G = BN <= 64 ? 5 : 1;
+    static_assert(NB % G == 0, "the column ring holds whole groups");
+    // Up to 32 columns tensor memory has room for whole decoded super-blocks (4 x 32 columns and 8 for the mins),
+    // two or three of them: the issuing warp then waits, issues (17 MMAs) and commits once per super-block, and
+    // the decoders run a super-block ahead. (Wider tiles keep the 64-weight stages.)
+    constexpr bool SBM = BN <= 32;
+    constexpr int SB_COLS = 136, SB_COL0 = 4 * BN, SLOTS = (TCOLS - SB_COL0) / SB_COLS;
+    static_assert(!SBM || (SLOTS >= 2 && 2 * SLOTS <= NA), "super-block slots and their barriers");
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     unsigned char* a_ring = smem;
-    unsigned char* b_ring = a_ring + QT_STAGES * A_BYTES;
-    unsigned char* raw_ring = b_ring + QT_STAGES * B_BYTES;
+    unsigned char* b_ring = a_ring + (ATM ? 0 : NA * A_BYTES);
+    unsigned char* raw_ring = b_ring + NB * B_BYTES;
     float2* hdr = reinterpret_cast<float2*>(raw_ring + RS * RAW_BYTES);          // [slot][row]: d, dmin
     float* csc = reinterpret_cast<float*>(hdr + HDR_SLOTS * QT_ROWS);            // [slot][BN]: the columns' scales
-    uint64_t* bars = reinterpret_cast<uint64_t*>(csc + HDR_SLOTS * BN);
-    const uint32_t full_a0 = smem_u32(bars), full_b0 = full_a0 + 8 * QT_STAGES, empty0 = full_b0 + 8 * QT_STAGES,
-                   raw_full0 = empty0 + 8 * QT_STAGES, raw_empty0 = raw_full0 + 8 * RS, tfull0 = raw_empty0 + 8 * RS,
-                   tempty0 = tfull0 + 16;
-    uint32_t* holder = reinterpret_cast<uint32_t*>(bars + 3 * QT_STAGES + 2 * RS + 4);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(csc + CSC_SLOTS * BN);
+    const uint32_t full_a0 = smem_u32(bars), empty_a0 = full_a0 + 8 * NA, full_b0 = empty_a0 + 8 * NA, empty_b0 = full_b0 + 8 * NB,
+                   raw_full0 = empty_b0 + 8 * NB, raw_empty0 = raw_full0 + 8 * RS, tfull0 = raw_empty0 + 8 * RS, tempty0 = tfull0 + 16;
+    uint32_t* holder = reinterpret_cast<uint32_t*>(bars + 2 * NA + 2 * NB + 2 * RS + 4);
     volatile uint32_t* abort_flag = holder + 1;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < QT_STAGES; s++) {
-            mbar_init(full_a0 + 8 * s, 128);
+        for (int s = 0; s < NA; s++) {
+            mbar_init(full_a0 + 8 * s, 4);
+            mbar_init(empty_a0 + 8 * s, 1);
+        }
+        for (int s = 0; s < NB; s++) {
             mbar_init(full_b0 + 8 * s, 1);
-            mbar_init(empty0 + 8 * s, 1);
+            mbar_init(empty_b0 + 8 * s, 1);
         }
         for (int s = 0; s < RS; s++) {
             mbar_init(raw_full0 + 8 * s, 1);
-            mbar_init(raw_empty0 + 8 * s, 128);
+            mbar_init(raw_empty0 + 8 * s, 8);
         }
         for (int a = 0; a < 2; a++) {
             mbar_init(tfull0 + 8 * a, 1);
@@ -172,6 +249,9 @@ __global__ void __launch_bounds__(QT_THREADS, 1)
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = holder[0];
+#ifdef QT_TRACE
+    const long long kernel_t0 = clock64();
+#endif
 
     const int seg = (int)blockIdx.x / q.tiles_per_seg, tile = (int)blockIdx.x % q.tiles_per_seg;
     const int row0 = tile * QT_ROWS;                          // within the segment
@@ -179,152 +259,358 @@ __global__ void __launch_bounds__(QT_THREADS, 1)
     const int c0 = (int)blockIdx.y * BN, z = (int)blockIdx.z;
     const int sb_lo = min(q.nsb, z * q.sb_per_slice), sb_hi = min(q.nsb, sb_lo + q.sb_per_slice);
     bool gave_up = false;
+    QT_DECL();
 
+    // (The two copy warps run their loops as whole warps too, one elected lane issuing: addresses stay warp-uniform.)
     if (warp == 0) {
-        if (lane == 0) {
-            int rs = 0;
-            uint32_t rphase = 0;
-            for (int sb = sb_lo; sb < sb_hi; sb++) {
-                if (!mbar_wait(raw_empty0 + 8 * rs, rphase ^ 1u, abort_flag)) {
-                    gave_up = true;
-                    break;
-                }
-                mbar_expect_tx(raw_full0 + 8 * rs, RAW_BYTES);
-                tma_load_2d(smem_u32(raw_ring + rs * RAW_BYTES), &wmap, sb * RAW_ROW, y0, raw_full0 + 8 * rs);
-                if (++rs == RS) rs = 0, rphase ^= 1u;
+        int rs = 0;
+        uint32_t rphase = 0;
+        for (int sb = sb_lo; sb < sb_hi; sb++) {
+            bool ok;
+            {
+                QT_T0();
+                ok = mbar_wait(raw_empty0 + 8 * rs, rphase ^ 1u, abort_flag);
+                QT_ADD(0, true);
             }
-            if (gave_up)
-                for (int i = 0; i < 200; i++) __nanosleep(1000);
-        }
-    } else if (warp == 1) {
-        if (lane == 0) {
-            int s = 0;
-            uint32_t phase = 0;
-            for (int sb = sb_lo; sb < sb_hi && !gave_up; sb++) {
-                for (int c = 0; c < 5; c++) {
-                    if (!mbar_wait(empty0 + 8 * s, phase ^ 1u, abort_flag)) {
-                        gave_up = true;
-                        break;
-                    }
-                    const uint32_t dst = smem_u32(b_ring + s * B_BYTES), fb = full_b0 + 8 * s;
-                    if (c < 4) {
-                        mbar_expect_tx(fb, B_BYTES);
-                        tma_load_2d(dst, &bmap, (sb * 256 + c * QT_CHUNK) * 2, c0, fb);
-                    } else {
-                        // the unit sums of this super-block, and the columns' scales for it
-                        mbar_expect_tx(fb, B_BYTES + BN * 4);
-                        tma_load_2d(dst, &smap, sb * 128, c0, fb);
-                        bulk_load(smem_u32(csc + ((sb - sb_lo) & (HDR_SLOTS - 1)) * BN), q.scales + (size_t)sb * q.cols_pad + c0, BN * 4, fb);
-                    }
-                    if (++s == QT_STAGES) s = 0, phase ^= 1u;
-                }
-            }
-            if (gave_up)
-                for (int i = 0; i < 200; i++) __nanosleep(1000);
-        }
-    } else if (warp == 2) {
-        if (lane == 0) {
-            const uint32_t idesc = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(QT_ROWS >> 4) << 24);
-            int s = 0, acc = 0;
-            uint32_t phase = 0, acc_phase = 0;
-            for (int sb = sb_lo; sb < sb_hi && !gave_up; sb++) {
-                if (!mbar_wait(tempty0 + 8 * acc, acc_phase ^ 1u, abort_flag)) {
-                    gave_up = true;
-                    break;
-                }
-                tc_fence_after();
-                const uint32_t d1 = tmem_base + (uint32_t)acc * 2 * BN, d2 = d1 + BN;
-                for (int c = 0; c < 5; c++) {
-                    if (!mbar_wait(full_a0 + 8 * s, phase, abort_flag) || !mbar_wait(full_b0 + 8 * s, phase, abort_flag)) {
-                        gave_up = true;
-                        break;
-                    }
-                    tc_fence_after();
-                    const uint64_t da = umma_desc_sw128(smem_u32(a_ring + s * A_BYTES)), db = umma_desc_sw128(smem_u32(b_ring + s * B_BYTES));
-                    if (c < 4) {
-#pragma unroll
-                        for (int kk = 0; kk < 4; kk++) umma_f16(d1, da + (uint64_t)(2 * kk), db + (uint64_t)(2 * kk), idesc, (c | kk) != 0);
-                    } else {
-                        umma_f16(d2, da, db, idesc, 0u);
-                    }
-                    umma_commit(empty0 + 8 * s);
-                    if (++s == QT_STAGES) s = 0, phase ^= 1u;
-                }
-                if (gave_up) break;
-                umma_commit(tfull0 + 8 * acc);
-                if (++acc == 2) acc = 0, acc_phase ^= 1u;
-            }
-        }
-    } else if (warp >= 4 && warp < 8) {
-        // ---- raw tile -> the tensor cores' operand. Thread r owns weight row r.
-        const int r = (int)threadIdx.x - 128;
-        const uint32_t swz = (uint32_t)(r & 7);
-        int s = 0, rs = 0;
-        uint32_t phase = 0, rphase = 0;
-        for (int sb = sb_lo; sb < sb_hi && !gave_up; sb++) {
-            if (!mbar_wait(raw_full0 + 8 * rs, rphase, abort_flag)) {
+            if (!__all_sync(0xffffffffu, ok)) {
                 gave_up = true;
                 break;
             }
-            const unsigned char* raw = raw_ring + rs * RAW_BYTES + r * RAW_ROW;
-            const uint4 h = *reinterpret_cast<const uint4*>(raw);
-            // 6-bit scales and mins of the eight units (src/ref/tensor.zig:95-104)
-            const uint32_t scw[2] = {h.y & 0x3f3f3f3fu, (h.w & 0x0f0f0f0fu) | ((h.y >> 2) & 0x30303030u)};
-            const uint32_t mnw[2] = {h.z & 0x3f3f3f3fu, ((h.w >> 4) & 0x0f0f0f0fu) | ((h.z >> 2) & 0x30303030u)};
-            hdr[((sb - sb_lo) & (HDR_SLOTS - 1)) * QT_ROWS + r] =
-                make_float2(__half2float(__ushort_as_half((unsigned short)(h.x & 0xffffu))), __half2float(__ushort_as_half((unsigned short)(h.x >> 16))));
-            for (int c = 0; c < 5; c++) {
-                if (!mbar_wait(empty0 + 8 * s, phase ^ 1u, abort_flag)) {
+            if (elect_one()) {
+                mbar_expect_tx(raw_full0 + 8 * rs, RAW_BYTES);
+                tma_load_2d(smem_u32(raw_ring + rs * RAW_BYTES), &wmap, sb * RAW_ROW, y0, raw_full0 + 8 * rs);
+            }
+            __syncwarp();
+            if (++rs == RS) rs = 0, rphase ^= 1u;
+        }
+        QT_FLUSH(0, lane == 0);
+        if (gave_up)
+            for (int i = 0; i < 200; i++) __nanosleep(1000);
+    } else if (warp == 1) {
+        int s = 0;
+        uint32_t phase = 0;
+        for (int sb = sb_lo; sb < sb_hi && !gave_up; sb++) {
+            if constexpr (G == 5) {
+                // the super-block's five tiles and its column scales complete one barrier
+                bool ok;
+                {
+                    QT_T0();
+                    ok = mbar_wait(empty_b0 + 8 * (s / G), phase ^ 1u, abort_flag);
+                    QT_ADD(1, true);
+                }
+                if (!__all_sync(0xffffffffu, ok)) {
                     gave_up = true;
                     break;
                 }
-                unsigned char* arow = a_ring + s * A_BYTES + r * 128;
-                if (c < 4) {
-                    const uint4 qa = *reinterpret_cast<const uint4*>(raw + 16 + 32 * c), qb = *reinterpret_cast<const uint4*>(raw + 32 + 32 * c);
-                    const uint32_t qw[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
-                    const int u = 2 * c;  // units 2c (low nibbles) and 2c + 1 (high nibbles)
-                    const float sl = (float)((scw[u >> 2] >> (8 * (u & 3))) & 0xffu), sh = (float)((scw[(u + 1) >> 2] >> (8 * ((u + 1) & 3))) & 0xffu);
-                    const __half2 scl = __float2half2_rn(sl), offl = __float2half2_rn(-1024.0f * sl);
-                    const __half2 sch = __float2half2_rn(sh), offh = __float2half2_rn(-1024.0f * sh);
+                if (elect_one()) {
+                    const uint32_t fb = full_b0 + 8 * (s / G), dst = smem_u32(b_ring + s * B_BYTES);
+                    mbar_expect_tx(fb, 5 * B_BYTES + BN * 4);
+#pragma unroll
+                    for (int c = 0; c < 4; c++) tma_load_2d(dst + c * B_BYTES, &bmap, (sb * 256 + c * QT_CHUNK) * 2, c0, fb);
+                    tma_load_2d(dst + 4 * B_BYTES, &smap, sb * 128, c0, fb);
+                    bulk_load(smem_u32(csc + ((sb - sb_lo) & (CSC_SLOTS - 1)) * BN), q.scales + (size_t)sb * q.cols_pad + c0, BN * 4, fb);
+                }
+                __syncwarp();
+                s += 5;
+                if (s == NB) s = 0, phase ^= 1u;
+            } else {
+                for (int c = 0; c < 5; c++) {
+                    bool ok;
+                    {
+                        QT_T0();
+                        ok = mbar_wait(empty_b0 + 8 * s, phase ^ 1u, abort_flag);
+                        QT_ADD(1, true);
+                    }
+                    if (!__all_sync(0xffffffffu, ok)) {
+                        gave_up = true;
+                        break;
+                    }
+                    if (elect_one()) {
+                        const uint32_t fb = full_b0 + 8 * s, dst = smem_u32(b_ring + s * B_BYTES);
+                        if (c < 4) {
+                            mbar_expect_tx(fb, B_BYTES);
+                            tma_load_2d(dst, &bmap, (sb * 256 + c * QT_CHUNK) * 2, c0, fb);
+                        } else {
+                            // the unit sums of this super-block, and the columns' scales for it
+                            mbar_expect_tx(fb, B_BYTES + BN * 4);
+                            tma_load_2d(dst, &smap, sb * 128, c0, fb);
+                            bulk_load(smem_u32(csc + ((sb - sb_lo) & (CSC_SLOTS - 1)) * BN), q.scales + (size_t)sb * q.cols_pad + c0, BN * 4, fb);
+                        }
+                    }
+                    __syncwarp();
+                    if (++s == NB) s = 0, phase ^= 1u;
+                }
+            }
+        }
+        QT_FLUSH(1, lane == 0);
+        if (gave_up)
+            for (int i = 0; i < 200; i++) __nanosleep(1000);
+    } else if (warp == 2) {
+        // The whole warp runs this loop, so that its addresses and descriptors stay warp-uniform (they feed the
+        // instructions from uniform registers); one elected lane issues the MMAs and the commits.
+        const uint32_t idesc = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(QT_ROWS >> 4) << 24);
+        const uint64_t a_desc0 = umma_desc_sw128(smem_u32(a_ring)), b_desc0 = umma_desc_sw128(smem_u32(b_ring));
+        int s = 0, t = 0, acc = 0;
+        uint32_t phase = 0, bphase = 0, acc_phase = 0;
+        for (int sb = sb_lo; sb < sb_hi && !gave_up; sb++) {
+            bool ok;
+            {
+                QT_T0();
+                ok = mbar_wait(tempty0 + 8 * acc, acc_phase ^ 1u, abort_flag);
+                QT_ADD(2, true);
+            }
+            if (!__all_sync(0xffffffffu, ok)) {
+                gave_up = true;
+                break;
+            }
+            tc_fence_after();
+            const uint32_t d1 = tmem_base + (uint32_t)acc * 2 * BN, d2 = d1 + BN;
+            if constexpr (SBM) {
+                const int sbi = sb - sb_lo, slot = sbi % SLOTS;
+                const uint32_t sphase = (uint32_t)(sbi / SLOTS) & 1u;
+                {
+                    QT_T0();
+                    ok = mbar_wait(full_a0 + 8 * (2 * slot), sphase, abort_flag) && mbar_wait(full_a0 + 8 * (2 * slot + 1), sphase, abort_flag);
+                    QT_ADD(3, true);
+                }
+                {
+                    QT_T0();
+                    ok = ok && mbar_wait(full_b0 + 8 * (t / G), bphase, abort_flag);
+                    QT_ADD(4, true);
+                }
+                if (!__all_sync(0xffffffffu, ok)) {
+                    gave_up = true;
+                    break;
+                }
+                QT_T0();
+                tc_fence_after();
+                const uint32_t ta = tmem_base + (uint32_t)(SB_COL0 + slot * SB_COLS);
+                const uint64_t db = b_desc0 + (uint64_t)(t * (B_BYTES >> 4));
+                if (elect_one()) {
+#pragma unroll
+                    for (int c = 0; c < 4; c++)
+#pragma unroll
+                        for (int kk = 0; kk < 4; kk++)
+                            umma_f16_ts(d1, ta + (uint32_t)(32 * c + 8 * kk), db + (uint64_t)(c * (B_BYTES >> 4) + 2 * kk), idesc, (c | kk) != 0);
+                    umma_f16_ts(d2, ta + 128u, db + (uint64_t)(4 * (B_BYTES >> 4)), idesc, 0u);
+                    umma_commit(empty_a0 + 8 * slot);
+                    umma_commit(empty_b0 + 8 * (t / G));
+                    umma_commit(tfull0 + 8 * acc);
+                }
+                __syncwarp();
+                QT_ADD(11, true);
+                t += 5;
+                if (t == NB) t = 0, bphase ^= 1u;
+                if (++acc == 2) acc = 0, acc_phase ^= 1u;
+                continue;
+            }
+            for (int c = 0; c < 5; c++) {
+                {
+                    QT_T0();
+                    ok = mbar_wait(full_a0 + 8 * s, phase, abort_flag);
+                    QT_ADD(3, true);
+                }
+                if (t % G == 0) {
+                    QT_T0();
+                    ok = ok && mbar_wait(full_b0 + 8 * (t / G), bphase, abort_flag);
+                    QT_ADD(4, true);
+                }
+                if (!__all_sync(0xffffffffu, ok)) {
+                    gave_up = true;
+                    break;
+                }
+                QT_T0();
+                tc_fence_after();
+                const uint64_t da = a_desc0 + (uint64_t)(s * (A_BYTES >> 4)), db = b_desc0 + (uint64_t)(t * (B_BYTES >> 4));
+                const uint32_t ta = tmem_base + (uint32_t)(A_COL0 + s * A_COLS);
+                if (elect_one()) {
+                    if (c < 4) {
+#pragma unroll
+                        for (int kk = 0; kk < 4; kk++) {
+                            if (ATM) umma_f16_ts(d1, ta + 8u * kk, db + (uint64_t)(2 * kk), idesc, (c | kk) != 0);
+                            else umma_f16(d1, da + (uint64_t)(2 * kk), db + (uint64_t)(2 * kk), idesc, (c | kk) != 0);
+                        }
+                    } else {
+                        if (ATM) umma_f16_ts(d2, ta, db, idesc, 0u);
+                        else umma_f16(d2, da, db, idesc, 0u);
+                    }
+                    umma_commit(empty_a0 + 8 * s);
+                    if (t % G == G - 1) umma_commit(empty_b0 + 8 * (t / G));
+                    if (c == 4) umma_commit(tfull0 + 8 * acc);
+                }
+                __syncwarp();
+                QT_ADD(11, true);
+                if (++s == NA) s = 0, phase ^= 1u;
+                if (++t == NB) t = 0, bphase ^= 1u;
+            }
+            if (gave_up) break;
+            if (++acc == 2) acc = 0, acc_phase ^= 1u;
+        }
+        QT_FLUSH(2, lane == 0);
+        QT_FLUSH(3, lane == 0);
+        QT_FLUSH(4, lane == 0);
+        QT_FLUSH(11, lane == 0);
+    } else if (warp >= 4 && warp < 12) {
+        // ---- raw tile -> the tensor cores' A operand. Two groups of four warps take alternate 64-weight chunks
+        //      (so two chunks are in flight per scheduler); in a group, thread r owns weight row r.
+        const int r = ((int)threadIdx.x - 128) & 127, grp = ((int)threadIdx.x - 128) >> 7;
+        const uint32_t swz = (uint32_t)(r & 7);
+        const int total = 5 * (sb_hi - sb_lo);
+        int cur = -1;                       // the super-block (index within the slice) whose raw tile this thread holds
+        const unsigned char* raw = nullptr;
+        uint32_t scw[2] = {0, 0}, mnw[2] = {0, 0}, dword = 0;
+        for (int ci = grp; ci < total && !gave_up; ci += 2) {
+            const int sbi = ci / 5, c = ci - 5 * sbi, s = SBM ? sbi % SLOTS : ci % NA;
+            const uint32_t phase = (uint32_t)(SBM ? sbi / SLOTS : ci / NA) & 1u;
+            const bool first_of_sb = sbi != cur, last_of_sb = (ci + 2) / 5 != sbi || ci + 2 >= total;
+            if (sbi != cur) {
+                if (cur >= 0) {
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(raw_empty0 + 8 * (cur % RS));
+                }
+                cur = sbi;
+                bool ok;
+                {
+                    QT_T0();
+                    ok = mbar_wait(raw_full0 + 8 * (sbi % RS), (uint32_t)(sbi / RS) & 1u, abort_flag);
+                    QT_ADD(5, threadIdx.x == 128);
+                }
+                if (!ok) {
+                    gave_up = true;
+                    break;
+                }
+                raw = raw_ring + (sbi % RS) * RAW_BYTES + r * RAW_ROW;
+                const uint4 h = *reinterpret_cast<const uint4*>(raw);
+                // 6-bit scales and mins of the eight units (src/ref/tensor.zig:95-104)
+                scw[0] = h.y & 0x3f3f3f3fu, scw[1] = (h.w & 0x0f0f0f0fu) | ((h.y >> 2) & 0x30303030u);
+                mnw[0] = h.z & 0x3f3f3f3fu, mnw[1] = ((h.w >> 4) & 0x0f0f0f0fu) | ((h.z >> 2) & 0x30303030u);
+                dword = h.x;
+            }
+            bool oka = true;
+            if (!SBM || first_of_sb) {
+                QT_T0();
+                oka = mbar_wait(empty_a0 + 8 * s, phase ^ 1u, abort_flag);
+                QT_ADD(6, threadIdx.x == 128);
+            }
+            if (!oka) {
+                gave_up = true;
+                break;
+            }
+            QT_T0();
+#ifdef QT_TRACE
+            long long td__ = clock64();
+#endif
+            unsigned char* arow = a_ring + s * A_BYTES + r * 128;
+            const uint32_t ta = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) +
+                                (uint32_t)(SBM ? SB_COL0 + s * SB_COLS + (c < 4 ? 32 * c : 128) : A_COL0 + s * A_COLS);
+            if (ATM) tc_fence_after();  // the wait above ordered this stage's last reads (the MMAs) before these writes
+            if (c < 4) {
+#if defined(QT_EXP) && QT_EXP == 5
+                if (ATM) {
+                    const uint32_t v = (uint32_t)c;
+                    tmem_st8(ta, v, v, v, v, v, v, v, v);
+                    tmem_st8(ta + 8u, v, v, v, v, v, v, v, v);
+                    tmem_st8(ta + 16u, v, v, v, v, v, v, v, v);
+                    tmem_st8(ta + 24u, v, v, v, v, v, v, v, v);
+                }
+                if (false) {
+#endif
+                const uint4 qa = *reinterpret_cast<const uint4*>(raw + 16 + 32 * c), qb = *reinterpret_cast<const uint4*>(raw + 32 + 32 * c);
+                const uint32_t qw[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+                // units 2c (low nibbles) and 2c + 1 (high nibbles): bytes 2c & 3 and (2c + 1) & 3 of word c >> 1
+                const uint32_t sw = c < 2 ? scw[0] : scw[1];
+                const __half2 scl = __half2half2(__int2half_rn((int)((sw >> (16 * (c & 1))) & 0xffu)));
+                const __half2 sch = __half2half2(__int2half_rn((int)((sw >> (16 * (c & 1) + 8)) & 0xffu)));
+                const __half2 m1024 = __half2half2(__int2half_rn(-1024));
+                const __half2 offl = __hmul2(scl, m1024), offh = __hmul2(sch, m1024);   // exact: at most 63 * 1024
+                uint4 lo[4], hi[4];
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    // 16 bytes = positions 8i .. 8i+7 of the unit: values (0,2,1,3 | 4,6,5,7) of two code words
+                    const uint32_t w0 = qw[2 * i], w1 = qw[2 * i + 1];
+                    lo[i].x = scaled_pair(w0 & 0x000f000fu, scl, offl);
+                    lo[i].y = scaled_pair((w0 >> 8) & 0x000f000fu, scl, offl);
+                    lo[i].z = scaled_pair(w1 & 0x000f000fu, scl, offl);
+                    lo[i].w = scaled_pair((w1 >> 8) & 0x000f000fu, scl, offl);
+                    hi[i].x = scaled_pair((w0 >> 4) & 0x000f000fu, sch, offh);
+                    hi[i].y = scaled_pair((w0 >> 12) & 0x000f000fu, sch, offh);
+                    hi[i].z = scaled_pair((w1 >> 4) & 0x000f000fu, sch, offh);
+                    hi[i].w = scaled_pair((w1 >> 12) & 0x000f000fu, sch, offh);
+                }
+#if defined(QT_EXP) && QT_EXP == 4
+                if (lo[0].x == 0x12345678u && hi[3].w == lo[1].y + lo[2].z + hi[0].x + hi[1].y + hi[2].z) {
+#else
+                if (ATM) {
+#endif
+                    // columns 0..15: the low unit (two values a column), 16..31: the high unit
+                    tmem_st8(ta, lo[0].x, lo[0].y, lo[0].z, lo[0].w, lo[1].x, lo[1].y, lo[1].z, lo[1].w);
+                    tmem_st8(ta + 8u, lo[2].x, lo[2].y, lo[2].z, lo[2].w, lo[3].x, lo[3].y, lo[3].z, lo[3].w);
+                    tmem_st8(ta + 16u, hi[0].x, hi[0].y, hi[0].z, hi[0].w, hi[1].x, hi[1].y, hi[1].z, hi[1].w);
+                    tmem_st8(ta + 24u, hi[2].x, hi[2].y, hi[2].z, hi[2].w, hi[3].x, hi[3].y, hi[3].z, hi[3].w);
+                } else {
 #pragma unroll
                     for (int i = 0; i < 4; i++) {
-                        // 16 bytes = positions 8i .. 8i+7 of the unit: values (0,2,1,3 | 4,6,5,7) of two code words
-                        const uint32_t w0 = qw[2 * i], w1 = qw[2 * i + 1];
-                        uint4 lo, hi;
-                        lo.x = scaled_pair(w0 & 0x000f000fu, scl, offl);
-                        lo.y = scaled_pair((w0 >> 8) & 0x000f000fu, scl, offl);
-                        lo.z = scaled_pair(w1 & 0x000f000fu, scl, offl);
-                        lo.w = scaled_pair((w1 >> 8) & 0x000f000fu, scl, offl);
-                        hi.x = scaled_pair((w0 >> 4) & 0x000f000fu, sch, offh);
-                        hi.y = scaled_pair((w0 >> 12) & 0x000f000fu, sch, offh);
-                        hi.z = scaled_pair((w1 >> 4) & 0x000f000fu, sch, offh);
-                        hi.w = scaled_pair((w1 >> 12) & 0x000f000fu, sch, offh);
-                        *reinterpret_cast<uint4*>(arow + (((uint32_t)i ^ swz) << 4)) = lo;
-                        *reinterpret_cast<uint4*>(arow + (((uint32_t)(i + 4) ^ swz) << 4)) = hi;
+                        *reinterpret_cast<uint4*>(arow + (((uint32_t)i ^ swz) << 4)) = lo[i];
+                        *reinterpret_cast<uint4*>(arow + (((uint32_t)(i + 4) ^ swz) << 4)) = hi[i];
                     }
+                }
+#if defined(QT_EXP) && QT_EXP == 5
+                }
+#endif
+            } else {
+                // the mins, each twice: K positions 2u, 2u + 1 meet the two terms of unit u's column sum
+                uint4 m0, m1;
+                auto dup = [](uint32_t byte) {
+                    const __half2 v = __half2half2(__int2half_rn((int)byte));
+                    return *reinterpret_cast<const uint32_t*>(&v);
+                };
+                m0.x = dup(mnw[0] & 0xffu), m0.y = dup((mnw[0] >> 8) & 0xffu), m0.z = dup((mnw[0] >> 16) & 0xffu), m0.w = dup(mnw[0] >> 24);
+                m1.x = dup(mnw[1] & 0xffu), m1.y = dup((mnw[1] >> 8) & 0xffu), m1.z = dup((mnw[1] >> 16) & 0xffu), m1.w = dup(mnw[1] >> 24);
+                if (ATM) {
+                    tmem_st8(ta, m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w);
                 } else {
-                    // the mins, each twice: K positions 2u, 2u + 1 meet the two terms of unit u's column sum
-                    uint4 m0, m1;
-                    auto dup = [](uint32_t byte) {
-                        const __half2 v = __float2half2_rn((float)byte);
-                        return *reinterpret_cast<const uint32_t*>(&v);
-                    };
-                    m0.x = dup(mnw[0] & 0xffu), m0.y = dup((mnw[0] >> 8) & 0xffu), m0.z = dup((mnw[0] >> 16) & 0xffu), m0.w = dup(mnw[0] >> 24);
-                    m1.x = dup(mnw[1] & 0xffu), m1.y = dup((mnw[1] >> 8) & 0xffu), m1.z = dup((mnw[1] >> 16) & 0xffu), m1.w = dup(mnw[1] >> 24);
                     *reinterpret_cast<uint4*>(arow + ((0u ^ swz) << 4)) = m0;
                     *reinterpret_cast<uint4*>(arow + ((1u ^ swz) << 4)) = m1;
                 }
-                // these stores are read through the async proxy (the tensor cores)
-                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-                mbar_arrive(full_a0 + 8 * s);
-                if (++s == QT_STAGES) s = 0, phase ^= 1u;
+                // the row's super-scales, for the drain of this super-block (it starts after this chunk's MMA)
+                hdr[(sbi & (HDR_SLOTS - 1)) * QT_ROWS + r] = make_float2(__half2float(__ushort_as_half((unsigned short)(dword & 0xffffu))),
+                                                                        __half2float(__ushort_as_half((unsigned short)(dword >> 16))));
             }
-            mbar_arrive(raw_empty0 + 8 * rs);
-            if (++rs == RS) rs = 0, rphase ^= 1u;
+            QT_MARK(15, td__);
+            if (SBM) {
+                if (last_of_sb) {   // this group's chunks of the super-block are written: publish them
+                    tmem_st_wait();
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(full_a0 + 8 * (2 * s + grp));
+                }
+            } else {
+                if (ATM) {
+                    tmem_st_wait();
+                    tc_fence_before();
+                } else {
+                    // these stores are read through the async proxy (the tensor cores)
+                    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(full_a0 + 8 * s);
+            }
+            QT_MARK(17, td__);
+            QT_ADD(7, threadIdx.x == 128);
         }
-    } else if (warp >= 8) {
+        if (cur >= 0 && !gave_up) {
+            __syncwarp();
+            if (lane == 0) mbar_arrive(raw_empty0 + 8 * (cur % RS));
+        }
+        QT_FLUSH(5, threadIdx.x == 128);
+        QT_FLUSH(6, threadIdx.x == 128);
+        QT_FLUSH(7, threadIdx.x == 128);
+        QT_FLUSH(15, threadIdx.x == 128);
+        QT_FLUSH(16, threadIdx.x == 128);
+        QT_FLUSH(17, threadIdx.x == 128);
+    } else if (warp >= 12) {
         // ---- drain. Thread (quad, lane) owns weight row quad * 32 + lane and CPT of the CTA's columns.
-        const int quad = warp & 3, chalf = (warp - 8) >> 2;
+        const int quad = warp & 3, chalf = (warp - 12) >> 2;
         const int r = quad * 32 + lane;
         float accv[CPT];
 #pragma unroll
@@ -332,14 +618,20 @@ __global__ void __launch_bounds__(QT_THREADS, 1)
         int acc = 0;
         uint32_t acc_phase = 0;
         for (int sb = sb_lo; sb < sb_hi; sb++) {
-            if (!__all_sync(0xffffffffu, mbar_wait(tfull0 + 8 * acc, acc_phase, abort_flag))) {
+            bool ok;
+            {
+                QT_T0();
+                ok = __all_sync(0xffffffffu, mbar_wait(tfull0 + 8 * acc, acc_phase, abort_flag));
+                QT_ADD(8, threadIdx.x == 384);
+            }
+            if (!ok) {
                 gave_up = true;
                 break;
             }
+            QT_T0();
             tc_fence_after();
-            const int slot = (sb - sb_lo) & (HDR_SLOTS - 1);
-            const float2 dd = hdr[slot * QT_ROWS + r];
-            const float* cs = csc + slot * BN + chalf * CPT;
+            const float2 dd = hdr[((sb - sb_lo) & (HDR_SLOTS - 1)) * QT_ROWS + r];
+            const float* cs = csc + ((sb - sb_lo) & (CSC_SLOTS - 1)) * BN + chalf * CPT;
             const uint32_t t1 = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)acc * 2 * BN + (uint32_t)(chalf * CPT), t2 = t1 + BN;
 #pragma unroll
             for (int i0 = 0; i0 < CPT; i0 += 8) {
@@ -353,8 +645,11 @@ __global__ void __launch_bounds__(QT_THREADS, 1)
             }
             tc_fence_before();
             mbar_arrive(tempty0 + 8 * acc);
+            QT_ADD(9, threadIdx.x == 384);
             if (++acc == 2) acc = 0, acc_phase ^= 1u;
         }
+        QT_FLUSH(8, threadIdx.x == 384);
+        QT_FLUSH(9, threadIdx.x == 384);
         if (!gave_up && row0 + r < q.seg_rows) {
             float* dst = q.out + (size_t)z * q.slice_stride + q.col0 + (size_t)seg * q.seg_out + row0 + r;
 #pragma unroll
@@ -370,6 +665,9 @@ __global__ void __launch_bounds__(QT_THREADS, 1)
     if (gave_up && q.status) atomicExch(q.status, 2);
     tc_fence_before();
     __syncthreads();
+#ifdef QT_TRACE
+    if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) qt_trace[10] += (unsigned long long)(clock64() - kernel_t0);
+#endif
     if (warp == 2) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(TCOLS) : "memory");
