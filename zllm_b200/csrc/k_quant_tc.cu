@@ -37,7 +37,12 @@
 
 namespace {
 
-constexpr int QT_ROWS = 128, QT_CHUNK = 64, QT_THREADS = 640;
+constexpr int QT_ROWS = 128, QT_CHUNK = 64;
+// Warps: 4 for the copy / issue roles (one idle), 4 per decoder group, 4 or 8 for the drain. Narrow tiles (<= 32
+// columns) drain little and are bound by the decoders: four groups there, two otherwise.
+__host__ __device__ constexpr int decode_groups(int bn) { return bn <= 32 ? 4 : 2; }
+__host__ __device__ constexpr int drain_warps(int bn) { return bn <= 32 ? 4 : 8; }
+__host__ __device__ constexpr int qt_threads(int bn) { return 32 * (4 + 4 * decode_groups(bn) + drain_warps(bn)); }
 constexpr int RAW_ROW = 144, RAW_BYTES = QT_ROWS * RAW_ROW;   // a super-block of 128 rows as stored
 constexpr int A_BYTES = QT_ROWS * 128;                        // 128 rows x 64 f16
 constexpr int HDR_SLOTS = 4, CSC_SLOTS = 8;   // super-blocks whose row scales / column scales are in flight
@@ -191,10 +196,11 @@ __device__ __forceinline__ uint32_t scaled_pair(uint32_t bits, __half2 sc, __hal
 }
 
 template <int BN>
-__global__ void __launch_bounds__(QT_THREADS, 1)
+__global__ void __launch_bounds__(qt_threads(BN), 1)
     qgemm_q4k_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap bmap,
                      const __grid_constant__ CUtensorMap smap, QtArgs q) {
-    constexpr int RS = raw_stages(BN), NA = a_stages(BN), NB = b_stages(BN), B_BYTES = BN * 128, CPT = BN / 2, TCOLS = 512;
+    constexpr int RS = raw_stages(BN), NA = a_stages(BN), NB = b_stages(BN), B_BYTES = BN * 128, TCOLS = 512;
+    constexpr int NG = decode_groups(BN), ND = drain_warps(BN), CPT = BN / (ND / 4), DRAIN0 = 4 + 4 * NG;
     constexpr bool ATM = a_in_tmem(BN);
     static_assert(!ATM || (4 * BN <= A_COL0 && A_COL0 + NA * A_COLS <= TCOLS), "accumulators and the A ring share tensor memory");
     // The columns' tiles of a super-block share one barrier pair where the ring holds whole super-blocks (narrow
@@ -206,7 +212,7 @@ __global__ void __launch_bounds__(QT_THREADS, 1)
     // the decoders run a super-block ahead. (Wider tiles keep the 64-weight stages.)
     constexpr bool SBM = BN <= 32;
     constexpr int SB_COLS = 136, SB_COL0 = 4 * BN, SLOTS = (TCOLS - SB_COL0) / SB_COLS;
-    static_assert(!SBM || (SLOTS >= 2 && 2 * SLOTS <= NA), "super-block slots and their barriers");
+    static_assert(!SBM || (SLOTS >= 2 && SLOTS <= NA), "super-block slots and their barriers");
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     unsigned char* a_ring = smem;
@@ -223,7 +229,7 @@ __global__ void __launch_bounds__(QT_THREADS, 1)
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < NA; s++) {
-            mbar_init(full_a0 + 8 * s, 4);
+            mbar_init(full_a0 + 8 * s, BN <= 32 ? 4 * NG : 4);
             mbar_init(empty_a0 + 8 * s, 1);
         }
         for (int s = 0; s < NB; s++) {
@@ -232,11 +238,11 @@ __global__ void __launch_bounds__(QT_THREADS, 1)
         }
         for (int s = 0; s < RS; s++) {
             mbar_init(raw_full0 + 8 * s, 1);
-            mbar_init(raw_empty0 + 8 * s, 8);
+            mbar_init(raw_empty0 + 8 * s, 4 * NG);
         }
         for (int a = 0; a < 2; a++) {
             mbar_init(tfull0 + 8 * a, 1);
-            mbar_init(tempty0 + 8 * a, 256);
+            mbar_init(tempty0 + 8 * a, 32 * ND);
         }
         holder[1] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -370,7 +376,7 @@ __global__ void __launch_bounds__(QT_THREADS, 1)
                 const uint32_t sphase = (uint32_t)(sbi / SLOTS) & 1u;
                 {
                     QT_T0();
-                    ok = mbar_wait(full_a0 + 8 * (2 * slot), sphase, abort_flag) && mbar_wait(full_a0 + 8 * (2 * slot + 1), sphase, abort_flag);
+                    ok = mbar_wait(full_a0 + 8 * slot, sphase, abort_flag);
                     QT_ADD(3, true);
                 }
                 {
@@ -450,7 +456,7 @@ __global__ void __launch_bounds__(QT_THREADS, 1)
         QT_FLUSH(3, lane == 0);
         QT_FLUSH(4, lane == 0);
         QT_FLUSH(11, lane == 0);
-    } else if (warp >= 4 && warp < 12) {
+    } else if (warp >= 4 && warp < DRAIN0) {
         // ---- raw tile -> the tensor cores' A operand. Two groups of four warps take alternate 64-weight chunks
         //      (so two chunks are in flight per scheduler); in a group, thread r owns weight row r.
         const int r = ((int)threadIdx.x - 128) & 127, grp = ((int)threadIdx.x - 128) >> 7;
@@ -459,10 +465,10 @@ __global__ void __launch_bounds__(QT_THREADS, 1)
         int cur = -1;                       // the super-block (index within the slice) whose raw tile this thread holds
         const unsigned char* raw = nullptr;
         uint32_t scw[2] = {0, 0}, mnw[2] = {0, 0}, dword = 0;
-        for (int ci = grp; ci < total && !gave_up; ci += 2) {
+        for (int ci = grp; ci < total && !gave_up; ci += NG) {
             const int sbi = ci / 5, c = ci - 5 * sbi, s = SBM ? sbi % SLOTS : ci % NA;
             const uint32_t phase = (uint32_t)(SBM ? sbi / SLOTS : ci / NA) & 1u;
-            const bool first_of_sb = sbi != cur, last_of_sb = (ci + 2) / 5 != sbi || ci + 2 >= total;
+            const bool first_of_sb = sbi != cur, last_of_sb = (ci + NG) / 5 != sbi || ci + NG >= total;
             if (sbi != cur) {
                 if (cur >= 0) {
                     __syncwarp();
@@ -505,43 +511,32 @@ __global__ void __launch_bounds__(QT_THREADS, 1)
                                 (uint32_t)(SBM ? SB_COL0 + s * SB_COLS + (c < 4 ? 32 * c : 128) : A_COL0 + s * A_COLS);
             if (ATM) tc_fence_after();  // the wait above ordered this stage's last reads (the MMAs) before these writes
             if (c < 4) {
-#if defined(QT_EXP) && QT_EXP == 5
-                if (ATM) {
-                    const uint32_t v = (uint32_t)c;
-                    tmem_st8(ta, v, v, v, v, v, v, v, v);
-                    tmem_st8(ta + 8u, v, v, v, v, v, v, v, v);
-                    tmem_st8(ta + 16u, v, v, v, v, v, v, v, v);
-                    tmem_st8(ta + 24u, v, v, v, v, v, v, v, v);
-                }
-                if (false) {
-#endif
                 const uint4 qa = *reinterpret_cast<const uint4*>(raw + 16 + 32 * c), qb = *reinterpret_cast<const uint4*>(raw + 32 + 32 * c);
                 const uint32_t qw[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
                 // units 2c (low nibbles) and 2c + 1 (high nibbles): bytes 2c & 3 and (2c + 1) & 3 of word c >> 1
                 const uint32_t sw = c < 2 ? scw[0] : scw[1];
                 const __half2 scl = __half2half2(__int2half_rn((int)((sw >> (16 * (c & 1))) & 0xffu)));
                 const __half2 sch = __half2half2(__int2half_rn((int)((sw >> (16 * (c & 1) + 8)) & 0xffu)));
-                const __half2 m1024 = __half2half2(__int2half_rn(-1024));
-                const __half2 offl = __hmul2(scl, m1024), offh = __hmul2(sch, m1024);   // exact: at most 63 * 1024
+                // Codes in bits 0-3 of a 16-bit lane: 0x6400 | q is the f16 1024 + q, and (1024 + q) sc - 1024 sc = q sc;
+                // codes in bits 4-7: 0x6400 | (q << 4) is 1024 + 16 q, and (1024 + 16 q) (sc / 16) - 64 sc = q sc. Both
+                // exact (one rounding of an exactly representable result), and only the upper bytes need a shift.
+                const __half2 offl = __hmul2(scl, __half2half2(__int2half_rn(-1024)));
+                const __half2 sch16 = __hmul2(sch, __float2half2_rn(0.0625f)), offh = __hmul2(sch, __half2half2(__int2half_rn(-64)));
                 uint4 lo[4], hi[4];
 #pragma unroll
                 for (int i = 0; i < 4; i++) {
                     // 16 bytes = positions 8i .. 8i+7 of the unit: values (0,2,1,3 | 4,6,5,7) of two code words
-                    const uint32_t w0 = qw[2 * i], w1 = qw[2 * i + 1];
+                    const uint32_t w0 = qw[2 * i], w1 = qw[2 * i + 1], v0 = w0 >> 8, v1 = w1 >> 8;
                     lo[i].x = scaled_pair(w0 & 0x000f000fu, scl, offl);
-                    lo[i].y = scaled_pair((w0 >> 8) & 0x000f000fu, scl, offl);
+                    lo[i].y = scaled_pair(v0 & 0x000f000fu, scl, offl);
                     lo[i].z = scaled_pair(w1 & 0x000f000fu, scl, offl);
-                    lo[i].w = scaled_pair((w1 >> 8) & 0x000f000fu, scl, offl);
-                    hi[i].x = scaled_pair((w0 >> 4) & 0x000f000fu, sch, offh);
-                    hi[i].y = scaled_pair((w0 >> 12) & 0x000f000fu, sch, offh);
-                    hi[i].z = scaled_pair((w1 >> 4) & 0x000f000fu, sch, offh);
-                    hi[i].w = scaled_pair((w1 >> 12) & 0x000f000fu, sch, offh);
+                    lo[i].w = scaled_pair(v1 & 0x000f000fu, scl, offl);
+                    hi[i].x = scaled_pair(w0 & 0x00f000f0u, sch16, offh);
+                    hi[i].y = scaled_pair(v0 & 0x00f000f0u, sch16, offh);
+                    hi[i].z = scaled_pair(w1 & 0x00f000f0u, sch16, offh);
+                    hi[i].w = scaled_pair(v1 & 0x00f000f0u, sch16, offh);
                 }
-#if defined(QT_EXP) && QT_EXP == 4
-                if (lo[0].x == 0x12345678u && hi[3].w == lo[1].y + lo[2].z + hi[0].x + hi[1].y + hi[2].z) {
-#else
                 if (ATM) {
-#endif
                     // columns 0..15: the low unit (two values a column), 16..31: the high unit
                     tmem_st8(ta, lo[0].x, lo[0].y, lo[0].z, lo[0].w, lo[1].x, lo[1].y, lo[1].z, lo[1].w);
                     tmem_st8(ta + 8u, lo[2].x, lo[2].y, lo[2].z, lo[2].w, lo[3].x, lo[3].y, lo[3].z, lo[3].w);
@@ -554,9 +549,6 @@ __global__ void __launch_bounds__(QT_THREADS, 1)
                         *reinterpret_cast<uint4*>(arow + (((uint32_t)(i + 4) ^ swz) << 4)) = hi[i];
                     }
                 }
-#if defined(QT_EXP) && QT_EXP == 5
-                }
-#endif
             } else {
                 // the mins, each twice: K positions 2u, 2u + 1 meet the two terms of unit u's column sum
                 uint4 m0, m1;
@@ -582,7 +574,7 @@ __global__ void __launch_bounds__(QT_THREADS, 1)
                     tmem_st_wait();
                     tc_fence_before();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(full_a0 + 8 * (2 * s + grp));
+                    if (lane == 0) mbar_arrive(full_a0 + 8 * s);
                 }
             } else {
                 if (ATM) {
@@ -608,9 +600,9 @@ __global__ void __launch_bounds__(QT_THREADS, 1)
         QT_FLUSH(15, threadIdx.x == 128);
         QT_FLUSH(16, threadIdx.x == 128);
         QT_FLUSH(17, threadIdx.x == 128);
-    } else if (warp >= 12) {
+    } else if (warp >= DRAIN0) {
         // ---- drain. Thread (quad, lane) owns weight row quad * 32 + lane and CPT of the CTA's columns.
-        const int quad = warp & 3, chalf = (warp - 12) >> 2;
+        const int quad = warp & 3, chalf = (warp - DRAIN0) >> 2;
         const int r = quad * 32 + lane;
         float accv[CPT];
 #pragma unroll
@@ -622,7 +614,7 @@ __global__ void __launch_bounds__(QT_THREADS, 1)
             {
                 QT_T0();
                 ok = __all_sync(0xffffffffu, mbar_wait(tfull0 + 8 * acc, acc_phase, abort_flag));
-                QT_ADD(8, threadIdx.x == 384);
+                QT_ADD(8, threadIdx.x == 32 * DRAIN0);
             }
             if (!ok) {
                 gave_up = true;
@@ -645,11 +637,11 @@ __global__ void __launch_bounds__(QT_THREADS, 1)
             }
             tc_fence_before();
             mbar_arrive(tempty0 + 8 * acc);
-            QT_ADD(9, threadIdx.x == 384);
+            QT_ADD(9, threadIdx.x == 32 * DRAIN0);
             if (++acc == 2) acc = 0, acc_phase ^= 1u;
         }
-        QT_FLUSH(8, threadIdx.x == 384);
-        QT_FLUSH(9, threadIdx.x == 384);
+        QT_FLUSH(8, threadIdx.x == 32 * DRAIN0);
+        QT_FLUSH(9, threadIdx.x == 32 * DRAIN0);
         if (!gave_up && row0 + r < q.seg_rows) {
             float* dst = q.out + (size_t)z * q.slice_stride + q.col0 + (size_t)seg * q.seg_out + row0 + r;
 #pragma unroll
@@ -834,7 +826,7 @@ zcu_result launch_qgemm_bn(const LaunchArgs& a, const QtPlan& pl) {
         return zcu_fail(a, ZCU_E_GPU, "q4_k multiply (tcgen05): %d bytes of shared memory refused", SMEM);
     }
     const dim3 grid((unsigned)(pl.q.tiles_per_seg * pl.q.nseg), (unsigned)((pl.cols + BN - 1) / BN), (unsigned)pl.slices);
-    kern<<<grid, QT_THREADS, SMEM, a.stream>>>(wmap, bmap, smap, pl.q);
+    kern<<<grid, qt_threads(BN), SMEM, a.stream>>>(wmap, bmap, smap, pl.q);
     ZCU_CHECK_LAUNCH(a);
     return ZCU_OK;
 }
