@@ -293,6 +293,9 @@ __global__ void __launch_bounds__(qt_threads(BN), 1)
         if (gave_up)
             for (int i = 0; i < 200; i++) __nanosleep(1000);
     } else if (warp == 1) {
+        // Launched as a programmatic dependent of the kernel that writes the columns: everything else in this CTA
+        // (the weight copies, the decoders) may run while that kernel finishes; the columns are read after it.
+        asm volatile("griddepcontrol.wait;\n" ::: "memory");
         int s = 0;
         uint32_t phase = 0;
         for (int sb = sb_lo; sb < sb_hi && !gave_up; sb++) {
@@ -642,6 +645,7 @@ __global__ void __launch_bounds__(qt_threads(BN), 1)
         }
         QT_FLUSH(8, threadIdx.x == 32 * DRAIN0);
         QT_FLUSH(9, threadIdx.x == 32 * DRAIN0);
+        asm volatile("griddepcontrol.wait;\n" ::: "memory");   // (long past: the MMAs needed the columns)
         if (!gave_up && row0 + r < q.seg_rows) {
             float* dst = q.out + (size_t)z * q.slice_stride + q.col0 + (size_t)seg * q.seg_out + row0 + r;
 #pragma unroll
@@ -678,6 +682,7 @@ __device__ __forceinline__ uint2 perm_pack(__half a, __half b, __half c, __half 
 // bit), and the block scales transposed. grid (k / 256, tokens), 64 threads, thread = four values.
 __global__ void __launch_bounds__(64) cols_from_q8_kernel(const int8_t* __restrict__ qx, const float* __restrict__ dx, __half* __restrict__ bcol,
                                                          __half* __restrict__ bsum, float* __restrict__ scales, int k, int cols_pad) {
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");   // the multiply may start its weight copies now
     const int li = threadIdx.x, sb = blockIdx.x, tok = blockIdx.y, nsb = k / 256;
     const char4 v = reinterpret_cast<const char4*>(qx + (size_t)tok * k + (size_t)sb * 256)[li];
     reinterpret_cast<uint2*>(bcol + (size_t)tok * k + (size_t)sb * 256)[li] =
@@ -701,6 +706,7 @@ __global__ void __launch_bounds__(64) cols_from_f32_kernel(const float* __restri
                                                           float eps, int cols_pad) {
     __shared__ double red[2];
     __shared__ float amax_s[2];
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");   // the multiply may start its weight copies now
     const int li = threadIdx.x, sb = blockIdx.x, tok = blockIdx.y, nsb = k / 256;
     const float* xt = x + (size_t)tok * x_stride;
     float4 v;
@@ -825,9 +831,18 @@ zcu_result launch_qgemm_bn(const LaunchArgs& a, const QtPlan& pl) {
         cudaGetLastError();
         return zcu_fail(a, ZCU_E_GPU, "q4_k multiply (tcgen05): %d bytes of shared memory refused", SMEM);
     }
-    const dim3 grid((unsigned)(pl.q.tiles_per_seg * pl.q.nseg), (unsigned)((pl.cols + BN - 1) / BN), (unsigned)pl.slices);
-    kern<<<grid, qt_threads(BN), SMEM, a.stream>>>(wmap, bmap, smap, pl.q);
-    ZCU_CHECK_LAUNCH(a);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(pl.q.tiles_per_seg * pl.q.nseg), (unsigned)((pl.cols + BN - 1) / BN), (unsigned)pl.slices);
+    cfg.blockDim = dim3(qt_threads(BN));
+    cfg.dynamicSmemBytes = SMEM;
+    cfg.stream = a.stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // see the wait in the kernel's column warp
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, kern, wmap, bmap, smap, pl.q);
+    if (e != cudaSuccess) return zcu_fail(a, ZCU_E_GPU, "q4_k multiply (tcgen05): launch failed: %s", cudaGetErrorString(e));
     return ZCU_OK;
 }
 
