@@ -159,6 +159,10 @@ class MatvecQ4K:
         from zllm_b200 import kernels as K
 
         self.torch, self.K, self.dist, self.batch, self.variant = torch, K, dist, batch, variant
+        # more than four tokens: one pass over the weights by the batched tcgen05 family (unless a variant was asked for;
+        # --variant 0x20000 = a pass per 2-4 tokens by the mma.sync family)
+        if variant == 0 and 4 < batch <= K.MATVEC_BATCHED_MAX_TOKENS:
+            self.variant = K.MATVEC_BATCHED
         self.dev = torch.device("cuda", dist.local)
         torch.cuda.set_device(self.dev)
         self.stream = torch.cuda.Stream(self.dev)
@@ -248,7 +252,8 @@ class MatvecQ4K:
         peak, kind = measured_hbm_peak()
         us = ms_per_step * 1e3 / self.launches_per_step()
         achieved = self.bytes_per_launch() / us / 1e3
-        return {"bound": "hbm", "kernel": "matvec_imma<Q4_K>", "achieved": achieved, "peak": peak, "unit": "GB/s",
+        kernel = "qgemm_q4k_kernel (tcgen05; with its column and reduction kernels)" if self.variant == self.K.MATVEC_BATCHED else "matvec_imma<Q4_K>"
+        return {"bound": "hbm", "kernel": kernel, "achieved": achieved, "peak": peak, "unit": "GB/s",
                 "frac": achieved / peak, "peak_kind": f"of {kind}", "frac_of_8000_nominal": achieved / 8000.0,
                 "traffic": None, "bytes_per_launch": self.bytes_per_launch(), "us_per_launch": us}
 
@@ -1005,6 +1010,26 @@ def run_reference(args):
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": 8 * 2.0 * wl.rows * wl.n * wl.k / value / 1e9,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": f"BF16 prefill matmul, {wl.rows} tokens x {wl.n} x {wl.k} (a 64-token sample per step)"},
+            "cpu_baseline": base,
+            "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        }), flush=True)
+        return
+    if args.workload == "prefill_q4_k":
+        wl = QuantPrefill.__new__(QuantPrefill)  # shapes only; nothing on a GPU
+        wl.k = QuantPrefill.k
+        vals, base = [], None
+        for i in range(args.warmup + args.steps):
+            base = wl.cpu_baseline(budget_s=3.0)
+            if i >= args.warmup:
+                vals.append(base["value"])
+        value = float(np.mean(vals))
+        base["value"] = value
+        print(json.dumps({
+            "impl": "reference", "metric": "prefill_q4_k_matmul_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": 4 * 2.0 * wl.rows * wl.n * wl.k / value / 1e9,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": QuantPrefill.dtype, "data": "synthetic",
+            "config": {"workload": f"Q4_K prefill matmul, {wl.rows} tokens x {wl.n} x {wl.k}, Q8_K-rounded activations "
+                                   "(a 32-token x 2048-row sample per step)"},
             "cpu_baseline": base,
             "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         }), flush=True)

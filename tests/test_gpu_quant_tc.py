@@ -162,3 +162,17 @@ def test_config_q4_k_ffn_up_batched(ref, gpu, launcher, batch):
     got = out.download(np.float32).reshape(batch, n)
     assert rel_err(got, want64) < TOL, rel_err(got, want64)
     assert np.abs(got - want32).max() / np.abs(want32).max() < HARD_TOL
+
+
+def test_matvec_batched_refuses_what_it_does_not_run(gpu, launcher):
+    from zllm_b200 import abi
+
+    k = 512
+    w, x, out = gpu.zeros(8 * K.row_bytes("q4_k", k)), gpu.zeros(65 * k * 4), gpu.zeros(65 * 8 * 4)
+    with pytest.raises(abi.ZcuError, match="at most 64"):
+        launcher.matvec("q4_k", x, w, out, 8, k, m=65, variant=BATCHED)
+    with pytest.raises(abi.ZcuError):
+        launcher.matvec("q8_0", x, w, out, 8, k, m=8, variant=BATCHED)       # Q4_K only: no such artifact
+    launcher.matvec("q4_k", x, w, out, 8, k, m=64, variant=BATCHED)           # the widest step: 128 columns
+    gpu.sync()
+    assert not out.download(np.float32).any()                                  # zero weights and activations

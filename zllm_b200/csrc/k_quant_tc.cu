@@ -255,6 +255,8 @@ __global__ void __launch_bounds__(qt_threads(BN), 1)
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = holder[0];
+    // a dependent kernel after this one (the reduction) may be scheduled once every CTA of this grid is running
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
 #ifdef QT_TRACE
     const long long kernel_t0 = clock64();
 #endif
@@ -706,6 +708,7 @@ __global__ void __launch_bounds__(64) cols_from_f32_kernel(const float* __restri
                                                           float eps, int cols_pad) {
     __shared__ double red[2];
     __shared__ float amax_s[2];
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");                // the kernels before this one are done (inputs, and the scratch's last readers)
     asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");   // the multiply may start its weight copies now
     const int li = threadIdx.x, sb = blockIdx.x, tok = blockIdx.y, nsb = k / 256;
     const float* xt = x + (size_t)tok * x_stride;
@@ -783,6 +786,8 @@ __global__ void __launch_bounds__(64) cols_from_f32_kernel(const float* __restri
 // multiply's epilogue applies them. part[z][column][seg * n + j].
 __global__ void __launch_bounds__(256) cols_reduce_kernel(const float* __restrict__ part, float* __restrict__ out, int n, int m, int slices,
                                                          int cols, int pair, int accumulate, uint32_t out_stride, uint32_t col0) {
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");                // the multiply is done
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");   // a dependent kernel after this one may be scheduled
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= (size_t)n * m) return;
     const int tok = (int)(i / n), j = (int)(i % n);
@@ -857,6 +862,45 @@ zcu_result launch_qgemm(const LaunchArgs& a, const QtPlan& pl) {
 
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
+// Staging memory of one multiply: the context's scratch when it is large enough (launches of a context run in
+// stream order, so the next multiply reuses it), else a stream-ordered allocation freed after the last kernel.
+struct Scratch {
+    unsigned char* p = nullptr;
+    bool owned = false;
+};
+inline bool scratch_get(const LaunchArgs& a, size_t bytes, Scratch& s) {
+    if (a.scratch && bytes <= a.scratch_bytes) {
+        s.p = static_cast<unsigned char*>(a.scratch);
+        return true;
+    }
+    if (cudaMallocAsync((void**)&s.p, bytes, a.stream) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    s.owned = true;
+    return true;
+}
+inline void scratch_put(const LaunchArgs& a, Scratch& s) {
+    if (s.owned) cudaFreeAsync(s.p, a.stream);
+}
+
+// A launch that may start while the kernel before it in the stream finishes (programmatic dependent launch): the
+// kernel orders itself with griddepcontrol.wait before it touches what that kernel wrote or still reads.
+template <class... KArgs, class... Args>
+cudaError_t launch_dependent(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kern, args...);
+}
+
 }  // namespace
 
 // matmul_q4_k, the tensor-core rung: params.MatmulQuant and the bindings qx, w, out, dx of the integer-dot identity.
@@ -877,11 +921,10 @@ zcu_result launch_matmul_q4_k_tc(const LaunchArgs& a) {
     const int cols_pad = (int)align_up((size_t)tokens, (size_t)bn);
     const size_t b_bytes = align_up((size_t)tokens * k * 2, 1024), s_bytes = align_up((size_t)tokens * nsb * 128, 1024),
                  c_bytes = align_up((size_t)nsb * cols_pad * 4, 1024);
-    unsigned char* scratch = nullptr;
-    if (cudaMallocAsync((void**)&scratch, b_bytes + s_bytes + c_bytes, a.stream) != cudaSuccess) {
-        cudaGetLastError();
+    Scratch sc;
+    if (!scratch_get(a, b_bytes + s_bytes + c_bytes, sc))
         return zcu_fail(a, ZCU_E_GPU, "matmul_q4_k (tcgen05): no memory for %zu bytes of columns", b_bytes + s_bytes + c_bytes);
-    }
+    unsigned char* scratch = sc.p;
     __half* bcol = reinterpret_cast<__half*>(scratch);
     __half* bsum = reinterpret_cast<__half*>(scratch + b_bytes);
     float* scales = reinterpret_cast<float*>(scratch + b_bytes + s_bytes);
@@ -914,7 +957,7 @@ zcu_result launch_matmul_q4_k_tc(const LaunchArgs& a) {
     pl.q.scales = scales;
     pl.q.status = a.status;
     const zcu_result r = launch_qgemm(a, pl);
-    cudaFreeAsync(scratch, a.stream);
+    scratch_put(a, sc);
     return r;
 }
 
@@ -942,18 +985,23 @@ zcu_result launch_matvec_q4_k_tc(const LaunchArgs& a, const mv::MvArgs& v) {
     const size_t width = (size_t)n * nseg;
     const size_t b_bytes = align_up((size_t)cols * k * 2, 1024), s_bytes = align_up((size_t)cols * nsb * 128, 1024),
                  c_bytes = align_up((size_t)nsb * cols_pad * 4, 1024), p_bytes = align_up((size_t)slices * cols * width * 4, 1024);
-    unsigned char* scratch = nullptr;
-    if (cudaMallocAsync((void**)&scratch, b_bytes + s_bytes + c_bytes + p_bytes, a.stream) != cudaSuccess) {
-        cudaGetLastError();
+    Scratch sc;
+    if (!scratch_get(a, b_bytes + s_bytes + c_bytes + p_bytes, sc))
         return zcu_fail(a, ZCU_E_GPU, "matvec_q4_k (tcgen05): no memory for %zu bytes of scratch", b_bytes + s_bytes + c_bytes + p_bytes);
-    }
+    unsigned char* scratch = sc.p;
     __half* bcol = reinterpret_cast<__half*>(scratch);
     __half* bsum = reinterpret_cast<__half*>(scratch + b_bytes);
     float* scales = reinterpret_cast<float*>(scratch + b_bytes + s_bytes);
     float* part = reinterpret_cast<float*>(scratch + b_bytes + s_bytes + c_bytes);
     if (cols_pad != cols) cudaMemsetAsync(scales, 0, c_bytes, a.stream);
     const int xr = p.x_stride ? (int)p.x_stride * 4 : k;
-    cols_from_f32_kernel<<<dim3((unsigned)nsb, (unsigned)m), 64, 0, a.stream>>>(v.x, v.nw, bcol, bsum, scales, k, xr, norm ? 1 : 0, p.eps, cols_pad);
+    // (the column kernel, the multiply and the reduction are programmatic dependents of one another and of the kernel
+    // before them: each may be scheduled while its predecessor finishes, and waits before it touches memory)
+    if (launch_dependent(cols_from_f32_kernel, dim3((unsigned)nsb, (unsigned)m), dim3(64), 0, a.stream, v.x, v.nw, bcol, bsum, scales, k, xr,
+                         norm ? 1 : 0, p.eps, cols_pad) != cudaSuccess) {
+        scratch_put(a, sc);
+        return zcu_fail(a, ZCU_E_GPU, "matvec_q4_k (tcgen05): launch failed: %s", cudaGetErrorString(cudaGetLastError()));
+    }
     QtPlan pl{};
     pl.w = v.w;
     pl.w_rows = pair ? (uint64_t)p.half + n : (uint64_t)n;
@@ -982,11 +1030,10 @@ zcu_result launch_matvec_q4_k_tc(const LaunchArgs& a, const mv::MvArgs& v) {
     zcu_result r = launch_qgemm(a, pl);
     if (r == ZCU_OK) {
         const size_t elems = (size_t)n * m;
-        cols_reduce_kernel<<<(unsigned)((elems + 255) / 256), 256, 0, a.stream>>>(part, v.out, n, m, slices, cols, pair ? 1 : 0,
-                                                                                (p.flags & MV_ACCUMULATE) ? 1 : 0, p.out_stride, p.col0);
-        const cudaError_t e = cudaGetLastError();
+        const cudaError_t e = launch_dependent(cols_reduce_kernel, dim3((unsigned)((elems + 255) / 256)), dim3(256), 0, a.stream, (const float*)part,
+                                               v.out, n, m, slices, cols, pair ? 1 : 0, (p.flags & MV_ACCUMULATE) ? 1 : 0, p.out_stride, p.col0);
         if (e != cudaSuccess) r = zcu_fail(a, ZCU_E_GPU, "matvec_q4_k (tcgen05): launch failed: %s", cudaGetErrorString(e));
     }
-    cudaFreeAsync(scratch, a.stream);
+    scratch_put(a, sc);
     return r;
 }

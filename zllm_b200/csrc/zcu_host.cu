@@ -103,6 +103,8 @@ struct zcu_context {
     std::vector<zcu_program*> programs;
     uint8_t* pinned = nullptr;  // staging for uploads and readbacks
     int* status = nullptr;      // mapped host word kernels set when a bounded wait gives up
+    void* scratch = nullptr;    // device scratch of the multiplies that stage their inputs (k_quant_tc.cu): work of one stream, used in order
+    size_t scratch_bytes = 0;
     size_t pinned_cap = 0;
 };
 
@@ -208,6 +210,8 @@ zcu_result dispatch_kernel(zcu_context* c, uint32_t kernel, uint32_t variant, co
     a.sm_count = c->dry ? 148 : c->prop.multiProcessorCount;
     a.status = c->status;
     a.peers = c->peers.world > 0 ? &c->peers : nullptr;
+    a.scratch = c->scratch;
+    a.scratch_bytes = c->scratch_bytes;
     a.err = c->err;
     a.err_cap = sizeof(c->err);
     char name[64];
@@ -750,6 +754,10 @@ ZCU_EXPORT zcu_result zcu_create(const zcu_options* options, zcu_context** out_c
         } else {
             *c->status = 0;
         }
+        // 64 MiB for the staged multiplies: allocated here so that no launch allocates (larger needs fall back to
+        // stream-ordered allocation)
+        if (cudaMalloc(&c->scratch, (size_t)64 << 20) == cudaSuccess) c->scratch_bytes = (size_t)64 << 20;
+        else cudaGetLastError(), c->scratch = nullptr;
     }
     *out_context = c;
     return ZCU_OK;
@@ -775,6 +783,7 @@ ZCU_EXPORT zcu_result zcu_destroy(zcu_context* c, uint32_t timeout_ms) {
         }
     if (c->pinned) cudaFreeHost(c->pinned);
     if (c->status) cudaFreeHost(c->status);
+    if (c->scratch) cudaFree(c->scratch);
     if (c->own_stream) cudaStreamDestroy(c->stream);
     delete c;
     return ZCU_OK;
@@ -1003,6 +1012,8 @@ ZCU_EXPORT zcu_result zcu_attention_decode_static(zcu_context* c, const void* pa
     a.sm_count = c->prop.multiProcessorCount;
     a.status = c->status;
     a.peers = nullptr;
+    a.scratch = nullptr;
+    a.scratch_bytes = 0;
     a.err = c->err;
     a.err_cap = sizeof(c->err);
     c->launches += 2;

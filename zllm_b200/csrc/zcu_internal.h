@@ -110,6 +110,8 @@ struct LaunchArgs {
     int sm_count;
     int* status;                   // device-visible word a kernel sets when a bounded wait gives up
     const PeerTable* peers;        // the context's tensor-parallel exchange table (null: none configured)
+    void* scratch;                 // the context's device scratch (null: none) for launches that stage inputs; one stream, in order
+    size_t scratch_bytes;
     char* err;                     // message buffer on failure
     size_t err_cap;
 };
