@@ -16,7 +16,9 @@ __global__ void __launch_bounds__(IM_THREADS, 1) matvec_imma(PMatvec p, const fl
                                                             int seg_max, int* __restrict__ status, const __grid_constant__ MvRope rope,
                                                             const __grid_constant__ PeerUse pu) {
     extern __shared__ __align__(128) uint8_t smem[];
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    // (broadcast from lane 0: the compiler then knows the warp index, and what derives from it - ring addresses, tile
+    // coordinates - to be the same in every lane, and feeds the copy instructions from uniform registers)
+    const int lane = threadIdx.x & 31, warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0);
     const ImLayout L = im_layout(4 * mt, (int)p.k, TYPE == W_Q4_K, 2 * NB, seg_max, STAGES);
     ImRing rg;
     ImIssue iss;

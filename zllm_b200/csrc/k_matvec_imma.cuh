@@ -283,7 +283,7 @@ __device__ __forceinline__ void im_multiply(uint8_t* smem, ImRing& rg, ImIssue& 
                                             Between between) {
     constexpr bool Q4 = TYPE == W_Q4_K;
     constexpr int SLOTS = 2 * NB;  // token slots of a pass
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int tid = threadIdx.x, lane = tid & 31, warp = __shfl_sync(0xffffffffu, tid >> 5, 0);   // warp-uniform to the compiler
     const int g = lane >> 2, t = lane & 3;
     const int k = (int)p.k, n = (int)p.n;
     const int xr = p.x_stride ? (int)p.x_stride * 4 : k;
