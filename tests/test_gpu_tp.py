@@ -88,11 +88,14 @@ def _rank_peer(rank: int, world: int, port: int, out_dir: str):
     cfg = DenseConfig(layers=2, hidden=512, heads=8, kv_heads=2, head_dim=64, ff=1024, vocab=1536, max_ctx=320)
     host = M.host_model(cfg, "tp-test")
     rng = np.random.default_rng(17)
-    batch = 2
+    # six sequences: more than one pass of the multiplies takes (four tokens), so one dispatch pushes its slices in
+    # two launches under one exchange tag
+    batch = 6
     kv_shape = (batch, cfg.max_ctx, cfg.kv_heads, cfg.head_dim)
     kc_host = [rng.normal(size=kv_shape).astype(np.float16) for _ in range(cfg.layers)]
     vc_host = [rng.normal(size=kv_shape).astype(np.float16) for _ in range(cfg.layers)]
-    steps = [(rng.integers(0, cfg.vocab, size=batch).astype(np.uint32), np.array(p, dtype=np.uint32)) for p in ([100, 37], [101, 38], [102, 39])]
+    first = np.array([100, 37, 5, 200, 64, 11])
+    steps = [(rng.integers(0, cfg.vocab, size=batch).astype(np.uint32), (first + i).astype(np.uint32)) for i in range(3)]
     ctx = abi.Context(rank)
 
     def exchange(handle: bytes):
@@ -102,7 +105,8 @@ def _rank_peer(rank: int, world: int, port: int, out_dir: str):
 
     def build(sh, arena):
         weights = M.upload(host, cfg, ctx.put, sh)
-        prog = DenseProgram(ctx, cfg, weights, batch, ctx.zeros, sh, arena=arena)
+        # (batched=False: the one-GPU program too takes the mma.sync family, whose bits the sharded one must give)
+        prog = DenseProgram(ctx, cfg, weights, batch, ctx.zeros, sh, arena=arena, batched=False)
         prog.set_rope_table(ctx.put(DenseProgram.rope_table(cfg)))
         g0, g1 = sh.kv_heads(cfg)
         for il in range(cfg.layers):

@@ -105,9 +105,12 @@ template <int TYPE>
 zcu_result launch_type(const LaunchArgs& a, const MvArgs& v, int stages) {
     const bool q4 = TYPE == W_Q4_K;
     const int cap = tokens_per_pass((int)v.p.k, q4);
+    MvArgs pass = v;
     for (int t0 = 0; t0 < v.m;) {
         const int mt = (v.m - t0) < cap ? (v.m - t0) : cap;
-        zcu_result r = mt > 2 ? launch_one<TYPE, 2>(a, v, t0, mt, stages) : launch_one<TYPE, 1>(a, v, t0, mt, stages);
+        // every pass of one dispatch pushes under the same exchange tag: only the last one advances the slot's count
+        pass.peer.hold = t0 + mt < v.m ? 1u : 0u;
+        zcu_result r = mt > 2 ? launch_one<TYPE, 2>(a, pass, t0, mt, stages) : launch_one<TYPE, 1>(a, pass, t0, mt, stages);
         if (r != ZCU_OK) return r;
         t0 += mt;
     }

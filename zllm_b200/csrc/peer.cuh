@@ -45,6 +45,8 @@ struct PeerTable {
 struct PeerUse {  // what one launch does with the table
     PeerTable t;
     uint32_t wait_slot, push_slot;
+    uint32_t hold, _pad;   // hold != 0: another launch of the same dispatch follows (a step of more tokens than one pass takes):
+                           // it pushes under the same tag, so this launch leaves the slot's count alone
 };
 
 #ifdef __CUDACC__
@@ -121,7 +123,7 @@ __device__ __forceinline__ void finish(const PeerUse& u, unsigned ncta) {
         __threadfence();
         if (atomicAdd(u.t.tickets + u.push_slot, 1u) == ncta - 1) {
             u.t.tickets[u.push_slot] = 0;
-            u.t.counts[u.push_slot] += 1;
+            if (!u.hold) u.t.counts[u.push_slot] += 1;
         }
     }
 }
