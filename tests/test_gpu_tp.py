@@ -103,10 +103,10 @@ def _rank_peer(rank: int, world: int, port: int, out_dir: str):
         dist.all_gather_object(got, handle)
         return got
 
-    def build(sh, arena):
+    def build(sh, arena, batched=False):
         weights = M.upload(host, cfg, ctx.put, sh)
         # (batched=False: the one-GPU program too takes the mma.sync family, whose bits the sharded one must give)
-        prog = DenseProgram(ctx, cfg, weights, batch, ctx.zeros, sh, arena=arena, batched=False)
+        prog = DenseProgram(ctx, cfg, weights, batch, ctx.zeros, sh, arena=arena, batched=batched)
         prog.set_rope_table(ctx.put(DenseProgram.rope_table(cfg)))
         g0, g1 = sh.kv_heads(cfg)
         for il in range(cfg.layers):
@@ -135,6 +135,20 @@ def _rank_peer(rank: int, world: int, port: int, out_dir: str):
             ctx.sync()
             want.append(whole.logits.download(np.float32).reshape(batch, cfg.vocab).copy())
         dist.barrier()  # a rank leaves a step only when every rank has read its logits
+    # the same steps with the batched tcgen05 family in the exchange (its column kernel waits on the slots, its
+    # reduction pushes): a second arena, since the first program owns the first one's buffers
+    arena2 = abi.PeerArena(ctx, rank, world, DenseProgram.arena_bytes(cfg, batch), DenseProgram.arena_slots(cfg), exchange)
+    sharded2 = build(Shard(rank, world), arena2, batched=True)
+    assert sharded2.batched
+    dist.barrier()
+    got2 = []
+    for tokens, positions in steps:
+        sharded2.write_step(tokens, positions)
+        sharded2.record_step(cfg.max_ctx)
+        ctx.sync()
+        got2.append(sharded2.logits.download(np.float32).reshape(batch, cfg.vocab).copy())
+        dist.barrier()
+    np.save(os.path.join(out_dir, f"peer_batched{rank}.npy"), np.stack(got2))
     if rank == 0:
         np.save(os.path.join(out_dir, "one.npy"), np.stack(want))
     np.save(os.path.join(out_dir, f"peer{rank}.npy"), np.stack(got))
@@ -164,9 +178,18 @@ def test_two_gpus_with_peer_pushes_give_the_single_gpu_logits():
         _spawn(_rank_peer, tmp)
         one = np.load(os.path.join(tmp, "one.npy"))
         peers = [np.load(os.path.join(tmp, f"peer{r}.npy")) for r in range(2)]
+        batched = [np.load(os.path.join(tmp, f"peer_batched{r}.npy")) for r in range(2)]
     assert np.isfinite(one).all() and np.abs(one).max() > 0
     for r in range(2):  # every rank holds the whole logits, and they are the single-GPU bits
         assert np.array_equal(one.view(np.uint32), peers[r].view(np.uint32)), r
+    # the batched family sums in another order (k slices, two f16 terms): the same logits within the model-tier bound,
+    # and every rank holds the same bits
+    assert np.array_equal(batched[0].view(np.uint32), batched[1].view(np.uint32))
+    for step in range(one.shape[0]):
+        for b in range(one.shape[1]):
+            d = batched[0][step, b].astype(np.float64) - one[step, b]
+            assert np.linalg.norm(d) / np.linalg.norm(one[step, b]) < 1e-4, (step, b)
+            assert int(np.argmax(batched[0][step, b])) == int(np.argmax(one[step, b]))
 
 
 def test_two_gpus_give_the_single_gpu_logits():

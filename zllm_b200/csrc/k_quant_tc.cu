@@ -705,24 +705,28 @@ __global__ void __launch_bounds__(64) cols_from_q8_kernel(const int8_t* __restri
 // scale is 2^-e for both columns. grid (k / 256, tokens), 64 threads.
 __global__ void __launch_bounds__(64) cols_from_f32_kernel(const float* __restrict__ x, const float* __restrict__ nw, __half* __restrict__ bcol,
                                                           __half* __restrict__ bsum, float* __restrict__ scales, int k, int x_stride, int mode,
-                                                          float eps, int cols_pad) {
+                                                          float eps, int cols_pad, const __grid_constant__ PeerUse pu, int* __restrict__ status) {
     __shared__ double red[2];
     __shared__ float amax_s[2];
     asm volatile("griddepcontrol.wait;\n" ::: "memory");                // the kernels before this one are done (inputs, and the scratch's last readers)
     asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");   // the multiply may start its weight copies now
     const int li = threadIdx.x, sb = blockIdx.x, tok = blockIdx.y, nsb = k / 256;
     const float* xt = x + (size_t)tok * x_stride;
+    // the activations: local memory, or the slots of a tensor-parallel exchange (each read waits for its tag)
+    const bool exchanged = pu.wait_slot != PEER_NONE;
+    const uint32_t x_tag = exchanged ? peer::want_tag(pu) : 0u;
+    auto ldx = [&](int i) { return exchanged ? peer::read4(pu, xt + 4 * i, x_tag, status) : reinterpret_cast<const float4*>(xt)[i]; };
     float4 v;
     if (mode == 2) {  // silu(gate) * up over rows of gate | up (src/kernels/quantize_q8.wgsl)
         const float4 g = reinterpret_cast<const float4*>(xt)[sb * 64 + li], u = reinterpret_cast<const float4*>(xt + k)[sb * 64 + li];
         v = make_float4(mv::silu_f(g.x) * u.x, mv::silu_f(g.y) * u.y, mv::silu_f(g.z) * u.z, mv::silu_f(g.w) * u.w);
     } else {
-        v = reinterpret_cast<const float4*>(xt)[sb * 64 + li];
+        v = ldx(sb * 64 + li);
     }
     if (mode == 1) {  // RMSNorm(x) * w: f32 squares summed in f64 (src/ref/ops.zig:30-41)
         double ss = 0.0;
         for (int i = li; i < k / 4; i += 64) {
-            const float4 r = reinterpret_cast<const float4*>(xt)[i];
+            const float4 r = ldx(i);
             ss += (double)__fmul_rn(r.x, r.x);
             ss += (double)__fmul_rn(r.y, r.y);
             ss += (double)__fmul_rn(r.z, r.z);
@@ -785,22 +789,28 @@ __global__ void __launch_bounds__(64) cols_from_f32_kernel(const float* __restri
 // Decode: the k slices and the two columns of a token, added in a fixed order; SILU_PAIR and ACCUMULATE as the
 // multiply's epilogue applies them. part[z][column][seg * n + j].
 __global__ void __launch_bounds__(256) cols_reduce_kernel(const float* __restrict__ part, float* __restrict__ out, int n, int m, int slices,
-                                                         int cols, int pair, int accumulate, uint32_t out_stride, uint32_t col0) {
+                                                         int cols, int pair, int accumulate, uint32_t out_stride, uint32_t col0,
+                                                         const __grid_constant__ PeerUse pu) {
     asm volatile("griddepcontrol.wait;\n" ::: "memory");                // the multiply is done
     asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");   // a dependent kernel after this one may be scheduled
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= (size_t)n * m) return;
-    const int tok = (int)(i / n), j = (int)(i % n);
-    const size_t width = (size_t)n * (pair ? 2 : 1), zs = (size_t)cols * width;
-    float v = 0.f, u = 0.f;
-    for (int z = 0; z < slices; z++) {
-        const float* p = part + z * zs + (size_t)(2 * tok) * width + j;
-        v = __fadd_rn(v, __fadd_rn(p[0], p[width]));
-        if (pair) u = __fadd_rn(u, __fadd_rn(p[n], p[width + n]));
+    if (i < (size_t)n * m) {
+        const int tok = (int)(i / n), j = (int)(i % n);
+        const size_t width = (size_t)n * (pair ? 2 : 1), zs = (size_t)cols * width;
+        float v = 0.f, u = 0.f;
+        for (int z = 0; z < slices; z++) {
+            const float* p = part + z * zs + (size_t)(2 * tok) * width + j;
+            v = __fadd_rn(v, __fadd_rn(p[0], p[width]));
+            if (pair) u = __fadd_rn(u, __fadd_rn(p[n], p[width + n]));
+        }
+        if (pair) v = mv::silu_f(v) * u;
+        const size_t o = (size_t)tok * out_stride + col0 + j;
+        if (accumulate) v += out[o];
+        out[o] = v;
+        // this rank's slice of an exchanged vector: to every rank's exchange slots
+        if (pu.push_slot != PEER_NONE) peer::push(pu, out + o, v, peer::push_tag(pu));
     }
-    if (pair) v = mv::silu_f(v) * u;
-    const size_t o = (size_t)tok * out_stride + col0 + j;
-    out[o] = accumulate ? out[o] + v : v;
+    peer::finish(pu, gridDim.x);
 }
 
 // ---------------------------------------------------------------------------------------------- host side
@@ -968,8 +978,6 @@ zcu_result launch_matvec_q4_k_tc(const LaunchArgs& a, const mv::MvArgs& v) {
     ZCU_NEED(a, m <= 64, "matvec_q4_k (tcgen05): %d tokens in one step (at most 64)", m);
     ZCU_NEED(a, k % 256 == 0, "matvec_q4_k (tcgen05): k = %d is not a multiple of 256", k);
     if (v.has_rope) return zcu_fail(a, ZCU_E_UNSUPPORTED_KERNEL, "matvec + rope_append: only the mma.sync family fuses it");
-    if (v.peer.wait_slot != PEER_NONE || v.peer.push_slot != PEER_NONE)
-        return zcu_fail(a, ZCU_E_UNSUPPORTED_KERNEL, "matvec in a peer exchange: only the mma.sync family takes part");
     const bool pair = (p.flags & MV_SILU_PAIR) != 0, norm = (p.flags & MV_NORM) != 0;
     const int cols = 2 * m;
     const int bn = cols > 64 ? 128 : cols > 32 ? 64 : cols > 16 ? 32 : 16;
@@ -998,7 +1006,7 @@ zcu_result launch_matvec_q4_k_tc(const LaunchArgs& a, const mv::MvArgs& v) {
     // (the column kernel, the multiply and the reduction are programmatic dependents of one another and of the kernel
     // before them: each may be scheduled while its predecessor finishes, and waits before it touches memory)
     if (launch_dependent(cols_from_f32_kernel, dim3((unsigned)nsb, (unsigned)m), dim3(64), 0, a.stream, v.x, v.nw, bcol, bsum, scales, k, xr,
-                         norm ? 1 : 0, p.eps, cols_pad) != cudaSuccess) {
+                         norm ? 1 : 0, p.eps, cols_pad, v.peer, a.status) != cudaSuccess) {
         scratch_put(a, sc);
         return zcu_fail(a, ZCU_E_GPU, "matvec_q4_k (tcgen05): launch failed: %s", cudaGetErrorString(cudaGetLastError()));
     }
@@ -1031,7 +1039,7 @@ zcu_result launch_matvec_q4_k_tc(const LaunchArgs& a, const mv::MvArgs& v) {
     if (r == ZCU_OK) {
         const size_t elems = (size_t)n * m;
         const cudaError_t e = launch_dependent(cols_reduce_kernel, dim3((unsigned)((elems + 255) / 256)), dim3(256), 0, a.stream, (const float*)part,
-                                               v.out, n, m, slices, cols, pair ? 1 : 0, (p.flags & MV_ACCUMULATE) ? 1 : 0, p.out_stride, p.col0);
+                                               v.out, n, m, slices, cols, pair ? 1 : 0, (p.flags & MV_ACCUMULATE) ? 1 : 0, p.out_stride, p.col0, v.peer);
         if (e != cudaSuccess) r = zcu_fail(a, ZCU_E_GPU, "matvec_q4_k (tcgen05): launch failed: %s", cudaGetErrorString(e));
     }
     scratch_put(a, sc);

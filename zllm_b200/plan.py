@@ -139,9 +139,9 @@ class DenseProgram:
         # 1, 2 or 4 sequences
         self.fuse_rope = (batch in (1, 2, 4)) if fuse_rope is None else fuse_rope
         # Q4_K multiplies of 5..64 sequences in ONE pass over the weights (the tcgen05 family) instead of a pass per
-        # 2-4 sequences; one GPU (that family takes no part in a peer exchange)
-        can_batch = 4 < batch <= K.MATVEC_BATCHED_MAX_TOKENS and arena is None
-        self.batched = can_batch if batched is None else (bool(batched) and batch <= K.MATVEC_BATCHED_MAX_TOKENS and arena is None)
+        # 2-4 sequences
+        can_batch = 4 < batch <= K.MATVEC_BATCHED_MAX_TOKENS
+        self.batched = can_batch if batched is None else (bool(batched) and batch <= K.MATVEC_BATCHED_MAX_TOKENS)
         # attn_combine by the last key block of each (sequence, KV head) inside attn_split (one launch fewer per
         # layer): the tensor-core fast path (f16 cache, GQA group <= 4, head_dim 64 or 128) with at most 128 blocks
         # of 128 keys, unless a form of attn_split was asked for
