@@ -193,3 +193,43 @@ def test_exchange_slots_chain_through_the_sharded_launch_list(merge):
     assert sorted(pushed) == list(range(DenseProgram.arena_slots(cfg)))
     assert len(bytes(K.with_peer(K.Matvec(1, 2, 3, 4, 0.0, 0, 0, 0), wait=3))) == C.sizeof(K.Matvec) + 16
     ctx.close()
+
+
+@pytest.mark.parametrize("batch,sharded", [(1, False), (4, False), (5, False), (8, True), (64, False), (65, False)])
+def test_batched_family_is_chosen_for_more_than_four_sequences(batch, sharded):
+    # The plan on a dry-run context: steps of 5..64 sequences take the batched tcgen05 family for every Q4_K multiply
+    # (also inside a tensor-parallel exchange, where its waits and pushes ride on the same dispatches); the Q8_0 head
+    # and smaller or larger steps keep the default family. rope_append is fused only at 1, 2 or 4 sequences.
+    from zllm_b200 import abi
+    from zllm_b200.plan import DenseProgram
+
+    ctx = abi.Context(dry_run=True)
+
+    class FakeArena:
+        def alloc(self, n):
+            return ctx.alloc(n)
+
+    cfg = DenseConfig(layers=2, hidden=512, heads=8, kv_heads=4, head_dim=64, ff=1024, vocab=1024, max_ctx=64)
+    weights = {"embed": ctx.alloc(256), "head": ctx.alloc(256), "out_norm": ctx.alloc(256),
+               "layers": [{k: ctx.alloc(256) for k in ("wqkv", "wo", "wgu", "wdown", "attn_norm", "ffn_norm")} for _ in range(cfg.layers)]}
+    prog = DenseProgram(ctx, cfg, weights, batch, ctx.alloc, Shard(1, 2) if sharded else None, arena=FakeArena() if sharded else None)
+    prog.set_rope_table(ctx.alloc(256))
+    seen = []
+    real = prog.L.launch
+
+    def spy(kernel, params, args, groups, variant=0):
+        seen.append((kernel, variant, groups))
+        real(kernel, params, args, groups, variant)
+
+    prog.L.launch = spy
+    prog.record_step(17)
+    want = 4 < batch <= K.MATVEC_BATCHED_MAX_TOKENS
+    assert prog.batched == want
+    q4 = [(v, g) for k, v, g in seen if k == K.MATVEC_KERNEL["q4_k"]]
+    assert len(q4) == 4 * cfg.layers and all(g[1] == batch for _, g in q4)
+    assert all(v == (K.MATVEC_BATCHED if want else 0) for v, _ in q4)
+    head = [(v, g) for k, v, g in seen if k == K.MATVEC_KERNEL["q8_0"]]
+    assert head == [(0, head[0][1])]
+    rope_launches = sum(1 for k, _, _ in seen if k == K.ROPE_APPEND)
+    assert rope_launches == (0 if batch in (1, 2, 4) else cfg.layers)
+    ctx.close()
