@@ -8,8 +8,9 @@
 // with q the 4-bit codes, sc_u / m_u the 6-bit scale and min of 32-weight unit u, X the column's values and
 // S[c][u] the sum of X over unit u. What changes is where the products run: the CUDA cores only turn a weight
 // tile into the f16 INTEGERS sc_u q_i (at most 63 * 15 = 945, exact in f16: one mask, one fused multiply-add per
-// two weights), written to shared memory in the tensor cores' K-major 128-byte-swizzled layout; tcgen05.mma
-// (kind::f16, M 128 weight rows, N columns, K 16) accumulates them against the columns in f32 tensor memory. The
+// two weights) and hand them to the tensor cores as the A operand - in tensor memory (tcgen05.st; up to 64 columns)
+// or in shared memory in the K-major 128-byte-swizzled layout (128 columns, whose accumulators fill tensor memory);
+// tcgen05.mma (kind::f16, M 128 weight rows, N columns, K 16) accumulates them against the columns in f32. The
 // min term is one more K = 16 instruction per super-block (each m_u twice, against S[c][u] as two f16 terms).
 // Once per super-block the two sums leave tensor memory and meet the f16 super-scales and the column's scale in
 // registers. A column is
@@ -19,15 +20,19 @@
 // Products are exact (10 x 11 bits), sums are f32 over at most 256 terms per drain: within 1e-6 of the integer
 // arithmetic, against the 1e-5 bar of the reference's kernel checks.
 //
-// One CTA owns 128 weight rows x BN columns x a slice of k. Roles (20 warps):
-//   warp 0       TMA: the raw weight tiles (128 rows x 144 bytes per super-block), several super-blocks ahead
-//   warp 1       TMA: the columns' tiles (BN x 64 values, 128-byte swizzle), the unit sums, the column scales
-//   warp 2       allocates tensor memory; one lane issues the MMAs and commits stages / accumulators
-//   warps 4-11   decode the raw tile: two groups of four warps take alternate 64-weight chunks, thread = weight row
-//   warps 12-19  drain: thread (quadrant, lane) owns a weight row's accumulators for half of the columns
-// Two accumulator sets alternate, so a super-block's products run while the one before it drains. Every wait is
-// bounded; one that gives up raises the CTA's abort flag, every role leaves, tensor memory is freed and the
-// context's status word reports it.
+// One CTA owns 128 weight rows x BN columns (16, 32, 64 or 128) x a slice of k. Roles (20 or 24 warps):
+//   warp 0          TMA: the raw weight tiles (128 rows x 144 bytes per super-block), several super-blocks ahead
+//   warp 1          TMA: the columns' tiles (BN x 64 values, 128-byte swizzle), the unit sums, the column scales
+//   warp 2          allocates tensor memory; issues the MMAs and commits stages / accumulators
+//   decoders        two (BN > 32) or four groups of four warps take alternate 64-weight chunks, thread = weight row
+//   drain           eight (BN > 32) or four warps: thread (quadrant, lane) owns a weight row's accumulators
+// Warps 0-2 run their loops as WHOLE warps with one elected lane issuing: addresses and descriptors then stay
+// warp-uniform and feed the TMA / MMA instructions from uniform registers (issued from a single-lane branch the same
+// loops took five times longer). Two accumulator sets alternate, so a super-block's products run while the one
+// before it drains; up to 32 columns tensor memory also holds two or three whole decoded super-blocks, and decoders,
+// issuing warp and drain meet once per super-block (17 MMAs) instead of once per 64 weights. Every wait suspends the
+// thread (mbarrier.try_wait with a time hint) and is bounded in time; one that gives up raises the CTA's abort
+// flag, every role leaves, tensor memory is freed and the context's status word reports it.
 
 #include <cuda.h>
 #include <cuda_fp16.h>
@@ -46,13 +51,12 @@ __host__ __device__ constexpr int qt_threads(int bn) { return 32 * (4 + 4 * deco
 constexpr int RAW_ROW = 144, RAW_BYTES = QT_ROWS * RAW_ROW;   // a super-block of 128 rows as stored
 constexpr int A_BYTES = QT_ROWS * 128;                        // 128 rows x 64 f16
 constexpr int HDR_SLOTS = 4, CSC_SLOTS = 8;   // super-blocks whose row scales / column scales are in flight
-constexpr int MODE_PREFILL = 0, MODE_DECODE = 1;
 
 // Ring depths. The decoded tiles are made on the SM (short latency: few stages); the columns' tiles and the raw
 // weights cross the chip (about a microsecond each): their rings must hold what the SM consumes in that time.
 // Up to 64 columns the decoded tiles live in TENSOR memory (the accumulators leave room: 4 BN <= 256 of the 512
 // columns), written there by tcgen05.st and read by the MMA as its A operand: the tile then crosses shared memory
-// neither on its way in nor out (16 KB each way per 64 weights of 128 rows, which bounded the narrow multiplies).
+// neither on its way in nor out (16 KB each way per 64 weights of 128 rows).
 __host__ __device__ constexpr bool a_in_tmem(int bn) { return bn <= 64; }
 constexpr int A_COL0 = 256, A_COLS = 32;   // tensor-memory columns of the A ring: 8 stages x 32 (64 f16 per row)
 __host__ __device__ constexpr int a_stages(int bn) { return bn > 64 ? 3 : 8; }
