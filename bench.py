@@ -299,7 +299,7 @@ class DecodeStep:
     name = "decode"
     context = 8192
 
-    def __init__(self, dist: Dist, batch: int = 1, variant: int = 0, layers: int = 32, replay: str = "auto",
+    def __init__(self, dist: Dist, batch: int = 1, variant: int = 0, layers: int = 32,
                  exchange: str = "peer", attn_variant: int = 0, batched: str = "auto"):
         import torch
 
@@ -367,10 +367,6 @@ class DecodeStep:
         self.graph = None
         self.tgraph = None
         self.mv_graph = None
-        self.program = None
-        # how a step is replayed on one GPU: "program" = one persistent kernel (batch 1), "graph" = a CUDA graph
-        # of the step's launches
-        self.replay = replay if replay != "auto" else "graph"  # the graph is the faster of the two today
         self.bytes = self.prog.algorithmic_bytes(self.positions)
 
     def _record(self):
@@ -378,13 +374,6 @@ class DecodeStep:
 
     def step(self):
         torch = self.torch
-        if not self.dist.on and self.replay == "program":
-            if self.program is None:
-                self.ctx.program_begin()
-                self._record()
-                self.program = self.ctx.program_end()
-            self.ctx.program_launch(self.program)
-            return
         if self.exchange != "nccl":
             if self.graph is None:
                 self.ctx.capture_begin()
@@ -415,8 +404,6 @@ class DecodeStep:
         return self.tokens.nbytes, self.pinned_logits.numel() * 4
 
     def launches_per_step(self) -> int:
-        if self.program is not None:
-            return 1  # one persistent kernel runs the step's whole dispatch list
         return self.prog.launches_per_step or (2 + 7 * self.cfg.layers)
 
     def metric(self):
@@ -431,8 +418,7 @@ class DecodeStep:
                             f"{c.heads}/{c.kv_heads} heads of {c.head_dim}, FFN {c.ff}, vocab {c.vocab} Q8_0 head), "
                             f"f16 KV cache at {self.context} positions, batch {self.batch}",
                 "batch": self.batch, "context": self.context,
-                "replay": ("one persistent kernel per step (step program)" if self.program is not None
-                           else "CUDA graph of the step's launches"),
+                "replay": "CUDA graph of the step's launches",
                 "l2": f"inputs larger than L2: a step reads {self.bytes['total'] / 1e9:.2f} GB per rank "
                       f"({self.bytes['weights'] / 1e9:.2f} GB weights + {self.bytes['kv'] / 1e9:.2f} GB KV)",
                 "parallelism": ("1 GPU" if not self.dist.on else
@@ -895,7 +881,6 @@ def run_cuda(args):
     dist = Dist(args.gpus)
     kw = {"batch": args.batch, "variant": int(args.variant, 0)}
     if args.workload == "decode":
-        kw["replay"] = args.replay
         kw["exchange"] = args.exchange
         kw["attn_variant"] = args.attn_variant
         kw["batched"] = args.batched
@@ -1076,8 +1061,6 @@ def main():
     ap.add_argument("--attn-variant", type=int, default=0, help="decode: form of attn_split's fast path (0 default, 1-4: k_attn.cu)")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                     help="decode on N > 1 GPUs: slices pushed by the kernels over peer memory, or NCCL all-gathers")
-    ap.add_argument("--replay", default="auto", choices=["auto", "program", "graph"],
-                    help="decode: replay a step as one persistent kernel or as a CUDA graph of its launches")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -268,25 +268,6 @@ zcu_result zcu_ipc_open(zcu_context *context, const void *handle64, void **out_p
 zcu_result zcu_peer_config(zcu_context *context, uint32_t rank, uint32_t world, const uint64_t *bases, uint64_t arena_bytes,
                            uint64_t exchange_offset, uint32_t slots);
 
-/* A step program: the dispatches issued between begin and end are recorded (not run) and later replayed by ONE
- * persistent kernel, one CTA per SM, with grid-wide barriers where the reference has dispatch boundaries and
- * the weight stream running through them. It is this backend's form of the reference's prebuilt, replayed
- * launch list (src/plan/qwen35.zig; one `submit` of src/gpu/cmd.zig). Results are bit for bit those of the
- * same dispatches launched one by one. Accepted: matvec_q4_k / matvec_q8_0 (tensor-core family, at most 2
- * tokens, k a multiple of 256), embed_*, rope_append, attn_split / attn_combine on the f16 cache with a GQA
- * group of at most 4 and head_dim 64 or 128. Any other dispatch fails with ZCU_E_UNSUPPORTED_KERNEL (the
- * recording stays open; call zcu_program_abandon and replay launch by launch instead). */
-zcu_result zcu_program_begin(zcu_context *context);
-zcu_result zcu_program_end(zcu_context *context, uint32_t *out_program);
-zcu_result zcu_program_abandon(zcu_context *context);
-zcu_result zcu_program_launch(zcu_context *context, uint32_t program);
-zcu_result zcu_program_destroy(zcu_context *context, uint32_t program);
-/* Per-operation GPU times of the program's last launch (the counterpart of the per-dispatch timestamps of
- * startProfile/timings, src/gpu/timings.zig): waits for the stream, then fills out[3 i] = kernel family of
- * operation i, out[3 i + 1] = nanoseconds CTA 0 spent in it, out[3 i + 2] = nanoseconds it then waited at the
- * barrier. *out_ops = operations in the program. */
-zcu_result zcu_program_timings(zcu_context *context, uint32_t program, uint64_t *out, size_t capacity, size_t *out_ops);
-
 #ifdef __cplusplus
 }
 #endif

@@ -124,62 +124,6 @@ def test_decode_step_graph_replay_and_batch_rows_are_independent(ref, gpu):
         assert np.array_equal(alone[0].view(np.uint32), whole[s].view(np.uint32)), s
 
 
-def test_step_program_equals_launch_by_launch(ref, gpu):
-    # The same launch list recorded into a step program (one persistent kernel, grid barriers between the
-    # operations, weight copies running ahead across them) gives the logits, the hidden state and the appended
-    # cache rows of the launch-by-launch step, bit for bit; and it replays with new step inputs.
-    cfg = CFG
-    host = M.host_model(cfg, "tiny")
-    weights = M.upload(host, cfg, gpu.put)
-    rng = np.random.default_rng(11)
-    kv_shape = (1, cfg.max_ctx, cfg.kv_heads, cfg.head_dim)
-    kc_host = [rng.normal(size=kv_shape).astype(np.float16) for _ in range(cfg.layers)]
-    vc_host = [rng.normal(size=kv_shape).astype(np.float16) for _ in range(cfg.layers)]
-
-    def fresh():
-        # the program runs attention's CUDA-core form (variant 1); the launch-by-launch side is told to as well
-        prog = DenseProgram(gpu, cfg, weights, 1, gpu.zeros, variants={"attn_split": 1})
-        prog.set_rope_table(gpu.put(DenseProgram.rope_table(cfg)))
-        for il in range(cfg.layers):
-            prog.kc[il].upload(kc_host[il].view(np.uint16))
-            prog.vc[il].upload(vc_host[il].view(np.uint16))
-        return prog
-
-    steps = [(int(rng.integers(0, cfg.vocab)), p) for p in (200, 201, 17)]
-    plain, fused = fresh(), fresh()
-    gpu.program_begin()
-    fused.record_step(cfg.max_ctx)
-    program = gpu.program_end()
-    for token, pos in steps:
-        tok, ps = np.array([token], dtype=np.uint32), np.array([pos], dtype=np.uint32)
-        plain.write_step(tok, ps)
-        plain.record_step(cfg.max_ctx)
-        fused.write_step(tok, ps)
-        gpu.program_launch(program)
-        gpu.sync()
-        for name in ("logits", "x", "att", "act"):
-            a = getattr(plain, name).download(np.uint32)
-            b = getattr(fused, name).download(np.uint32)
-            assert np.array_equal(a, b), (name, pos)
-        for il in range(cfg.layers):
-            assert np.array_equal(plain.kc[il].download(np.uint16), fused.kc[il].download(np.uint16))
-            assert np.array_equal(plain.vc[il].download(np.uint16), fused.vc[il].download(np.uint16))
-    assert np.abs(fused.logits.download(np.float32)).max() > 0
-
-
-def test_step_program_refuses_what_it_cannot_run(gpu, launcher):
-    # a dispatch outside the persistent kernel's set fails the recording call; nothing falls back silently
-    from zllm_b200 import abi
-
-    gpu.program_begin()
-    try:
-        x, w, y = gpu.zeros(4 * 64), gpu.zeros(4 * 64), gpu.zeros(4 * 64)
-        with pytest.raises(abi.ZcuError):
-            launcher.rmsnorm(x, w, y, 1, 64, 1e-5)
-    finally:
-        gpu.program_abandon()
-
-
 @pytest.mark.parametrize("batch", [1, 2, 4])
 def test_rope_append_in_the_multiply_epilogue_equals_its_own_launch(gpu, batch):
     # rope_append fused into the Q|K|V multiply (one launch fewer per layer) gives the same rotated queries,

@@ -35,8 +35,7 @@ EXPORTS = [
     "zcu_start_profile", "zcu_stop_profile", "zcu_read_timings", "zcu_alloc", "zcu_free", "zcu_upload",
     "zcu_download", "zcu_memset", "zcu_launch", "zcu_sync", "zcu_launch_count", "zcu_capture_begin",
     "zcu_capture_end", "zcu_graph_launch", "zcu_graph_destroy", "zcu_rope_table",
-    "zcu_attention_decode_static", "zcu_program_begin", "zcu_program_end", "zcu_program_abandon", "zcu_program_launch",
-    "zcu_program_destroy", "zcu_program_timings", "zcu_ipc_export", "zcu_ipc_open", "zcu_peer_config",
+    "zcu_attention_decode_static", "zcu_ipc_export", "zcu_ipc_open", "zcu_peer_config",
 ]
 
 
@@ -116,12 +115,6 @@ def lib() -> C.CDLL:
         "zcu_graph_destroy": (C.c_int32, [vp, u32]),
         "zcu_rope_table": (C.c_int32, [vp, u32, u32, C.c_float, vp]),
         "zcu_attention_decode_static": (C.c_int32, [vp, vp, u32, C.POINTER(Binding), u32, u32, u32]),
-        "zcu_program_begin": (C.c_int32, [vp]),
-        "zcu_program_end": (C.c_int32, [vp, C.POINTER(u32)]),
-        "zcu_program_abandon": (C.c_int32, [vp]),
-        "zcu_program_launch": (C.c_int32, [vp, u32]),
-        "zcu_program_destroy": (C.c_int32, [vp, u32]),
-        "zcu_program_timings": (C.c_int32, [vp, u32, vp, C.c_size_t, C.POINTER(C.c_size_t)]),
         "zcu_ipc_export": (C.c_int32, [vp, vp, vp]),
         "zcu_ipc_open": (C.c_int32, [vp, vp, C.POINTER(vp)]),
         "zcu_peer_config": (C.c_int32, [vp, u32, u32, C.POINTER(u64), u64, u64, u32]),
@@ -361,28 +354,6 @@ class Context:
 
     def graph_launch(self, graph: int):
         self._check(lib().zcu_graph_launch(self.h, graph))
-
-    # -- step programs: dispatches recorded, then replayed by one persistent kernel
-    def program_begin(self):
-        self._check(lib().zcu_program_begin(self.h))
-
-    def program_end(self) -> int:
-        g = C.c_uint32()
-        self._check(lib().zcu_program_end(self.h, C.byref(g)))
-        return g.value
-
-    def program_abandon(self):
-        lib().zcu_program_abandon(self.h)
-
-    def program_launch(self, program: int):
-        self._check(lib().zcu_program_launch(self.h, program))
-
-    def program_timings(self, program: int, cap_ops: int = 4096) -> np.ndarray:
-        """[ops, 3] of (operation family, ns in the operation, ns at the barrier after it) for the last launch."""
-        out = np.zeros(3 * cap_ops, dtype=np.uint64)
-        n = C.c_size_t()
-        self._check(lib().zcu_program_timings(self.h, program, out.ctypes.data, out.size, C.byref(n)))
-        return out[: 3 * min(n.value, cap_ops)].reshape(-1, 3)
 
     def close(self):
         if self.h:

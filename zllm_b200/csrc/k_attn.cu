@@ -321,7 +321,7 @@ zcu_result launch_attn_split(const LaunchArgs& a) {
         const PStep* step = (const PStep*)a.b[4].ptr;
         const uint32_t* seq_pos = (a.nb >= 6 && p._pad[0] != 0) ? (const uint32_t*)a.b[5].ptr : nullptr;
         // Variants: 0 (default) / 4 = tensor cores, persistent walk with pipelined tiles; 3 = tensor cores, one CTA
-        // per block; 1 = CUDA cores (exact f32 products), one CTA per block (the form the step program runs);
+        // per block; 1 = CUDA cores (exact f32 products), one CTA per block;
         // 2 = CUDA cores, persistent walk; 5 = as 3, and the last block of each (row, KV head) merges the partials
         // (no attn_combine launch).
         const int total_blocks = (int)(grid.x * grid.y * grid.z);

@@ -1,5 +1,5 @@
-// The decode-attention fast path (f16 cache) and the merge of its partials, written for virtual blocks so that
-// the standalone kernels (k_attn.cu) and the persistent step program (k_program.cu) run the same code.
+// The decode-attention fast path (f16 cache) and the merge of its partials, written for virtual blocks (vblock.cuh);
+// the kernels of k_attn.cu map one CUDA block to each.
 #pragma once
 
 #include <cfloat>
@@ -12,8 +12,8 @@
 namespace attn {
 
 // ---- the fast path: f16 cache, GQA group <= 4, head_dim 64 or 128; 128 cache positions per CTA.
-// The cache and the queries are read past L1 (ld.global.cg): inside the step program the newest row of the
-// cache and the queries were written by another SM earlier in the same kernel.
+// The cache and the queries are read past L1 (ld.global.cg): the newest row of the cache and the queries were
+// written by another SM just before (the kernel may overlap the end of its producer as a programmatic dependent).
 // Scores: 8 threads per key, each with its hd/8 dims of the group's queries in registers, so K is read
 // with 16-byte loads and no shared-memory traffic; the 8 partial dots meet by shuffles. Softmax: one warp
 // per head. Sum of exp * v: 16 threads per key (8 dims each, 16-byte V loads), 16 key groups per CTA

@@ -1,5 +1,5 @@
-// rope_append and the embedding rows, written for virtual blocks so that the standalone kernels (k_glue.cu)
-// and the persistent step program (k_program.cu) run the same code.
+// rope_append and the embedding rows, written for virtual blocks (vblock.cuh); the kernels of k_glue.cu map one
+// CUDA block to each.
 #pragma once
 
 #include <cuda_fp16.h>

@@ -1,6 +1,5 @@
-// A virtual thread block: the unit the small kernels are written for. A standalone launch maps one CUDA
-// block to it; the persistent step program (k_program.cu) runs several of them side by side inside one
-// 512-thread CTA, each with its own named barrier and slice of shared memory.
+// A virtual thread block: the unit the small kernels are written for. A launch maps one CUDA block to it; a
+// larger CTA could run several side by side, each with its own named barrier and slice of shared memory.
 #pragma once
 
 #include <cstdint>

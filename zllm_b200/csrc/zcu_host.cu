@@ -97,10 +97,8 @@ struct zcu_context {
     uint64_t launches = 0;
     bool capturing = false;
     std::vector<cudaGraphExec_t> graphs;
-    zcu_program* recording = nullptr;     // dispatches go into this step program instead of running
     PeerTable peers = {};                 // tensor-parallel exchange (world == 0: not configured)
     std::vector<void*> ipc_open;          // peer arenas this context mapped
-    std::vector<zcu_program*> programs;
     uint8_t* pinned = nullptr;  // staging for uploads and readbacks
     int* status = nullptr;      // mapped host word kernels set when a bounded wait gives up
     void* scratch = nullptr;    // device scratch of the multiplies that stage their inputs (k_quant_tc.cu): work of one stream, used in order
@@ -217,7 +215,6 @@ zcu_result dispatch_kernel(zcu_context* c, uint32_t kernel, uint32_t variant, co
     char name[64];
     if (zcu_artifact(kernel, variant, name, sizeof(name)) == 0)
         return fail(c, ZCU_E_UNSUPPORTED_KERNEL, "kernel %u variant 0x%x is not implemented by the cuda backend", kernel, variant);
-    if (c->recording) return c->dry ? ZCU_OK : program_record(c->recording, kernel, a);
     c->launches++;
     if (c->dry) return ZCU_OK;
     switch (kernel) {
@@ -772,8 +769,6 @@ ZCU_EXPORT zcu_result zcu_destroy(zcu_context* c, uint32_t timeout_ms) {
     }
     for (void* m : c->ipc_open) cudaIpcCloseMemHandle(m);
     if (c->peers.counts) cudaFree(c->peers.counts);
-    for (zcu_program* pr : c->programs) program_free(pr);
-    program_free(c->recording);
     for (cudaGraphExec_t g : c->graphs)
         if (g) cudaGraphExecDestroy(g);
     for (size_t i = 0; i < c->buffers.size(); i++)
@@ -1107,60 +1102,6 @@ ZCU_EXPORT zcu_result zcu_peer_config(zcu_context* c, uint32_t rank, uint32_t wo
     return ZCU_OK;
 }
 
-ZCU_EXPORT zcu_result zcu_program_begin(zcu_context* c) {
-    LIVE(c);
-    if (c->dry) return fail(c, ZCU_E_INVALID, "a step program needs a device");
-    if (c->recording || c->capturing) return fail(c, ZCU_E_INVALID, "a recording or capture is already open");
-    c->recording = program_new();
-    return ZCU_OK;
-}
-ZCU_EXPORT zcu_result zcu_program_end(zcu_context* c, uint32_t* out_program) {
-    LIVE(c);
-    if (!c->recording || !out_program) return fail(c, ZCU_E_INVALID, "no step program is being recorded");
-    zcu_program* pr = c->recording;
-    c->recording = nullptr;
-    LaunchArgs a;
-    fill_args(c, a);
-    cudaSetDevice(c->device);
-    const zcu_result r = program_finish(pr, a);
-    if (r != ZCU_OK) {
-        program_free(pr);
-        return r;
-    }
-    c->programs.push_back(pr);
-    *out_program = (uint32_t)c->programs.size() - 1;
-    return ZCU_OK;
-}
-ZCU_EXPORT zcu_result zcu_program_abandon(zcu_context* c) {
-    if (!c) return ZCU_E_INVALID;
-    program_free(c->recording);
-    c->recording = nullptr;
-    return ZCU_OK;
-}
-ZCU_EXPORT zcu_result zcu_program_launch(zcu_context* c, uint32_t program) {
-    LIVE(c);
-    if (program >= c->programs.size() || !c->programs[program]) return fail(c, ZCU_E_BAD_ID, "no step program %u", program);
-    LaunchArgs a;
-    fill_args(c, a);
-    c->launches += 1;
-    return program_launch(c->programs[program], a);
-}
-ZCU_EXPORT zcu_result zcu_program_timings(zcu_context* c, uint32_t program, uint64_t* out, size_t capacity, size_t* out_ops) {
-    LIVE(c);
-    if (program >= c->programs.size() || !c->programs[program] || !out) return fail(c, ZCU_E_BAD_ID, "no step program %u", program);
-    zcu_result r = wait_stream(c, 60000u);
-    if (r != ZCU_OK) return r;
-    LaunchArgs a;
-    fill_args(c, a);
-    return program_timings(c->programs[program], a, out, capacity, out_ops);
-}
-ZCU_EXPORT zcu_result zcu_program_destroy(zcu_context* c, uint32_t program) {
-    if (!c) return ZCU_E_INVALID;
-    if (program >= c->programs.size() || !c->programs[program]) return fail(c, ZCU_E_BAD_ID, "no step program %u", program);
-    program_free(c->programs[program]);
-    c->programs[program] = nullptr;
-    return ZCU_OK;
-}
 ZCU_EXPORT zcu_result zcu_graph_destroy(zcu_context* c, uint32_t graph) {
     if (!c) return ZCU_E_INVALID;
     if (graph >= c->graphs.size() || !c->graphs[graph]) return fail(c, ZCU_E_BAD_ID, "no graph %u", graph);

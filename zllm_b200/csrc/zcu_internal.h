@@ -149,16 +149,6 @@ zcu_result launch_matmul_q4_k_tc(const LaunchArgs& a);       // the tcgen05 pref
 // ranges it stores to, which must lie in the local arena when it pushes. Fills `u` (both slots PEER_NONE without one).
 zcu_result parse_peer(const LaunchArgs& a, PeerUse& u, const void* out_lo, const void* out_hi);
 
-// The step program (k_program.cu): a recorded list of dispatches run by one persistent kernel.
-struct zcu_program;
-zcu_program* program_new();
-void program_free(zcu_program* pr);
-uint64_t program_dispatches(const zcu_program* pr);
-zcu_result program_record(zcu_program* pr, uint32_t kernel, const LaunchArgs& a);
-zcu_result program_finish(zcu_program* pr, const LaunchArgs& a);
-zcu_result program_launch(zcu_program* pr, const LaunchArgs& a);
-zcu_result program_timings(zcu_program* pr, const LaunchArgs& a, uint64_t* out, size_t cap, size_t* n_out);
-
 // Whether (kernel, variant) exists, and its artifact name.
 bool matvec_variant_ok(uint32_t kernel, uint32_t variant);
 
