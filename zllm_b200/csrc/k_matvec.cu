@@ -322,7 +322,7 @@ zcu_result launch_quant(const LaunchArgs& a, uint32_t block) {
     // Q8_0 rows that are not whole 256-weight pieces have ragged tiles: the scalar family takes them.
     const bool imma_ok = TYPE != W_Q8_0 || v.p.k % 256 == 0;
     if ((a.variant == 0 && imma_ok) || family == ZCU_FAMILY_MMA)
-        return launch_matvec_imma(a, v, TYPE, (int)(a.variant & 0xffu), 0);
+        return launch_matvec_imma(a, v, TYPE, (int)(a.variant & 0xffu), (int)((a.variant >> 8) & 0xffu));
     if (v.has_rope) return zcu_fail(a, ZCU_E_UNSUPPORTED_KERNEL, "matvec + rope_append: only the tensor-core family fuses it");
     if (v.peer.wait_slot != PEER_NONE || v.peer.push_slot != PEER_NONE)
         return zcu_fail(a, ZCU_E_UNSUPPORTED_KERNEL, "matvec in a peer exchange: only the tensor-core family takes part");
@@ -341,7 +341,7 @@ bool matvec_variant_ok(uint32_t kernel, uint32_t variant) {
     if (family == ZCU_FAMILY_SCALAR) return ks == 0;
     if (family == ZCU_FAMILY_MMA) {
         const uint32_t stages = variant & 0xffu;
-        return ks == 0 && (stages == 0 || (stages >= 2 && stages <= 6));
+        return ks <= 1 && (stages == 0 || (stages >= 2 && stages <= 6));
     }
     if (family == ZCU_FAMILY_TCGEN05) return kernel == ZCU_K_MATVEC_Q4_K && (variant & 0xffffu) == 0;
     return false;

@@ -75,7 +75,8 @@ struct MvArgs {
 
 }  // namespace mv
 
-// The tensor-core family (k_matvec_imma.cu). stages = 0 picks the deepest ring that fits.
-zcu_result launch_matvec_imma(const LaunchArgs& a, const mv::MvArgs& v, int type, int stages, int reserved);
+// The tensor-core family (k_matvec_imma.cu). stages = 0 picks the deepest ring that fits; shape 0 = CTAs of 16
+// warps, 1 = CTAs of 8 warps (two per SM).
+zcu_result launch_matvec_imma(const LaunchArgs& a, const mv::MvArgs& v, int type, int stages, int shape);
 // The batched tcgen05 family of matvec_q4_k (k_quant_tc.cu): up to 64 tokens in one pass over the weights.
 zcu_result launch_matvec_q4_k_tc(const LaunchArgs& a, const mv::MvArgs& v);

@@ -20,11 +20,14 @@
 
 #include <cuda_fp16.h>
 
-#include "k_matvec_imma.cuh"
+#include "imma_util.cuh"
+#include "k_matvec_common.cuh"
+#include "tma_util.cuh"
 
 namespace {
 
 using namespace imma;
+using namespace mv;
 
 // ---------------------------------------------------------------------------------------------- quantize_q8
 struct PQuantize {  // kernels.zig:495-501
