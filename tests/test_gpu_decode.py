@@ -61,7 +61,7 @@ def test_decode_step_matches_oracle(ref, gpu, batch):
     hidden = prog.x.download(np.float32).reshape(batch, cfg.hidden)
     # (six sequences: the Q4_K multiplies take the batched family - columns, multiply, reduction)
     assert prog.batched == (batch == 6)
-    assert prog.launches_per_step == 1 + (7 - prog.fuse_rope - prog.fuse_combine + 8 * prog.batched) * cfg.layers + 1
+    assert prog.launches_per_step == 1 + (7 - prog.fuse_rope + 8 * prog.batched) * cfg.layers + 1
     for b in range(batch):
         kc = [np.ascontiguousarray(kc_host[il][b]).view(np.uint16).copy() for il in range(cfg.layers)]
         vc = [np.ascontiguousarray(vc_host[il][b]).view(np.uint16).copy() for il in range(cfg.layers)]
@@ -192,37 +192,3 @@ def test_peer_exchange_with_one_rank_equals_the_plain_step(gpu):
         gpu.sync()
         for name in ("logits", "x", "att", "act"):
             assert np.array_equal(getattr(plain, name).download(np.uint32), getattr(peer, name).download(np.uint32)), (name, pos)
-
-
-def test_merging_attention_equals_split_then_combine(gpu):
-    # attn_combine done by the last key block of each (sequence, KV head) inside attn_split gives the bits of the
-    # two launches, step after step (the ticket words return to zero).
-    cfg = CFG
-    host = M.host_model(cfg, "tiny")
-    weights = M.upload(host, cfg, gpu.put)
-    rng = np.random.default_rng(123)
-    batch = 3
-    kv_shape = (batch, cfg.max_ctx, cfg.kv_heads, cfg.head_dim)
-    kc_host = [rng.normal(size=kv_shape).astype(np.float16) for _ in range(cfg.layers)]
-    vc_host = [rng.normal(size=kv_shape).astype(np.float16) for _ in range(cfg.layers)]
-    progs = []
-    for merge in (False, True):
-        prog = DenseProgram(gpu, cfg, weights, batch, gpu.zeros, fuse_combine=merge, variants=None if merge else {"attn_split": 3})
-        assert prog.fuse_combine == merge
-        prog.set_rope_table(gpu.put(DenseProgram.rope_table(cfg)))
-        for il in range(cfg.layers):
-            prog.kc[il].upload(kc_host[il].view(np.uint16))
-            prog.vc[il].upload(vc_host[il].view(np.uint16))
-        progs.append(prog)
-    for step_no in range(3):
-        positions = np.array([300 - step_no, 5 + step_no, 130 + step_no], dtype=np.uint32)  # 3, 1 and 2 key blocks
-        tokens = rng.integers(0, cfg.vocab, size=batch).astype(np.uint32)
-        outs = []
-        for prog in progs:
-            prog.write_step(tokens, positions)
-            prog.record_step(int(positions.max()) + 1)
-            gpu.sync()
-            outs.append([prog.logits.download(np.uint32), prog.att.download(np.uint32)])
-        assert np.array_equal(outs[0][1], outs[1][1]), step_no
-        assert np.array_equal(outs[0][0], outs[1][0]), step_no
-    assert not progs[1].tickets.download(np.uint32).any()

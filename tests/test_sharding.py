@@ -140,8 +140,7 @@ def test_two_gloo_ranks_reproduce_the_unsharded_layer(ref):
     assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
 
 
-@pytest.mark.parametrize("merge", [False, True])
-def test_exchange_slots_chain_through_the_sharded_launch_list(merge):
+def test_exchange_slots_chain_through_the_sharded_launch_list():
     # The sharded plan on a dry-run context (no device): every multiply that reads a gathered vector waits for the
     # exchange that the vector's producer pushes, slots are used once per step, and the list ends with the wait
     # that hands the logits to the host.
@@ -159,8 +158,8 @@ def test_exchange_slots_chain_through_the_sharded_launch_list(merge):
     cfg = DenseConfig(layers=3, hidden=512, heads=8, kv_heads=4, head_dim=64, ff=1024, vocab=1024, max_ctx=64)
     weights = {"embed": ctx.alloc(256), "head": ctx.alloc(256), "out_norm": ctx.alloc(256),
                "layers": [{k: ctx.alloc(256) for k in ("wqkv", "wo", "wgu", "wdown", "attn_norm", "ffn_norm")} for _ in range(cfg.layers)]}
-    prog = DenseProgram(ctx, cfg, weights, 1, ctx.alloc, Shard(1, 2), arena=FakeArena(), fuse_combine=merge)
-    per_layer = 5 if merge else 6
+    prog = DenseProgram(ctx, cfg, weights, 1, ctx.alloc, Shard(1, 2), arena=FakeArena())
+    per_layer = 6
     prog.set_rope_table(ctx.alloc(256))
     seen = []
     real = prog.L.launch
@@ -182,10 +181,7 @@ def test_exchange_slots_chain_through_the_sharded_launch_list(merge):
         ops = exts[1 + per_layer * il: 1 + per_layer * (il + 1)]
         qkv, (wo, gu, down) = ops[0], ops[-3:]
         assert qkv == (None if il == 0 else (4 * il - 1, none))  # the residual stream of the layer before
-        if merge:
-            assert ops[1] == (none, 4 * il)                      # the merging attn_split pushes the heads' columns
-        else:
-            assert ops[1] is None and ops[2] == (none, 4 * il)   # attn_split, then attn_combine pushes them
+        assert ops[1] is None and ops[2] == (none, 4 * il)       # attn_split, then attn_combine pushes the heads' columns
         assert wo == (4 * il, 4 * il + 1) and gu == (4 * il + 1, 4 * il + 2) and down == (4 * il + 2, 4 * il + 3)
     assert exts[-2] == (4 * cfg.layers - 1, 4 * cfg.layers)       # the head
     assert seen[-1] == (K.EXT_PEER_WAIT, (4 * cfg.layers, none))  # the host's wait for the logits

@@ -207,25 +207,12 @@ __global__ void __launch_bounds__(attn::AM_THREADS, 3) attn_split_mma(PAttention
                                                                      const __half* __restrict__ kc,
                                                                      const __half* __restrict__ vc, float* __restrict__ part,
                                                                      const PStep* __restrict__ step,
-                                                                     const uint32_t* __restrict__ seq_pos) {
+                                                                     const uint32_t* __restrict__ seq_pos, int* __restrict__ status) {
     extern __shared__ __align__(128) unsigned char dyn_smem[];
-    attn::attn_split_mma_body<HD>(dyn_smem, p, qg, kc, vc, part, step, seq_pos, (int)blockIdx.x, (int)blockIdx.y, (int)blockIdx.z);
-}
-
-template <int HD>
-__global__ void __launch_bounds__(attn::AM_THREADS, 3) attn_split_mma_fused(PAttention p, const float* __restrict__ qg,
-                                                                           const __half* __restrict__ kc,
-                                                                           const __half* __restrict__ vc, float* __restrict__ part,
-                                                                           const PStep* __restrict__ step,
-                                                                           const uint32_t* __restrict__ seq_pos, float* __restrict__ out,
-                                                                           uint32_t* __restrict__ tickets,
-                                                                           const __grid_constant__ PeerUse pu) {
-    extern __shared__ __align__(128) unsigned char dyn_smem[];
-    attn::attn_split_mma_fused_body<HD>(dyn_smem, p, qg, kc, vc, part, step, seq_pos, out, tickets, (int)blockIdx.x, (int)blockIdx.y,
-                                        (int)blockIdx.z, &pu);
-    // in an exchange every CTA that produced a partial is counted by the ticket above; the grid-wide count of
-    // finished CTAs that advances the slot's count is separate
-    peer::finish(pu, gridDim.x * gridDim.y * gridDim.z);
+    // launched as a programmatic dependent: the queries and the newest cache row come from the kernel before
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+    attn::attn_split_mma_body<HD>(dyn_smem, p, qg, kc, vc, part, step, seq_pos, (int)blockIdx.x, (int)blockIdx.y, (int)blockIdx.z, status);
 }
 
 template <int HD>
@@ -249,13 +236,17 @@ __global__ void __launch_bounds__(attn::AF_THREADS, 1) attn_split_persistent(PAt
     attn::attn_split_persistent_body<HD, GROUP_CAP>(dyn_smem, p, qg, kc, vc, part, step, seq_pos, by, rows);
 }
 
-__global__ void __launch_bounds__(256) attn_combine_kernel(PAttention p, const float* __restrict__ qg,
-                                                          const float* __restrict__ part, float* __restrict__ out,
-                                                          const PStep* __restrict__ step,
-                                                          const uint32_t* __restrict__ seq_pos, int kb,
-                                                          const __grid_constant__ PeerUse pu) {
+__global__ void __launch_bounds__(attn::AC_THREADS) attn_combine_kernel(PAttention p, const float* __restrict__ qg,
+                                                                       const float* __restrict__ part, float* __restrict__ out,
+                                                                       const PStep* __restrict__ step,
+                                                                       const uint32_t* __restrict__ seq_pos, int kb, int* __restrict__ status,
+                                                                       const __grid_constant__ PeerUse pu) {
     extern __shared__ __align__(16) unsigned char dyn_smem[];
-    attn::attn_combine_body(vblock_of_cta(dyn_smem), p, qg, part, out, step, seq_pos, kb, &pu);
+    // launched as a programmatic dependent of attn_split; what follows it (a multiply) may move in and start its
+    // weight copies at once
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+    attn::attn_combine_body(vblock_of_cta(dyn_smem), p, qg, part, out, step, seq_pos, kb, status, &pu);
     peer::finish(pu, gridDim.x * gridDim.y);
 }
 
@@ -320,35 +311,10 @@ zcu_result launch_attn_split(const LaunchArgs& a) {
         float* part = (float*)a.b[3].ptr;
         const PStep* step = (const PStep*)a.b[4].ptr;
         const uint32_t* seq_pos = (a.nb >= 6 && p._pad[0] != 0) ? (const uint32_t*)a.b[5].ptr : nullptr;
-        // Variants: 0 (default) / 4 = tensor cores, persistent walk with pipelined tiles; 3 = tensor cores, one CTA
-        // per block; 1 = CUDA cores (exact f32 products), one CTA per block;
-        // 2 = CUDA cores, persistent walk; 5 = as 3, and the last block of each (row, KV head) merges the partials
-        // (no attn_combine launch).
+        // Variants: 0 (default) and 3 = tensor cores, one CTA per block; 4 = tensor cores, persistent walk with
+        // pipelined tiles; 1 = CUDA cores (exact f32 products), one CTA per block;
+        // 2 = CUDA cores, persistent walk.
         const int total_blocks = (int)(grid.x * grid.y * grid.z);
-        if (a.variant == 5) {
-            // one CTA per block on the tensor cores, and the last block of each (row, KV head) merges the partials:
-            // bindings 7 and 8 are attn_combine's output and the ticket words (u32 per row and KV head, zero)
-            ZCU_NEED(a, a.nb >= 8, "attn_split (merging form): needs the output and the ticket bindings");
-            ZCU_NEED(a, (grid.y + 0u) <= 128u, "attn_split (merging form): %u key blocks above 128", grid.y);
-            float* out = (float*)a.b[6].ptr;
-            PeerUse pu;
-            {
-                const size_t orow = p._pad[1] ? (size_t)p._pad[1] : (size_t)p.heads * p.head_dim;
-                const float* lo = out + (size_t)p.row0 * orow;
-                const float* hi = lo + (size_t)(a.grid[2] - 1) * orow + (size_t)p.heads * p.head_dim;
-                zcu_result pr = parse_peer(a, pu, lo, hi);
-                if (pr != ZCU_OK) return pr;
-            }
-            const size_t msmem = attn::attn_mma_smem(hd);
-            auto mk = hd == 128 ? attn_split_mma_fused<128> : attn_split_mma_fused<64>;
-            if (cudaFuncSetAttribute(mk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)msmem) != cudaSuccess) {
-                cudaGetLastError();
-                return zcu_fail(a, ZCU_E_GPU, "attn_split: %zu bytes of shared memory refused", msmem);
-            }
-            mk<<<grid, attn::AM_THREADS, msmem, a.stream>>>(p, qg, kc, vc, part, step, seq_pos, out, (uint32_t*)a.b[7].ptr, pu);
-            ZCU_CHECK_LAUNCH(a);
-            return ZCU_OK;
-        }
         if (a.variant == 4) {
             // the tensor-core arithmetic as a persistent walk, one CTA per SM, TMA tiles pipelined
             const size_t msmem = attn::attn_mma_persist_smem(hd);
@@ -382,8 +348,8 @@ zcu_result launch_attn_split(const LaunchArgs& a) {
                 cudaGetLastError();
                 return zcu_fail(a, ZCU_E_GPU, "attn_split: %zu bytes of shared memory refused", msmem);
             }
-            mk<<<grid, attn::AM_THREADS, msmem, a.stream>>>(p, qg, kc, vc, part, step, seq_pos);
-            ZCU_CHECK_LAUNCH(a);
+            cudaError_t e = launch_pdl(mk, grid, dim3(attn::AM_THREADS), msmem, a.stream, p, qg, kc, vc, part, step, seq_pos, a.status);
+            if (e != cudaSuccess) return zcu_fail(a, ZCU_E_GPU, "attn_split: launch failed: %s", cudaGetErrorString(e));
             return ZCU_OK;
         }
         if (a.variant == 1) {
@@ -429,10 +395,14 @@ zcu_result launch_attn_combine(const LaunchArgs& a) {
         zcu_result pr = parse_peer(a, pu, lo, hi);
         if (pr != ZCU_OK) return pr;
     }
-    attn_combine_kernel<<<dim3(p.heads, a.grid[1]), 256, smem, a.stream>>>(p, (const float*)a.b[0].ptr, (const float*)a.b[1].ptr,
-                                                                           (float*)a.b[2].ptr, (const PStep*)a.b[3].ptr, seq_pos,
-                                                                           attn_keys_per_block(p), pu);
-    ZCU_CHECK_LAUNCH(a);
+    if (smem > 48 * 1024 && cudaFuncSetAttribute(attn_combine_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+        cudaGetLastError();
+        return zcu_fail(a, ZCU_E_GPU, "attn_combine: %zu bytes of shared memory refused", smem);
+    }
+    cudaError_t e = launch_pdl(attn_combine_kernel, dim3(p.heads, a.grid[1]), dim3(attn::AC_THREADS), smem, a.stream, p, (const float*)a.b[0].ptr,
+                               (const float*)a.b[1].ptr, (float*)a.b[2].ptr, (const PStep*)a.b[3].ptr, seq_pos, attn_keys_per_block(p),
+                               a.status, pu);
+    if (e != cudaSuccess) return zcu_fail(a, ZCU_E_GPU, "attn_combine: launch failed: %s", cudaGetErrorString(e));
     return ZCU_OK;
 }
 

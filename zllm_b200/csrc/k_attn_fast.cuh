@@ -365,7 +365,8 @@ template <int HD>
 __device__ __forceinline__ void attn_split_mma_body(unsigned char* smem, const PAttention& p, const float* __restrict__ qg,
                                                     const __half* __restrict__ kc, const __half* __restrict__ vc,
                                                     float* __restrict__ part, const PStep* __restrict__ step,
-                                                    const uint32_t* __restrict__ seq_pos, int g_kv, int b, int t) {
+                                                    const uint32_t* __restrict__ seq_pos, int g_kv, int b, int t,
+                                                    int* __restrict__ status = nullptr) {
     constexpr int RS = HD * 2 + 16;              // bytes between the rows of a staged tile
     constexpr int PIECES = AF_KEYS * (HD / 8) / AM_THREADS;
     unsigned char* Kt = smem;
@@ -378,7 +379,12 @@ __device__ __forceinline__ void attn_split_mma_body(unsigned char* smem, const P
     const int group = (int)(p.heads / p.kv_heads);
     const int row = (int)p.row0 + t;
     const size_t seq_off = (size_t)row * p._pad[0];
-    const int keys = (seq_pos ? (int)seq_pos[row] : (int)step->pos0 + row) + 1;
+    int keys = (seq_pos ? (int)seq_pos[row] : (int)step->pos0 + row) + 1;
+    // the launch covers gridDim.y blocks of the cache: a step past them is an error of the caller, reported, not followed
+    if (keys > (int)gridDim.y * AF_KEYS) {
+        keys = (int)gridDim.y * AF_KEYS;
+        if (tid == 0 && status) atomicExch(status, 6);
+    }
     const int k0 = b * AF_KEYS;
     const size_t kv_stride = (size_t)p.kv_heads * HD;
     const int q_head = p.gated ? 2 * HD : HD;
@@ -420,115 +426,6 @@ constexpr int AP_STAGES = 3;
 __host__ __device__ constexpr size_t attn_persist_smem(int group_cap, int group, int hd) {
     return (size_t)AP_STAGES * 2 * AF_KEYS * hd * 2 + ((size_t)group_cap * AF_KEYS + 2 * group_cap + 8) * sizeof(float) +
            (size_t)(AF_THREADS / 32) * group * hd * sizeof(float);
-}
-
-// The merge of a KV head's partials by the CTA that finished last (attn_combine's arithmetic in attn_combine's order:
-// the same bits), so a decode step needs no combine launch. 256 threads: two warps per head of the group; the
-// block weights go through `wsm` ([4][128] floats), the halves' sums through `hsm` ([4][HD] float + [4] l).
-// Needs at most 128 blocks.
-template <int HD>
-__device__ __forceinline__ void combine_group_tail(const PAttention& p, const float* __restrict__ qg, const float* __restrict__ part,
-                                                   float* __restrict__ out, float (*wsm)[AF_KEYS], float* hsm, int g_kv, int t,
-                                                   int blocks, const PeerUse* __restrict__ pu) {
-    constexpr int DPL = HD / 32;  // dims per lane
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int group = (int)(p.heads / p.kv_heads);
-    const int hh = warp >> 1, sub = warp & 1;  // head of the group, half of the blocks
-    const int h = g_kv * group + min(hh, group - 1);
-    const int row = (int)p.row0 + t;
-    const size_t bs = (size_t)HD + 2, base0 = ((size_t)t * p.heads + h) * p.max_blocks * bs;
-    // the largest block maximum, then the block weights
-    float mb[4], mx = -FLT_MAX;
-#pragma unroll
-    for (int i = 0; i < 4; i++) {
-        const int b = lane + 32 * i;
-        mb[i] = b < blocks ? __ldcg(part + base0 + b * bs) : -FLT_MAX;
-        mx = fmaxf(mx, mb[i]);
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-    if (sub == 0) {
-#pragma unroll
-        for (int i = 0; i < 4; i++)
-            if (lane + 32 * i < blocks) wsm[hh][lane + 32 * i] = expf(mb[i] - mx);
-    }
-    __syncthreads();
-    // each half of the blocks in block order (attn_combine's two halves), then low + high
-    const int per = (blocks + 1) / 2, b0 = sub * per, b1 = min(blocks, b0 + per);
-    float l = 0.f, o[DPL];
-#pragma unroll
-    for (int d = 0; d < DPL; d++) o[d] = 0.f;
-#pragma unroll 4
-    for (int b = b0; b < b1; b++) {
-        const float w = wsm[hh][b];
-        const float* pb = part + base0 + b * bs;
-        l = __fmaf_rn(__ldcg(pb + 1), w, l);
-#pragma unroll
-        for (int d = 0; d < DPL; d += 2) {
-            const float2 v = __ldcg(reinterpret_cast<const float2*>(pb + 2 + DPL * lane + d));
-            o[d] = __fmaf_rn(v.x, w, o[d]);
-            o[d + 1] = __fmaf_rn(v.y, w, o[d + 1]);
-        }
-    }
-    if (sub == 1) {
-#pragma unroll
-        for (int d = 0; d < DPL; d++) hsm[hh * HD + DPL * lane + d] = o[d];
-        if (lane == 0) hsm[4 * HD + hh] = l;
-    }
-    __syncthreads();
-    if (sub == 1 || hh >= group) return;
-    l = __fadd_rn(l, hsm[4 * HD + hh]);
-    const size_t orow = p._pad[1] ? (size_t)p._pad[1] : (size_t)p.heads * HD;
-    const bool pushing = pu != nullptr && pu->push_slot != PEER_NONE;
-    const uint32_t tag = pushing ? peer::push_tag(*pu) : 0u;
-#pragma unroll
-    for (int d = 0; d < DPL; d++) {
-        const int dim = DPL * lane + d;
-        const float ov = __fadd_rn(o[d], hsm[hh * HD + dim]);
-        float res = ov / l;
-        if (p.gated) {
-            const float gate = __ldcg(qg + (size_t)row * p.q_row + (size_t)2 * h * HD + HD + dim);
-            res = ov / l / (1.0f + expf(-gate));
-        }
-        const size_t oi = (size_t)row * orow + (size_t)h * HD + dim;
-        out[oi] = res;
-        if (pushing) peer::push(*pu, out + oi, res, tag);
-    }
-}
-
-// attn_split_mma_body followed by the merge when this CTA is the last of its (row, KV head) to finish.
-// tickets[row * kv_heads + g]: blocks of that pair that have finished (zero before the first use; the last block
-// puts the zero back).
-template <int HD>
-__device__ __forceinline__ void attn_split_mma_fused_body(unsigned char* smem, const PAttention& p, const float* __restrict__ qg,
-                                                          const __half* __restrict__ kc, const __half* __restrict__ vc,
-                                                          float* __restrict__ part, const PStep* __restrict__ step,
-                                                          const uint32_t* __restrict__ seq_pos, float* __restrict__ out,
-                                                          uint32_t* __restrict__ tickets, int g_kv, int b, int t,
-                                                          const PeerUse* __restrict__ pu) {
-    __shared__ int is_last;
-    const int row = (int)p.row0 + t;
-    const int keys = (seq_pos ? (int)seq_pos[row] : (int)step->pos0 + row) + 1;
-    if (b * AF_KEYS >= keys) return;  // no keys here: neither a partial nor a ticket
-    const int blocks = (keys + AF_KEYS - 1) / AF_KEYS;
-    attn_split_mma_body<HD>(smem, p, qg, kc, vc, part, step, seq_pos, g_kv, b, t);
-    __threadfence();  // this thread's part of the partial before the ticket
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        uint32_t* tk = tickets + (size_t)t * p.kv_heads + g_kv;
-        const bool last = atomicAdd(tk, 1u) == (uint32_t)blocks - 1;
-        if (last) {
-            *tk = 0;
-            __threadfence();  // the others' partials (published before their tickets) before this CTA reads them
-        }
-        is_last = last;
-    }
-    __syncthreads();
-    if (!is_last) return;
-    constexpr int RS = HD * 2 + 16;
-    float (*wsm)[AF_KEYS] = reinterpret_cast<float (*)[AF_KEYS]>(smem + (size_t)2 * AF_KEYS * RS);  // the block's score scratch
-    float* hsm = reinterpret_cast<float*>(smem);                                                 // the K tile's place
-    combine_group_tail<HD>(p, qg, part, out, wsm, hsm, g_kv, t, blocks, pu);
 }
 
 // The tensor-core block arithmetic as a persistent walk: one CTA per SM, the K/V tiles of the next two blocks in
@@ -828,29 +725,53 @@ __device__ __forceinline__ void attn_split_persistent_body(unsigned char* smem, 
 // grid (heads, rows). Merges the blocks' partials (src/kernels/attn_combine.wgsl):
 //   M = max m_b,  L = sum l_b e^(m_b - M),  o = sum o_b e^(m_b - M) / L,  times sigmoid(gate) when gated.
 // Bindings: qg, part, out, step (+ per-row positions for batched sequences). `kb`: cache positions per block.
-// The block weights are computed once into shared memory; each thread then adds its dim over the blocks
-// in block order with independent loads.
+// AC_THREADS threads = AC_THREADS / 128 (or / 256) lanes of blocks per dim: thread (q, d) owns blocks q, q + Q, ...
+// of dim d. Everything a thread needs from memory is asked for before anything is computed (the block maxima and
+// sums by the first `blocks` threads, the thread's AC_KEEP first partial outputs into registers), so the kernel
+// pays one round trip to L2, not one per phase. Sums run in a fixed order: a lane's blocks in block order, then
+// the lanes in lane order.
 constexpr int AC_MAX_BLOCKS = 4096;
-__host__ __device__ constexpr size_t attn_combine_smem(int max_blocks) { return ((size_t)max_blocks + 32 + 2 + 2 * 128) * sizeof(float); }
+constexpr int AC_THREADS = 512;
+constexpr int AC_KEEP = 20;
+__host__ __device__ constexpr size_t attn_combine_smem(int max_blocks) { return ((size_t)2 * max_blocks + 64 + 2 * AC_THREADS) * sizeof(float); }
 
 __device__ __forceinline__ void attn_combine_body(const VBlock& vb, const PAttention& p, const float* __restrict__ qg,
                                                   const float* __restrict__ part, float* __restrict__ out,
                                                   const PStep* __restrict__ step, const uint32_t* __restrict__ seq_pos,
-                                                  int kb, const PeerUse* __restrict__ pu = nullptr) {
-    float* wsm = reinterpret_cast<float*>(vb.smem);  // [blocks] weights, [32] scratch, [128] float2 of the upper half
+                                                  int kb, int* __restrict__ status, const PeerUse* __restrict__ pu = nullptr) {
+    float* wsm = reinterpret_cast<float*>(vb.smem);  // [blocks] weights, [blocks] weighted sums, [64] scratch, [AC_THREADS] float2
     const int tid = vb.tid, lane = tid & 31, warp = tid >> 5, h = vb.x, t = vb.y;
     const int hd = (int)p.head_dim;
     const int row = (int)p.row0 + t;
     const int keys = (seq_pos ? (int)seq_pos[row] : (int)step->pos0 + row) + 1;
-    const int blocks = (keys + kb - 1) / kb;
-    float* red = wsm + blocks;
+    int blocks = (keys + kb - 1) / kb;
+    // the partials hold p.max_blocks blocks per head: a step past that is an error of the caller, reported, not followed
+    const int cap = (int)p.max_blocks;
+    if (blocks > cap) {
+        blocks = cap;
+        if (tid == 0 && status) atomicExch(status, 6);
+    }
+    float* lsm = wsm + cap;
+    float* red = lsm + cap;
+    float2* lanes_sm = reinterpret_cast<float2*>(red + 64);
     const size_t base0 = ((size_t)t * p.heads + h) * p.max_blocks * (hd + 2);
     const size_t bs = (size_t)hd + 2;
+    const int dims = hd <= 128 ? 128 : 256;
+    const int Q = AC_THREADS / dims;                 // lanes of blocks
+    const int d = tid % dims, q = tid / dims;
+    // ---- every load first
+    float keep[AC_KEEP];
+#pragma unroll
+    for (int i = 0; i < AC_KEEP; i++) {
+        const int b = q + Q * i;
+        keep[i] = (b < blocks && d < hd) ? __ldcg(part + base0 + b * bs + 2 + d) : 0.f;
+    }
     float mx = -FLT_MAX;
-    for (int b = tid; b < blocks; b += 256) {
-        const float m = __ldcg(part + base0 + b * bs);
-        wsm[b] = m;
-        mx = fmaxf(mx, m);
+    for (int b = tid; b < blocks; b += AC_THREADS) {
+        const float2 ml = __ldcg(reinterpret_cast<const float2*>(part + base0 + b * bs));
+        wsm[b] = ml.x;
+        lsm[b] = ml.y;
+        mx = fmaxf(mx, ml.x);
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
@@ -858,40 +779,43 @@ __device__ __forceinline__ void attn_combine_body(const VBlock& vb, const PAtten
     vb.sync();
     mx = red[0];
 #pragma unroll
-    for (int wv = 1; wv < 8; wv++) mx = fmaxf(mx, red[wv]);
+    for (int wv = 1; wv < AC_THREADS / 32; wv++) mx = fmaxf(mx, red[wv]);
     vb.sync();
-    for (int b = tid; b < blocks; b += 256) wsm[b] = expf(wsm[b] - mx);
+    for (int b = tid; b < blocks; b += AC_THREADS) {
+        const float w = expf(wsm[b] - mx);
+        wsm[b] = w;
+        lsm[b] = __fmul_rn(lsm[b], w);
+    }
     vb.sync();
-    // Two halves of the blocks per dim (threads d and d + 128 when head_dim <= 128), eight loads in flight
-    // each; the halves are added low half first, so the order of the sum is fixed.
-    const int halves = hd <= 128 ? 2 : 1;
-    const int d = tid % (256 / halves), half = tid / (256 / halves);
-    const int per = (blocks + halves - 1) / halves;
-    const int b0 = half * per, b1 = min(blocks, b0 + per);
+    // ---- this thread's lane of blocks
     float l = 0.f, o = 0.f;
-    if (d < hd) {
-#pragma unroll 8
-        for (int b = b0; b < b1; b++) {
-            const float w = wsm[b];
-            l = __fmaf_rn(__ldcg(part + base0 + b * bs + 1), w, l);
-            o = __fmaf_rn(__ldcg(part + base0 + b * bs + 2 + d), w, o);
+#pragma unroll
+    for (int i = 0; i < AC_KEEP; i++) {
+        const int b = q + Q * i;
+        if (b < blocks) {
+            o = __fmaf_rn(keep[i], wsm[b], o);
+            l = __fadd_rn(l, lsm[b]);
         }
     }
-    float2* hi_half = reinterpret_cast<float2*>(wsm + ((blocks + 32 + 1) & ~1));  // 8-byte aligned
-    if (half == 1 && d < hd) hi_half[d] = make_float2(l, o);
+    if (d < hd)
+        for (int b = q + Q * AC_KEEP; b < blocks; b += Q) {
+            o = __fmaf_rn(__ldcg(part + base0 + b * bs + 2 + d), wsm[b], o);
+            l = __fadd_rn(l, lsm[b]);
+        }
+    lanes_sm[tid] = make_float2(l, o);
     vb.sync();
-    if (half == 1 || d >= hd) return;
-    if (halves == 2) {
-        l = __fadd_rn(l, hi_half[d].x);
-        o = __fadd_rn(o, hi_half[d].y);
+    if (q != 0 || d >= hd) return;
+    for (int qq = 1; qq < Q; qq++) {
+        const float2 v = lanes_sm[qq * dims + d];
+        l = __fadd_rn(l, v.x);
+        o = __fadd_rn(o, v.y);
     }
-    const int tid_d = d;
     // _pad[1] != 0 (extension): floats between output rows, for writing a rank's head columns of a wider row.
     const size_t orow = p._pad[1] ? (size_t)p._pad[1] : (size_t)p.heads * hd;
-    const size_t oi = (size_t)row * orow + (size_t)h * hd + tid_d;
+    const size_t oi = (size_t)row * orow + (size_t)h * hd + d;
     float res = o / l;
     if (p.gated) {
-        const float gate = __ldcg(qg + (size_t)row * p.q_row + (size_t)2 * h * hd + hd + tid_d);
+        const float gate = __ldcg(qg + (size_t)row * p.q_row + (size_t)2 * h * hd + hd + d);
         res = o / l / (1.0f + expf(-gate));
     }
     out[oi] = res;

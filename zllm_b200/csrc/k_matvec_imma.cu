@@ -45,18 +45,19 @@ constexpr int FIX_BITS = 25;   // |X| <= 2^25, so a 32-element sub-block sum fit
 constexpr int XPAD = 32;       // bytes of padding per digit plane: the four planes a half-warp reads hit different banks
 constexpr int Q8_UNIT = 4;     // blocks per Q8_0 tile
 constexpr int TILE_SCALES = 16 * TILE_ROW;       // where a Q8_0 tile's [16 rows][16 bytes] of scales sit
-constexpr int TILE_BYTES = 16 * TILE_ROW + 256;  // a stage: a multiple of 128 bytes
-constexpr int SMEM_MAX = 220 * 1024;
+// a stage of the ring (a multiple of 128 bytes): 16 rows of 160 bytes, and for Q8_0 the 256 bytes of scales
+__host__ __device__ constexpr int tile_bytes(bool q4) { return 16 * TILE_ROW + (q4 ? 0 : 256); }
+constexpr int SMEM_MAX = 220 * 1024;   // (a fifth stage at k = 4096 would fit in 227 KB; measured: no gain)
 
 #ifdef ZCU_TRACE
 // Debug build only: per-CTA timestamps of the kernel's phases (globaltimer, ns).
-__device__ unsigned long long g_mv_trace[256 * 8];
+__device__ unsigned long long g_mv_trace[256 * 12];
 #define TRACE(i)                                                                    \
     do {                                                                            \
         if (threadIdx.x == 0 && blockIdx.x < 256) {                                 \
             unsigned long long t__;                                                 \
             asm volatile("mov.u64 %0, %globaltimer;\n" : "=l"(t__));                \
-            g_mv_trace[blockIdx.x * 8 + (i)] = t__;                                 \
+            g_mv_trace[blockIdx.x * 12 + (i)] = t__;                                 \
         }                                                                           \
     } while (0)
 #else
@@ -85,7 +86,7 @@ __host__ __device__ inline Layout layout(int warps, int tokens, int k, bool q4, 
     Layout L;
     int off = 0;
     L.ring = off;
-    off += warps * stages * TILE_BYTES;
+    off += warps * stages * tile_bytes(q4);
     L.mbar = off;
     off += warps * stages * 8;
     off = (off + 127) & ~127;
@@ -189,6 +190,7 @@ __global__ void __launch_bounds__(W * 32, 16 / W) matvec_imma(PMatvec p, const f
     TRACE(0);
 
     // ---- the ring: this warp's stages and their barriers; the first STAGES - 1 tiles are asked for at once
+    constexpr int TILE_BYTES = tile_bytes(Q4);
     const uint32_t ring = (uint32_t)__cvta_generic_to_shared(smem + L.ring) + (uint32_t)warp * STAGES * TILE_BYTES;
     const uint32_t mbar = (uint32_t)__cvta_generic_to_shared(smem + L.mbar) + (uint32_t)warp * STAGES * 8;
     if (lane == 0) {
@@ -201,6 +203,7 @@ __global__ void __launch_bounds__(W * 32, 16 / W) matvec_imma(PMatvec p, const f
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
     __syncwarp();
+    TRACE(8);
     int is_stage = 0, issued = lo;
     int is_rp = lo / units, is_unit = lo % units;   // (row tile, part) index and k tile of the next copy
     auto issue = [&]() {
@@ -448,10 +451,20 @@ __global__ void __launch_bounds__(W * 32, 16 / W) matvec_imma(PMatvec p, const f
     // this lane's B bytes: plane (4 b + (g & 3)), the group's second half for g >= 4, bytes 8t..8t+7
     const uint32_t xb_lane = xd_s + (uint32_t)(g & 3) * (uint32_t)xcol + 32u * (uint32_t)(g >> 2) + 8u * (uint32_t)t;
     bool timed_out = false;
+#ifdef ZCU_TRACE
+    long long tr_wait = 0, tr_comp = 0;
+#endif
 #pragma unroll 1
     for (int tau = lo; tau < hi; tau++) {
+#ifdef ZCU_TRACE
+        const long long tr0 = clock64();
+#endif
         issue();  // tile tau + STAGES - 1
         if (!mbar_wait(mbar + 8 * cs_stage, (phase_bits >> cs_stage) & 1u)) timed_out = true;
+#ifdef ZCU_TRACE
+        const long long tr1 = clock64();
+        tr_wait += tr1 - tr0;
+#endif
         phase_bits ^= 1u << cs_stage;
         const uint32_t tile = ring + (uint32_t)cs_stage * TILE_BYTES;
         cs_stage = cs_stage + 1 == STAGES ? 0 : cs_stage + 1;
@@ -554,7 +567,13 @@ __global__ void __launch_bounds__(W * 32, 16 / W) matvec_imma(PMatvec p, const f
                 cur_rp++;
             }
         }
+#ifdef ZCU_TRACE
+        tr_comp += clock64() - tr1;
+#endif
     }
+#ifdef ZCU_TRACE
+    if (tid == 0 && blockIdx.x < 256) g_mv_trace[blockIdx.x * 12 + 7] = ((unsigned long long)tr_wait << 32) | (unsigned long long)(tr_comp & 0xffffffffll);
+#endif
     if (timed_out && lane == 0 && status) atomicExch(status, 1);
     TRACE(4);
     __syncthreads();

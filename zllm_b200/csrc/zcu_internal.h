@@ -149,6 +149,23 @@ zcu_result launch_matmul_q4_k_tc(const LaunchArgs& a);       // the tcgen05 pref
 // ranges it stores to, which must lie in the local arena when it pushes. Fills `u` (both slots PEER_NONE without one).
 zcu_result parse_peer(const LaunchArgs& a, PeerUse& u, const void* out_lo, const void* out_hi);
 
+// Launches `kern` as a programmatic dependent of the kernel before it in the stream: its CTAs may be placed while
+// that kernel drains; it orders itself with griddepcontrol.wait before it reads what that kernel wrote.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
 // Whether (kernel, variant) exists, and its artifact name.
 bool matvec_variant_ok(uint32_t kernel, uint32_t variant);
 

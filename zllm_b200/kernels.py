@@ -133,10 +133,6 @@ X_HALF, OUT_HALF = 1, 2
 VARIANT_DELTA_CHUNK64 = 0xFFFD0000
 
 
-# attn_split's fast path in its merging form: tensor cores, and the last key block of each (row, KV head) does
-# attn_combine's work (bindings: q, kc, vc, part, step, positions, out, tickets)
-ATTN_SPLIT_MERGING = 5
-
 # The tensor-parallel exchange a dispatch takes part in (zcu_peer_ext): appended to its parameter block.
 PEER_MAGIC, PEER_NONE, EXT_PEER_WAIT = 0x52454550, 0xFFFFFFFF, 64
 PeerExt = _struct("PeerExt", [("magic", u32), ("wait_slot", u32), ("push_slot", u32), ("reserved", u32)])

@@ -123,8 +123,7 @@ class DenseProgram:
     """
 
     def __init__(self, ctx, cfg: DenseConfig, weights, batch: int, alloc, shard: Shard | None = None, gather=None,
-                 variants: dict | None = None, fuse_rope: bool | None = None, arena=None, fuse_combine: bool | None = None,
-                 batched: bool | None = None):
+                 variants: dict | None = None, fuse_rope: bool | None = None, arena=None, batched: bool | None = None):
         self.ctx, self.cfg, self.w, self.B = ctx, cfg, weights, batch
         self.sh = shard or Shard()
         self.gather = gather
@@ -142,14 +141,6 @@ class DenseProgram:
         # 2-4 sequences
         can_batch = 4 < batch <= K.MATVEC_BATCHED_MAX_TOKENS
         self.batched = can_batch if batched is None else (bool(batched) and batch <= K.MATVEC_BATCHED_MAX_TOKENS)
-        # attn_combine by the last key block of each (sequence, KV head) inside attn_split (one launch fewer per
-        # layer): the tensor-core fast path (f16 cache, GQA group <= 4, head_dim 64 or 128) with at most 128 blocks
-        # of 128 keys, unless a form of attn_split was asked for
-        group = cfg.heads // cfg.kv_heads
-        can_merge = group <= 4 and cfg.head_dim in (64, 128) and cfg.max_ctx <= 128 * 128 and "attn_split" not in self.variants
-        # (off by default: measured 1 % slower than the separate launch - the merge of a KV head's four query heads
-        # by one CTA takes longer than 32 CTAs merging one head each, and that outweighs the saved launch)
-        self.fuse_combine = bool(fuse_combine) and can_merge
         self.launches_per_step = 0
         sh, hd = self.sh, cfg.head_dim
         h0, h1 = sh.heads(cfg)
@@ -177,7 +168,6 @@ class DenseProgram:
         self.kc = [alloc(B * self.seq_stride * 2) for _ in range(cfg.layers)]
         self.vc = [alloc(B * self.seq_stride * 2) for _ in range(cfg.layers)]
         self.dummy = alloc(256)
-        self.tickets = alloc(max(256, B * self.lg * 4))     # zero; the merging attn_split keeps them zero
         self.rope = None
 
     # ---- host-built tables and per-step state
@@ -254,19 +244,12 @@ class DenseProgram:
                 self.L.launch(K.ROPE_APPEND, rp, [self.qkv, self.dummy, self.dummy, self.rope, self.kc[il], self.vc[il],
                                                   self.step, self.positions], (self.lh + self.lg, B, 1))
                 self.launches_per_step += 1
-            # 3-4. split attention over each sequence's cache, merged into this rank's head columns of att (by
-            #      attn_combine, or by the split's own last block)
-            if self.fuse_combine:
-                self.L.launch(K.ATTN_SPLIT, K.with_peer(ap, push=s_att),
-                              [self.qkv, self.kc[il], self.vc[il], self.part, self.step, self.positions, att_cols, self.tickets],
-                              (self.lg, blocks, B), K.ATTN_SPLIT_MERGING)
-                self.launches_per_step += 1
-            else:
-                self.L.launch(K.ATTN_SPLIT, ap, [self.qkv, self.kc[il], self.vc[il], self.part, self.step, self.positions],
-                              (self.lg, blocks, B), self.variants.get("attn_split", 0))
-                self.L.launch(K.ATTN_COMBINE, K.with_peer(ap, push=s_att), [self.qkv, self.part, att_cols, self.step, self.positions],
-                              (self.lh, B, 1))
-                self.launches_per_step += 2
+            # 3-4. split attention over each sequence's cache, merged into this rank's head columns of att
+            self.L.launch(K.ATTN_SPLIT, ap, [self.qkv, self.kc[il], self.vc[il], self.part, self.step, self.positions],
+                          (self.lg, blocks, B), self.variants.get("attn_split", 0))
+            self.L.launch(K.ATTN_COMBINE, K.with_peer(ap, push=s_att), [self.qkv, self.part, att_cols, self.step, self.positions],
+                          (self.lh, B, 1))
+            self.launches_per_step += 2
             self._gather(self.att, cfg.q_dim)
             # 5. Wo rows of this rank, accumulated into the residual stream's slice
             self._matvec(cfg.body_type, self.att, lw["wo"], self.x, self.le, cfg.q_dim, col0=sh.rank * self.le,
