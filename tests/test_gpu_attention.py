@@ -39,7 +39,7 @@ def test_attn_decode_f16_cache(ref, gpu, launcher, heads, kv_heads, hd, gated):
     q_head = 2 * hd if gated else hd
     q_rows = uniform(rng, (m, heads * q_head), 1.0)
     fast = heads // kv_heads <= 4 and hd in (64, 128)
-    for variant in ((0, 1, 2, 3, 4) if fast else (0,)):  # every form of the fast path; the generic path otherwise
+    for variant in ((0, 1, 3) if fast else (0,)):  # both arithmetics of the fast path; the generic path otherwise
         got = run_attention(gpu, launcher, q_rows, kcf.view(np.uint16), vcf.view(np.uint16), pos0, heads, kv_heads, hd,
                             gated, K.KV_F16, 256, variant=variant)
         _check_rows(ref, got, q_rows, kcf, vcf, pos0, m, heads, kv_heads, hd, gated, q_head)
@@ -144,10 +144,10 @@ def test_rope_append_writes_rounded_cache(ref, gpu, launcher, normal, qk_norm, g
         assert not kcache[:pos0].any() and not kcache[pos0 + m:].any()
 
 
-def test_both_forms_of_the_split_give_the_same_partials(gpu, launcher):
-    # One CTA per key block (variant 1) and the persistent walk with pipelined tiles (variant 2) keep the same
-    # order in every sum: identical partials and outputs, for rows with different key counts (batched
-    # sequences: 700, 1 and 333 keys; blocks past a row's keys are skipped by both).
+def test_both_arithmetics_of_the_split_agree(gpu, launcher):
+    # The CUDA-core form (variant 1: exact f32 products) and the tensor-core form (variant 3 = the default: queries
+    # and probabilities as two f16 terms) agree, for rows with different key counts (batched sequences: 700, 1 and
+    # 333 keys, so some blocks hold no keys at all and some warps of a block hold none).
     rng = np.random.default_rng(91)
     heads, kv_heads, hd, rows, ctx = 8, 2, 128, 3, 768
     positions = np.array([699, 0, 332], dtype=np.uint32)
@@ -160,20 +160,17 @@ def test_both_forms_of_the_split_give_the_same_partials(gpu, launcher):
     dq, dk, dv = gpu.put(q), gpu.put(kc.view(np.uint16)), gpu.put(vc.view(np.uint16))
     step, dpos = gpu.put(np.array([rows, 0, 0, 0], dtype=np.uint32)), gpu.put(positions)
     got = []
-    for variant in (1, 2, 3, 4):
+    for variant in (1, 3):
         part = gpu.zeros(rows * heads * max_blocks * (hd + 2) * 4)
         out = gpu.zeros(rows * heads * hd * 4)
         launcher.launch(K.ATTN_SPLIT, p, [dq, dk, dv, part, step, dpos], (kv_heads, max_blocks, rows), variant)
         launcher.launch(K.ATTN_COMBINE, p, [dq, part, out, step, dpos], (heads, rows, 1))
         gpu.sync()
         got.append((part.download(np.uint32), out.download(np.uint32)))
-    assert np.array_equal(got[0][1], got[1][1])   # CUDA cores: per block == walk
-    assert np.array_equal(got[2][1], got[3][1])   # tensor cores: per block == walk
-    assert rel_err(got[2][1].view(np.float32), got[0][1].view(np.float32)) < TOL  # the two arithmetics agree
+    assert rel_err(got[1][1].view(np.float32), got[0][1].view(np.float32)) < TOL
     assert np.abs(got[0][1].view(np.float32)).max() > 0
-    # the partials of every block that holds keys (128 per block on this path); the one-CTA-per-block form also
-    # writes the unused slots past a row's keys, the walk skips them
-    pa, pb = (g[0].reshape(rows, heads, max_blocks, hd + 2) for g in got[:2])
+    # a block's partial {max, sum exp, sum exp * v} is the same softmax state in both forms
+    pa, pb = (g[0].view(np.float32).reshape(rows, heads, max_blocks, hd + 2) for g in got)
     for t in range(rows):
         used = -(-(int(positions[t]) + 1) // 128)
-        assert np.array_equal(pa[t, :, :used], pb[t, :, :used]), t
+        assert rel_err(pb[t, :, :used, 0], pa[t, :, :used, 0]) < TOL and rel_err(pb[t, :, :used, 1:], pa[t, :, :used, 1:]) < TOL, t

@@ -209,31 +209,11 @@ __global__ void __launch_bounds__(attn::AM_THREADS, 3) attn_split_mma(PAttention
                                                                      const PStep* __restrict__ step,
                                                                      const uint32_t* __restrict__ seq_pos, int* __restrict__ status) {
     extern __shared__ __align__(128) unsigned char dyn_smem[];
+    ATRACE(0);
     // launched as a programmatic dependent: the queries and the newest cache row come from the kernel before
     asm volatile("griddepcontrol.wait;\n" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
     attn::attn_split_mma_body<HD>(dyn_smem, p, qg, kc, vc, part, step, seq_pos, (int)blockIdx.x, (int)blockIdx.y, (int)blockIdx.z, status);
-}
-
-template <int HD>
-__global__ void __launch_bounds__(attn::AM_THREADS, 1) attn_split_mma_persistent(PAttention p, const float* __restrict__ qg,
-                                                                                const __grid_constant__ CUtensorMap kmap,
-                                                                                const __grid_constant__ CUtensorMap vmap,
-                                                                                float* __restrict__ part, const PStep* __restrict__ step,
-                                                                                const uint32_t* __restrict__ seq_pos, int by, int rows,
-                                                                                int* __restrict__ status) {
-    extern __shared__ __align__(128) unsigned char dyn_smem[];
-    attn::attn_split_mma_persistent_body<HD>(dyn_smem, p, qg, &kmap, &vmap, part, step, seq_pos, by, rows, status);
-}
-
-template <int HD, int GROUP_CAP>
-__global__ void __launch_bounds__(attn::AF_THREADS, 1) attn_split_persistent(PAttention p, const float* __restrict__ qg,
-                                                                            const __half* __restrict__ kc,
-                                                                            const __half* __restrict__ vc, float* __restrict__ part,
-                                                                            const PStep* __restrict__ step,
-                                                                            const uint32_t* __restrict__ seq_pos, int by, int rows) {
-    extern __shared__ __align__(128) unsigned char dyn_smem[];
-    attn::attn_split_persistent_body<HD, GROUP_CAP>(dyn_smem, p, qg, kc, vc, part, step, seq_pos, by, rows);
 }
 
 __global__ void __launch_bounds__(attn::AC_THREADS) attn_combine_kernel(PAttention p, const float* __restrict__ qg,
@@ -311,35 +291,7 @@ zcu_result launch_attn_split(const LaunchArgs& a) {
         float* part = (float*)a.b[3].ptr;
         const PStep* step = (const PStep*)a.b[4].ptr;
         const uint32_t* seq_pos = (a.nb >= 6 && p._pad[0] != 0) ? (const uint32_t*)a.b[5].ptr : nullptr;
-        // Variants: 0 (default) and 3 = tensor cores, one CTA per block; 4 = tensor cores, persistent walk with
-        // pipelined tiles; 1 = CUDA cores (exact f32 products), one CTA per block;
-        // 2 = CUDA cores, persistent walk.
-        const int total_blocks = (int)(grid.x * grid.y * grid.z);
-        if (a.variant == 4) {
-            // the tensor-core arithmetic as a persistent walk, one CTA per SM, TMA tiles pipelined
-            const size_t msmem = attn::attn_mma_persist_smem(hd);
-            auto mk = hd == 128 ? attn_split_mma_persistent<128> : attn_split_mma_persistent<64>;
-            if (cudaFuncSetAttribute(mk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)msmem) != cudaSuccess) {
-                cudaGetLastError();
-                return zcu_fail(a, ZCU_E_GPU, "attn_split: %zu bytes of shared memory refused", msmem);
-            }
-            // the caches as [sequences][positions][kv_heads * head_dim] f16: a sequence's rows end where the
-            // binding (or the next sequence) does
-            const uint64_t row_bytes = (uint64_t)p.kv_heads * hd * 2;
-            const uint64_t seq_bytes = p._pad[0] ? (uint64_t)p._pad[0] * 2 : a.b[1].size;
-            const uint64_t seqs = p._pad[0] ? a.b[1].size / seq_bytes : 1;
-            const uint64_t ctx_rows = (seq_bytes < a.b[1].size ? seq_bytes : a.b[1].size) / row_bytes;
-            CUtensorMap kmap, vmap;
-            ZCU_NEED(a, ((uintptr_t)kc & 15) == 0 && ((uintptr_t)vc & 15) == 0 && row_bytes % 16 == 0 && seq_bytes % 16 == 0 && seqs >= 1 && ctx_rows >= 1,
-                     "attn_split: the cache is not laid out for tile copies");
-            if (!tma::bytes_3d_swizzled(&kmap, kc, seqs, ctx_rows, row_bytes, seq_bytes, attn::AF_KEYS) ||
-                !tma::bytes_3d_swizzled(&vmap, vc, seqs, ctx_rows, row_bytes, seq_bytes, attn::AF_KEYS))
-                return zcu_fail(a, ZCU_E_GPU, "attn_split: the driver refused a tensor map");
-            const int ctas = total_blocks < a.sm_count ? total_blocks : a.sm_count;
-            mk<<<ctas, attn::AM_THREADS, msmem, a.stream>>>(p, qg, kmap, vmap, part, step, seq_pos, (int)grid.y, (int)grid.z, a.status);
-            ZCU_CHECK_LAUNCH(a);
-            return ZCU_OK;
-        }
+        // Variants: 0 (default) and 3 = tensor cores; 1 = CUDA cores (exact f32 products). One CTA per block.
         if (a.variant == 0 || a.variant == 3) {
             // one CTA per block on the f16 tensor cores (queries and probabilities as two f16 terms)
             const size_t msmem = attn::attn_mma_smem(hd);
@@ -358,16 +310,7 @@ zcu_result launch_attn_split(const LaunchArgs& a) {
             ZCU_CHECK_LAUNCH(a);
             return ZCU_OK;
         }
-        const size_t psmem = attn::attn_persist_smem(4, group, hd);
-        const int ctas = total_blocks < a.sm_count ? total_blocks : a.sm_count;
-        auto kern = hd == 128 ? attn_split_persistent<128, 4> : attn_split_persistent<64, 4>;
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)psmem) != cudaSuccess) {
-            cudaGetLastError();
-            return zcu_fail(a, ZCU_E_GPU, "attn_split: %zu bytes of shared memory refused", psmem);
-        }
-        kern<<<ctas, AF_THREADS, psmem, a.stream>>>(p, qg, kc, vc, part, step, seq_pos, (int)grid.y, (int)grid.z);
-        ZCU_CHECK_LAUNCH(a);
-        return ZCU_OK;
+        return zcu_fail(a, ZCU_E_UNSUPPORTED_KERNEL, "attn_split: variant %u is not built", a.variant);
     }
     const int dpairs = hd / 2;
     const int parts = AT_THREADS / dpairs > AT_BLOCK ? AT_BLOCK : AT_THREADS / dpairs;
@@ -494,3 +437,9 @@ zcu_result launch_peer_wait(const LaunchArgs& a) {
     ZCU_CHECK_LAUNCH(a);
     return ZCU_OK;
 }
+
+#ifdef ZCU_TRACE
+extern "C" __attribute__((visibility("default"))) int zcu_dbg_attn_trace_read(unsigned long long* out, size_t count) {
+    return (int)cudaMemcpyFromSymbol(out, g_at_trace, count * sizeof(unsigned long long));
+}
+#endif
