@@ -436,6 +436,8 @@ class DecodeStep:
         shapes = layer_weight_shapes(cfg, self.shard)
         p = self.prog
         if self.mv_graph is None:
+            # the body multiplies of a step as the step launches them, without the attention between them (inputs as
+            # they lie: nothing pushes exchange slots here, so no multiply waits for one)
             self.ctx.capture_begin()
             for il in range(cfg.layers):
                 lw = self.weights["layers"][il]
@@ -458,22 +460,24 @@ class DecodeStep:
             self.ctx.graph_launch(self.mv_graph)
         e1.record(self.stream)
         self.stream.synchronize()
-        launches = 4 * cfg.layers
+        multiplies = 4 * cfg.layers
+        launches = multiplies
         us = e0.elapsed_time(e1) * 1e3 / (reps * launches)
         wbytes = sum(r * K.row_bytes(cfg.body_type, k) for r, k in shapes.values()) * cfg.layers
         act = 4 * self.batch * cfg.layers * (cfg.hidden * 2 + cfg.q_dim + cfg.ff + p.qkv_row + 2 * p.le + p.lff)
         per_launch = (wbytes + act) / launches
         achieved = per_launch / us / 1e3
         peak, kind = measured_hbm_peak()
-        return {"bound": "hbm", "kernel": "matvec_imma<Q4_K> (the 4 body multiplies of each layer, mean over a step)",
+        kernel = "matvec_imma<Q4_K> (the 4 body multiplies of each layer, mean over a step)"
+        return {"bound": "hbm", "kernel": kernel,
                 "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": f"of {kind}",
                 "frac_of_8000_nominal": achieved / 8000.0,
-                # dram__bytes_read + write per launch of the same four multiplies from an ncu capture of this workload
-                # on one GPU (14.26, 9.54, 66.16 and 33.17 MB: profiles/matvec_imma_decode_traffic.md); not captured
-                # for sharded or batched runs
-                "traffic": 30.78e6 if (self.dist.world == 1 and self.batch == 1) else None,
-                "bytes_per_launch": per_launch,
-                "us_per_launch": us, "launches_per_step": launches,
+                # dram__bytes_read + write of the same four multiplies from an ncu capture of this workload on one GPU
+                # (14.26, 9.54, 66.16 and 33.17 MB: profiles/matvec_imma_decode_traffic.md); not captured for sharded
+                # or batched runs
+                "traffic": (30.78e6 * multiplies / launches) if (self.dist.world == 1 and self.batch == 1) else None,
+                "bytes_per_launch": per_launch, "multiplies_per_launch": multiplies / launches,
+                "us_per_launch": us, "us_per_multiply": us * launches / multiplies, "launches_per_step": launches,
                 "step_hbm_gbs": self.bytes["total"] / (ms_per_step * 1e-3) / 1e9,
                 "step_frac": self.bytes["total"] / (ms_per_step * 1e-3) / 1e9 / peak}
 
@@ -875,10 +879,89 @@ WORKLOADS = {"matvec_q4_k": MatvecQ4K, "decode": DecodeStep, "prefill_matmul": P
 
 # ------------------------------------------------------------------ arms
 
+def tp_parity(dist, args):
+    """N > 1 ranks, outside any timed region: ONE random model (2 layers, the benchmark's widths, its Q8_0 head)
+    run sharded over all ranks with the step's exchange, and unsharded on rank 0; the logits are compared on rank 0.
+    Returns {"max_rel_l2", "argmax_equal", "bitwise", ...} on rank 0, None elsewhere."""
+    import torch
+
+    from zllm_b200 import abi
+    from zllm_b200 import model as M
+    from zllm_b200.plan import DenseConfig, DenseProgram, Shard
+    from zllm_b200.torch_util import TorchBuf, nccl_gather
+
+    dev = torch.device("cuda", dist.local)
+    torch.cuda.set_device(dev)
+    stream = torch.cuda.Stream(dev)
+    ctx = abi.Context(dist.local, stream=stream.cuda_stream)
+    batch, context, layers = min(args.batch, 4), 1024, 2
+    cfg = DenseConfig(layers=layers, max_ctx=context + 64)
+    full = M.device_full_model(cfg, torch, dev, seed=4242)
+    bufs = []
+
+    def alloc(nbytes):
+        b = TorchBuf(torch, dev, nbytes)
+        bufs.append(b)
+        return b
+
+    def program(shard, arena=None, gather=None):
+        weights, keep = M.device_shard(full, cfg, torch, shard)
+        prog = DenseProgram(ctx, cfg, weights, batch, alloc, shard, arena=arena, gather=gather)
+        table = alloc(cfg.max_ctx * cfg.head_dim * 4)
+        table.upload(DenseProgram.rope_table(cfg))
+        prog.set_rope_table(table)
+        gen = torch.Generator(device=dev)
+        gen.manual_seed(777)   # the same cache on every rank; a rank keeps its KV heads
+        g0, g1 = shard.kv_heads(cfg)
+        for il in range(cfg.layers):
+            for cache in (prog.kc[il], prog.vc[il]):
+                whole = torch.randn((batch, cfg.max_ctx, cfg.kv_heads, cfg.head_dim), device=dev, generator=gen).to(torch.float16)
+                mine = whole[:, :, g0:g1, :].contiguous().view(-1)
+                cache.t[: mine.numel() * 2].view(torch.float16).copy_(mine)
+        prog.write_step(np.arange(batch, dtype=np.uint32) * 1009 % cfg.vocab + 17, np.full(batch, context, dtype=np.uint32))
+        return prog, keep
+
+    shard = Shard(dist.rank, dist.world)
+    arena, gather = None, None
+    if args.exchange == "peer":
+        def handles(h: bytes):
+            got = [None] * dist.world
+            dist.dist.all_gather_object(got, h)
+            return got
+
+        arena = abi.PeerArena(ctx, dist.rank, dist.world, DenseProgram.arena_bytes(cfg, batch), DenseProgram.arena_slots(cfg), handles)
+    else:
+        gather = nccl_gather(dist.dist, dist.rank, dist.world)
+    sharded, keep_s = program(shard, arena=arena, gather=gather)
+    torch.cuda.synchronize()
+    dist.barrier()
+    with torch.cuda.stream(stream):
+        sharded.record_step(context + 1)
+    ctx.sync()
+    dist.barrier()
+    out = None
+    if dist.rank == 0:
+        got = sharded.logits.download(np.float32)[: batch * cfg.vocab].copy()
+        whole, keep_w = program(Shard())
+        with torch.cuda.stream(stream):
+            whole.record_step(context + 1)
+        ctx.sync()
+        want = whole.logits.download(np.float32)[: batch * cfg.vocab]
+        got, want = got.reshape(batch, cfg.vocab), want.reshape(batch, cfg.vocab)
+        rel = float(max(np.linalg.norm(got[b] - want[b]) / np.linalg.norm(want[b]) for b in range(batch)))
+        out = {"max_rel_l2": rel, "argmax_equal": bool((got.argmax(axis=1) == want.argmax(axis=1)).all()),
+               "bitwise": bool(np.array_equal(got.view(np.uint32), want.view(np.uint32))),
+               "what": f"{layers} layers of the benchmark's widths + its Q8_0 head, one random model sharded over {dist.world} ranks "
+                       f"against the same model on rank 0 alone; batch {batch}, context {context}; exchange {args.exchange}"}
+    dist.barrier()
+    return out
+
+
 def run_cuda(args):
     import torch
 
     dist = Dist(args.gpus)
+    parity = tp_parity(dist, args) if (dist.on and args.workload == "decode") else None
     kw = {"batch": args.batch, "variant": int(args.variant, 0)}
     if args.workload == "decode":
         kw["exchange"] = args.exchange
@@ -932,8 +1015,14 @@ def run_cuda(args):
     }
     if dist.rank == 0 and dist.world == 1 and not args.no_cpu:
         line["cpu_baseline"] = wl.cpu_baseline()
+    failed = False
+    if parity is not None:
+        line["tp_parity"] = parity
+        failed = not (parity["max_rel_l2"] <= 1e-4 and parity["argmax_equal"])
     if dist.rank == 0:
         print(json.dumps(line), flush=True)
+        if failed:
+            print(f"bench: the sharded step differs from the unsharded one: {parity}", file=sys.stderr)
     if dist.on:
         # Leave without tearing NCCL down: captured graphs still hold its kernels, and a teardown that
         # waits on them has hung here. Every rank is past its last collective.
@@ -942,7 +1031,7 @@ def run_cuda(args):
         torch.cuda.synchronize()
         sys.stdout.flush()
         sys.stderr.flush()
-        os._exit(0)
+        os._exit(1 if failed else 0)
     dist.close()
 
 

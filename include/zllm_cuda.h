@@ -253,8 +253,11 @@ zcu_result zcu_graph_destroy(zcu_context *context, uint32_t graph);
  * and wait, element by element, for the tag of the exchange; ZCU_K_EXT_PEER_WAIT (binding: the vector) waits the
  * same way and fills in the plain floats, for a host about to read them. The reference has no multi-GPU path;
  * this is the row/head sharding its kernels allow (every output row, head and state column is computed by one
- * rank with unchanged arithmetic, so results are bitwise those of one GPU). A wait gives up after 2 s with
- * ZCU_E_GPU at the next sync. */
+ * rank with unchanged arithmetic, so results are bitwise those of one GPU). A wait gives up after 2 s (or the limit
+ * set by zcu_peer_wait_limit) with ZCU_E_GPU at the next sync; every later wait of the context then gives up at once
+ * until zcu_peer_config is called again. zcu_peer_config zeroes this rank's exchange slots: every rank must have
+ * returned from it (a barrier of the caller's) before any rank launches a kernel that pushes; and it must not be
+ * called again while graphs captured under the old configuration are still replayed. */
 #define ZCU_PEER_MAGIC 0x52454550u
 #define ZCU_PEER_NONE 0xffffffffu
 typedef struct zcu_peer_ext {
@@ -267,6 +270,8 @@ zcu_result zcu_ipc_export(zcu_context *context, void *ptr, void *out_handle64);
 zcu_result zcu_ipc_open(zcu_context *context, const void *handle64, void **out_ptr);
 zcu_result zcu_peer_config(zcu_context *context, uint32_t rank, uint32_t world, const uint64_t *bases, uint64_t arena_bytes,
                            uint64_t exchange_offset, uint32_t slots);
+/* How long a kernel waits for a slice of an exchange before it gives up (launches from now on; 0 = 2000 ms). */
+zcu_result zcu_peer_wait_limit(zcu_context *context, uint32_t milliseconds);
 
 #ifdef __cplusplus
 }

@@ -153,7 +153,8 @@ def test_rope_append_in_the_multiply_epilogue_equals_its_own_launch(gpu, batch):
         assert np.array_equal(a, b)
 
 
-def test_peer_exchange_with_one_rank_equals_the_plain_step(gpu):
+@pytest.mark.parametrize("batch", [1, 2])
+def test_peer_exchange_with_one_rank_equals_the_plain_step(gpu, batch):
     # The tensor-parallel path with a world of one: outputs go through the arena, every producer publishes its
     # exchange slot and every consumer waits for it (its own count). Same bits as the plain step, also when the
     # step is captured once and replayed (the counters keep growing).
@@ -163,13 +164,13 @@ def test_peer_exchange_with_one_rank_equals_the_plain_step(gpu):
     host = M.host_model(cfg, "tiny")
     weights = M.upload(host, cfg, gpu.put)
     rng = np.random.default_rng(77)
-    kv_shape = (1, cfg.max_ctx, cfg.kv_heads, cfg.head_dim)
+    kv_shape = (batch, cfg.max_ctx, cfg.kv_heads, cfg.head_dim)
     kc_host = [rng.normal(size=kv_shape).astype(np.float16) for _ in range(cfg.layers)]
     vc_host = [rng.normal(size=kv_shape).astype(np.float16) for _ in range(cfg.layers)]
-    arena = abi.PeerArena(gpu, 0, 1, DenseProgram.arena_bytes(cfg, 1), DenseProgram.arena_slots(cfg))
+    arena = abi.PeerArena(gpu, 0, 1, DenseProgram.arena_bytes(cfg, batch), DenseProgram.arena_slots(cfg))
 
     def fresh(**kw):
-        prog = DenseProgram(gpu, cfg, weights, 1, gpu.zeros, **kw)
+        prog = DenseProgram(gpu, cfg, weights, batch, gpu.zeros, **kw)
         prog.set_rope_table(gpu.put(DenseProgram.rope_table(cfg)))
         for il in range(cfg.layers):
             prog.kc[il].upload(kc_host[il].view(np.uint16))
@@ -179,7 +180,8 @@ def test_peer_exchange_with_one_rank_equals_the_plain_step(gpu):
     plain, peer = fresh(), fresh(arena=arena)
     graph = None
     for token, pos in [(5, 100), (900, 101), (31, 102)]:
-        tok, ps = np.array([token], dtype=np.uint32), np.array([pos], dtype=np.uint32)
+        tok = (np.arange(batch, dtype=np.uint32) * 37 + token) % cfg.vocab
+        ps = np.array([pos + 11 * s for s in range(batch)], dtype=np.uint32)
         plain.write_step(tok, ps)
         plain.record_step(cfg.max_ctx)
         peer.write_step(tok, ps)

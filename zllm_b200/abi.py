@@ -35,7 +35,7 @@ EXPORTS = [
     "zcu_start_profile", "zcu_stop_profile", "zcu_read_timings", "zcu_alloc", "zcu_free", "zcu_upload",
     "zcu_download", "zcu_memset", "zcu_launch", "zcu_sync", "zcu_launch_count", "zcu_capture_begin",
     "zcu_capture_end", "zcu_graph_launch", "zcu_graph_destroy", "zcu_rope_table",
-    "zcu_attention_decode_static", "zcu_ipc_export", "zcu_ipc_open", "zcu_peer_config",
+    "zcu_attention_decode_static", "zcu_peer_wait_limit", "zcu_ipc_export", "zcu_ipc_open", "zcu_peer_config",
 ]
 
 
@@ -109,6 +109,7 @@ def lib() -> C.CDLL:
         "zcu_launch": (C.c_int32, [vp, u32, u32, vp, u32, C.POINTER(Binding), u32, C.POINTER(u32)]),
         "zcu_sync": (C.c_int32, [vp, u32]),
         "zcu_launch_count": (u64, [vp]),
+        "zcu_peer_wait_limit": (C.c_int32, [vp, u32]),
         "zcu_capture_begin": (C.c_int32, [vp]),
         "zcu_capture_end": (C.c_int32, [vp, C.POINTER(u32)]),
         "zcu_graph_launch": (C.c_int32, [vp, u32]),
@@ -309,6 +310,9 @@ class Context:
 
     def sync(self, timeout_ms: int = 60000):
         self._check(lib().zcu_sync(self.h, timeout_ms))
+
+    def peer_wait_limit(self, milliseconds: int):
+        self._check(lib().zcu_peer_wait_limit(self.h, milliseconds))
 
     def launch_count(self) -> int:
         return lib().zcu_launch_count(self.h)

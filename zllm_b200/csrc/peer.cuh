@@ -13,8 +13,8 @@
 // tag from its own count of the slot, which its own producer advanced before (stream order).
 // A fast rank cannot overwrite a slot that a slow rank still has to read: to reach the next write of a buffer it
 // must have read, through the exchanges in between, data that the slow rank produces only after that read.
-// Every wait is bounded in time (2 s); a rank that gives up sets the context's status word and an abort word that
-// ends every later wait at once.
+// Every wait is bounded in time (2 s unless the host sets another limit); a rank that gives up sets the context's
+// status word and an abort word that ends every later wait at once.
 #pragma once
 
 #include <cstdint>
@@ -33,7 +33,8 @@ struct PPeer {
 
 struct PeerTable {
     int32_t rank, world;
-    uint32_t slots, _pad;
+    uint32_t slots;
+    uint32_t wait_ms;          // how long a wait for a slot may last before it gives up (0: 2000)
     uint64_t base[PEER_MAX];   // every rank's arena as mapped here (base[rank] is the local one)
     uint64_t arena_bytes;
     uint64_t ll_off;           // arena offset of the exchange region: the float at offset q has its slot at ll_off + 2 q
@@ -80,7 +81,7 @@ __device__ __forceinline__ void push(const PeerUse& u, const float* local, float
 __device__ __forceinline__ bool gave_up(const PeerUse& u, unsigned long long t0, unsigned spins, int* status) {
     if ((spins & 1023u) != 1023u) return false;
     if (__ldcg(u.t.tickets + u.t.slots) != 0) return true;  // another wait of this context gave up
-    if (now_ns() - t0 > 2000000000ull) {
+    if (now_ns() - t0 > (unsigned long long)(u.t.wait_ms ? u.t.wait_ms : 2000u) * 1000000ull) {
         if (status) atomicExch(status, 5);
         atomicExch(u.t.tickets + u.t.slots, 1u);
         return true;
@@ -92,11 +93,12 @@ __device__ __forceinline__ bool gave_up(const PeerUse& u, unsigned long long t0,
 __device__ __forceinline__ float4 read4(const PeerUse& u, const float* local, uint32_t tag, int* status) {
     const uint2* s = slot_of(u, local, u.t.rank);
     uint4 a, b;
-    const unsigned long long t0 = now_ns();
+    unsigned long long t0 = 0;   // the clock is read only once a first look has failed
     for (unsigned spins = 0;; spins++) {
         asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(a.x), "=r"(a.y), "=r"(a.z), "=r"(a.w) : "l"(s) : "memory");
         asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(b.x), "=r"(b.y), "=r"(b.z), "=r"(b.w) : "l"(s + 2) : "memory");
         if (a.y == tag && a.w == tag && b.y == tag && b.w == tag) break;
+        if (spins == 0) t0 = now_ns();
         if (gave_up(u, t0, spins, status)) break;
     }
     return make_float4(__uint_as_float(a.x), __uint_as_float(a.z), __uint_as_float(b.x), __uint_as_float(b.z));
@@ -105,10 +107,11 @@ __device__ __forceinline__ float4 read4(const PeerUse& u, const float* local, ui
 __device__ __forceinline__ float read1(const PeerUse& u, const float* local, uint32_t tag, int* status) {
     const uint2* s = slot_of(u, local, u.t.rank);
     uint2 a;
-    const unsigned long long t0 = now_ns();
+    unsigned long long t0 = 0;
     for (unsigned spins = 0;; spins++) {
         asm volatile("ld.volatile.global.v2.u32 {%0,%1}, [%2];\n" : "=r"(a.x), "=r"(a.y) : "l"(s) : "memory");
         if (a.y == tag) break;
+        if (spins == 0) t0 = now_ns();
         if (gave_up(u, t0, spins, status)) break;
     }
     return __uint_as_float(a.x);

@@ -51,7 +51,8 @@ struct Group {
 struct Write {
     uint32_t buffer;
     uint64_t offset;
-    size_t start, len;  // into write_data
+    size_t start, len;        // write_buffer: a copy of the caller's bytes in write_data (they may be gone by the submit)
+    const uint8_t* file_src;  // write_file: the bytes where they lie in the mapped file (nothing is copied until the submit)
 };
 enum OpKind { OP_DISPATCH, OP_COPY, OP_FILL, OP_READ };
 struct Op {
@@ -99,7 +100,16 @@ struct zcu_context {
     std::vector<cudaGraphExec_t> graphs;
     PeerTable peers = {};                 // tensor-parallel exchange (world == 0: not configured)
     std::vector<void*> ipc_open;          // peer arenas this context mapped
-    uint8_t* pinned = nullptr;  // staging for uploads and readbacks
+    std::vector<void*> retired;           // count words of earlier peer configurations
+    uint8_t* pinned = nullptr;  // staging for readbacks
+    // uploads go through a small ring of pinned chunks: the payload is copied once (mapping or write_data -> chunk)
+    // and the chunk is handed to the copy engine; a chunk is reused once its copy has finished
+    static constexpr int UP_CHUNKS = 2;
+    static constexpr size_t UP_CHUNK_BYTES = (size_t)32 << 20;
+    uint8_t* up_chunk[UP_CHUNKS] = {nullptr, nullptr};
+    cudaEvent_t up_done[UP_CHUNKS] = {nullptr, nullptr};
+    int up_next = 0;
+    bool unfinished = false;    // a wait timed out: work may still be in flight and may still read the pinned memory
     int* status = nullptr;      // mapped host word kernels set when a bounded wait gives up
     void* scratch = nullptr;    // device scratch of the multiplies that stage their inputs (k_quant_tc.cu): work of one stream, used in order
     size_t scratch_bytes = 0;
@@ -139,6 +149,26 @@ T* get(std::vector<T>& v, uint32_t id) {
     return &v[id];
 }
 
+// One upload of `len` bytes from host memory `src` to device memory `dst`, through the chunk ring.
+zcu_result upload_streamed(zcu_context* c, uint8_t* dst, const uint8_t* src, size_t len) {
+    for (size_t done = 0; done < len;) {
+        const int i = c->up_next;
+        if (!c->up_chunk[i]) {
+            CU(c, cudaMallocHost((void**)&c->up_chunk[i], zcu_context::UP_CHUNK_BYTES));
+            CU(c, cudaEventCreateWithFlags(&c->up_done[i], cudaEventDisableTiming));
+        } else {
+            CU(c, cudaEventSynchronize(c->up_done[i]));   // the chunk's last copy (a bounded, short transfer)
+        }
+        const size_t n = len - done < zcu_context::UP_CHUNK_BYTES ? len - done : zcu_context::UP_CHUNK_BYTES;
+        memcpy(c->up_chunk[i], src + done, n);
+        CU(c, cudaMemcpyAsync(dst + done, c->up_chunk[i], n, cudaMemcpyHostToDevice, c->stream));
+        CU(c, cudaEventRecord(c->up_done[i], c->stream));
+        c->up_next = (i + 1) % zcu_context::UP_CHUNKS;
+        done += n;
+    }
+    return ZCU_OK;
+}
+
 zcu_result ensure_pinned(zcu_context* c, size_t bytes) {
     if (c->dry || bytes <= c->pinned_cap) return ZCU_OK;
     if (c->pinned) cudaFreeHost(c->pinned);
@@ -175,10 +205,12 @@ zcu_result wait_stream(zcu_context* c, uint32_t timeout_ms) {
         const auto ms = std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::steady_clock::now() - start).count();
         if (timeout_ms != 0 && ms > (long long)timeout_ms) {
             cudaEventDestroy(ev);
+            c->unfinished = true;
             return fail(c, ZCU_E_TIMEOUT, "the device did not finish within %u ms", timeout_ms);
         }
     }
     cudaEventDestroy(ev);
+    c->unfinished = false;
     if (c->status && *(volatile int*)c->status != 0) {
         const int what = *(volatile int*)c->status;
         *c->status = 0;
@@ -186,8 +218,11 @@ zcu_result wait_stream(zcu_context* c, uint32_t timeout_ms) {
             return fail(c, ZCU_E_GPU, "delta_rule (chunked): the token count in the parameter block is not the step's, or a kept row "
                                       "lies inside the chunked part; the step was not applied past its whole chunks");
         if (what == 5)
-            return fail(c, ZCU_E_GPU, "a slice of a tensor-parallel exchange did not arrive within 2 s; every later wait of this context "
+            return fail(c, ZCU_E_GPU, "a slice of a tensor-parallel exchange did not arrive within the wait limit; every later wait of this context "
                                       "gives up at once (configure the peers again to clear it)");
+        if (what == 6)
+            return fail(c, ZCU_E_GPU, "attention: the step's position lies past the key blocks the dispatch covers (or past max_blocks); "
+                                      "the keys beyond were left out");
         return fail(c, ZCU_E_GPU, "a kernel gave up a bounded wait (a copy or a peer never arrived); its results are invalid");
     }
     return ZCU_OK;
@@ -294,28 +329,34 @@ zcu_result run_submit(zcu_context* c, uint32_t timeout_ms) {
     for (const Op& op : c->ops)
         if (op.kind == OP_READ) read_bytes += (op.size + 255) & ~(uint64_t)255;
     if (!c->dry) {
-        zcu_result r = ensure_pinned(c, c->write_data.size() + read_bytes + 256);
+        if (c->unfinished) {
+            // an earlier wait gave up: its work may still read the pinned memory that is about to be reused
+            zcu_result w = wait_stream(c, timeout_ms);
+            if (w != ZCU_OK) return w;
+        }
+        zcu_result r = ensure_pinned(c, read_bytes + 256);
         if (r != ZCU_OK) return r;
-        if (!c->write_data.empty()) memcpy(c->pinned, c->write_data.data(), c->write_data.size());
     }
     for (const Write& w : c->writes) {
         Buffer* b = get(c->buffers, w.buffer);
         if (!b) return fail(c, ZCU_E_BAD_ID, "write: buffer %u was destroyed", w.buffer);
+        const uint8_t* src = w.file_src ? w.file_src : c->write_data.data() + w.start;
         if (c->dry) {
-            memcpy(b->ptr + w.offset, c->write_data.data() + w.start, w.len);
+            memcpy(b->ptr + w.offset, src, w.len);
         } else {
-            CU(c, cudaMemcpyAsync(b->ptr + w.offset, c->pinned + w.start, w.len, cudaMemcpyHostToDevice, c->stream));
+            zcu_result r = upload_streamed(c, b->ptr + w.offset, src, w.len);
+            if (r != ZCU_OK) return r;
             if (b->usage & USAGE_UNIFORM) {
                 if (b->shadow.size() != b->size) {
                     b->shadow.assign(b->size, 0);
                     b->shadow_stale = b->shadow_stale || false;
                 }
-                memcpy(b->shadow.data() + w.offset, c->write_data.data() + w.start, w.len);
+                memcpy(b->shadow.data() + w.offset, src, w.len);
             }
         }
     }
     // 2. ops in recorded order
-    size_t read_at = (c->write_data.size() + 255) & ~(size_t)255;
+    size_t read_at = 0;
     struct PendingRead { void* dst; size_t at, size; };
     std::vector<PendingRead> pending;
     std::vector<uint8_t> params;
@@ -467,7 +508,7 @@ zcu_result run_command(zcu_context* c, uint32_t op, const uint32_t* a, size_t na
             const size_t start = (c->write_data.size() + 15) & ~(size_t)15;
             c->write_data.resize(start + len);
             memcpy(c->write_data.data() + start, data, len);
-            c->writes.push_back(Write{a[0], off, start, (size_t)len});
+            c->writes.push_back(Write{a[0], off, start, (size_t)len, nullptr});
             return ZCU_OK;
         }
         case 12: {  // write_file: buffer, offset u64, file_offset u64, size u64
@@ -478,10 +519,9 @@ zcu_result run_command(zcu_context* c, uint32_t op, const uint32_t* a, size_t na
             if (!c->file) return fail(c, ZCU_E_BAD_COMMAND, "write_file: no file set");
             if (foff + len > c->file_len || off + len > b->size || (off | len) % 4 != 0) return fail(c, ZCU_E_BAD_COMMAND, "write_file: range outside the file or the buffer");
             if (len == 0) return ZCU_OK;
-            const size_t start = (c->write_data.size() + 15) & ~(size_t)15;
-            c->write_data.resize(start + len);
-            memcpy(c->write_data.data() + start, c->file + foff, len);
-            c->writes.push_back(Write{a[0], off, start, (size_t)len});
+            // only the range is recorded: the bytes go from the mapping to the device at the submit, a chunk at a time
+            // (the mapping belongs to the caller and stays valid while it is the context's file: zcu_set_file)
+            c->writes.push_back(Write{a[0], off, 0, (size_t)len, c->file + foff});
             return ZCU_OK;
         }
         case 3: {  // create_kernel: id, kernel, variant, writes, artifact ptr, len
@@ -731,7 +771,7 @@ ZCU_EXPORT zcu_result zcu_create(const zcu_options* options, zcu_context** out_c
             delete c;
             return ZCU_E_GPU;
         }
-        if (c->prop.major < 10) {
+        if (c->prop.major != 10) {   // sm_100a code runs on sm_10x only (not on sm_9x, nor on sm_12x)
             fprintf(stderr, "zllm_cuda: device %d is sm_%d%d; the kernels are built for sm_100a only\n", c->device, c->prop.major, c->prop.minor);
             delete c;
             return ZCU_E_GPU;
@@ -769,6 +809,7 @@ ZCU_EXPORT zcu_result zcu_destroy(zcu_context* c, uint32_t timeout_ms) {
     }
     for (void* m : c->ipc_open) cudaIpcCloseMemHandle(m);
     if (c->peers.counts) cudaFree(c->peers.counts);
+    for (void* w : c->retired) cudaFree(w);
     for (cudaGraphExec_t g : c->graphs)
         if (g) cudaGraphExecDestroy(g);
     for (size_t i = 0; i < c->buffers.size(); i++)
@@ -777,6 +818,10 @@ ZCU_EXPORT zcu_result zcu_destroy(zcu_context* c, uint32_t timeout_ms) {
             else cudaFree(c->buffers[i].ptr);
         }
     if (c->pinned) cudaFreeHost(c->pinned);
+    for (int i = 0; i < zcu_context::UP_CHUNKS; i++) {
+        if (c->up_chunk[i]) cudaFreeHost(c->up_chunk[i]);
+        if (c->up_done[i]) cudaEventDestroy(c->up_done[i]);
+    }
     if (c->status) cudaFreeHost(c->status);
     if (c->scratch) cudaFree(c->scratch);
     if (c->own_stream) cudaStreamDestroy(c->stream);
@@ -1097,11 +1142,20 @@ ZCU_EXPORT zcu_result zcu_peer_config(zcu_context* c, uint32_t rank, uint32_t wo
     CU(c, cudaMemset(reinterpret_cast<void*>(t.base[rank] + exchange_offset), 0, (size_t)exchange_offset * 2));  // tag 0: nothing yet
     t.counts = words;
     t.tickets = words + slots;
-    if (c->peers.counts) cudaFree(c->peers.counts);
+    // (the old count words stay allocated until the context goes: graphs captured under the old configuration hold
+    // their address)
+    if (c->peers.counts) c->retired.push_back(c->peers.counts);
+    t.wait_ms = c->peers.wait_ms;
     c->peers = t;
     return ZCU_OK;
 }
 
+ZCU_EXPORT zcu_result zcu_peer_wait_limit(zcu_context* c, uint32_t milliseconds) {
+    LIVE(c);
+    if (c->peers.world == 0) return fail(c, ZCU_E_INVALID, "peer_wait_limit: zcu_peer_config was not called");
+    c->peers.wait_ms = milliseconds;   // launches from now on carry it
+    return ZCU_OK;
+}
 ZCU_EXPORT zcu_result zcu_graph_destroy(zcu_context* c, uint32_t graph) {
     if (!c) return ZCU_E_INVALID;
     if (graph >= c->graphs.size() || !c->graphs[graph]) return fail(c, ZCU_E_BAD_ID, "no graph %u", graph);

@@ -7,7 +7,7 @@ import numpy as np
 
 from . import kernels as K
 from . import synth
-from .plan import DenseConfig, Shard, layer_weight_shapes, slice_full_weights
+from .plan import DenseConfig, Shard, layer_weight_shapes, shard_rows, slice_full_weights
 
 
 def _quant(rng, ttype: str, n: int, k: int) -> np.ndarray:
@@ -119,3 +119,69 @@ def device_model(cfg: DenseConfig, torch, dev, shard: Shard | None = None, seed:
     w = {"layers": layers, "embed": quant(cfg.embed_type, cfg.vocab, cfg.hidden),
          "head": quant(cfg.head_type, cfg.vocab // sh.world, cfg.hidden), "out_norm": vec(cfg.hidden)}
     return w, keep
+
+
+def device_full_model(cfg: DenseConfig, torch, dev, seed: int = 0):
+    """A full (unsharded) random model on the device as 2-D uint8 / f32 tensors in the kernels' layouts, the same
+    on every rank that calls it with the same seed: what `device_shard` cuts a rank's part out of, so that a
+    sharded step and the unsharded step run the SAME model (the parity leg of the multi-GPU bench)."""
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(seed)
+
+    def q4k(n, k):
+        nb = k // 256
+        w = torch.randint(0, 256, (n, nb, 144), dtype=torch.uint8, device=dev, generator=gen)
+        d = (torch.rand((n, nb, 2), device=dev, generator=gen) * (1e-2 - 1e-4) + 1e-4).to(torch.float16)
+        w[:, :, 0:4] = d.view(torch.uint8).view(n, nb, 4)
+        return w.view(n, nb * 144)
+
+    def q80(n, k):
+        nb = k // 32
+        stride = (k + k // 16 + 15) & ~15
+        w = torch.zeros((n, stride), dtype=torch.uint8, device=dev)
+        w[:, :k] = torch.randint(1, 256, (n, k), dtype=torch.uint8, device=dev, generator=gen)
+        d = (torch.rand((n, nb), device=dev, generator=gen) * (2e-3 - 1e-4) + 1e-4).to(torch.float16)
+        w[:, k:k + 2 * nb] = d.view(torch.uint8).view(n, 2 * nb)
+        return w
+
+    def quant(ttype, n, k):
+        return q4k(n, k) if ttype == "q4_k" else q80(n, k)
+
+    def vec(n):
+        return (1 + 0.1 * torch.randn(n, device=dev, generator=gen)).float()
+
+    layers = []
+    for _ in range(cfg.layers):
+        layers.append({"wqkv": quant(cfg.body_type, cfg.q_dim + 2 * cfg.kv_dim, cfg.hidden), "wo": quant(cfg.body_type, cfg.hidden, cfg.q_dim),
+                       "wgu": quant(cfg.body_type, 2 * cfg.ff, cfg.hidden), "wdown": quant(cfg.body_type, cfg.hidden, cfg.ff),
+                       "attn_norm": vec(cfg.hidden), "ffn_norm": vec(cfg.hidden)})
+    return {"layers": layers, "embed": quant(cfg.embed_type, cfg.vocab, cfg.hidden), "head": quant(cfg.head_type, cfg.vocab, cfg.hidden),
+            "out_norm": vec(cfg.hidden)}
+
+
+def device_shard(full, cfg: DenseConfig, torch, shard: Shard | None = None):
+    """One rank's part of a `device_full_model`, in plan layout: ({name: (ptr, nbytes)}, the tensors that own the
+    memory). The rows are the ones `slice_full_weights` names."""
+    sh = shard or Shard()
+    keep = []
+    hd = cfg.head_dim
+    h0, h1 = sh.heads(cfg)
+    g0, g1 = sh.kv_heads(cfg)
+    f0, f1 = shard_rows(cfg.ff, sh.rank, sh.world)
+    e0, e1 = shard_rows(cfg.hidden, sh.rank, sh.world)
+    v0, v1 = shard_rows(cfg.vocab, sh.rank, sh.world)
+
+    def own(t):
+        t = t.contiguous()
+        keep.append(t)
+        return (t.data_ptr(), t.numel() * t.element_size())
+
+    layers = []
+    for lw in full["layers"]:
+        w = lw["wqkv"]
+        qkv = torch.cat([w[h0 * hd:h1 * hd], w[cfg.q_dim + g0 * hd:cfg.q_dim + g1 * hd],
+                         w[cfg.q_dim + cfg.kv_dim + g0 * hd:cfg.q_dim + cfg.kv_dim + g1 * hd]])
+        gu = torch.cat([lw["wgu"][f0:f1], lw["wgu"][cfg.ff + f0:cfg.ff + f1]])
+        layers.append({"wqkv": own(qkv), "wo": own(lw["wo"][e0:e1]), "wgu": own(gu), "wdown": own(lw["wdown"][e0:e1]),
+                       "attn_norm": own(lw["attn_norm"]), "ffn_norm": own(lw["ffn_norm"])})
+    return {"layers": layers, "embed": own(full["embed"]), "head": own(full["head"][v0:v1]), "out_norm": own(full["out_norm"])}, keep

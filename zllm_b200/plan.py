@@ -228,12 +228,11 @@ class DenseProgram:
         blocks = -(-max_keys // K.ATTN_BLOCK)
         att_cols = self.att.at(self.h0 * hd * 4)                # this rank's head columns of att
         peer = self.arena is not None
-        for il in range(cfg.layers):
-            lw = self.w["layers"][il]
-            s_att, s_xwo, s_act, s_xdown = (4 * il, 4 * il + 1, 4 * il + 2, 4 * il + 3) if peer else (None,) * 4
-            s_prev = (4 * il - 1) if (peer and il > 0) else None  # the x this layer starts from
+        def qkv(il):
             # 1. fused attn_norm + Q|K|V projection (local heads); 2. RoPE (normal pairs) and the cache append at
             #    each sequence's position, in the multiply's epilogue or as rope_append's own launch
+            lw = self.w["layers"][il]
+            s_prev = (4 * il - 1) if (peer and il > 0) else None  # the x this layer starts from
             if self.fuse_rope:
                 self._matvec(cfg.body_type, self.x, lw["wqkv"], self.qkv, self.qkv_row, e, flags=K.NORM, eps=cfg.eps,
                              norm_w=lw["attn_norm"], rope=(rp, [self.rope, self.kc[il], self.vc[il], self.step, self.positions]),
@@ -244,6 +243,11 @@ class DenseProgram:
                 self.L.launch(K.ROPE_APPEND, rp, [self.qkv, self.dummy, self.dummy, self.rope, self.kc[il], self.vc[il],
                                                   self.step, self.positions], (self.lh + self.lg, B, 1))
                 self.launches_per_step += 1
+
+        qkv(0)
+        for il in range(cfg.layers):
+            lw = self.w["layers"][il]
+            s_att, s_xwo, s_act, s_xdown = (4 * il, 4 * il + 1, 4 * il + 2, 4 * il + 3) if peer else (None,) * 4
             # 3-4. split attention over each sequence's cache, merged into this rank's head columns of att
             self.L.launch(K.ATTN_SPLIT, ap, [self.qkv, self.kc[il], self.vc[il], self.part, self.step, self.positions],
                           (self.lg, blocks, B), self.variants.get("attn_split", 0))
@@ -264,6 +268,8 @@ class DenseProgram:
             self._matvec(cfg.body_type, self.act, lw["wdown"], self.x, self.le, cfg.ff, col0=sh.rank * self.le,
                          out_stride=e, flags=K.ACCUMULATE, wait=s_act, push=s_xdown)
             self._gather(self.x, e)
+            if il + 1 < cfg.layers:
+                qkv(il + 1)
         # output norm fused into the LM head
         s_logits = 4 * cfg.layers if peer else None
         self._matvec(cfg.head_type, self.x, self.w["head"], self.logits, self.lv, e, col0=sh.rank * self.lv,
