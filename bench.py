@@ -300,7 +300,7 @@ class DecodeStep:
     context = 8192
 
     def __init__(self, dist: Dist, batch: int = 1, variant: int = 0, layers: int = 32,
-                 exchange: str = "peer", attn_variant: int = 0, batched: str = "auto"):
+                 exchange: str = "peer", attn_variant: int = 0, batched: str = "auto", tune: bool = True):
         import torch
 
         from zllm_b200 import abi
@@ -364,6 +364,12 @@ class DecodeStep:
         self.pinned_logits = torch.empty((batch, self.cfg.vocab), dtype=torch.float32).pin_memory()
         self.prog.write_step(self.tokens, self.positions)
         torch.cuda.synchronize()
+        # the load-time sweep over the decode multiply's variants (tiles in flight, CTA shape, CTA count) on the
+        # model's own weights, as the reference tunes at load (src/tune/tune.zig); steps of up to four sequences
+        self.tuned = {}
+        if tune and batch <= 4:
+            self.tuned = self.prog.sweep()
+            torch.cuda.synchronize()
         self.graph = None
         self.tgraph = None
         self.mv_graph = None
@@ -419,6 +425,7 @@ class DecodeStep:
                             f"f16 KV cache at {self.context} positions, batch {self.batch}",
                 "batch": self.batch, "context": self.context,
                 "replay": "CUDA graph of the step's launches",
+                "tuned_variants": {f"{t} {n}x{k}": hex(v) for (t, n, k), v in self.tuned.items()},
                 "l2": f"inputs larger than L2: a step reads {self.bytes['total'] / 1e9:.2f} GB per rank "
                       f"({self.bytes['weights'] / 1e9:.2f} GB weights + {self.bytes['kv'] / 1e9:.2f} GB KV)",
                 "parallelism": ("1 GPU" if not self.dist.on else
@@ -967,6 +974,7 @@ def run_cuda(args):
         kw["exchange"] = args.exchange
         kw["attn_variant"] = args.attn_variant
         kw["batched"] = args.batched
+        kw["tune"] = not args.no_tune
         if args.layers:
             kw["layers"] = args.layers
     wl = WORKLOADS[args.workload](dist, **kw)
@@ -1147,6 +1155,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
     ap.add_argument("--batched", default="auto", choices=["auto", "on", "off"],
                     help="decode: Q4_K multiplies in one pass for all sequences (tcgen05 family; auto = for 5..64 sequences on one GPU)")
+    ap.add_argument("--no-tune", action="store_true", help="decode: skip the load-time sweep over the multiply's variants")
     ap.add_argument("--attn-variant", type=int, default=0, help="decode: form of attn_split's fast path (0 default, 1-4: k_attn.cu)")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                     help="decode on N > 1 GPUs: slices pushed by the kernels over peer memory, or NCCL all-gathers")

@@ -194,3 +194,71 @@ def test_peer_exchange_with_one_rank_equals_the_plain_step(gpu, batch):
         gpu.sync()
         for name in ("logits", "x", "att", "act"):
             assert np.array_equal(getattr(plain, name).download(np.uint32), getattr(peer, name).download(np.uint32)), (name, pos)
+
+
+@pytest.mark.parametrize("batch", [1, 8])
+def test_one_layer_at_the_benchmark_shape_matches_oracle(ref, gpu, batch):
+    # The shapes the decode benchmark times (hidden 4096, SwiGLU 14336, 32 query / 8 KV heads of 128, 128256-row Q8_0
+    # head, f16 cache at position 8192), one layer deep: the step against the oracle's layer and head, per sequence.
+    # (batch 8: the Q4_K multiplies take the batched family, the head runs in passes of four.)
+    cfg = DenseConfig(layers=1, max_ctx=8192 + 64)
+    host = M.host_model(cfg, "bench-shape")
+    weights = M.upload(host, cfg, gpu.put)
+    prog = DenseProgram(gpu, cfg, weights, batch, gpu.zeros)
+    prog.set_rope_table(gpu.put(DenseProgram.rope_table(cfg)))
+    rng = np.random.default_rng(8192)
+    positions = np.array([8192 - 3 * b for b in range(batch)], dtype=np.uint32)
+    tokens = rng.integers(0, cfg.vocab, size=batch).astype(np.uint32)
+    kv_shape = (batch, cfg.max_ctx, cfg.kv_heads, cfg.head_dim)
+    kc_host = rng.normal(size=kv_shape).astype(np.float16)
+    vc_host = rng.normal(size=kv_shape).astype(np.float16)
+    prog.kc[0].upload(kc_host.view(np.uint16))
+    prog.vc[0].upload(vc_host.view(np.uint16))
+    prog.write_step(tokens, positions)
+    prog.record_step(int(positions.max()) + 1)
+    gpu.sync()
+    logits = prog.logits.download(np.float32).reshape(batch, cfg.vocab)
+    hidden = prog.x.download(np.float32).reshape(batch, cfg.hidden)
+    for b in range(batch):
+        kc = [np.ascontiguousarray(kc_host[b]).view(np.uint16).copy()]
+        vc = [np.ascontiguousarray(vc_host[b]).view(np.uint16).copy()]
+        want_logits, want_x = oracle_step(ref, cfg, host, int(tokens[b]), int(positions[b]), kc, vc)
+        assert rel_l2(hidden[b], want_x) < 1e-4, (b, rel_l2(hidden[b], want_x))
+        assert rel_l2(logits[b], want_logits) < 1e-4, (b, rel_l2(logits[b], want_logits))
+        assert rel_err(logits[b], want_logits) < 1e-3   # the hard ceiling: largest error over the largest logit
+        assert int(np.argmax(logits[b])) == int(np.argmax(want_logits))
+
+
+def test_a_wait_for_an_exchange_that_nobody_pushes_runs_out(gpu, launcher):
+    # A multiply told to take its input from an exchange slot that no kernel ever pushes: its wait runs out after the
+    # limit the host set (50 ms here, 2 s by default), the kernel returns, the next sync reports the error, and the
+    # context works again once the peers are configured again. No hang, no fault: a bounded wait expiring.
+    from zllm_b200 import abi, synth
+
+    rng = np.random.default_rng(3)
+    n, k = 64, 1024
+    w = gpu.put(synth.q4_k_weights(rng, n, k))
+    x_host = synth.normal_f32(rng, 1, k)
+    arena = abi.PeerArena(gpu, 0, 1, 1 << 16, 4)
+    gpu.peer_wait_limit(50)
+    x, out = arena.alloc(k * 4), arena.alloc(n * 4)
+    x.upload(x_host)
+    launcher.matvec("q4_k", x, w, out, n, k, wait=2)
+    with pytest.raises(abi.ZcuError) as e:
+        gpu.sync()
+    assert e.value.name == "GpuError" and "did not arrive" in e.value.message
+    # configured again (fresh counts and abort word): a plain multiply and an exchanged pair both work
+    arena = abi.PeerArena(gpu, 0, 1, 1 << 16, 4)
+    gpu.peer_wait_limit(0)
+    x, mid, out = arena.alloc(k * 4), arena.alloc(k * 4), arena.alloc(n * 4)
+    x.upload(x_host)
+    w2 = gpu.put(synth.q4_k_weights(rng, k, k))
+    launcher.matvec("q4_k", x, w2, mid, k, k, push=1)
+    launcher.matvec("q4_k", mid, w, out, n, k, wait=1)
+    gpu.sync()
+    plain_mid, plain_out = gpu.zeros(k * 4), gpu.zeros(n * 4)
+    launcher.matvec("q4_k", gpu.put(x_host), w2, plain_mid, k, k)
+    launcher.matvec("q4_k", plain_mid, w, plain_out, n, k)
+    gpu.sync()
+    assert np.array_equal(out.download(np.uint32), plain_out.download(np.uint32))
+

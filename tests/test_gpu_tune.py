@@ -32,6 +32,31 @@ def test_sweep_picks_an_agreeing_candidate_per_shape(gpu):
     assert all((r[3] == 0 or (r[3] >> 16) & 0xFF == K.FAMILY_SCALAR) for r in sweep.report if r[2] == 96)
 
 
+def test_the_sweep_times_a_shape_as_the_plan_uses_it_and_a_plan_takes_the_table(gpu):
+    # A plan's own sweep: every shape of the model with its flags (norm prologue, SiLU pair), every layer's matrix in
+    # turn; the table lands in the plan, and the tuned step gives the untuned step's logits within the sweep's bar.
+    from zllm_b200 import model as M
+    from zllm_b200.plan import DenseConfig, DenseProgram
+
+    cfg = DenseConfig(layers=2, hidden=512, heads=8, kv_heads=2, head_dim=64, ff=1024, vocab=1536, max_ctx=192)
+    weights = M.upload(M.host_model(cfg, "tune-plan"), cfg, gpu.put)
+
+    def step(prog):
+        prog.set_rope_table(gpu.put(DenseProgram.rope_table(cfg)))
+        prog.write_step(np.array([7], dtype=np.uint32), np.array([33], dtype=np.uint32))
+        prog.record_step(34)
+        gpu.sync()
+        return prog.logits.download(np.float32)
+
+    plain = step(DenseProgram(gpu, cfg, weights, 1, gpu.zeros))
+    prog = DenseProgram(gpu, cfg, weights, 1, gpu.zeros)
+    table = prog.sweep()
+    assert set(table) == {("q4_k", prog.qkv_row, 512), ("q4_k", 512, 512), ("q4_k", 1024, 512), ("q4_k", 512, 1024), ("q8_0", 1536, 512)}
+    assert all(prog.variants[key] == v for key, v in table.items())
+    tuned = step(prog)
+    assert np.linalg.norm(tuned - plain) / np.linalg.norm(plain) <= 1e-5
+
+
 def test_a_diverging_candidate_is_dropped(gpu, monkeypatch):
     rng = synth.rng_for("tune", "diverge")
     n, k = 128, 512

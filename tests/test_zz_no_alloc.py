@@ -58,3 +58,27 @@ def test_static_partials_reject_sizes_beyond_the_fixed_array(gpu):
         gpu.attention_decode_static(p, [dummy, dummy, dummy, dummy, dummy], 20000, 1)
     assert e.value.name == "Invalid" and "4 MiB" in e.value.message
     gpu.sync()  # the context is still usable
+
+
+def test_a_step_past_max_keys_is_reported_not_followed(gpu, launcher):
+    # max_keys is fixed when the call is made (or captured) while the Step buffer moves on with every replay: a
+    # position past what the call covers must neither read past the cache nor past the fixed array - the kernels
+    # leave the keys beyond out and the next sync says so.
+    rng = np.random.default_rng(77)
+    heads, kv_heads, hd, max_keys = 32, 8, 128, 256
+    kc = rng.normal(size=(max_keys, kv_heads, hd)).astype(np.float16).view(np.uint16)
+    vc = rng.normal(size=(max_keys, kv_heads, hd)).astype(np.float16).view(np.uint16)
+    q = rng.normal(size=(1, heads * hd)).astype(np.float32)
+    dq, dk, dv, out = gpu.put(q), gpu.put(kc), gpu.put(vc), gpu.zeros(heads * hd * 4)
+    p = K.Attention(heads, kv_heads, hd, K.KV_F16, K.attention_scale(hd), 0, heads * hd, 0, 0, 0)
+    step = gpu.put(np.array([1, 5000, 0, 0], dtype=np.uint32))   # position 5000, cache and call cover 256 keys
+    gpu.attention_decode_static(p, [dq, dk, dv, out, step], max_keys, 1)
+    with pytest.raises(abi.ZcuError) as e:
+        gpu.sync()
+    assert e.value.name == "GpuError" and "past the key blocks" in e.value.message
+    # the same call with the Step inside the range works, and the context is intact
+    step = gpu.put(np.array([1, max_keys - 1, 0, 0], dtype=np.uint32))
+    gpu.attention_decode_static(p, [dq, dk, dv, out, step], max_keys, 1)
+    gpu.sync()
+    assert np.isfinite(out.download(np.float32)).all() and np.abs(out.download(np.float32)).max() > 0
+

@@ -16,6 +16,8 @@
 #include <cfloat>
 #include <cuda_fp16.h>
 
+#include <atomic>
+
 #include "k_attn_fast.cuh"
 #include "zcu_internal.h"
 
@@ -363,7 +365,7 @@ zcu_result launch_attn_combine(const LaunchArgs& a) {
 // comes from cudaGetSymbolAddress, asked once per device with that device current.
 constexpr size_t ATTN_STATIC_FLOATS = (size_t)1 << 20;  // 4 MiB
 static __device__ __align__(256) float g_attn_partials[ATTN_STATIC_FLOATS];
-static float* g_attn_partials_ptr[64] = {};
+static std::atomic<float*> g_attn_partials_ptr[64] = {};   // contexts on several threads may resolve it at once
 
 // Bindings: qg, kc, vc, out, step (+ per-row positions for batched sequences). `max_keys`: the largest
 // number of cache positions any row attends to (its position + 1). The partials are laid out as
@@ -375,6 +377,11 @@ zcu_result launch_attn_static(const LaunchArgs& a, uint32_t max_keys, uint32_t r
     ZCU_NEED(a, p.kv_heads > 0 && p.heads % p.kv_heads == 0 && max_keys > 0 && rows > 0,
              "attention (static partials): heads %u over kv_heads %u, %u keys, %u rows", p.heads, p.kv_heads, max_keys, rows);
     p.max_blocks = (max_keys + AT_BLOCK - 1) / AT_BLOCK;
+    // everything either launch would refuse is refused here, before the first of them is enqueued
+    ZCU_NEED(a, p.heads / p.kv_heads <= AT_MAX_GROUP && p.head_dim % 32 == 0 && p.head_dim >= 32 && p.head_dim <= 256 &&
+                    (p.kv == KV_F32 || p.kv == KV_F16) && p.max_blocks <= AC_MAX_BLOCKS,
+             "attention (static partials): group %u, head_dim %u, cache format %u or %u key blocks is not built", p.heads / p.kv_heads,
+             p.head_dim, p.kv, p.max_blocks);
     const size_t need = (size_t)rows * p.heads * p.max_blocks * (p.head_dim + 2);
     if (need > ATTN_STATIC_FLOATS)
         return zcu_fail(a, ZCU_E_INVALID,
@@ -384,16 +391,16 @@ zcu_result launch_attn_static(const LaunchArgs& a, uint32_t max_keys, uint32_t r
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess || dev < 0 || dev >= 64) return zcu_fail(a, ZCU_E_GPU, "attention (static partials): no current device");
-    if (!g_attn_partials_ptr[dev]) {
+    if (!g_attn_partials_ptr[dev].load()) {
         // First call on this device: resolve the symbol's device address. Not a stream operation, so it
         // should happen before any stream capture starts.
         float* ptr = nullptr;
         e = cudaGetSymbolAddress((void**)&ptr, g_attn_partials);
         if (e != cudaSuccess || !ptr)
             return zcu_fail(a, ZCU_E_GPU, "attention (static partials): cudaGetSymbolAddress: %s", cudaGetErrorString(e));
-        g_attn_partials_ptr[dev] = ptr;
+        g_attn_partials_ptr[dev].store(ptr);
     }
-    const zcu_binding part = {g_attn_partials_ptr[dev], need * sizeof(float)};
+    const zcu_binding part = {g_attn_partials_ptr[dev].load(), need * sizeof(float)};
     const bool batched = a.nb >= 6 && p._pad[0] != 0;
     // attn_split: qg, kc, vc, part, step [, positions]; grid (kv_heads, 64-key blocks, rows)
     zcu_binding sb[6] = {a.b[0], a.b[1], a.b[2], part, a.b[4], {nullptr, 0}};

@@ -341,7 +341,7 @@ bool matvec_variant_ok(uint32_t kernel, uint32_t variant) {
     if (family == ZCU_FAMILY_SCALAR) return ks == 0;
     if (family == ZCU_FAMILY_MMA) {
         const uint32_t stages = variant & 0xffu;
-        return ks <= 1 && (stages == 0 || (stages >= 2 && stages <= 6));
+        return (ks & ~0x11u) == 0 && (stages == 0 || (stages >= 2 && stages <= 6));   // ks: CTA shape | every-SM bit
     }
     if (family == ZCU_FAMILY_TCGEN05) return kernel == ZCU_K_MATVEC_Q4_K && (variant & 0xffffu) == 0;
     return false;

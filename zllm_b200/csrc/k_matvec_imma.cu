@@ -705,10 +705,10 @@ int stages_that_fit(int k, int seg_max, int want, int smem_cap) {
 }
 
 template <int TYPE, int NT, int W>
-zcu_result launch_one(const LaunchArgs& a, const MvArgs& v, int t0, int want_stages) {
+zcu_result launch_one(const LaunchArgs& a, const MvArgs& v, int t0, int want_stages, bool every_sm) {
     const bool q4 = TYPE == W_Q4_K, pair = (v.p.flags & MV_SILU_PAIR) != 0;
     const int row_tiles = ((int)v.p.n + 15) / 16;
-    const int grid = balanced_grid(row_tiles, a.sm_count);
+    const int grid = every_sm ? (row_tiles < a.sm_count ? row_tiles : a.sm_count) : balanced_grid(row_tiles, a.sm_count);
     const int seg_max = segments_needed((int)v.p.n, (int)v.p.k, q4, pair, grid, W);
     // two CTAs of eight warps share an SM (this kernel's and its neighbour's in the stream): half the memory each
     const int cap = W == 16 ? SMEM_MAX : 110 * 1024;
@@ -733,7 +733,7 @@ int tokens_per_pass(int k, int cap) {
 }
 
 template <int TYPE, int W>
-zcu_result launch_type(const LaunchArgs& a, const MvArgs& v, int stages) {
+zcu_result launch_type(const LaunchArgs& a, const MvArgs& v, int stages, bool every_sm) {
     const int cap = tokens_per_pass<TYPE, W>((int)v.p.k, W == 16 ? SMEM_MAX : 110 * 1024);
     MvArgs pass = v;
     for (int t0 = 0; t0 < v.m;) {
@@ -742,10 +742,10 @@ zcu_result launch_type(const LaunchArgs& a, const MvArgs& v, int stages) {
         pass.peer.hold = t0 + mt < v.m ? 1u : 0u;
         zcu_result r;
         switch (mt) {
-            case 1: r = launch_one<TYPE, 1, W>(a, pass, t0, stages); break;
-            case 2: r = launch_one<TYPE, 2, W>(a, pass, t0, stages); break;
-            case 3: r = launch_one<TYPE, 3, W>(a, pass, t0, stages); break;
-            default: r = launch_one<TYPE, 4, W>(a, pass, t0, stages); break;
+            case 1: r = launch_one<TYPE, 1, W>(a, pass, t0, stages, every_sm); break;
+            case 2: r = launch_one<TYPE, 2, W>(a, pass, t0, stages, every_sm); break;
+            case 3: r = launch_one<TYPE, 3, W>(a, pass, t0, stages, every_sm); break;
+            default: r = launch_one<TYPE, 4, W>(a, pass, t0, stages, every_sm); break;
         }
         if (r != ZCU_OK) return r;
         t0 += mt;
@@ -755,17 +755,20 @@ zcu_result launch_type(const LaunchArgs& a, const MvArgs& v, int stages) {
 
 }  // namespace
 
-// `stages`: tiles in flight per warp (2..6; 0 = as deep as fits). `shape`: 0 = CTAs of 16 warps, one per SM;
-// 1 = CTAs of 8 warps with at most half an SM's shared memory, so that the next kernel's CTAs can move in and
-// fill their rings while this one still computes. Q8_0 needs k % 256 == 0.
+// `stages`: tiles in flight per warp (2..6; 0 = as deep as fits). `shape`, low nibble: 0 = CTAs of 16 warps, one per
+// SM; 1 = CTAs of 8 warps with at most half an SM's shared memory, so that the next kernel's CTAs can move in and
+// fill their rings while this one still computes. `shape` bit 4: a CTA on every SM (the last ones with a row tile
+// fewer) instead of the CTA count that divides the row tiles most evenly. Q8_0 needs k % 256 == 0.
 zcu_result launch_matvec_imma(const LaunchArgs& a, const mv::MvArgs& v, int type, int stages, int shape) {
     if (type == mv::W_Q8_0 && v.p.k % 256 != 0) return zcu_fail(a, ZCU_E_UNSUPPORTED_KERNEL, "matvec_q8_0: k = %u is not a multiple of 256", v.p.k);
     if (type == mv::W_Q4_K && v.p.k % 256 != 0) return zcu_fail(a, ZCU_E_BAD_COMMAND, "matvec_q4_k: k = %u is not a multiple of 256", v.p.k);
     if (stages != 0 && (stages < 2 || stages > 6))
         return zcu_fail(a, ZCU_E_UNSUPPORTED_KERNEL, "matvec: %d stages is not built", stages);
-    if (shape == 1) return type == mv::W_Q4_K ? launch_type<mv::W_Q4_K, 8>(a, v, stages) : launch_type<mv::W_Q8_0, 8>(a, v, stages);
-    if (shape != 0) return zcu_fail(a, ZCU_E_UNSUPPORTED_KERNEL, "matvec: CTA shape %d is not built", shape);
-    return type == mv::W_Q4_K ? launch_type<mv::W_Q4_K, 16>(a, v, stages) : launch_type<mv::W_Q8_0, 16>(a, v, stages);
+    const bool every_sm = (shape & 0x10) != 0;
+    const int warps = shape & 0x0f;
+    if ((shape & ~0x1f) != 0 || warps > 1) return zcu_fail(a, ZCU_E_UNSUPPORTED_KERNEL, "matvec: CTA shape 0x%x is not built", shape);
+    if (warps == 1) return type == mv::W_Q4_K ? launch_type<mv::W_Q4_K, 8>(a, v, stages, every_sm) : launch_type<mv::W_Q8_0, 8>(a, v, stages, every_sm);
+    return type == mv::W_Q4_K ? launch_type<mv::W_Q4_K, 16>(a, v, stages, every_sm) : launch_type<mv::W_Q8_0, 16>(a, v, stages, every_sm);
 }
 
 #ifdef ZCU_TRACE

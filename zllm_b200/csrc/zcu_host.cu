@@ -1056,8 +1056,9 @@ ZCU_EXPORT zcu_result zcu_attention_decode_static(zcu_context* c, const void* pa
     a.scratch_bytes = 0;
     a.err = c->err;
     a.err_cap = sizeof(c->err);
-    c->launches += 2;
-    return launch_attn_static(a, max_keys, rows);
+    const zcu_result r = launch_attn_static(a, max_keys, rows);
+    if (r == ZCU_OK) c->launches += 2;
+    return r;
 }
 
 ZCU_EXPORT zcu_result zcu_sync(zcu_context* c, uint32_t timeout_ms) {

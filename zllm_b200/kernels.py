@@ -44,9 +44,14 @@ def variant(tiles: int = 0, splitk: int = 0, family: int = 0) -> int:
     return tiles | (splitk << 8) | (family << 16)
 
 
-# Candidates the tuning sweep tries (the cuda arm of MatvecVariant.candidates).
-# Tensor-core family: tiles in flight per warp (byte 0); scalar family: one shape.
-MATVEC_CANDIDATES = [variant(st, 0, FAMILY_MMA) for st in (2, 4, 6)] + [variant(0, 0, FAMILY_SCALAR)]
+# Candidates the tuning sweep tries (the cuda arm of MatvecVariant.candidates, src/kernels/kernels.zig:365-373: there
+# workgroup size x lanes per row x rows per lane; here the knobs this backend's multiply has). Tensor-core family:
+# tiles in flight per warp (byte 0: 3..6), CTA shape (byte 1, low nibble: 0 = 16 warps and one CTA per SM, 1 = 8
+# warps and two), CTA count (byte 1, bit 4: 0 = the count that divides the row tiles evenly, 1 = a CTA on every SM);
+# scalar family: one shape.
+SHAPE_16_WARPS, SHAPE_8_WARPS, GRID_EVERY_SM = 0, 1, 0x10
+MATVEC_CANDIDATES = ([variant(st, shape | grid, FAMILY_MMA) for st in (3, 4, 5, 6) for shape in (SHAPE_16_WARPS, SHAPE_8_WARPS)
+                      for grid in (0, GRID_EVERY_SM)] + [variant(0, 0, FAMILY_SCALAR)])
 # matvec_q4_k for up to 64 tokens in one pass over the weights (tcgen05, accumulators in tensor memory).
 MATVEC_BATCHED = variant(0, 0, FAMILY_TCGEN05)
 MATVEC_BATCHED_MAX_TOKENS = 64

@@ -197,6 +197,26 @@ class DenseProgram:
         self.L.matvec(ttype, x, w, out, n, k, m=self.B, variant=v, **kw)
         self.launches_per_step += 3 if v == K.MATVEC_BATCHED else 1  # columns, multiply, reduction
 
+    def sweep(self, tokens: int | None = None) -> dict:
+        """The load-time sweep over this program's multiply shapes on the model's own weights (tune.Sweep, the
+        counterpart of src/tune/tune.zig; every layer's matrix of a shape takes its turn, so the timings are of
+        weights that come from HBM). Takes the table for the launches recorded from now on and returns it."""
+        from . import tune
+
+        cfg, e = self.cfg, self.cfg.hidden
+        layers = self.w["layers"]
+        s = tune.Sweep(self.ctx, tokens=min(tokens or self.B, 4))
+        s.add(cfg.body_type, [lw["wqkv"] for lw in layers], self.qkv_row, e, flags=K.NORM, eps=cfg.eps, norm_w=layers[0]["attn_norm"])
+        s.add(cfg.body_type, [lw["wo"] for lw in layers], self.le, cfg.q_dim)
+        s.add(cfg.body_type, [lw["wgu"] for lw in layers], self.lff, e, flags=K.NORM | K.SILU_PAIR, eps=cfg.eps, half=self.lff,
+              norm_w=layers[0]["ffn_norm"])
+        s.add(cfg.body_type, [lw["wdown"] for lw in layers], self.le, cfg.ff)
+        s.add(cfg.head_type, self.w["head"], self.lv, e, flags=K.NORM, eps=cfg.eps, norm_w=self.w["out_norm"])
+        table = s.run()
+        self.variants = {**self.variants, **table}
+        self.sweep_report = s.report
+        return table
+
     def _gather(self, buf, width):
         if self.gather is not None:
             self.gather(buf, self.B, width)

@@ -1,7 +1,7 @@
 """Load-time tuning of the quantised decode multiplies: the counterpart of the reference's tune.Sweep
 (src/tune/tune.zig:1-27, 77-106). For each shape (type, n, k) every candidate variant of this backend
-(kernels.MATVEC_CANDIDATES: tiles in flight per warp 2/4/6 of the tensor-core family, and the scalar family) runs on
-the shape's real weights: it is first checked against the default variant (relative L2 error above `TOLERANCE`
+(kernels.MATVEC_CANDIDATES: tiles in flight per warp, CTA shape and CTA count of the tensor-core family, and the
+scalar family) runs on the shape's real weights: it is first checked against the default variant (relative L2 error above `TOLERANCE`
 drops it: candidates differ only in the order of each row's sums), then timed - `WARMUP` batches, then the median
 of `TIMED` batches, each batch repeating the dispatch so that it lasts about a millisecond. The fastest per shape
 goes into the table a plan passes as `variants`.
@@ -34,19 +34,26 @@ class Sweep:
         self.shapes, self.dropped, self.report = [], 0, []
         self.L = K.Launcher(ctx)
 
-    def add(self, ttype: str, weights, n: int, k: int):
+    def add(self, ttype: str, weights, n: int, k: int, **flags):
+        """`weights`: the shape's matrix, or a list of matrices of this shape (every layer's): a batch then rotates
+        through them, so that a shape smaller than L2 is still timed from HBM, where a decode step finds it.
+        `flags`: what the plan passes with this shape (flags, eps, half, norm_w), so that the variant is timed as used."""
         if ttype not in ("q4_k", "q8_0") or any(s[0] == ttype and s[2] == n and s[3] == k for s in self.shapes):
             return
+        ws = list(weights) if isinstance(weights, list) else [weights]
+        if "flags" in flags:
+            flags["flags"] &= ~K.ACCUMULATE   # every run must give the same output: nothing accumulates in the sweep
         row_bytes = K.row_bytes(ttype, k)
-        reps = int(np.clip((256 << 20) // max(n * row_bytes, 1), 2, 64))
-        self.shapes.append((ttype, weights, n, k, reps))
+        rows = n + (flags.get("half", 0) if flags.get("flags", 0) & K.SILU_PAIR else 0)
+        reps = int(np.clip((256 << 20) // max(rows * row_bytes, 1), 2, 64))
+        self.shapes.append((ttype, ws, n, k, reps, flags))
 
     def _batch(self, shape, variant, x, out) -> float:
-        ttype, w, n, k, reps = shape
+        ttype, ws, n, k, reps, flags = shape
         self.ctx.sync()
         t0 = time.perf_counter()
-        for _ in range(reps):
-            self.L.matvec(ttype, x, w, out, n, k, m=self.tokens, variant=variant)
+        for i in range(reps):
+            self.L.matvec(ttype, x, ws[i % len(ws)], out, n, k, m=self.tokens, variant=variant, **flags)
         self.ctx.sync()
         return (time.perf_counter() - t0) / reps
 
@@ -60,7 +67,7 @@ class Sweep:
         xs = np.sin(np.arange(self.tokens * k_max, dtype=np.float32) * np.float32(0.7)).astype(np.float32)
         out = self.ctx.zeros(self.tokens * n_max * 4)
         for shape in self.shapes:
-            ttype, w, n, k, reps = shape
+            ttype, _, n, k, reps, _ = shape
             x = self.ctx.put(xs[: self.tokens * k])
             reference, best = None, None
             for variant in self.candidates:
