@@ -763,6 +763,121 @@ class DeltaPrefill:
                           "(C++ restatement of the reference's src/ref recurHead, one head per task)"}
 
 
+class DeltaDecode:
+    """configs[3], recurrent decode: one token of a Gated DeltaNet layer (16 heads of 128, q / k L2-normalised bf16
+    values, v bf16 values, beta = sigmoid(N(0,1)), log-decay = -softplus(N(0,1))) on a seeded f32 state. A step is a
+    CUDA graph over `layers` independent layer states (as many DeltaNet layers of a model, 1 MiB of state each,
+    together above the L2 size), each updated by one delta_rule launch. With N ranks the value heads (and their key
+    heads) are sharded; heads are independent, so no collective."""
+
+    heads, d, layers = 16, 128, 160
+    name = "deltanet_decode"
+    dtype = "f32"
+    scaling = "strong"
+
+    def __init__(self, dist: Dist, batch: int = 1, variant: int = 0, **_):
+        import torch
+
+        from zllm_b200 import abi, synth
+        from zllm_b200 import kernels as K
+
+        self.torch, self.K, self.dist = torch, K, dist
+        self.dev = torch.device("cuda", dist.local)
+        torch.cuda.set_device(self.dev)
+        self.stream = torch.cuda.Stream(self.dev)
+        self.ctx = abi.Context(dist.local, stream=self.stream.cuda_stream)
+        self.launcher = K.Launcher(self.ctx)
+        self.lh = self.heads // dist.world
+        self.cd = 3 * self.lh * self.d
+        gen = torch.Generator(device=self.dev)
+        gen.manual_seed(99 + dist.rank)
+        # the state a 64-token prefix leaves is of order one; a seeded random state of that size stands in per layer
+        self.state = (torch.randn((self.layers, self.lh, self.d, self.d), device=self.dev, generator=gen) * 0.1).float()
+        conv, g, beta = synth.deltanet_inputs(synth.rng_for("cfg4", f"decode-bench{dist.rank}"), self.layers, self.lh, self.lh, self.d)
+        self.pinned_conv = torch.from_numpy(conv).pin_memory()          # one token's q | k | v per layer
+        self.conv = self.pinned_conv.to(self.dev)
+        self.g = torch.from_numpy(g).to(self.dev)
+        self.beta = torch.from_numpy(beta).to(self.dev)
+        self.out = torch.zeros((self.layers, self.lh * self.d), dtype=torch.float32, device=self.dev)
+        self.pinned_out = torch.empty((self.layers, self.lh * self.d), dtype=torch.float32).pin_memory()
+        self.step_buf = torch.tensor([1, 64, 0, 0], dtype=torch.int32, device=self.dev)
+        self.graph = None
+        torch.cuda.synchronize()
+
+    def launches_per_step(self) -> int:
+        return self.layers
+
+    def _buf(self, t):
+        return (t.data_ptr(), t.numel() * t.element_size())
+
+    def step(self):
+        K = self.K
+        if self.graph is None:
+            self.ctx.capture_begin()
+            p = K.DeltaRule(self.lh, self.lh, self.d, self.cd, 1, self.cd, 0)
+            for il in range(self.layers):
+                self.launcher.delta_rule(p, self._buf(self.conv[il]), self._buf(self.g[il]), self._buf(self.beta[il]),
+                                         self._buf(self.state[il]), self._buf(self.out[il]), self._buf(self.step_buf))
+            self.graph = self.ctx.capture_end()
+        self.ctx.graph_launch(self.graph)
+
+    def e2e_step(self):
+        torch = self.torch
+        with torch.cuda.stream(self.stream):
+            self.conv.copy_(self.pinned_conv, non_blocking=True)
+        self.step()
+        with torch.cuda.stream(self.stream):
+            self.pinned_out.copy_(self.out, non_blocking=True)
+        self.stream.synchronize()
+
+    def e2e_bytes(self):
+        return self.pinned_conv.numel() * 4, self.pinned_out.numel() * 4
+
+    def bytes_per_launch(self) -> float:
+        # the state in and out, q | k | v, g, beta in, o out
+        return 2 * 4.0 * self.lh * self.d * self.d + 4.0 * (self.cd + self.lh * self.d + 2 * self.lh)
+
+    def roofline(self, ms_per_step: float):
+        peak, kind = measured_hbm_peak()
+        us = ms_per_step * 1e3 / self.layers
+        achieved = self.bytes_per_launch() / us / 1e3
+        return {"bound": "hbm", "kernel": "delta_rule_kernel (recurrent form, one token)", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                "frac": achieved / peak, "peak_kind": f"of {kind}", "traffic": None, "bytes_per_launch": self.bytes_per_launch(),
+                "us_per_launch": us,
+                "note": "2.1 MB per launch is a third of a microsecond at the roofline: the launch's latency is what is measured"}
+
+    def metric(self):
+        return "deltanet_decode_layer_tokens_per_s", "layer-tokens/s"
+
+    def value(self, seconds_per_step: float) -> float:
+        return self.layers / seconds_per_step
+
+    def config(self):
+        return {"workload": f"Gated DeltaNet recurrent decode, 1 token on a seeded state, {self.heads} heads of {self.d}; "
+                            f"{self.layers} independent layer states per step",
+                "l2": f"inputs larger than L2: {self.layers} states of {self.lh * self.d * self.d * 4 / 1e6:.2f} MB per rank per step",
+                "parallelism": f"value heads sharded over {self.dist.world} ranks, no collective" if self.dist.on else "1 GPU"}
+
+    def cpu_baseline(self, budget_s: float = 10.0):
+        from oracle import ref
+        from zllm_b200 import synth
+
+        ref.build()
+        rng = synth.rng_for("cfg4", "cpu-decode")
+        conv, g, beta = synth.deltanet_inputs(rng, 1, self.heads, self.heads, self.d)
+        state = (rng.normal(size=(self.heads, self.d, self.d)) * 0.1).astype(np.float32)
+        ref.delta_rule(state, conv, g, beta, 1, self.heads, self.heads, self.d)
+        t0, reps = time.perf_counter(), 0
+        while time.perf_counter() - t0 < budget_s and reps < 20000:
+            ref.delta_rule(state, conv, g, beta, 1, self.heads, self.heads, self.d)
+            reps += 1
+        dt = (time.perf_counter() - t0) / reps
+        return {"value": 1.0 / dt, "unit": "layer-tokens/s", "cores": min(ref.default_pool().threads, self.heads), "kind": "port",
+                "isa": ref.build_info(),
+                "sample": f"{reps} single-token updates of one layer's state ({self.heads} heads), {dt * 1e6:.0f} us each "
+                          "(C++ restatement of the reference's src/ref recurHead, one head per task)"}
+
+
 class QuantPrefill:
     """The quantised prefill multiply (the reference's prefill path for K-quant models: quantize_q8 + matmul_q4_k):
     2048 tokens x the Llama-3-8B FFN-up matrix (14336 x 4096, Q4_K); activations f32 ~ N(0,1) rounded to Q8_K blocks
@@ -880,7 +995,7 @@ class QuantPrefill:
 
 
 WORKLOADS = {"matvec_q4_k": MatvecQ4K, "decode": DecodeStep, "prefill_matmul": PrefillMatmul, "deltanet_prefill": DeltaPrefill,
-             "prefill_q4_k": QuantPrefill}
+             "deltanet_decode": DeltaDecode, "prefill_q4_k": QuantPrefill}
 
 
 
@@ -1072,7 +1187,8 @@ def run_reference(args):
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 / value, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": f"decode step, Llama-3-8B-shaped Q4_K model, f16 KV cache at {DecodeStep.context} "
-                                   "positions, batch 1", "batch": 1, "context": DecodeStep.context,
+                                   "positions, batch 1 (extrapolated from sampled layers and one head per step: see cpu_baseline.sample; "
+                                   "the C++ port of the reference's src/ref, not its Zig binary)", "batch": 1, "context": DecodeStep.context,
                        "wall_s": dt},
             "cpu_baseline": base,
             "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -1094,6 +1210,27 @@ def run_reference(args):
             "config": {"workload": f"BF16 prefill matmul, {wl.rows} tokens x {wl.n} x {wl.k} (a 64-token sample per step)"},
             "cpu_baseline": base,
             "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        }), flush=True)
+        return
+    if args.workload in ("deltanet_prefill", "deltanet_decode"):
+        cls = WORKLOADS[args.workload]
+        wl = cls.__new__(cls)  # shapes only; nothing on a GPU
+        vals, base = [], None
+        t0 = time.perf_counter()
+        for i in range(args.warmup + args.steps):
+            base = wl.cpu_baseline(budget_s=3.0)
+            if i >= args.warmup:
+                vals.append(base["value"])
+        value = float(np.mean(vals))
+        base["value"] = value
+        metric, unit = wl.metric()
+        print(json.dumps({
+            "impl": "reference", "metric": metric, "value": value, "unit": unit, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": (time.perf_counter() - t0) / (args.warmup + args.steps) * 1e3,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"Gated DeltaNet, {cls.heads} heads of {cls.d}: " + base["sample"]},
+            "cpu_baseline": base,
+            "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         }), flush=True)
         return
     if args.workload == "prefill_q4_k":

@@ -211,3 +211,80 @@ def test_two_gpus_give_the_single_gpu_logits():
         one, two = np.load(os.path.join(tmp, "one.npy")), np.load(os.path.join(tmp, "two.npy"))
     assert np.isfinite(one).all() and np.abs(one).max() > 0
     assert np.array_equal(one.view(np.uint32), two.view(np.uint32))
+
+
+def _rank_peer_hybrid(rank: int, world: int, port: int, out_dir: str):
+    """A hybrid model (DeltaNet layers sharded by value head, the recurrent states and conv histories per rank)
+    over the library's exchange: consecutive steps of one sequence from an empty state against one GPU."""
+    import torch.distributed as dist
+
+    from zllm_b200 import abi
+    from zllm_b200 import model as M
+    from zllm_b200.plan import HybridConfig, HybridProgram, Shard
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    cfg = HybridConfig(layers=4, hidden=512, heads=8, kv_heads=2, head_dim=64, ff=1024, vocab=1536, max_ctx=192,
+                       gdn_head_dim=64, gdn_k_heads=2, gdn_v_heads=4, conv_kernel=4, attention_every=4)
+    host = M.hybrid_host_model(cfg, "tp-hybrid")
+    ctx = abi.Context(rank)
+
+    def exchange(handle: bytes):
+        got = [None] * world
+        dist.all_gather_object(got, handle)
+        return got
+
+    def build(sh, arena):
+        prog = HybridProgram(ctx, cfg, M.upload_hybrid(host, cfg, ctx.put, sh), 1, ctx.zeros, sh, arena=arena)
+        prog.set_rope_table(ctx.put(HybridProgram.rope_table(cfg)))
+        return prog
+
+    arena = abi.PeerArena(ctx, rank, world, HybridProgram.arena_bytes(cfg, 1), HybridProgram.arena_slots(cfg), exchange)
+    sharded = build(Shard(rank, world), arena)
+    whole = build(Shard(0, 1), None) if rank == 0 else None
+    dist.barrier()
+    graph, got, want = None, [], []
+    for pos, token in enumerate([11, 700, 3, 1500, 42]):
+        tok, ps = np.array([token], dtype=np.uint32), np.array([pos], dtype=np.uint32)
+        sharded.write_step(tok, ps)
+        if graph is None:
+            ctx.sync()
+            ctx.capture_begin()
+            sharded.record_step(cfg.max_ctx)
+            graph = ctx.capture_end()
+        ctx.graph_launch(graph)
+        ctx.sync()
+        got.append(sharded.logits.download(np.float32).copy())
+        if whole is not None:
+            whole.write_step(tok, ps)
+            whole.record_step(cfg.max_ctx)
+            ctx.sync()
+            want.append(whole.logits.download(np.float32).copy())
+        dist.barrier()
+    if rank == 0:
+        np.save(os.path.join(out_dir, "one.npy"), np.stack(want))
+        v0, lv = sharded.v0, sharded.lvh
+        d = cfg.gdn_head_dim
+        np.save(os.path.join(out_dir, "state_one.npy"), whole.state[0].download(np.float32).reshape(-1, d, d)[v0:v0 + lv])
+    np.save(os.path.join(out_dir, f"state{rank}.npy"), sharded.state[0].download(np.float32))
+    np.save(os.path.join(out_dir, f"peer{rank}.npy"), np.stack(got))
+    dist.barrier()
+    os._exit(0)
+
+
+def test_two_gpus_hybrid_with_value_heads_sharded_give_the_single_gpu_logits():
+    import torch
+
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    with tempfile.TemporaryDirectory() as tmp:
+        _spawn(_rank_peer_hybrid, tmp)
+        one = np.load(os.path.join(tmp, "one.npy"))
+        peers = [np.load(os.path.join(tmp, f"peer{r}.npy")) for r in range(2)]
+        state_one, state0 = np.load(os.path.join(tmp, "state_one.npy")), np.load(os.path.join(tmp, "state0.npy"))
+    assert np.isfinite(one).all() and np.abs(one).max() > 0
+    # a head's recurrence, a row's multiply: each on exactly one rank with the same arithmetic
+    assert np.array_equal(state_one.ravel().view(np.uint32), state0.view(np.uint32))
+    for r in range(2):
+        assert np.array_equal(one.view(np.uint32), peers[r].view(np.uint32)), r

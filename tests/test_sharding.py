@@ -229,3 +229,143 @@ def test_batched_family_is_chosen_for_more_than_four_sequences(batch, sharded):
     rope_launches = sum(1 for k, _, _ in seen if k == K.ROPE_APPEND)
     assert rope_launches == (0 if batch in (1, 2, 4) else cfg.layers)
     ctx.close()
+
+
+# ---- the hybrid model: DeltaNet layers sharded by value head
+from zllm_b200.plan import HybridConfig, delta_shard, slice_delta_weights  # noqa: E402
+
+HCFG = HybridConfig(layers=4, hidden=512, heads=8, kv_heads=2, head_dim=64, ff=1024, vocab=1024, max_ctx=64,
+                    gdn_head_dim=64, gdn_k_heads=2, gdn_v_heads=4, conv_kernel=4, attention_every=4)
+
+
+@pytest.mark.parametrize("world", [1, 2, 4])
+def test_value_head_shards_keep_the_key_heads_they_use(world):
+    cfg = HCFG
+    d, hk, hv = cfg.gdn_head_dim, cfg.gdn_k_heads, cfg.gdn_v_heads
+    conv_dim = 2 * hk * d + hv * d
+    rows = conv_dim + hv * d + 2 * hv
+    full = np.arange(rows, dtype=np.int64)[:, None]          # each row holds its own index
+    seen_v = []
+    for rank in range(world):
+        v0, lv, k0, lk = delta_shard(cfg, Shard(rank, world))
+        # local value head j uses local key head j mod lk: the global head it maps to is the one the full model uses
+        assert all((k0 + j % lk) == (v0 + j) % hk for j in range(lv))
+        got = slice_delta_weights(cfg, Shard(rank, world), "wproj", full).ravel()
+        q, k, v = got[:lk * d], got[lk * d:2 * lk * d], got[2 * lk * d:2 * lk * d + lv * d]
+        assert q[0] == k0 * d and k[0] == hk * d + k0 * d and v[0] == 2 * hk * d + v0 * d
+        z = got[2 * lk * d + lv * d:2 * lk * d + 2 * lv * d]
+        assert z[0] == conv_dim + v0 * d and got[-2 * lv] == conv_dim + hv * d + v0 and got[-lv] == conv_dim + hv * d + hv + v0
+        assert slice_delta_weights(cfg, Shard(rank, world), "conv", full[:conv_dim]).shape[0] == 2 * lk * d + lv * d
+        seen_v += list(range(v0, v0 + lv))
+    assert seen_v == list(range(hv))
+
+
+def _delta_layer(ref, cfg, lw_mats, lw, x_rows, hk, hv):
+    """A DeltaNet mixer over consecutive tokens on the oracle, with `hk` key and `hv` value heads: the columns of o."""
+    d, taps = cfg.gdn_head_dim, cfg.conv_kernel
+    cd, inner = 2 * hk * d + hv * d, hv * d
+    n = x_rows.shape[0]
+    h = np.stack([ref.rms_norm(x, lw["attn_norm"], cfg.eps) for x in x_rows])
+    proj = ref.matmul(h, lw_mats["wproj"])
+    conv = ref.conv_norm(proj[:, :cd].copy(), lw_mats["conv"], n, hk, inner, d, taps, cfg.eps)
+    beta = (1 / (1 + np.exp(-proj[:, cd + inner:cd + inner + hv].astype(np.float64)))).astype(np.float32)
+    g = (np.log1p(np.exp(proj[:, cd + inner + hv:].astype(np.float64) + lw_mats["dt_bias"])) * lw_mats["a"]).astype(np.float32)
+    _, o = ref.delta_rule(np.zeros((hv, d, d), dtype=np.float32), conv, g, beta, n, hk, hv, d)
+    return ref.gated_norm(o, proj[:, cd:cd + inner].copy(), lw["norm"], n, hv, d, cfg.eps)
+
+
+def _hybrid_rank_main(rank: int, world: int, port: int, out_path: str):
+    import torch
+    import torch.distributed as dist
+
+    from oracle import ref
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    cfg, sh = HCFG, Shard(rank, world)
+    e = cfg.hidden
+    lw = M.hybrid_host_model(cfg, "hybrid-shard")["layers"][0]
+    x_rows = np.random.default_rng(5).normal(size=(3, e)).astype(np.float32)
+    _, lv, _, lk = delta_shard(cfg, sh)
+    sl = {name: slice_delta_weights(cfg, sh, name, lw[name]) for name in ("wproj", "conv", "dt_bias", "a", "wout")}
+    mats = dict(sl, wproj=ref.Matrix(ref.Q4_K, sl["wproj"], sl["wproj"].shape[0], e))
+    o_local = _delta_layer(ref, cfg, mats, lw, x_rows, lk, lv)            # [tokens, lv * d]
+    parts = [torch.empty(o_local.shape, dtype=torch.float32) for _ in range(world)]
+    dist.all_gather(parts, torch.from_numpy(np.ascontiguousarray(o_local)))
+    o = torch.cat(parts, dim=1).numpy()                                    # exchange: head columns
+    e0, e1 = shard_rows(e, rank, world)
+    x_local = x_rows[:, e0:e1] + ref.matmul(o, ref.Matrix(ref.Q4_K, sl["wout"], e1 - e0, cfg.gdn_inner))
+    parts = [torch.empty(x_local.shape, dtype=torch.float32) for _ in range(world)]
+    dist.all_gather(parts, torch.from_numpy(np.ascontiguousarray(x_local)))
+    if rank == 0:
+        np.save(out_path, torch.cat(parts, dim=1).numpy())
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_gloo_ranks_reproduce_the_unsharded_deltanet_layer(ref):
+    import torch.multiprocessing as mp
+
+    cfg, e = HCFG, HCFG.hidden
+    with tempfile.TemporaryDirectory() as tmp:
+        out_path = os.path.join(tmp, "x.npy")
+        port = 29950 + os.getpid() % 300
+        mp.spawn(_hybrid_rank_main, args=(2, port, out_path), nprocs=2, join=True)
+        got = np.load(out_path)
+    lw = M.hybrid_host_model(cfg, "hybrid-shard")["layers"][0]
+    x_rows = np.random.default_rng(5).normal(size=(3, e)).astype(np.float32)
+    mats = dict(lw, wproj=ref.Matrix(ref.Q4_K, lw["wproj"], lw["wproj"].shape[0], e))
+    o = _delta_layer(ref, cfg, mats, lw, x_rows, cfg.gdn_k_heads, cfg.gdn_v_heads)
+    want = x_rows + ref.matmul(o, ref.Matrix(ref.Q4_K, lw["wout"], e, cfg.gdn_inner))
+    # every head and every output row is computed by exactly one rank with the same arithmetic: same bits
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
+def test_exchange_slots_chain_through_the_sharded_hybrid_launch_list():
+    # DeltaNet layers use the same four exchanges per layer as attention layers: gated_norm pushes the rank's head
+    # columns where attn_combine would, the output projection waits for them.
+    from zllm_b200 import abi
+    from zllm_b200.plan import HybridProgram
+
+    ctx = abi.Context(dry_run=True)
+
+    class FakeArena:
+        def alloc(self, n):
+            return ctx.alloc(n)
+
+    cfg = HCFG
+    names = {True: ("wqkv", "wo"), False: ("wproj", "conv", "dt_bias", "a", "norm", "wout")}
+    weights = {"embed": ctx.alloc(256), "head": ctx.alloc(256), "out_norm": ctx.alloc(256),
+               "layers": [{k: ctx.alloc(256) for k in names[cfg.is_attention(il)] + ("wgu", "wdown", "attn_norm", "ffn_norm")}
+                          for il in range(cfg.layers)]}
+    prog = HybridProgram(ctx, cfg, weights, 1, ctx.alloc, Shard(1, 2), arena=FakeArena())
+    prog.set_rope_table(ctx.alloc(256))
+    assert (prog.lvh, prog.lkh, prog.v0, prog.k0) == (2, 2, 2, 0)
+    assert [c is not None for c in prog.kc] == [False, False, False, True]
+    seen = []
+    real = prog.L.launch
+
+    def spy(kernel, params, args, groups, variant=0):
+        raw = bytes(params)
+        ext = K.PeerExt.from_buffer_copy(raw[-16:]) if len(raw) >= 16 else None
+        seen.append((kernel, (ext.wait_slot, ext.push_slot) if ext is not None and ext.magic == K.PEER_MAGIC else None))
+        real(kernel, params, args, groups, variant)
+
+    prog.L.launch = spy
+    prog.record_step(9)
+    none = K.PEER_NONE
+    assert len(seen) == prog.launches_per_step                  # the host's wait for the logits included
+    i = 1
+    for il in range(cfg.layers):
+        n = 6 if cfg.is_attention(il) else 7
+        ops = seen[i:i + n]
+        i += n
+        assert ops[0][1] == (None if il == 0 else (4 * il - 1, none))
+        if not cfg.is_attention(il):
+            assert [k for k, _ in ops[1:4]] == [K.DELTA_PREP, K.DELTA_RULE, K.GATED_NORM]
+            assert ops[1][1] is None and ops[2][1] is None and ops[3][1] == (none, 4 * il)
+        assert [e for _, e in ops[-3:]] == [(4 * il, 4 * il + 1), (4 * il + 1, 4 * il + 2), (4 * il + 2, 4 * il + 3)]
+    pushed = [e[1] for _, e in seen if e is not None and e[1] != none]
+    assert sorted(pushed) == list(range(HybridProgram.arena_slots(cfg)))
+    ctx.close()

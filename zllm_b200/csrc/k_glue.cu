@@ -103,8 +103,11 @@ __global__ void __launch_bounds__(256) rope_append_kernel(PRopeAppend p, float* 
 
 // ---- gated_norm (src/kernels/gated_norm.wgsl): bindings o (rw), z, w. One
 // CTA per (head, token): o <- rmsnorm(o) * w * silu(z) (or sigmoid(z)).
+// In a tensor-parallel exchange the rank's heads are pushed to every rank (they are columns of the vector the
+// output projection reads whole).
 __global__ void __launch_bounds__(256) gated_norm_kernel(PGatedNorm p, float* __restrict__ o,
-                                                        const float* __restrict__ z, const float* __restrict__ w) {
+                                                        const float* __restrict__ z, const float* __restrict__ w,
+                                                        const __grid_constant__ PeerUse pu) {
     __shared__ double red[32];
     const uint32_t b = threadIdx.x;
     const size_t base = ((size_t)blockIdx.y * p.v_heads + blockIdx.x) * p.dim;
@@ -118,8 +121,11 @@ __global__ void __launch_bounds__(256) gated_norm_kernel(PGatedNorm p, float* __
         const float r = 1.0f / sqrtf(mean + p.eps);
         const float gate = p.sigmoid ? 1.0f / (1.0f + expf(-zz)) : zz / (1.0f + expf(-zz));
         // rmsNorm then the gate (src/ref/qwen35.zig:543-545): ((v * r) * w) * gate
-        o[base + b] = __fmul_rn(__fmul_rn(__fmul_rn(v, r), w[b]), gate);
+        const float res = __fmul_rn(__fmul_rn(__fmul_rn(v, r), w[b]), gate);
+        o[base + b] = res;
+        if (pu.push_slot != PEER_NONE) peer::push(pu, o + base + b, res, peer::push_tag(pu));
     }
+    peer::finish(pu, gridDim.x * gridDim.y);
 }
 
 // ---- delta_prep (src/kernels/delta_prep.wgsl): bindings proj, conv_w, hist,
@@ -256,7 +262,13 @@ zcu_result launch_gated_norm(const LaunchArgs& a) {
     ZCU_NEED(a, p.dim <= 256, "gated_norm: dim %u", p.dim);
     const uint32_t m = a.grid[1];
     if (m == 0 || p.v_heads == 0) return ZCU_OK;
-    gated_norm_kernel<<<dim3(p.v_heads, m), 256, 0, a.stream>>>(p, (float*)a.b[0].ptr, (const float*)a.b[1].ptr, (const float*)a.b[2].ptr);
+    PeerUse pu;
+    {
+        const float* lo = (const float*)a.b[0].ptr;
+        zcu_result pr = parse_peer(a, pu, lo, lo + (size_t)m * p.v_heads * p.dim);
+        if (pr != ZCU_OK) return pr;
+    }
+    gated_norm_kernel<<<dim3(p.v_heads, m), 256, 0, a.stream>>>(p, (float*)a.b[0].ptr, (const float*)a.b[1].ptr, (const float*)a.b[2].ptr, pu);
     ZCU_CHECK_LAUNCH(a);
     return ZCU_OK;
 }

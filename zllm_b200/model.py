@@ -185,3 +185,48 @@ def device_shard(full, cfg: DenseConfig, torch, shard: Shard | None = None):
         layers.append({"wqkv": own(qkv), "wo": own(lw["wo"][e0:e1]), "wgu": own(gu), "wdown": own(lw["wdown"][e0:e1]),
                        "attn_norm": own(lw["attn_norm"]), "ffn_norm": own(lw["ffn_norm"])})
     return {"layers": layers, "embed": own(full["embed"]), "head": own(full["head"][v0:v1]), "out_norm": own(full["out_norm"])}, keep
+
+
+def hybrid_host_model(cfg, seed: str = "hybrid"):
+    """The full (unsharded) hybrid model on the host: attention layers as host_model's, DeltaNet layers with the
+    stacked input projection wproj (rows q | k | v | z | beta | alpha, src/plan/qwen35.zig:556-566), the conv taps
+    [channel][tap], dt_bias, a (negative), the gated norm's weight and the output projection."""
+    d, hk, hv, taps, e = cfg.gdn_head_dim, cfg.gdn_k_heads, cfg.gdn_v_heads, cfg.conv_kernel, cfg.hidden
+    conv_dim = 2 * hk * d + hv * d
+    base = host_model(cfg, seed)
+    for il in range(cfg.layers):
+        if cfg.is_attention(il):
+            continue
+        r = lambda name: synth.rng_for(seed, f"l{il}.{name}")  # noqa: E731
+        lw = base["layers"][il]
+        for k in ("wqkv", "wo"):
+            del lw[k]
+        lw["wproj"] = _quant(r("wproj"), cfg.body_type, conv_dim + hv * d + 2 * hv, e)
+        lw["conv"] = (r("conv").uniform(-0.5, 0.5, size=(conv_dim, taps))).astype(np.float32)
+        lw["dt_bias"] = r("dt_bias").uniform(-0.5, 0.5, size=hv).astype(np.float32)
+        lw["a"] = (-np.abs(r("a").uniform(0.05, 1.0, size=hv))).astype(np.float32)
+        lw["norm"] = (1 + 0.1 * r("norm").normal(size=d)).astype(np.float32)
+        lw["wout"] = _quant(r("wout"), cfg.body_type, e, hv * d)
+    return base
+
+
+def upload_hybrid(host, cfg, put, shard: Shard | None = None):
+    """Device weights of one rank from a hybrid host model."""
+    from .plan import slice_delta_weights
+
+    sh = shard or Shard()
+    layers = []
+    for il, lw in enumerate(host["layers"]):
+        d = {"attn_norm": put(lw["attn_norm"]), "ffn_norm": put(lw["ffn_norm"]),
+             "wgu": put(slice_full_weights(cfg, sh, "wgu", lw["wgu"])), "wdown": put(slice_full_weights(cfg, sh, "wdown", lw["wdown"]))}
+        if cfg.is_attention(il):
+            d["wqkv"] = put(slice_full_weights(cfg, sh, "wqkv", lw["wqkv"]))
+            d["wo"] = put(slice_full_weights(cfg, sh, "wo", lw["wo"]))
+        else:
+            for name in ("wproj", "conv", "dt_bias", "a", "wout"):
+                d[name] = put(np.ascontiguousarray(slice_delta_weights(cfg, sh, name, lw[name])))
+            d["norm"] = put(lw["norm"])
+        layers.append(d)
+    head = host["head"] if cfg.head_type != "q8_0" else split_q8_0_rows(slice_full_weights(cfg, sh, "head", host["head"]), cfg.hidden)
+    return {"layers": layers, "embed": put(host["embed"]), "head": put(head), "out_norm": put(host["out_norm"])}
+

@@ -165,10 +165,13 @@ class DenseProgram:
         self.max_blocks = -(-cfg.max_ctx // K.ATTN_BLOCK)
         self.part = alloc(B * self.lh * self.max_blocks * (hd + 2) * f4)
         self.seq_stride = cfg.max_ctx * self.lg * hd          # cache elements per sequence
-        self.kc = [alloc(B * self.seq_stride * 2) for _ in range(cfg.layers)]
-        self.vc = [alloc(B * self.seq_stride * 2) for _ in range(cfg.layers)]
+        self.kc = [alloc(B * self.seq_stride * 2) if self._has_cache(il) else None for il in range(cfg.layers)]
+        self.vc = [alloc(B * self.seq_stride * 2) if self._has_cache(il) else None for il in range(cfg.layers)]
         self.dummy = alloc(256)
         self.rope = None
+
+    def _has_cache(self, il: int) -> bool:
+        return True
 
     # ---- host-built tables and per-step state
     def set_rope_table(self, table_buf):
@@ -203,19 +206,23 @@ class DenseProgram:
         weights that come from HBM). Takes the table for the launches recorded from now on and returns it."""
         from . import tune
 
-        cfg, e = self.cfg, self.cfg.hidden
-        layers = self.w["layers"]
         s = tune.Sweep(self.ctx, tokens=min(tokens or self.B, 4))
-        s.add(cfg.body_type, [lw["wqkv"] for lw in layers], self.qkv_row, e, flags=K.NORM, eps=cfg.eps, norm_w=layers[0]["attn_norm"])
-        s.add(cfg.body_type, [lw["wo"] for lw in layers], self.le, cfg.q_dim)
-        s.add(cfg.body_type, [lw["wgu"] for lw in layers], self.lff, e, flags=K.NORM | K.SILU_PAIR, eps=cfg.eps, half=self.lff,
-              norm_w=layers[0]["ffn_norm"])
-        s.add(cfg.body_type, [lw["wdown"] for lw in layers], self.le, cfg.ff)
-        s.add(cfg.head_type, self.w["head"], self.lv, e, flags=K.NORM, eps=cfg.eps, norm_w=self.w["out_norm"])
+        self._sweep_shapes(s)
         table = s.run()
         self.variants = {**self.variants, **table}
         self.sweep_report = s.report
         return table
+
+    def _sweep_shapes(self, s):
+        cfg, e = self.cfg, self.cfg.hidden
+        layers = self.w["layers"]
+        att = [lw for lw in layers if "wqkv" in lw]
+        s.add(cfg.body_type, [lw["wqkv"] for lw in att], self.qkv_row, e, flags=K.NORM, eps=cfg.eps, norm_w=att[0]["attn_norm"])
+        s.add(cfg.body_type, [lw["wo"] for lw in att], self.le, cfg.q_dim)
+        s.add(cfg.body_type, [lw["wgu"] for lw in layers], self.lff, e, flags=K.NORM | K.SILU_PAIR, eps=cfg.eps, half=self.lff,
+              norm_w=layers[0]["ffn_norm"])
+        s.add(cfg.body_type, [lw["wdown"] for lw in layers], self.le, cfg.ff)
+        s.add(cfg.head_type, self.w["head"], self.lv, e, flags=K.NORM, eps=cfg.eps, norm_w=self.w["out_norm"])
 
     def _gather(self, buf, width):
         if self.gather is not None:
@@ -233,64 +240,80 @@ class DenseProgram:
     def record_step(self, max_keys: int):
         """Issues the step's launches on the context's stream (inside a graph capture they are captured).
         `max_keys`: the largest position + 1 of the batch (sizes the attention grid)."""
-        cfg, B, hd, sh = self.cfg, self.B, self.cfg.head_dim, self.sh
-        e = cfg.hidden
+        cfg, B, e = self.cfg, self.B, self.cfg.hidden
         self.launches_per_step = 0
+        self._max_keys = max_keys
         # embedding rows of the step's tokens (replicated on every rank)
         self.L.embed(cfg.embed_type, self.tokens, self.w["embed"], self.x, B, e, 0, cfg.vocab)
         self.launches_per_step += 1
+        for il in range(cfg.layers):
+            self._mixer(il)
+            self._ffn(il)
+        self._head()
+
+    def _slots(self, il):
+        """The layer's four exchanges (mixer output, x after the mixer's output projection, the FFN activations, x
+        after down) and the one its input x arrived under."""
+        if self.arena is None:
+            return (None,) * 5
+        return 4 * il, 4 * il + 1, 4 * il + 2, 4 * il + 3, ((4 * il - 1) if il > 0 else None)
+
+    def _mixer(self, il):
+        """Attention: the reference's LayerBuilder.attention (src/plan/qwen35.zig:989-1036)."""
+        cfg, B, hd, sh, e = self.cfg, self.B, self.cfg.head_dim, self.sh, self.cfg.hidden
+        lw = self.w["layers"][il]
+        s_att, s_xwo, _, _, s_prev = self._slots(il)
         rp = K.RopeAppend(self.lh, self.lg, hd, hd, self.qkv_row, self.lh * hd, (self.lh + self.lg) * hd, K.KV_F16,
                           cfg.eps, 0, 0, 1, 0)
         rp._pad[0] = self.seq_stride
         ap = K.Attention(self.lh, self.lg, hd, K.KV_F16, K.attention_scale(hd), self.max_blocks, self.qkv_row, 0, 0, 0)
         ap._pad[0] = self.seq_stride
         ap._pad[1] = cfg.q_dim                                  # att rows are full width on every rank
-        blocks = -(-max_keys // K.ATTN_BLOCK)
+        blocks = -(-self._max_keys // K.ATTN_BLOCK)
         att_cols = self.att.at(self.h0 * hd * 4)                # this rank's head columns of att
-        peer = self.arena is not None
-        def qkv(il):
-            # 1. fused attn_norm + Q|K|V projection (local heads); 2. RoPE (normal pairs) and the cache append at
-            #    each sequence's position, in the multiply's epilogue or as rope_append's own launch
-            lw = self.w["layers"][il]
-            s_prev = (4 * il - 1) if (peer and il > 0) else None  # the x this layer starts from
-            if self.fuse_rope:
-                self._matvec(cfg.body_type, self.x, lw["wqkv"], self.qkv, self.qkv_row, e, flags=K.NORM, eps=cfg.eps,
-                             norm_w=lw["attn_norm"], rope=(rp, [self.rope, self.kc[il], self.vc[il], self.step, self.positions]),
-                             wait=s_prev)
-            else:
-                self._matvec(cfg.body_type, self.x, lw["wqkv"], self.qkv, self.qkv_row, e, flags=K.NORM, eps=cfg.eps,
-                             norm_w=lw["attn_norm"], wait=s_prev)
-                self.L.launch(K.ROPE_APPEND, rp, [self.qkv, self.dummy, self.dummy, self.rope, self.kc[il], self.vc[il],
-                                                  self.step, self.positions], (self.lh + self.lg, B, 1))
-                self.launches_per_step += 1
+        # 1. fused attn_norm + Q|K|V projection (local heads); 2. RoPE (normal pairs) and the cache append at
+        #    each sequence's position, in the multiply's epilogue or as rope_append's own launch
+        if self.fuse_rope:
+            self._matvec(cfg.body_type, self.x, lw["wqkv"], self.qkv, self.qkv_row, e, flags=K.NORM, eps=cfg.eps,
+                         norm_w=lw["attn_norm"], rope=(rp, [self.rope, self.kc[il], self.vc[il], self.step, self.positions]),
+                         wait=s_prev)
+        else:
+            self._matvec(cfg.body_type, self.x, lw["wqkv"], self.qkv, self.qkv_row, e, flags=K.NORM, eps=cfg.eps,
+                         norm_w=lw["attn_norm"], wait=s_prev)
+            self.L.launch(K.ROPE_APPEND, rp, [self.qkv, self.dummy, self.dummy, self.rope, self.kc[il], self.vc[il],
+                                              self.step, self.positions], (self.lh + self.lg, B, 1))
+            self.launches_per_step += 1
+        # 3-4. split attention over each sequence's cache, merged into this rank's head columns of att
+        self.L.launch(K.ATTN_SPLIT, ap, [self.qkv, self.kc[il], self.vc[il], self.part, self.step, self.positions],
+                      (self.lg, blocks, B), self.variants.get("attn_split", 0))
+        self.L.launch(K.ATTN_COMBINE, K.with_peer(ap, push=s_att), [self.qkv, self.part, att_cols, self.step, self.positions],
+                      (self.lh, B, 1))
+        self.launches_per_step += 2
+        self._gather(self.att, cfg.q_dim)
+        # 5. Wo rows of this rank, accumulated into the residual stream's slice
+        self._matvec(cfg.body_type, self.att, lw["wo"], self.x, self.le, cfg.q_dim, col0=sh.rank * self.le,
+                     out_stride=e, flags=K.ACCUMULATE, wait=s_att, push=s_xwo)
+        self._gather(self.x, e)
 
-        qkv(0)
-        for il in range(cfg.layers):
-            lw = self.w["layers"][il]
-            s_att, s_xwo, s_act, s_xdown = (4 * il, 4 * il + 1, 4 * il + 2, 4 * il + 3) if peer else (None,) * 4
-            # 3-4. split attention over each sequence's cache, merged into this rank's head columns of att
-            self.L.launch(K.ATTN_SPLIT, ap, [self.qkv, self.kc[il], self.vc[il], self.part, self.step, self.positions],
-                          (self.lg, blocks, B), self.variants.get("attn_split", 0))
-            self.L.launch(K.ATTN_COMBINE, K.with_peer(ap, push=s_att), [self.qkv, self.part, att_cols, self.step, self.positions],
-                          (self.lh, B, 1))
-            self.launches_per_step += 2
-            self._gather(self.att, cfg.q_dim)
-            # 5. Wo rows of this rank, accumulated into the residual stream's slice
-            self._matvec(cfg.body_type, self.att, lw["wo"], self.x, self.le, cfg.q_dim, col0=sh.rank * self.le,
-                         out_stride=e, flags=K.ACCUMULATE, wait=s_att, push=s_xwo)
-            self._gather(self.x, e)
-            # 6. fused ffn_norm + gate|up + SwiGLU (local ff rows)
-            self._matvec(cfg.body_type, self.x, lw["wgu"], self.act, self.lff, e, col0=sh.rank * self.lff,
-                         out_stride=cfg.ff, flags=K.NORM | K.SILU_PAIR, eps=cfg.eps, half=self.lff,
-                         norm_w=lw["ffn_norm"], wait=s_xwo, push=s_act)
-            self._gather(self.act, cfg.ff)
-            # 7. Wdown rows of this rank, accumulated
-            self._matvec(cfg.body_type, self.act, lw["wdown"], self.x, self.le, cfg.ff, col0=sh.rank * self.le,
-                         out_stride=e, flags=K.ACCUMULATE, wait=s_act, push=s_xdown)
-            self._gather(self.x, e)
-            if il + 1 < cfg.layers:
-                qkv(il + 1)
-        # output norm fused into the LM head
+    def _ffn(self, il):
+        """LayerBuilder.ffn (src/plan/qwen35.zig:1039-1052)."""
+        cfg, sh, e = self.cfg, self.sh, self.cfg.hidden
+        lw = self.w["layers"][il]
+        _, s_xwo, s_act, s_xdown, _ = self._slots(il)
+        # 6. fused ffn_norm + gate|up + SwiGLU (local ff rows)
+        self._matvec(cfg.body_type, self.x, lw["wgu"], self.act, self.lff, e, col0=sh.rank * self.lff,
+                     out_stride=cfg.ff, flags=K.NORM | K.SILU_PAIR, eps=cfg.eps, half=self.lff,
+                     norm_w=lw["ffn_norm"], wait=s_xwo, push=s_act)
+        self._gather(self.act, cfg.ff)
+        # 7. Wdown rows of this rank, accumulated
+        self._matvec(cfg.body_type, self.act, lw["wdown"], self.x, self.le, cfg.ff, col0=sh.rank * self.le,
+                     out_stride=e, flags=K.ACCUMULATE, wait=s_act, push=s_xdown)
+        self._gather(self.x, e)
+
+    def _head(self):
+        """The output norm fused into the LM head (src/plan/qwen35.zig:609)."""
+        cfg, sh, e = self.cfg, self.sh, self.cfg.hidden
+        peer = self.arena is not None
         s_logits = 4 * cfg.layers if peer else None
         self._matvec(cfg.head_type, self.x, self.w["head"], self.logits, self.lv, e, col0=sh.rank * self.lv,
                      out_stride=cfg.vocab, flags=K.NORM, eps=cfg.eps, norm_w=self.w["out_norm"],
@@ -308,3 +331,119 @@ class DenseProgram:
         head = self.lv * K.row_bytes(cfg.head_type, cfg.hidden)
         kv = sum(2 * (int(p) + 1) * self.lg * cfg.head_dim * 2 for p in positions) * cfg.layers
         return {"weights": body + head, "kv": kv, "total": body + head + kv}
+
+
+@dataclass
+class HybridConfig(DenseConfig):
+    """A Qwen 3.5-style hybrid: Gated DeltaNet layers with a full-attention layer every `attention_every` layers
+    (src/graph/qwen35.zig:21-56). DeltaNet: `gdn_v_heads` value heads over `gdn_k_heads` key heads (value head j
+    uses key head j mod k_heads) of `gdn_head_dim`, a causal depthwise conv of `conv_kernel` taps."""
+    gdn_head_dim: int = 128
+    gdn_k_heads: int = 16
+    gdn_v_heads: int = 16
+    conv_kernel: int = 4
+    attention_every: int = 4
+
+    def is_attention(self, il: int) -> bool:
+        return (il + 1) % self.attention_every == 0
+
+    @property
+    def gdn_inner(self):
+        return self.gdn_v_heads * self.gdn_head_dim
+
+
+def delta_shard(cfg: HybridConfig, sh: Shard):
+    """(first value head, value heads, first key head, key heads) a rank holds: value heads are cut into contiguous
+    equal parts; a rank keeps the key heads its value heads use (j mod k_heads: a contiguous run)."""
+    v0, v1 = shard_rows(cfg.gdn_v_heads, sh.rank, sh.world)
+    lv = v1 - v0
+    lk = min(lv, cfg.gdn_k_heads)
+    k0 = v0 % cfg.gdn_k_heads
+    assert lv % lk == 0 and k0 + lk <= cfg.gdn_k_heads and cfg.gdn_v_heads % cfg.gdn_k_heads == 0, (v0, lv, k0, lk)
+    return v0, lv, k0, lk
+
+
+def slice_delta_weights(cfg: HybridConfig, sh: Shard, name: str, full: np.ndarray) -> np.ndarray:
+    """A rank's rows of a DeltaNet layer's full matrices / vectors (model.hybrid_host_model's names)."""
+    d, hk, hv = cfg.gdn_head_dim, cfg.gdn_k_heads, cfg.gdn_v_heads
+    v0, lv, k0, lk = delta_shard(cfg, sh)
+    key, inner = hk * d, hv * d
+    if name in ("wproj", "conv"):
+        # rows (channels): q heads | k heads | v heads [| z heads | beta | alpha]
+        parts = [full[k0 * d:(k0 + lk) * d], full[key + k0 * d:key + (k0 + lk) * d], full[2 * key + v0 * d:2 * key + (v0 + lv) * d]]
+        if name == "wproj":
+            z0 = 2 * key + inner
+            parts += [full[z0 + v0 * d:z0 + (v0 + lv) * d], full[z0 + inner + v0:z0 + inner + v0 + lv],
+                      full[z0 + inner + hv + v0:z0 + inner + hv + v0 + lv]]
+        return np.concatenate(parts)
+    if name in ("dt_bias", "a"):
+        return full[v0:v0 + lv]
+    if name == "wout":
+        e0, e1 = shard_rows(cfg.hidden, sh.rank, sh.world)
+        return full[e0:e1]
+    raise KeyError(name)
+
+
+class HybridProgram(DenseProgram):
+    """The decode step of a hybrid model for ONE sequence (the DeltaNet kernels take a step's rows as consecutive
+    tokens of one sequence, as the reference does): attention layers as in DenseProgram, DeltaNet layers as the
+    reference's plan builds them (src/plan/qwen35.zig:556-599):
+        proj = matvec(x, wproj, NORM)   rows q | k | v | z | beta | alpha of the rank's heads
+        delta_prep -> delta_rule -> gated_norm     (conv history and state per layer; o = the rank's head columns)
+        x += matvec(o, wout)            the output projection reads o whole: one exchange, like attention's
+    then the FFN. With W ranks the value heads are sharded (delta_shard), so is every state.
+    A DeltaNet layer's weights: {"wproj", "conv", "dt_bias", "a", "norm", "wout", "attn_norm", "ffn_norm", "wgu", "wdown"}."""
+
+    def __init__(self, ctx, cfg: HybridConfig, weights, batch: int, alloc, shard: Shard | None = None, **kw):
+        assert batch == 1, "a hybrid step is one sequence"
+        super().__init__(ctx, cfg, weights, batch, alloc, shard, **kw)
+        d, taps = cfg.gdn_head_dim, cfg.conv_kernel
+        self.v0, self.lvh, self.k0, self.lkh = delta_shard(cfg, self.sh)
+        self.conv_dim = 2 * self.lkh * d + self.lvh * d
+        self.proj_row = self.conv_dim + self.lvh * d + 2 * self.lvh
+        shared = self.arena.alloc if self.arena is not None else alloc
+        self.proj = alloc(self.proj_row * 4)
+        self.conv = alloc(self.conv_dim * 4)
+        self.g, self.beta = alloc(max(256, self.lvh * 4)), alloc(max(256, self.lvh * 4))
+        self.o = shared(cfg.gdn_inner * 4)                                # full width: head columns are exchanged
+        self.state = {il: alloc(self.lvh * d * d * 4) for il in range(cfg.layers) if not cfg.is_attention(il)}
+        self.hist = {il: alloc((taps - 1) * self.conv_dim * 4) for il in range(cfg.layers) if not cfg.is_attention(il)}
+
+    def _has_cache(self, il: int) -> bool:
+        return self.cfg.is_attention(il)
+
+    def _sweep_shapes(self, s):
+        super()._sweep_shapes(s)
+        cfg = self.cfg
+        delta = [lw for lw in self.w["layers"] if "wproj" in lw]
+        s.add(cfg.body_type, [lw["wproj"] for lw in delta], self.proj_row, cfg.hidden, flags=K.NORM, eps=cfg.eps, norm_w=delta[0]["attn_norm"])
+        s.add(cfg.body_type, [lw["wout"] for lw in delta], self.le, cfg.gdn_inner)
+
+    @staticmethod
+    def arena_bytes(cfg, batch: int) -> int:
+        return DenseProgram.arena_bytes(cfg, batch) + ((batch * cfg.gdn_inner * 4 + 255) & ~255)
+
+    def _mixer(self, il):
+        cfg = self.cfg
+        if cfg.is_attention(il):
+            return super()._mixer(il)
+        sh, e, d = self.sh, cfg.hidden, cfg.gdn_head_dim
+        lw = self.w["layers"][il]
+        s_o, s_xwo, _, _, s_prev = self._slots(il)
+        self._matvec(cfg.body_type, self.x, lw["wproj"], self.proj, self.proj_row, e, flags=K.NORM, eps=cfg.eps,
+                     norm_w=lw["attn_norm"], wait=s_prev)
+        inner = self.lvh * d
+        pp = K.DeltaPrep(self.conv_dim, cfg.conv_kernel, 2 * self.lkh * d, d, self.proj_row, self.lvh, self.conv_dim + inner,
+                         self.conv_dim + inner + self.lvh, cfg.eps)
+        self.L.delta_prep(pp, self.proj, lw["conv"], self.hist[il], self.conv, lw["dt_bias"], lw["a"], self.g, self.beta, 1)
+        o_cols = self.o.at(self.v0 * d * 4)                               # this rank's head columns of o
+        pr = K.DeltaRule(self.lkh, self.lvh, d, self.conv_dim, cfg.conv_kernel, self.proj_row, 0)
+        self.L.delta_rule(pr, self.conv, self.g, self.beta, self.state[il], o_cols, self.step, self.proj, self.hist[il], self.dummy)
+        gn = K.GatedNorm(self.lvh, d, cfg.eps, self.proj_row, self.conv_dim, 0)
+        self.L.launch(K.GATED_NORM, K.with_peer(gn, push=s_o), [o_cols, self.proj, lw["norm"]], (self.lvh, 1, 1))
+        self.launches_per_step += 3
+        self._gather(self.o, cfg.gdn_inner)
+        self._matvec(cfg.body_type, self.o, lw["wout"], self.x, self.le, cfg.gdn_inner, col0=sh.rank * self.le, out_stride=e,
+                     flags=K.ACCUMULATE, wait=s_o, push=s_xwo)
+        self._gather(self.x, e)
+
