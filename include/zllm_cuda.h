@@ -105,6 +105,8 @@ enum {
 /* delta_rule in its chunked form (64-token chunks, the remainder by the recurrent kernel). No reference
  * counterpart: the reference runs every token serially. DeltaRule._pad must hold the step's token count. */
 #define ZCU_VARIANT_DELTA_CHUNK64 0xfffd0000u
+/* the same chunked form in f32 on the CUDA cores (the default runs its contractions on the tensor cores) */
+#define ZCU_VARIANT_DELTA_CHUNK64_F32 0xfffd0001u
 
 typedef struct zcu_options {
     uint32_t abi_version;  /* ZCU_ABI_VERSION */

@@ -144,7 +144,7 @@ __global__ void __launch_bounds__(DR_THREADS) delta_rule_kernel(PDeltaRule p, co
 // proj/hist/kept may be absent (fewer bindings): the history is then left alone,
 // which is what a caller that supplies q, k, v directly wants.
 zcu_result launch_delta_rule(const LaunchArgs& a) {
-    if (a.variant == ZCU_VARIANT_DELTA_CHUNK64) return launch_delta_chunked(a);
+    if (a.variant == ZCU_VARIANT_DELTA_CHUNK64 || a.variant == ZCU_VARIANT_DELTA_CHUNK64_F32) return launch_delta_chunked(a);
     return launch_delta_recurrent(a, 0, 0xffffffffu);
 }
 

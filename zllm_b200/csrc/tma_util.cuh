@@ -46,4 +46,15 @@ inline bool bytes_3d_swizzled(CUtensorMap* map, const void* base, uint64_t seqs,
                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// [rows][64] bf16 (rows of 128 bytes), boxes of box_rows whole rows, 128-byte swizzle: the K-major operand tiles of
+// the tensor cores. Rows past the end read as zero.
+inline bool bf16_rows64_sw128(CUtensorMap* map, const void* base, uint64_t rows, uint32_t box_rows) {
+    EncodeTiledFn enc = encode_tiled();
+    if (!enc) return false;
+    const cuuint64_t dims[2] = {64, rows}, strides[1] = {128};
+    const cuuint32_t box[2] = {64, box_rows}, elem[2] = {1, 1};
+    return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 }  // namespace tma

@@ -136,6 +136,7 @@ VARIANT_PREFILL_TC = 0xFFFC0000
 X_HALF, OUT_HALF = 1, 2
 # delta_rule in 64-token chunks; DeltaRule._pad carries the step's token count.
 VARIANT_DELTA_CHUNK64 = 0xFFFD0000
+VARIANT_DELTA_CHUNK64_F32 = 0xFFFD0001   # the same form in f32 on the CUDA cores
 
 
 # The tensor-parallel exchange a dispatch takes part in (zcu_peer_ext): appended to its parameter block.
@@ -235,7 +236,8 @@ class Launcher:
     def attn_combine(self, p: "Attention", qg, part, out, step, rows):
         self.launch(ATTN_COMBINE, p, [qg, part, out, step], (p.heads, rows, 1))
 
-    def delta_rule(self, p: "DeltaRule", conv, g, beta, state, out, step, proj=None, hist=None, kept=None, chunked_tokens=None):
+    def delta_rule(self, p: "DeltaRule", conv, g, beta, state, out, step, proj=None, hist=None, kept=None, chunked_tokens=None,
+                   chunk_variant=VARIANT_DELTA_CHUNK64):
         """The gated delta rule over a step. `chunked_tokens` = the step's token count selects the chunked form
         (64-token chunks, the remainder by the recurrent kernel; dim 128 only), which has no reference counterpart."""
         args = [conv, g, beta, state, out, step]
@@ -244,7 +246,7 @@ class Launcher:
         variant = 0
         if chunked_tokens is not None:
             p._pad = int(chunked_tokens)
-            variant = VARIANT_DELTA_CHUNK64
+            variant = chunk_variant
         self.launch(DELTA_RULE, p, args, (p.v_heads, -(-p.dim // 32), 1), variant)
 
     def delta_prep(self, p: "DeltaPrep", proj, conv_w, hist, out, dt_bias, a, g, beta, m):
