@@ -669,6 +669,7 @@ class DeltaPrefill:
         self.ctx = abi.Context(dist.local, stream=self.stream.cuda_stream)
         self.launcher = K.Launcher(self.ctx)
         self.recurrent = variant == 1                     # --variant 1: the serial kernel, for comparison
+        self.f32_form = variant == 2                      # --variant 2: the chunked form in f32 on the CUDA cores
         self.lh = self.heads // dist.world
         self.sets = 2                                     # two input sets alternate: 2 x 133 MB > the 126 MB L2
         self.cd = 3 * self.lh * self.d
@@ -700,7 +701,8 @@ class DeltaPrefill:
         p = K.DeltaRule(self.lh, self.lh, self.d, self.cd, 1, self.cd, 0)
         self.launcher.delta_rule(p, self._buf(self.dconv[i]), self._buf(self.g[i]), self._buf(self.beta[i]), self._buf(self.state),
                                  self._buf(self.out[i]), self._buf(self.step_buf),
-                                 chunked_tokens=None if self.recurrent else self.tokens)
+                                 chunked_tokens=None if self.recurrent else self.tokens,
+                                 chunk_variant=K.VARIANT_DELTA_CHUNK64_F32 if self.f32_form else K.VARIANT_DELTA_CHUNK64)
 
     def e2e_step(self):
         torch, i = self.torch, self.turn % self.sets
@@ -725,10 +727,12 @@ class DeltaPrefill:
     def roofline(self, ms_per_step: float):
         peak, kind = measured_hbm_peak()
         achieved = self.bytes_per_step() / (ms_per_step * 1e-3) / 1e9
-        return {"bound": "hbm", "kernel": "delta_chunk_scan + delta_chunk_prep" if not self.recurrent else "delta_rule_kernel",
+        kernel = "delta_rule_kernel" if self.recurrent else ("delta_chunk_scan + delta_chunk_prep (f32, CUDA cores)" if self.f32_form
+                                                           else "delta_chunk_scan_tc (tcgen05, bf16 x 2 terms) + delta_chunk_prep_tc")
+        return {"bound": "hbm", "kernel": kernel,
                 "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": f"of {kind}",
                 "traffic": None, "bytes_per_launch": self.bytes_per_step(),
-                "f32_tflops": self.flops_per_step() / (ms_per_step * 1e-3) / 1e12,
+                "algorithmic_tflops": self.flops_per_step() / (ms_per_step * 1e-3) / 1e12,
                 "us_per_chunk_step": ms_per_step * 1e3 / (self.tokens / 64),
                 "note": "neither roofline binds: a head's 64 chunks are a serial chain; the chunk step's latency is the figure to lower"}
 
@@ -740,7 +744,8 @@ class DeltaPrefill:
 
     def config(self):
         return {"workload": f"Gated DeltaNet layer prefill, batch 1, {self.tokens} tokens, {self.heads} heads of {self.d}, "
-                            + ("recurrent form" if self.recurrent else "chunked form (chunk 64)"),
+                            + ("recurrent form" if self.recurrent else "chunked form (chunk 64), f32 on the CUDA cores" if self.f32_form
+                               else "chunked form (chunk 64) on the tensor cores"),
                 "l2": f"inputs larger than L2: {self.sets} input sets alternate, {self.bytes_per_step() / 1e6:.0f} MB each",
                 "parallelism": f"heads sharded over {self.dist.world} ranks, no collective" if self.dist.on else "1 GPU"}
 
