@@ -74,6 +74,9 @@ enum {
     ZCU_K_DELTA_PREP = 18,
     ZCU_K_DELTA_RULE = 19,
     ZCU_K_GATED_NORM = 20,
+    ZCU_K_MARK_TOKENS = 21,
+    ZCU_K_SAMPLE = 22,
+    ZCU_K_DRAFT = 23,
     ZCU_K_REPACK_Q8_0 = 38,
     ZCU_K_QUANTIZE_Q8 = 39,
     ZCU_K_MATVEC_Q8_0 = 40,

@@ -269,6 +269,9 @@ zcu_result dispatch_kernel(zcu_context* c, uint32_t kernel, uint32_t variant, co
         case ZCU_K_ATTN_COMBINE: return launch_attn_combine(a);
         case ZCU_K_DELTA_PREP: return launch_delta_prep(a);
         case ZCU_K_DELTA_RULE: return launch_delta_rule(a);
+        case ZCU_K_MARK_TOKENS: return launch_mark_tokens(a);
+        case ZCU_K_SAMPLE: return launch_sample(a);
+        case ZCU_K_DRAFT: return launch_draft(a);
         case ZCU_K_EXT_PEER_WAIT: return launch_peer_wait(a);
         case ZCU_K_QUANTIZE_Q8: return launch_quantize_q8(a);
         case ZCU_K_MATMUL_Q4_K: return variant == ZCU_VARIANT_PREFILL_BF16_TC ? launch_matmul_q4_k_tc(a) : launch_matmul_q4_k(a);
@@ -680,6 +683,9 @@ const char* kernel_name(uint32_t k) {
         case ZCU_K_ATTN_COMBINE: return "attn_combine";
         case ZCU_K_DELTA_PREP: return "delta_prep";
         case ZCU_K_DELTA_RULE: return "delta_rule";
+        case ZCU_K_MARK_TOKENS: return "mark_tokens";
+        case ZCU_K_SAMPLE: return "sample";
+        case ZCU_K_DRAFT: return "draft";
         case ZCU_K_EXT_PEER_WAIT: return "ext_peer_wait";
         case ZCU_K_GATED_NORM: return "gated_norm";
         case ZCU_K_REPACK_Q8_0: return "repack_q8_0";

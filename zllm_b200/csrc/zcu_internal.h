@@ -132,6 +132,9 @@ zcu_result launch_rope_append(const LaunchArgs& a);
 zcu_result launch_attn_split(const LaunchArgs& a);
 zcu_result launch_attn_combine(const LaunchArgs& a);
 zcu_result launch_delta_prep(const LaunchArgs& a);
+zcu_result launch_sample(const LaunchArgs& a);        // the whole draw on the sequence's first phase (k_sample.cu)
+zcu_result launch_mark_tokens(const LaunchArgs& a);
+zcu_result launch_draft(const LaunchArgs& a);
 zcu_result launch_delta_rule(const LaunchArgs& a);
 zcu_result launch_delta_recurrent(const LaunchArgs& a, uint32_t t_first, uint32_t m_expect);
 zcu_result launch_delta_chunked(const LaunchArgs& a);          // 64-token chunks, then the recurrent tail

@@ -16,6 +16,7 @@ from . import abi
 RMSNORM, MATMUL_BF16, MATMUL_F16, MATMUL_REDUCE, MATVEC_BF16, MATVEC_F16, SILU_MUL = 0, 1, 2, 3, 4, 5, 6
 EMBED_BF16, EMBED_F16, ROPE_APPEND, ATTN_SPLIT, ATTN_SPLIT_WIDE, ATTN_SPLIT_SPARSE, ATTN_COMBINE = 7, 8, 9, 10, 11, 12, 13
 DELTA_PREP, DELTA_RULE, GATED_NORM = 18, 19, 20
+MARK_TOKENS, SAMPLE, DRAFT = 21, 22, 23
 REPACK_Q8_0, QUANTIZE_Q8, MATVEC_Q8_0, MATVEC_Q4_K = 38, 39, 40, 42
 MATMUL_Q8_0, MATMUL_Q4_K, EMBED_Q8_0, EMBED_Q4_K = 45, 48, 51, 53
 MATMUL_Q8_0_FLOAT = 46
@@ -28,7 +29,7 @@ NORM, ACCUMULATE, SILU_PAIR = 1, 2, 4
 ROPE_APPEND_FUSED = 8
 
 # plan.common.KvFormat
-KV_F32, KV_F16 = 0, 1
+KV_F32, KV_F16, KV_FP8 = 0, 1, 2
 
 ATTN_BLOCK = 64        # kernels.attn_block
 ATTN_ROWS = 32         # kernels.attn_rows
@@ -105,6 +106,54 @@ GatedNorm = _struct("GatedNorm", [("v_heads", u32), ("dim", u32), ("eps", f32), 
 
 assert C.sizeof(Matvec) == 32 and C.sizeof(RopeAppend) == 64 and C.sizeof(Attention) == 48
 assert C.sizeof(DeltaPrep) == 48 and C.sizeof(DeltaRule) == 32 and C.sizeof(GatedNorm) == 32
+
+# The sampler (kernels.zig:424-430, 622-725)
+MAX_BIAS, MAX_STOPS, SAMPLE_SPAN, SAMPLE_CAP, SAMPLE_BISECT_ROUNDS = 1024, 16, 1024, 1024, 32
+Sample = _struct("Sample", [("vocab", u32), ("n_bias", u32), ("n_stop", u32), ("greedy", u32), ("temperature", f32),
+                            ("top_k", u32), ("top_p", f32), ("min_p", f32), ("repetition", f32), ("presence", f32),
+                            ("frequency", f32), ("n_prompt", u32), ("stops", u32 * MAX_STOPS)])
+SamplePhase = _struct("SamplePhase", [("phase", u32), ("round", u32), ("_pad", u32 * 2)])
+Draft = _struct("Draft", [("vocab", u32), ("row", u32), ("slot", u32), ("_pad", u32)])
+assert C.sizeof(Sample) == 112 and C.sizeof(SamplePhase) == 16 and C.sizeof(Draft) == 16
+(PH_PREP, PH_REDUCE, PH_HIST, PH_DIGIT, PH_GATHER, PH_FINAL, PH_MASS, PH_PICK, PH_BISECT_INIT, PH_BISECT_MASS,
+ PH_BISECT_STEP, PH_UNBUMP) = range(12)
+WIDE_PHASES = (PH_PREP, PH_HIST, PH_GATHER, PH_MASS, PH_BISECT_MASS)
+GREEDY_BELOW = 1e-5   # sampler.greedy_below
+
+
+def sample_params(vocab: int, temperature=1.0, top_k=0, top_p=1.0, min_p=0.0, repetition=1.0, presence=0.0, frequency=0.0,
+                  n_bias=0, stops=(), n_prompt=0) -> "Sample":
+    """Params.gpu (src/sampler/sampler.zig:58-79)."""
+    assert len(stops) <= MAX_STOPS and n_bias <= MAX_BIAS
+    s = Sample(vocab, n_bias, len(stops), int(temperature < GREEDY_BELOW), temperature, 0 if top_k >= vocab else top_k, top_p, min_p,
+               repetition, presence, frequency, n_prompt)
+    for i, t in enumerate(stops):
+        s.stops[i] = t
+    return s
+
+
+def sample_steps(s: "Sample"):
+    """The (phase, round) dispatches of one draw: kernels.sampleSteps (kernels.zig:683-715). This backend makes the
+    draw in the first of them and accepts the rest without launching."""
+    steps = [(PH_PREP, 0), (PH_REDUCE, 0)]
+    if s.greedy:
+        return steps
+    if s.top_k > 0:
+        for r in range(4):
+            steps += [(PH_HIST, r), (PH_DIGIT, r)]
+    if s.top_p < 1 and s.top_k > 0 and s.top_k <= SAMPLE_CAP:
+        return steps + [(PH_GATHER, 0), (PH_FINAL, 0)]
+    if s.top_p < 1:
+        steps += [(PH_MASS, 0), (PH_BISECT_INIT, 0)] + [(PH_BISECT_MASS, 0), (PH_BISECT_STEP, 0)] * SAMPLE_BISECT_ROUNDS
+    return steps + [(PH_MASS, 0), (PH_PICK, 0)]
+
+
+def sample_groups(vocab: int) -> int:
+    return -(-vocab // SAMPLE_SPAN)
+
+
+def sample_state_words(vocab: int) -> int:
+    return 16 + 256 + 2 * sample_groups(vocab) + 2 * SAMPLE_CAP
 
 
 def row_bytes(ttype: str, k: int) -> int:
@@ -254,6 +303,22 @@ class Launcher:
 
     def gated_norm(self, p: "GatedNorm", o, z, w, m):
         self.launch(GATED_NORM, p, [o, z, w], (p.v_heads, m, 1))
+
+    def sample(self, s: "Sample", params_buf, logits, bias, prompt_mask, counts, work, state, nxt, step, steps=None):
+        """One draw: every dispatch of kernels.sampleSteps, as the reference's host issues them."""
+        for phase, rnd in (sample_steps(s) if steps is None else steps):
+            groups = sample_groups(s.vocab) if phase in WIDE_PHASES else 1
+            self.launch(SAMPLE, SamplePhase(phase, rnd), [logits, bias, prompt_mask, counts, work, state, nxt, step, params_buf],
+                        (groups, 1, 1))
+
+    def sample_unbump(self, s: "Sample", params_buf, logits, bias, prompt_mask, counts, work, state, nxt, step):
+        self.launch(SAMPLE, SamplePhase(PH_UNBUMP, 0), [logits, bias, prompt_mask, counts, work, state, nxt, step, params_buf], (1, 1, 1))
+
+    def mark_tokens(self, s: "Sample", tokens, mask):
+        self.launch(MARK_TOKENS, s, [tokens, mask], elementwise(max(s.n_prompt, 1)))
+
+    def draft(self, vocab: int, row: int, slot: int, logits, out):
+        self.launch(DRAFT, Draft(vocab, row, slot, 0), [logits, out], (1, 1, 1))
 
 
 def attention_scale(head_dim: int) -> float:
