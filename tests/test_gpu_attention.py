@@ -174,3 +174,70 @@ def test_both_arithmetics_of_the_split_agree(gpu, launcher):
     for t in range(rows):
         used = -(-(int(positions[t]) + 1) // 128)
         assert rel_err(pb[t, :, :used, 0], pa[t, :, :used, 0]) < TOL and rel_err(pb[t, :, :used, 1:], pa[t, :, :used, 1:]) < TOL, t
+
+
+def test_fp8_cache_append_and_attention(ref, gpu, launcher):
+    # The FP8 KV cache (src/ref/fp8.zig, src/kernels/fp8.wgsl): rope_append stores each (position, KV head) row as
+    # E4M3FN bytes over a power-of-two scale kept as f32 after the values; attention reads value * scale. The bytes
+    # and scales are the codec oracle's, bit for bit (Llama style: no norm, so K before rounding is bit-equal too);
+    # attention over the cache then matches the oracle's attention over the decoded values.
+    from oracle import sampler as S
+
+    rng = np.random.default_rng(77)
+    heads, kv_heads, hd, n_rot, base = 8, 2, 128, 128, 500000.0
+    m, pos0, max_pos = 3, 70, 128
+    k_off = heads * hd
+    v_off = k_off + kv_heads * hd
+    row = v_off + kv_heads * hd
+    width = kv_heads * hd
+    scales = max_pos * width // 4                        # the scales follow the values, in words
+    words = scales + max_pos * kv_heads
+    table = ref.rope_table(max_pos, n_rot, base)
+    # a cache of earlier positions: rows of widely different magnitudes, encoded by the oracle
+    kq, vq = np.zeros(words, dtype=np.uint32), np.zeros(words, dtype=np.uint32)
+    kdec = np.zeros((max_pos, kv_heads, hd), dtype=np.float32)
+    vdec = np.zeros((max_pos, kv_heads, hd), dtype=np.float32)
+
+    def store(cache, dec, pos, g, vec):
+        s = S.fp8_row_scale(vec)
+        codes = np.array([S.fp8_encode(x / s) for x in vec], dtype=np.uint8)
+        cache.view(np.uint8)[(pos * width + g * hd):(pos * width + (g + 1) * hd)] = codes
+        cache[scales + pos * kv_heads + g] = np.float32(s).view(np.uint32)
+        dec[pos, g] = S.FP8_TABLE[codes] * np.float32(s)
+
+    for pos in range(pos0):
+        for g in range(kv_heads):
+            store(kq, kdec, pos, g, (rng.normal(size=hd) * 10.0 ** rng.uniform(-2, 2)).astype(np.float32))
+            store(vq, vdec, pos, g, (rng.normal(size=hd) * 10.0 ** rng.uniform(-2, 2)).astype(np.float32))
+    qkv = uniform(rng, (m, row), 3.0)
+    qkv[1, k_off:k_off + hd] = 0.0                       # a zero K row: scale 1
+    dq, kc, vc = gpu.put(qkv), gpu.put(kq), gpu.put(vq)
+    p = K.RopeAppend(heads, kv_heads, hd, n_rot, row, k_off, v_off, K.KV_FP8, 1e-6, 0, 0, 1, scales)
+    step = gpu.put(np.array([m, pos0, 0, 0], dtype=np.uint32))
+    one = gpu.put(np.ones(hd, dtype=np.float32))
+    launcher.rope_append(p, dq, one, one, gpu.put(table), kc, vc, step, m)
+    gpu.sync()
+    got_k, got_v = kc.download(np.uint32), vc.download(np.uint32)
+    for t in range(m):
+        for g in range(kv_heads):
+            store(kq, kdec, pos0 + t, g, ref.rope_normal(qkv[t, k_off + g * hd:k_off + (g + 1) * hd], pos0 + t, n_rot, base))
+            store(vq, vdec, pos0 + t, g, qkv[t, v_off + g * hd:v_off + (g + 1) * hd])
+    assert np.array_equal(got_k, kq) and np.array_equal(got_v, vq)
+    assert kq[scales + (pos0 + 1) * kv_heads] == np.float32(1).view(np.uint32)
+    # attention over the FP8 cache (the queries rope_append rotated in place)
+    q_rows = dq.download(np.float32).reshape(m, row)[:, :heads * hd].copy()
+    max_blocks = -(-max_pos // K.ATTN_BLOCK)
+    ap = K.Attention(heads, kv_heads, hd, K.KV_FP8, K.attention_scale(hd), max_blocks, heads * hd, 0, 0, scales)
+    part, out = gpu.zeros(m * heads * max_blocks * (hd + 2) * 4), gpu.zeros(m * heads * hd * 4)
+    dqr = gpu.put(q_rows)
+    launcher.attn_split(ap, dqr, kc, vc, part, step, pos0 + m, m)
+    launcher.attn_combine(ap, dqr, part, out, step, m)
+    got = out.download(np.float32).reshape(m, heads, hd)
+    for t in range(m):
+        n = pos0 + t + 1
+        for h in range(heads):
+            g = h // (heads // kv_heads)
+            s = kdec[:n, g].astype(np.float64) @ q_rows[t].reshape(heads, hd)[h].astype(np.float64) / math.sqrt(hd)
+            pr = np.exp(s - s.max())
+            want = (pr[:, None] * vdec[:n, g].astype(np.float64)).sum(0) / pr.sum()
+            assert rel_err(got[t, h], want) < TOL, (t, h, rel_err(got[t, h], want))

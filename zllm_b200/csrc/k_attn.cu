@@ -28,9 +28,24 @@ constexpr int AT_BLOCK = 64;       // cache positions per CTA (kernels.attn_bloc
 constexpr int AT_MAX_GROUP = 12;   // kernels.attn_max_group_wide
 constexpr int AT_SPLIT = AT_THREADS / AT_BLOCK;  // threads per key
 
-template <bool F16>
+// FP8 E4M3FN (src/kernels/fp8.wgsl:59-64, src/ref/fp8.zig:37-42): 1 sign, 4 exponent (bias 7), 3 mantissa bits.
+__device__ __forceinline__ float fp8_value(uint32_t b) {
+    const uint32_t e = (b >> 3) & 15u, m = b & 7u;
+    const float mag = e == 0 ? (float)m * 0.001953125f : __uint_as_float(((e + 120u) << 23) | (m << 20));
+    return (b & 0x80u) ? -mag : mag;
+}
+
+// FMT: 0 f32, 1 f16, 2 FP8 bytes (the caller applies the row's scale).
+template <int FMT>
 __device__ __forceinline__ void load8(const void* base, size_t elem, float* out) {
-    if (F16) {
+    if (FMT == 2) {
+        const uint2 v = *reinterpret_cast<const uint2*>(reinterpret_cast<const uint8_t*>(base) + elem);
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            out[i] = fp8_value((v.x >> (8 * i)) & 0xffu);
+            out[4 + i] = fp8_value((v.y >> (8 * i)) & 0xffu);
+        }
+    } else if (FMT == 1) {
         const uint4 v = *reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(base) + elem);
         const __half2* h = reinterpret_cast<const __half2*>(&v);
 #pragma unroll
@@ -47,15 +62,19 @@ __device__ __forceinline__ void load8(const void* base, size_t elem, float* out)
     }
 }
 
-template <bool F16>
+template <int FMT>
 __device__ __forceinline__ float2 load2(const void* base, size_t elem) {
-    if (F16) return __half22float2(*reinterpret_cast<const __half2*>(reinterpret_cast<const __half*>(base) + elem));
+    if (FMT == 2) {
+        const uint32_t v = *reinterpret_cast<const unsigned short*>(reinterpret_cast<const uint8_t*>(base) + elem);
+        return make_float2(fp8_value(v & 0xffu), fp8_value(v >> 8));
+    }
+    if (FMT == 1) return __half22float2(*reinterpret_cast<const __half2*>(reinterpret_cast<const __half*>(base) + elem));
     return *reinterpret_cast<const float2*>(reinterpret_cast<const float*>(base) + elem);
 }
 
 // grid (kv_heads, blocks, rows). Dynamic shared memory:
 //   qs[group * hd] | sc[group * 64] | stat[2 * group] | pv[parts * group * hd]
-template <bool F16, int GROUP_CAP>
+template <int FMT, int GROUP_CAP>
 __global__ void __launch_bounds__(AT_THREADS) attn_split_kernel(PAttention p, const float* __restrict__ qg,
                                                                const void* __restrict__ kc,
                                                                const void* __restrict__ vc, float* __restrict__ part,
@@ -98,9 +117,16 @@ __global__ void __launch_bounds__(AT_THREADS) attn_split_kernel(PAttention p, co
     for (int h = 0; h < GROUP_CAP; h++) dot[h] = 0.f;
     if (live) {
         const size_t kb = seq_off + (size_t)key * kv_stride + (size_t)g * hd + (size_t)s * span;
+        // FP8: the (position, KV head) row's power-of-two scale, stored as f32 at word `scales` on; applying it to
+        // each value is exact (src/kernels/attn_split.wgsl:71-78)
+        const float ks = FMT == 2 ? reinterpret_cast<const float*>(kc)[p.scales + kb / hd] : 1.0f;
         for (int d = 0; d < span; d += 8) {
             float kk[8];
-            load8<F16>(kc, kb + d, kk);
+            load8<FMT>(kc, kb + d, kk);
+            if (FMT == 2) {
+#pragma unroll
+                for (int q = 0; q < 8; q++) kk[q] *= ks;
+            }
             const int e = s * span + d;
 #pragma unroll
             for (int h = 0; h < GROUP_CAP; h++) {
@@ -161,7 +187,12 @@ __global__ void __launch_bounds__(AT_THREADS) attn_split_kernel(PAttention p, co
     for (int h = 0; h < GROUP_CAP; h++) acc[h][0] = acc[h][1] = 0.f;
     if (kp < parts) {
         for (int i = kp; i < n; i += parts) {
-            const float2 v = load2<F16>(vc, seq_off + (size_t)(k0 + i) * kv_stride + (size_t)g * hd + 2 * dp);
+            const size_t vi = seq_off + (size_t)(k0 + i) * kv_stride + (size_t)g * hd + 2 * dp;
+            float2 v = load2<FMT>(vc, vi);
+            if (FMT == 2) {
+                const float vs = reinterpret_cast<const float*>(vc)[p.scales + vi / hd];
+                v.x *= vs, v.y *= vs;
+            }
 #pragma unroll
             for (int h = 0; h < GROUP_CAP; h++) {
                 if (h < group) {
@@ -252,18 +283,18 @@ int attn_keys_per_block(const PAttention& p) {
     return fast ? AF_KEYS : AT_BLOCK;
 }
 
-template <bool F16>
+template <int FMT>
 zcu_result launch_split_fmt(const LaunchArgs& a, const PAttention& p, dim3 grid, size_t smem, int group) {
     const float* qg = (const float*)a.b[0].ptr;
     float* part = (float*)a.b[3].ptr;
     const PStep* step = (const PStep*)a.b[4].ptr;
     const uint32_t* seq_pos = (a.nb >= 6 && p._pad[0] != 0) ? (const uint32_t*)a.b[5].ptr : nullptr;
     if (group <= 4) {
-        attn_split_kernel<F16, 4><<<grid, AT_THREADS, smem, a.stream>>>(p, qg, a.b[1].ptr, a.b[2].ptr, part, step, seq_pos);
+        attn_split_kernel<FMT, 4><<<grid, AT_THREADS, smem, a.stream>>>(p, qg, a.b[1].ptr, a.b[2].ptr, part, step, seq_pos);
     } else if (group <= 8) {
-        attn_split_kernel<F16, 8><<<grid, AT_THREADS, smem, a.stream>>>(p, qg, a.b[1].ptr, a.b[2].ptr, part, step, seq_pos);
+        attn_split_kernel<FMT, 8><<<grid, AT_THREADS, smem, a.stream>>>(p, qg, a.b[1].ptr, a.b[2].ptr, part, step, seq_pos);
     } else {
-        attn_split_kernel<F16, AT_MAX_GROUP><<<grid, AT_THREADS, smem, a.stream>>>(p, qg, a.b[1].ptr, a.b[2].ptr, part, step, seq_pos);
+        attn_split_kernel<FMT, AT_MAX_GROUP><<<grid, AT_THREADS, smem, a.stream>>>(p, qg, a.b[1].ptr, a.b[2].ptr, part, step, seq_pos);
     }
     ZCU_CHECK_LAUNCH(a);
     return ZCU_OK;
@@ -279,7 +310,8 @@ zcu_result launch_attn_split(const LaunchArgs& a) {
     const int group = (int)(p.heads / p.kv_heads);
     ZCU_NEED(a, group <= AT_MAX_GROUP, "attn_split: GQA group %d above %d", group, AT_MAX_GROUP);
     ZCU_NEED(a, p.head_dim % 32 == 0 && p.head_dim <= 256 && p.head_dim >= 32, "attn_split: head_dim %u", p.head_dim);
-    ZCU_NEED(a, p.kv == KV_F32 || p.kv == KV_F16, "attn_split: cache format %u is not built", p.kv);
+    ZCU_NEED(a, p.kv == KV_F32 || p.kv == KV_F16 || p.kv == KV_FP8, "attn_split: cache format %u is not built", p.kv);
+    ZCU_NEED(a, p.kv != KV_FP8 || p.head_dim % 64 == 0, "attn_split: an FP8 cache needs head_dim %u in whole 64s (8-byte loads)", p.head_dim);
     ZCU_NEED(a, a.grid[1] <= p.max_blocks, "attn_split: %u key blocks above max_blocks %u", a.grid[1], p.max_blocks);
     if (a.grid[1] == 0 || a.grid[2] == 0) return ZCU_OK;
     const int hd = (int)p.head_dim;
@@ -319,7 +351,8 @@ zcu_result launch_attn_split(const LaunchArgs& a) {
     const size_t smem = ((size_t)group * hd + (size_t)group * AT_BLOCK + 2 * AT_MAX_GROUP + (size_t)parts * group * hd) * sizeof(float);
     ZCU_NEED(a, smem <= 48 * 1024, "attn_split: %zu bytes of shared memory", smem);
     const dim3 grid(p.kv_heads, a.grid[1], a.grid[2]);
-    return p.kv == KV_F16 ? launch_split_fmt<true>(a, p, grid, smem, group) : launch_split_fmt<false>(a, p, grid, smem, group);
+    if (p.kv == KV_FP8) return launch_split_fmt<2>(a, p, grid, smem, group);
+    return p.kv == KV_F16 ? launch_split_fmt<1>(a, p, grid, smem, group) : launch_split_fmt<0>(a, p, grid, smem, group);
 }
 
 zcu_result launch_attn_combine(const LaunchArgs& a) {
@@ -379,7 +412,7 @@ zcu_result launch_attn_static(const LaunchArgs& a, uint32_t max_keys, uint32_t r
     p.max_blocks = (max_keys + AT_BLOCK - 1) / AT_BLOCK;
     // everything either launch would refuse is refused here, before the first of them is enqueued
     ZCU_NEED(a, p.heads / p.kv_heads <= AT_MAX_GROUP && p.head_dim % 32 == 0 && p.head_dim >= 32 && p.head_dim <= 256 &&
-                    (p.kv == KV_F32 || p.kv == KV_F16) && p.max_blocks <= AC_MAX_BLOCKS,
+                    (p.kv == KV_F32 || p.kv == KV_F16 || (p.kv == KV_FP8 && p.head_dim % 64 == 0)) && p.max_blocks <= AC_MAX_BLOCKS,
              "attention (static partials): group %u, head_dim %u, cache format %u or %u key blocks is not built", p.heads / p.kv_heads,
              p.head_dim, p.kv, p.max_blocks);
     const size_t need = (size_t)rows * p.heads * p.max_blocks * (p.head_dim + 2);

@@ -244,7 +244,7 @@ zcu_result launch_rope_append(const LaunchArgs& a) {
     ZCU_NEED(a, a.params_bytes >= sizeof(p) && a.nb >= 7, "rope_append: bad parameter block or bindings");
     memcpy(&p, a.params, sizeof(p));
     ZCU_NEED(a, p.head_dim <= 256 && p.head_dim % 2 == 0, "rope_append: head_dim %u", p.head_dim);
-    ZCU_NEED(a, p.kv == KV_F32 || p.kv == KV_F16, "rope_append: cache format %u is not built", p.kv);
+    ZCU_NEED(a, p.kv == KV_F32 || p.kv == KV_F16 || (p.kv == KV_FP8 && p.head_dim % 4 == 0), "rope_append: cache format %u is not built", p.kv);
     const uint32_t m = a.grid[1];
     if (m == 0) return ZCU_OK;
     rope_append_kernel<<<dim3(p.heads + p.kv_heads, m), 256, 0, a.stream>>>(

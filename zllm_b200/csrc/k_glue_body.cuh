@@ -92,6 +92,35 @@ __device__ __forceinline__ void embed_body(const VBlock& vb, const PEmbed& p, co
 // pos0 + t; the f16 cache rounds to nearest even (src/ref/qwen35.zig:32-42).
 constexpr size_t ROPE_SMEM = 32 * sizeof(double) + 256 * sizeof(float);
 
+// The exponent k of an FP8 row's scale 2^k: the smallest with m <= 448 * 2^k; 0 for a zero or subnormal maximum.
+__device__ __forceinline__ int fp8_scale_exp(float m) {
+    const uint32_t bits = __float_as_uint(m);
+    const int e = (int)((bits >> 23) & 255u);
+    if (e == 0) return 0;
+    return e - 127 - 8 + ((bits & 0x7fffffu) > 0x600000u ? 1 : 0);
+}
+// |x| <= 448 (clamped) -> E4M3FN bits, round to nearest, ties to even (src/ref/fp8.zig:12-35).
+__device__ __forceinline__ uint32_t fp8_bits(float x) {
+    const uint32_t sign = (__float_as_uint(x) >> 24) & 0x80u;
+    const float a = fminf(fabsf(x), 448.0f);
+    if (a < 0.015625f) {
+        const float s = a * 512.0f;   // exact
+        uint32_t q = (uint32_t)floorf(s);
+        const float r = s - (float)q;
+        if (r > 0.5f || (r == 0.5f && (q & 1u) == 1u)) q += 1u;
+        return sign | q;
+    }
+    const uint32_t ab = __float_as_uint(a);
+    uint32_t e = (ab >> 23) - 120u;
+    const uint32_t mant = ab & 0x7fffffu;
+    uint32_t q = mant >> 20;
+    const uint32_t rem = mant & 0xfffffu;
+    if (rem > 0x80000u || (rem == 0x80000u && (q & 1u) == 1u)) q += 1u;
+    if (q == 8u) q = 0u, e += 1u;
+    const uint32_t code = (e << 3) | q;
+    return sign | (code < 0x7eu ? code : 0x7eu);
+}
+
 __device__ __forceinline__ void rope_append_body(const VBlock& vb, const PRopeAppend& p, float* __restrict__ qkv,
                                                  const float* __restrict__ q_norm, const float* __restrict__ k_norm,
                                                  const float2* __restrict__ rope, uint32_t* __restrict__ kc,
@@ -146,6 +175,39 @@ __device__ __forceinline__ void rope_append_body(const VBlock& vb, const PRopeAp
     const size_t width = (size_t)p.kv_heads * hd;
     const size_t e = (size_t)t * p._pad[0] + (size_t)pos * width + (size_t)g * hd;
     const size_t vo = (size_t)t * p.row + p.v_off + (size_t)g * hd;
+    if (p.kv == KV_FP8) {
+        // each row divided by its power-of-two scale (the smallest with amax / scale <= 448), four codes a word, the
+        // scale as f32 at word `scales` + row (src/kernels/rope_append.wgsl:118-137, src/ref/fp8.zig:44-55)
+        float* mx = reinterpret_cast<float*>(red);   // [2][warps]; the sums it held are consumed
+        float ka = i < hd ? fabsf(vals[i]) : 0.f, va = i < hd ? fabsf(__ldcg(qkv + vo + i)) : 0.f;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            ka = fmaxf(ka, __shfl_xor_sync(0xffffffffu, ka, o));
+            va = fmaxf(va, __shfl_xor_sync(0xffffffffu, va, o));
+        }
+        const int warps = vb.nthreads / 32;
+        if ((i & 31u) == 0) mx[i / 32] = ka, mx[32 + i / 32] = va;
+        vb.sync();
+        ka = va = 0.f;
+        for (int w = 0; w < warps; w++) ka = fmaxf(ka, mx[w]), va = fmaxf(va, mx[32 + w]);
+        const int k_exp = fp8_scale_exp(ka), v_exp = fp8_scale_exp(va);
+        const float k_inv = __uint_as_float((uint32_t)(127 - k_exp) << 23), v_inv = __uint_as_float((uint32_t)(127 - v_exp) << 23);
+        if (i < hd / 4) {
+            uint32_t kw = 0, vw = 0;
+#pragma unroll
+            for (uint32_t q = 0; q < 4; q++) {
+                kw |= fp8_bits(vals[4 * i + q] * k_inv) << (8 * q);
+                vw |= fp8_bits(__ldcg(qkv + vo + 4 * i + q) * v_inv) << (8 * q);
+            }
+            kc[e / 4 + i] = kw;
+            vc[e / 4 + i] = vw;
+        }
+        if (i == 0) {
+            kc[p.scales + e / hd] = (uint32_t)(127 + k_exp) << 23;
+            vc[p.scales + e / hd] = (uint32_t)(127 + v_exp) << 23;
+        }
+        return;
+    }
     if (i < hd / 2) {
         const float k0 = vals[2 * i], k1 = vals[2 * i + 1];
         const float v0 = __ldcg(qkv + vo + 2 * i), v1 = __ldcg(qkv + vo + 2 * i + 1);
