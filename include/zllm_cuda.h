@@ -77,15 +77,24 @@ enum {
     ZCU_K_MARK_TOKENS = 21,
     ZCU_K_SAMPLE = 22,
     ZCU_K_DRAFT = 23,
+    ZCU_K_REPAD = 36,
+    ZCU_K_REPACK_Q3_K = 37,
     ZCU_K_REPACK_Q8_0 = 38,
     ZCU_K_QUANTIZE_Q8 = 39,
     ZCU_K_MATVEC_Q8_0 = 40,
+    ZCU_K_MATVEC_Q3_K = 41,
     ZCU_K_MATVEC_Q4_K = 42,
+    ZCU_K_MATVEC_Q5_K = 43,
+    ZCU_K_MATVEC_Q6_K = 44,
     ZCU_K_MATMUL_Q8_0 = 45,
     ZCU_K_MATMUL_Q8_0_FLOAT = 46,
     ZCU_K_MATMUL_Q4_K = 48,
     ZCU_K_EMBED_Q8_0 = 51,
+    ZCU_K_EMBED_Q3_K = 52,
     ZCU_K_EMBED_Q4_K = 53,
+    ZCU_K_EMBED_Q5_K = 54,
+    ZCU_K_EMBED_Q6_K = 55,
+    ZCU_K_EMBED_IQ4_XS = 56,
     ZCU_K_COUNT = 57,
     /* identities of this backend only (above the reference's enum) */
     ZCU_K_EXT_PEER_WAIT = 64   /* waits for one tensor-parallel exchange; parameter block = zcu_peer_ext, no bindings */

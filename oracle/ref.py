@@ -16,8 +16,9 @@ HERE = Path(__file__).resolve().parent
 BUILD = HERE / "_build"
 
 # GGUF tensor type ids (src/gguf/gguf.zig TensorType).
-F32, F16, Q8_0, Q4_K, BF16 = 0, 1, 8, 12, 30
-BLOCK = {F32: (1, 4), F16: (1, 2), BF16: (1, 2), Q8_0: (32, 34), Q4_K: (256, 144)}
+F32, F16, Q8_0, Q3_K, Q4_K, Q5_K, Q6_K, IQ4_XS, BF16 = 0, 1, 8, 11, 12, 13, 14, 23, 30
+BLOCK = {F32: (1, 4), F16: (1, 2), BF16: (1, 2), Q8_0: (32, 34), Q4_K: (256, 144), Q3_K: (256, 110), Q5_K: (256, 176),
+         Q6_K: (256, 210), IQ4_XS: (256, 136)}
 
 # Accumulation modes of ref_matmul / ref_delta_rule.
 MUL_ADD, FMA, F64 = 0, 1, 2
@@ -256,7 +257,7 @@ class Matrix:
 
     def dense(self) -> np.ndarray:
         """All rows decoded to f32 (n x k)."""
-        if self.type in (Q8_0, Q4_K):
+        if BLOCK[self.type][0] > 1:
             return dequantize(self.type, self.bytes, self.n * self.k).reshape(self.n, self.k)
         return np.stack([self.row(j) for j in range(self.n)])
 

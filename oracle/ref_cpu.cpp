@@ -39,7 +39,7 @@
 #define REF_API extern "C" __attribute__((visibility("default")))
 
 // GGUF tensor type ids (src/gguf/gguf.zig TensorType).
-enum : int { T_F32 = 0, T_F16 = 1, T_Q8_0 = 8, T_Q4_K = 12, T_BF16 = 30 };
+enum : int { T_F32 = 0, T_F16 = 1, T_Q8_0 = 8, T_Q3_K = 11, T_Q4_K = 12, T_Q5_K = 13, T_Q6_K = 14, T_IQ4_XS = 23, T_BF16 = 30 };
 
 // ---------------------------------------------------------------- f16 / bf16
 
@@ -148,6 +148,98 @@ static void q4_k_block(const uint8_t* b, float* y) {
     }
 }
 
+// ref/tensor.zig:54-93 — block_q3_K: hmask[32], qs[64], scales[12] (16 six-bit scales, packed), d (f16);
+// y = (d * (scale - 32)) * (two bits - (4 unless the mask bit is set)).
+static void q3_k_block(const uint8_t* b, float* y) {
+    const uint8_t* hm = b;
+    const float d_all = f16_to_f32(rd16(b + 108));
+    uint32_t aux[4];
+    for (int i = 0; i < 4; i++) aux[i] = i < 3 ? (uint32_t)(b[96 + 4 * i] | (b[97 + 4 * i] << 8) | (b[98 + 4 * i] << 16) | ((uint32_t)b[99 + 4 * i] << 24)) : 0;
+    const uint32_t kmask1 = 0x03030303u, kmask2 = 0x0f0f0f0fu, tmp = aux[2];
+    aux[2] = ((aux[0] >> 4) & kmask2) | (((tmp >> 4) & kmask1) << 4);
+    aux[3] = ((aux[1] >> 4) & kmask2) | (((tmp >> 6) & kmask1) << 4);
+    aux[0] = (aux[0] & kmask2) | (((tmp >> 0) & kmask1) << 4);
+    aux[1] = (aux[1] & kmask2) | (((tmp >> 2) & kmask1) << 4);
+    int8_t scales[16];
+    memcpy(scales, aux, 16);
+    size_t out = 0, is = 0;
+    uint8_t m = 1;
+    for (int n = 0; n < 2; n++) {
+        const uint8_t* q = b + 32 + n * 32;
+        int shift = 0;
+        for (int r = 0; r < 4; r++) {
+            for (int h = 0; h < 2; h++) {
+                const float dl = d_all * (float)((int)scales[is++] - 32);
+                for (int l = 0; l < 16; l++) {
+                    const int lo = (q[l + 16 * h] >> shift) & 3;
+                    const int v = lo - ((hm[l + 16 * h] & m) ? 0 : 4);
+                    y[out++] = dl * (float)v;
+                }
+            }
+            shift += 2;
+            m = (uint8_t)(m << 1);
+        }
+    }
+}
+
+// ref/tensor.zig:118-137 — block_q5_K: d, dmin (f16), scales[12], qh[32] (fifth bits), qs[128].
+static void q5_k_block(const uint8_t* b, float* y) {
+    const float d = f16_to_f32(rd16(b));
+    const float mn = f16_to_f32(rd16(b + 2));
+    const uint8_t* scales = b + 4;
+    const uint8_t* qh = b + 16;
+    for (int j = 0; j < 4; j++) {
+        const uint8_t* ql = b + 48 + 32 * j;
+        const uint8_t bit_lo = (uint8_t)(1u << (2 * j)), bit_hi = (uint8_t)(2u << (2 * j));
+        uint8_t sc1, mm1, sc2, mm2;
+        scale_min_k4(2 * j, scales, &sc1, &mm1);
+        scale_min_k4(2 * j + 1, scales, &sc2, &mm2);
+        const float d1 = d * (float)sc1, m1 = mn * (float)mm1, d2 = d * (float)sc2, m2 = mn * (float)mm2;
+        for (int l = 0; l < 32; l++) y[64 * j + l] = d1 * (float)((ql[l] & 0xF) + ((qh[l] & bit_lo) ? 16 : 0)) - m1;
+        for (int l = 0; l < 32; l++) y[64 * j + 32 + l] = d2 * (float)((ql[l] >> 4) + ((qh[l] & bit_hi) ? 16 : 0)) - m2;
+    }
+}
+
+// ref/tensor.zig:139-160 — block_q6_K: ql[128], qh[64], scales[16] (i8), d (f16); y = (d * sc) * (q - 32).
+static void q6_k_block(const uint8_t* b, float* y) {
+    const float d = f16_to_f32(rd16(b + 208));
+    for (int n = 0; n < 2; n++) {
+        const uint8_t* ql = b + 64 * n;
+        const uint8_t* qh = b + 128 + 32 * n;
+        const int8_t* sc = (const int8_t*)(b + 192 + 8 * n);
+        float* out = y + 128 * n;
+        for (int l = 0; l < 32; l++) {
+            const int is = l / 16;
+            const int q1 = (int)((ql[l] & 0xF) | (((qh[l] >> 0) & 3) << 4)) - 32;
+            const int q2 = (int)((ql[l + 32] & 0xF) | (((qh[l] >> 2) & 3) << 4)) - 32;
+            const int q3 = (int)((ql[l] >> 4) | (((qh[l] >> 4) & 3) << 4)) - 32;
+            const int q4 = (int)((ql[l + 32] >> 4) | (((qh[l] >> 6) & 3) << 4)) - 32;
+            out[l] = d * (float)sc[is] * (float)q1;
+            out[l + 32] = d * (float)sc[is + 2] * (float)q2;
+            out[l + 64] = d * (float)sc[is + 4] * (float)q3;
+            out[l + 96] = d * (float)sc[is + 6] * (float)q4;
+        }
+    }
+}
+
+// ref/tensor.zig:162-181 — block_iq4_xs: d (f16), scales_h (u16), scales_l[4], qs[128]; signed six-bit group
+// scales biased by 32, nonlinear four-bit values (low nibbles precede high nibbles).
+static void iq4_xs_block(const uint8_t* b, float* y) {
+    static const int8_t values[16] = {-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113};
+    const float d = f16_to_f32(rd16(b));
+    const uint32_t scales_h = rd16(b + 2);
+    for (int group = 0; group < 8; group++) {
+        const uint32_t low = (b[4 + group / 2] >> (4 * (group % 2))) & 15u;
+        const uint32_t high = (scales_h >> (2 * group)) & 3u;
+        const float dl = d * (float)((int)(low | (high << 4)) - 32);
+        const uint8_t* qs = b + 8 + 16 * group;
+        for (int j = 0; j < 16; j++) {
+            y[32 * group + j] = dl * (float)values[qs[j] & 15];
+            y[32 * group + 16 + j] = dl * (float)values[qs[j] >> 4];
+        }
+    }
+}
+
 struct Layout { size_t block_elems, block_bytes; };
 static bool layout_of(int t, Layout* l) {
     switch (t) {
@@ -156,6 +248,10 @@ static bool layout_of(int t, Layout* l) {
         case T_BF16: *l = {1, 2}; return true;
         case T_Q8_0: *l = {32, 34}; return true;
         case T_Q4_K: *l = {256, 144}; return true;
+        case T_Q3_K: *l = {256, 110}; return true;
+        case T_Q5_K: *l = {256, 176}; return true;
+        case T_Q6_K: *l = {256, 210}; return true;
+        case T_IQ4_XS: *l = {256, 136}; return true;
         default: return false;
     }
 }
@@ -169,6 +265,18 @@ REF_API int ref_dequantize(int type, const uint8_t* bytes, float* out, size_t n)
             return 0;
         case T_Q4_K:
             for (size_t i = 0; i < n / 256; i++) q4_k_block(bytes + i * 144, out + i * 256);
+            return 0;
+        case T_Q3_K:
+            for (size_t i = 0; i < n / 256; i++) q3_k_block(bytes + i * 110, out + i * 256);
+            return 0;
+        case T_Q5_K:
+            for (size_t i = 0; i < n / 256; i++) q5_k_block(bytes + i * 176, out + i * 256);
+            return 0;
+        case T_Q6_K:
+            for (size_t i = 0; i < n / 256; i++) q6_k_block(bytes + i * 210, out + i * 256);
+            return 0;
+        case T_IQ4_XS:
+            for (size_t i = 0; i < n / 256; i++) iq4_xs_block(bytes + i * 136, out + i * 256);
             return 0;
         case T_F32:
             memcpy(out, bytes, n * 4);
@@ -476,7 +584,7 @@ REF_API Matrix* ref_matrix_create(Pool* pool, int type, const uint8_t* bytes, si
     m->n = n;
     m->k = k;
     m->type = type;
-    if (type == T_Q8_0 || type == T_Q4_K) {
+    if (l.block_elems > 1) {  // every block-quantised type is decoded panel by panel as it is used
         m->quant = bytes;  // must outlive the matrix
         return m;
     }

@@ -35,9 +35,10 @@ def test_no_device_means_an_error_not_a_fallback():
 def test_artifacts_and_missing_kernels():
     for k in (K.MATVEC_Q4_K, K.MATVEC_Q8_0, K.MATVEC_BF16, K.ATTN_SPLIT, K.ATTN_COMBINE, K.DELTA_RULE, K.ROPE_APPEND,
               K.RMSNORM, K.EMBED_Q4_K, K.REPACK_Q8_0, K.MATMUL_BF16, K.QUANTIZE_Q8, K.MATMUL_Q4_K, K.MATMUL_Q8_0,
-              K.MATMUL_Q8_0_FLOAT, K.MATMUL_REDUCE, K.SAMPLE, K.MARK_TOKENS, K.DRAFT):
+              K.MATMUL_Q8_0_FLOAT, K.MATMUL_REDUCE, K.SAMPLE, K.MARK_TOKENS, K.DRAFT, K.REPAD, K.REPACK_Q3_K, K.MATVEC_Q3_K,
+              K.MATVEC_Q5_K, K.MATVEC_Q6_K, K.EMBED_Q3_K, K.EMBED_Q5_K, K.EMBED_Q6_K, K.EMBED_IQ4_XS):
         assert abi.artifact(k).startswith(b"cuda:")
-    for k in (14, 24, 41, 56):  # qsa_keys, gyro_matvec, matvec_q3_k, embed_iq4_xs: not on this path
+    for k in (14, 24, 47, 50):  # qsa_keys, gyro_matvec, matmul_q3_k, matmul_q6_k: not on this path
         assert abi.artifact(k) == b""
     for v in K.MATVEC_CANDIDATES:
         assert abi.artifact(K.MATVEC_Q4_K, v)

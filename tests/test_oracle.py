@@ -75,6 +75,26 @@ def test_dequantize_matches_gguf_golden_bitwise(ref):
     assert np.array_equal(bits(got8), g["q8_0_f32_bits"].ravel())
     got4 = ref.dequantize(ref.Q4_K, g["q4_k_bytes"], g["q4_k_bytes"].shape[0] * 256)
     assert np.array_equal(bits(got4), g["q4_k_f32_bits"].ravel())
+    # the other block types of the loader path (src/ref/tensor.zig:54-181)
+    for name, t in (("q3_k", ref.Q3_K), ("q5_k", ref.Q5_K), ("q6_k", ref.Q6_K), ("iq4_xs", ref.IQ4_XS)):
+        by = g[f"{name}_bytes"]
+        got = ref.dequantize(t, by, by.shape[0] * 256)
+        assert np.array_equal(bits(got), g[f"{name}_f32_bits"].ravel()), name
+
+
+def test_block_quantised_matrices_of_every_type_multiply_like_their_decoded_rows(ref):
+    from zllm_b200 import synth
+
+    rng = np.random.default_rng(9)
+    x = rng.normal(size=(2, 512)).astype(np.float32)
+    for name, t in (("q3_k", ref.Q3_K), ("q5_k", ref.Q5_K), ("q6_k", ref.Q6_K), ("iq4_xs", ref.IQ4_XS)):
+        w = synth.kquant_weights(rng, name, 37, 512)
+        m = ref.Matrix(t, w, 37, 512)
+        dense = m.dense()
+        assert np.array_equal(m.row(5), dense[5])
+        want = x.astype(np.float64) @ dense.astype(np.float64).T
+        got = ref.matmul(x, m, mode=ref.F64)
+        assert np.abs(got - want).max() <= 1e-6 * np.abs(want).max(), name
 
 
 def test_q4_k_hand_built_block(ref):

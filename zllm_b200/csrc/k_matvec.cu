@@ -153,6 +153,115 @@ struct BlockDot<W_BF16, MT> : BlockDotHalf<W_BF16, MT> {};
 template <int MT>
 struct BlockDot<W_F16, MT> : BlockDotHalf<W_F16, MT> {};
 
+// The other K-quants, in the layouts the reference's kernels read (kernels.blockStride, src/kernels/kernels.zig:
+// 137-151): Q6_K blocks padded from 210 to 224 bytes by `repad`, Q5_K as in the file (176), Q3_K repacked by
+// repack_q3_k into eight 16-byte units (128). Eight parts of 32 weights per 256-weight block; a weight is decoded
+// with the CPU reference's roundings (src/ref/tensor.zig:54-160: the scale product first, then the value).
+__device__ __forceinline__ void k4_scale_min(const uint8_t* s, int j, uint32_t& sc, uint32_t& m) {
+    if (j < 4) {
+        sc = s[j] & 63u, m = s[j + 4] & 63u;
+    } else {
+        sc = (s[j + 4] & 0xFu) | ((uint32_t)(s[j - 4] >> 6) << 4), m = (uint32_t)(s[j + 4] >> 4) | ((uint32_t)(s[j] >> 6) << 4);
+    }
+}
+
+template <int MT>
+struct BlockDot<W_Q6_K, MT> {
+    static constexpr int BLOCK = 256, PARTS = 8;
+    __device__ static size_t row_bytes(int k) { return (size_t)(k / 256) * 224; }
+    __device__ static void run(const uint8_t* __restrict__ row, int /*k*/, int gblk, int part, const float* xs, int xs_stride, float* acc) {
+        const uint8_t* b = row + (size_t)gblk * 224;
+        const int n = part >> 2, c = part & 3;
+        const uint4 l0 = *reinterpret_cast<const uint4*>(b + 64 * n + 32 * (c & 1)), l1 = *reinterpret_cast<const uint4*>(b + 64 * n + 32 * (c & 1) + 16);
+        const uint4 h0 = *reinterpret_cast<const uint4*>(b + 128 + 32 * n), h1 = *reinterpret_cast<const uint4*>(b + 128 + 32 * n + 16);
+        const float d = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short*>(b + 208)));
+        const int8_t* sc = reinterpret_cast<const int8_t*>(b + 192 + 8 * n + 2 * c);
+        const float ds0 = __fmul_rn(d, (float)sc[0]), ds1 = __fmul_rn(d, (float)sc[1]);
+        const uint32_t lw[8] = {l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w}, hw[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
+        const int ls = 4 * (c >> 1), hs = 2 * c;
+#pragma unroll
+        for (int t = 0; t < MT; t++) {
+            const float* xv = xs + (size_t)t * xs_stride + 32 * part;
+            float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+            for (int v = 0; v < 8; v++) {
+                const float4 a = *reinterpret_cast<const float4*>(xv + 4 * v);
+                const uint32_t q = ((lw[v] >> ls) & 0x0f0f0f0fu) | (((hw[v] >> hs) & 0x03030303u) << 4);
+                float& s = v < 4 ? s0 : s1;
+                s = __fmaf_rn(a.x, (float)((int)(q & 0xffu) - 32), s);
+                s = __fmaf_rn(a.y, (float)((int)((q >> 8) & 0xffu) - 32), s);
+                s = __fmaf_rn(a.z, (float)((int)((q >> 16) & 0xffu) - 32), s);
+                s = __fmaf_rn(a.w, (float)((int)(q >> 24) - 32), s);
+            }
+            acc[t] = __fmaf_rn(ds1, s1, __fmaf_rn(ds0, s0, acc[t]));
+        }
+    }
+};
+
+template <int MT>
+struct BlockDot<W_Q5_K, MT> {
+    static constexpr int BLOCK = 256, PARTS = 8;
+    __device__ static size_t row_bytes(int k) { return (size_t)(k / 256) * 176; }
+    __device__ static void run(const uint8_t* __restrict__ row, int /*k*/, int gblk, int part, const float* xs, int xs_stride, float* acc) {
+        const uint8_t* b = row + (size_t)gblk * 176;
+        const int j = part >> 1, hi = part & 1;
+        const uint4 q0 = *reinterpret_cast<const uint4*>(b + 48 + 32 * j), q1 = *reinterpret_cast<const uint4*>(b + 48 + 32 * j + 16);
+        const uint4 h0 = *reinterpret_cast<const uint4*>(b + 16), h1 = *reinterpret_cast<const uint4*>(b + 32);
+        const float d = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short*>(b)));
+        const float dmin = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short*>(b + 2)));
+        uint32_t sc, mn;
+        k4_scale_min(b + 4, part, sc, mn);
+        const float d1 = __fmul_rn(d, (float)sc), m1 = __fmul_rn(dmin, (float)mn);
+        const uint32_t qw[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w}, hw[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
+#pragma unroll
+        for (int t = 0; t < MT; t++) {
+            const float* xv = xs + (size_t)t * xs_stride + 32 * part;
+            float s = 0.f, xsum = 0.f;
+#pragma unroll
+            for (int v = 0; v < 8; v++) {
+                const float4 a = *reinterpret_cast<const float4*>(xv + 4 * v);
+                const uint32_t q = ((qw[v] >> (4 * hi)) & 0x0f0f0f0fu) | (((hw[v] >> part) & 0x01010101u) << 4);
+                s = __fmaf_rn(a.x, (float)(q & 0xffu), s);
+                s = __fmaf_rn(a.y, (float)((q >> 8) & 0xffu), s);
+                s = __fmaf_rn(a.z, (float)((q >> 16) & 0xffu), s);
+                s = __fmaf_rn(a.w, (float)(q >> 24), s);
+                xsum = __fadd_rn(xsum, __fadd_rn(__fadd_rn(a.x, a.y), __fadd_rn(a.z, a.w)));
+            }
+            acc[t] = __fmaf_rn(-m1, xsum, __fmaf_rn(d1, s, acc[t]));
+        }
+    }
+};
+
+template <int MT>
+struct BlockDot<W_Q3_K, MT> {
+    static constexpr int BLOCK = 256, PARTS = 8;
+    __device__ static size_t row_bytes(int k) { return (size_t)(k / 256) * 128; }
+    __device__ static void run(const uint8_t* __restrict__ row, int /*k*/, int gblk, int part, const float* xs, int xs_stride, float* acc) {
+        // one repacked unit (src/kernels/repack_q3_k.wgsl): two words of 2-bit values, one of high bits, two scales
+        // minus 32 as signed bytes, d
+        const uint4 u = *reinterpret_cast<const uint4*>(row + (size_t)gblk * 128 + 16 * part);
+        const float d = __half2float(__ushort_as_half((unsigned short)(u.w >> 16)));
+        const float dl0 = __fmul_rn(d, (float)(int)(int8_t)(u.w & 0xffu)), dl1 = __fmul_rn(d, (float)(int)(int8_t)((u.w >> 8) & 0xffu));
+#pragma unroll
+        for (int t = 0; t < MT; t++) {
+            const float* xv = xs + (size_t)t * xs_stride + 32 * part;
+            float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+            for (int e = 0; e < 8; e++) {   // weights 4e .. 4e + 3: byte b of the word holds position 4e + b
+                const float4 a = *reinterpret_cast<const float4*>(xv + 4 * e);
+                const uint32_t q = ((e < 4 ? u.x : u.y) >> (2 * (e & 3))) & 0x03030303u;
+                const uint32_t h = (u.z >> e) & 0x01010101u;
+                float& s = e < 4 ? s0 : s1;
+                s = __fmaf_rn(a.x, (float)((int)(q & 0xffu) - ((h & 1u) ? 0 : 4)), s);
+                s = __fmaf_rn(a.y, (float)((int)((q >> 8) & 0xffu) - (((h >> 8) & 1u) ? 0 : 4)), s);
+                s = __fmaf_rn(a.z, (float)((int)((q >> 16) & 0xffu) - (((h >> 16) & 1u) ? 0 : 4)), s);
+                s = __fmaf_rn(a.w, (float)((int)(q >> 24) - (((h >> 24) & 1u) ? 0 : 4)), s);
+            }
+            acc[t] = __fmaf_rn(dl1, s1, __fmaf_rn(dl0, s0, acc[t]));
+        }
+    }
+};
+
 constexpr int SC_THREADS = 256;
 constexpr int SC_TILE = 2048;  // staged floats per token per tile (the reference's TILE_ONE)
 
@@ -337,7 +446,9 @@ bool matvec_variant_ok(uint32_t kernel, uint32_t variant) {
     const uint32_t family = (variant >> 16) & 0xffu, ks = (variant >> 8) & 0xffu;
     if (variant == 0) return true;
     if (variant >> 24) return false;
-    if (kernel == ZCU_K_MATVEC_BF16 || kernel == ZCU_K_MATVEC_F16) return family == ZCU_FAMILY_SCALAR && ks == 0;
+    if (kernel == ZCU_K_MATVEC_BF16 || kernel == ZCU_K_MATVEC_F16 || kernel == ZCU_K_MATVEC_Q3_K || kernel == ZCU_K_MATVEC_Q5_K ||
+        kernel == ZCU_K_MATVEC_Q6_K)
+        return family == ZCU_FAMILY_SCALAR && ks == 0;
     if (family == ZCU_FAMILY_SCALAR) return ks == 0;
     if (family == ZCU_FAMILY_MMA) {
         const uint32_t stages = variant & 0xffu;
@@ -349,6 +460,21 @@ bool matvec_variant_ok(uint32_t kernel, uint32_t variant) {
 
 zcu_result launch_matvec_q4_k(const LaunchArgs& a) { return launch_quant<W_Q4_K>(a, 256); }
 zcu_result launch_matvec_q8_0(const LaunchArgs& a) { return launch_quant<W_Q8_0>(a, 32); }
+
+// Q3_K (repacked), Q5_K and Q6_K (padded): the scalar family only.
+template <int TYPE>
+static zcu_result launch_kquant(const LaunchArgs& a) {
+    MvArgs v;
+    zcu_result r = parse_matvec(a, v, 256, true);
+    if (r != ZCU_OK) return r;
+    if (v.p.n == 0) return ZCU_OK;
+    if (v.has_rope || v.peer.wait_slot != PEER_NONE || v.peer.push_slot != PEER_NONE)
+        return zcu_fail(a, ZCU_E_UNSUPPORTED_KERNEL, "matvec: this weight type runs the scalar family, which takes no fused rope_append or peer exchange");
+    return launch_scalar<TYPE>(a, v);
+}
+zcu_result launch_matvec_q3_k(const LaunchArgs& a) { return launch_kquant<W_Q3_K>(a); }
+zcu_result launch_matvec_q5_k(const LaunchArgs& a) { return launch_kquant<W_Q5_K>(a); }
+zcu_result launch_matvec_q6_k(const LaunchArgs& a) { return launch_kquant<W_Q6_K>(a); }
 
 zcu_result launch_matvec_bf16(const LaunchArgs& a) {
     MvArgs v;

@@ -7,7 +7,7 @@
 
 namespace mv {
 
-enum { W_Q4_K = 0, W_Q8_0 = 1, W_BF16 = 2, W_F16 = 3 };
+enum { W_Q4_K = 0, W_Q8_0 = 1, W_BF16 = 2, W_F16 = 3, W_Q3_K = 4, W_Q5_K = 5, W_Q6_K = 6 };
 
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

@@ -282,6 +282,15 @@ zcu_result dispatch_kernel(zcu_context* c, uint32_t kernel, uint32_t variant, co
         case ZCU_K_REPACK_Q8_0: return launch_repack_q8_0(a);
         case ZCU_K_MATVEC_Q8_0: return launch_matvec_q8_0(a);
         case ZCU_K_MATVEC_Q4_K: return launch_matvec_q4_k(a);
+        case ZCU_K_MATVEC_Q3_K: return launch_matvec_q3_k(a);
+        case ZCU_K_MATVEC_Q5_K: return launch_matvec_q5_k(a);
+        case ZCU_K_MATVEC_Q6_K: return launch_matvec_q6_k(a);
+        case ZCU_K_REPAD: return launch_repad(a);
+        case ZCU_K_REPACK_Q3_K: return launch_repack_q3_k(a);
+        case ZCU_K_EMBED_Q3_K:
+        case ZCU_K_EMBED_Q5_K:
+        case ZCU_K_EMBED_Q6_K:
+        case ZCU_K_EMBED_IQ4_XS: return launch_embed_kquant(a, kernel);
         default: return fail(c, ZCU_E_UNSUPPORTED_KERNEL, "kernel %u is not implemented by the cuda backend", kernel);
     }
 }
@@ -693,6 +702,15 @@ const char* kernel_name(uint32_t k) {
         case ZCU_K_MATVEC_Q4_K: return "matvec_q4_k";
         case ZCU_K_EMBED_Q8_0: return "embed_q8_0";
         case ZCU_K_EMBED_Q4_K: return "embed_q4_k";
+        case ZCU_K_REPAD: return "repad";
+        case ZCU_K_REPACK_Q3_K: return "repack_q3_k";
+        case ZCU_K_MATVEC_Q3_K: return "matvec_q3_k";
+        case ZCU_K_MATVEC_Q5_K: return "matvec_q5_k";
+        case ZCU_K_MATVEC_Q6_K: return "matvec_q6_k";
+        case ZCU_K_EMBED_Q3_K: return "embed_q3_k";
+        case ZCU_K_EMBED_Q5_K: return "embed_q5_k";
+        case ZCU_K_EMBED_Q6_K: return "embed_q6_k";
+        case ZCU_K_EMBED_IQ4_XS: return "embed_iq4_xs";
         default: return nullptr;
     }
 }
@@ -740,7 +758,8 @@ ZCU_EXPORT size_t zcu_artifact(uint32_t kernel, uint32_t variant, char* out, siz
     const char* name = kernel_name(kernel);
     bool ok = name != nullptr;
     if (ok) {
-        const bool is_matvec = kernel == ZCU_K_MATVEC_Q4_K || kernel == ZCU_K_MATVEC_Q8_0 || kernel == ZCU_K_MATVEC_BF16 || kernel == ZCU_K_MATVEC_F16;
+        const bool is_matvec = kernel == ZCU_K_MATVEC_Q4_K || kernel == ZCU_K_MATVEC_Q8_0 || kernel == ZCU_K_MATVEC_BF16 || kernel == ZCU_K_MATVEC_F16 ||
+                               kernel == ZCU_K_MATVEC_Q3_K || kernel == ZCU_K_MATVEC_Q5_K || kernel == ZCU_K_MATVEC_Q6_K;
         const bool has_rung = kernel == ZCU_K_MATMUL_BF16 || kernel == ZCU_K_MATMUL_F16 || kernel == ZCU_K_MATMUL_Q4_K;  // tensor-core prefill rung
         if (is_matvec) ok = matvec_variant_ok(kernel, variant);
         else ok = variant == 0 || (has_rung && variant == ZCU_VARIANT_PREFILL_BF16_TC) ||

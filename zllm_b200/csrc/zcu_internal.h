@@ -119,6 +119,12 @@ struct LaunchArgs {
 // Each returns ZCU_OK or a negative result with a message in a.err.
 zcu_result launch_matvec_q4_k(const LaunchArgs& a);
 zcu_result launch_matvec_q8_0(const LaunchArgs& a);
+zcu_result launch_matvec_q3_k(const LaunchArgs& a);   // repacked units (repack_q3_k)
+zcu_result launch_matvec_q5_k(const LaunchArgs& a);
+zcu_result launch_matvec_q6_k(const LaunchArgs& a);   // blocks padded to 224 bytes (repad)
+zcu_result launch_repad(const LaunchArgs& a);
+zcu_result launch_repack_q3_k(const LaunchArgs& a);
+zcu_result launch_embed_kquant(const LaunchArgs& a, uint32_t kernel);
 zcu_result launch_matvec_bf16(const LaunchArgs& a);
 zcu_result launch_matvec_f16(const LaunchArgs& a);
 zcu_result launch_matmul_bf16(const LaunchArgs& a);

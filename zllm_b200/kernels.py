@@ -17,7 +17,10 @@ RMSNORM, MATMUL_BF16, MATMUL_F16, MATMUL_REDUCE, MATVEC_BF16, MATVEC_F16, SILU_M
 EMBED_BF16, EMBED_F16, ROPE_APPEND, ATTN_SPLIT, ATTN_SPLIT_WIDE, ATTN_SPLIT_SPARSE, ATTN_COMBINE = 7, 8, 9, 10, 11, 12, 13
 DELTA_PREP, DELTA_RULE, GATED_NORM = 18, 19, 20
 MARK_TOKENS, SAMPLE, DRAFT = 21, 22, 23
+REPAD, REPACK_Q3_K = 36, 37
 REPACK_Q8_0, QUANTIZE_Q8, MATVEC_Q8_0, MATVEC_Q4_K = 38, 39, 40, 42
+MATVEC_Q3_K, MATVEC_Q5_K, MATVEC_Q6_K = 41, 43, 44
+EMBED_Q3_K, EMBED_Q5_K, EMBED_Q6_K, EMBED_IQ4_XS = 52, 54, 55, 56
 MATMUL_Q8_0, MATMUL_Q4_K, EMBED_Q8_0, EMBED_Q4_K = 45, 48, 51, 53
 MATMUL_Q8_0_FLOAT = 46
 KERNEL_COUNT = 57
@@ -156,19 +159,30 @@ def sample_state_words(vocab: int) -> int:
     return 16 + 256 + 2 * sample_groups(vocab) + 2 * SAMPLE_CAP
 
 
+# Bytes per 256-weight block as the kernels read it (kernels.blockStride, kernels.zig:137-151) and as the file holds it.
+BLOCK_STRIDE = {"q3_k": 128, "q5_k": 176, "q6_k": 224, "iq4_xs": 144}
+FILE_BLOCK = {"q3_k": 110, "q5_k": 176, "q6_k": 210, "iq4_xs": 136}
+Repad = _struct("Repad", [("blocks", u32), ("src_bytes", u32), ("dst_bytes", u32), ("_pad", u32)])
+RepackQ3K = _struct("RepackQ3K", [("blocks", u32), ("_pad", u32 * 3)])
+
+
 def row_bytes(ttype: str, k: int) -> int:
     """Bytes per row as the kernels read it (kernels.rowBytes, kernels.zig:157-160)."""
     if ttype == "q8_0":
         return (k + k // 16 + 15) & ~15
     if ttype == "q4_k":
         return k // 256 * 144
+    if ttype in BLOCK_STRIDE:
+        return k // 256 * BLOCK_STRIDE[ttype]
     if ttype in ("bf16", "f16"):
         return 2 * k
     raise ValueError(ttype)
 
 
-MATVEC_KERNEL = {"q4_k": MATVEC_Q4_K, "q8_0": MATVEC_Q8_0, "bf16": MATVEC_BF16, "f16": MATVEC_F16}
-EMBED_KERNEL = {"q4_k": EMBED_Q4_K, "q8_0": EMBED_Q8_0, "bf16": EMBED_BF16, "f16": EMBED_F16}
+MATVEC_KERNEL = {"q4_k": MATVEC_Q4_K, "q8_0": MATVEC_Q8_0, "bf16": MATVEC_BF16, "f16": MATVEC_F16, "q3_k": MATVEC_Q3_K, "q5_k": MATVEC_Q5_K,
+                 "q6_k": MATVEC_Q6_K}
+EMBED_KERNEL = {"q4_k": EMBED_Q4_K, "q8_0": EMBED_Q8_0, "bf16": EMBED_BF16, "f16": EMBED_F16, "q3_k": EMBED_Q3_K, "q5_k": EMBED_Q5_K,
+                "q6_k": EMBED_Q6_K, "iq4_xs": EMBED_IQ4_XS}
 
 
 def elementwise(count: int):
@@ -270,6 +284,14 @@ class Launcher:
 
     def embed(self, ttype, tokens, w, out, m, dim, row0, chunk_rows, stride=0):
         self.launch(EMBED_KERNEL[ttype], Embed(dim, row0, chunk_rows, stride), [tokens, w, out], (m, 1, 1))
+
+    def layout(self, ttype: str, src, dst, blocks: int):
+        """File blocks -> the layout the multiplies read (Launcher.layout, kernels.zig): repack_q3_k for Q3_K, repad for
+        the types whose blocks are padded."""
+        if ttype == "q3_k":
+            self.launch(REPACK_Q3_K, RepackQ3K(blocks), [src, dst], elementwise(blocks * 8))
+        else:
+            self.launch(REPAD, Repad(blocks, FILE_BLOCK[ttype], BLOCK_STRIDE[ttype], 0), [src, dst], elementwise(blocks * BLOCK_STRIDE[ttype] // 4))
 
     def repack_q8_0(self, src, dst, rows, k):
         self.launch(REPACK_Q8_0, RepackQ80(rows, k), [src, dst], elementwise(rows * row_bytes("q8_0", k) // 4))

@@ -56,6 +56,25 @@ def q4_k_weights(rng: np.random.Generator, n: int, k: int, lo: float = 1e-4, hi:
     return blocks.reshape(n, nb * 144)
 
 
+KQUANT_BLOCK_BYTES = {"q3_k": 110, "q5_k": 176, "q6_k": 210, "iq4_xs": 136}
+_KQUANT_D_AT = {"q3_k": (108,), "q5_k": (0, 2), "q6_k": (208,), "iq4_xs": (0,)}   # byte offsets of the f16 super-scales
+
+
+def kquant_weights(rng: np.random.Generator, ttype: str, n: int, k: int, lo: float = 1e-4, hi: float = 1e-2,
+                   signed_scales: bool = False) -> np.ndarray:
+    """[n, k/256 * block_bytes] uint8 in the GGUF file layout of Q3_K, Q5_K, Q6_K or IQ4_XS (src/ref/tensor.zig:54-181):
+    random bytes for the packed values and sub-block scales, f16 super-scales uniform in [lo, hi]."""
+    assert k % 256 == 0
+    nb, bb = k // 256, KQUANT_BLOCK_BYTES[ttype]
+    blocks = rng.integers(0, 256, size=(n, nb, bb), dtype=np.uint8)
+    for at in _KQUANT_D_AT[ttype]:
+        d = f16_uniform(rng, lo, hi, (n, nb, 1))
+        if signed_scales:
+            d = d * rng.choice(np.array([-1, 1], dtype=np.float16), size=(n, nb, 1))
+        blocks[:, :, at:at + 2] = d.view(np.uint8).reshape(n, nb, 2)
+    return blocks.reshape(n, nb * bb)
+
+
 def to_bf16_bits(x: np.ndarray) -> np.ndarray:
     """f32 -> bf16 bits, round to nearest even (src/ref/matmul.zig:250-255)."""
     b = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32)
