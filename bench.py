@@ -287,10 +287,6 @@ class MatvecQ4K:
     def e2e_bytes(self):
         return self.host_x.nbytes, self.pinned_out.numel() * 4
 
-    def check(self):
-        """A cheap guard that the timed kernel does the work: rows of copy 0 against numpy."""
-        return True
-
     def roofline(self, ms_per_step: float):
         peak, kind = measured_hbm_peak()
         us = ms_per_step * 1e3 / self.launches_per_step()

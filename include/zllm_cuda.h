@@ -53,7 +53,13 @@ enum {
     ZCU_E_INVALID = -12            /* a bad argument to this interface */
 };
 
-/* Kernel identities: @intFromEnum(kernels.Kernel), src/kernels/kernels.zig:24-101.
+/* Notes on identities whose dispatch differs in shape from the reference's (parameter blocks and bindings are the
+ * reference's in every case):
+ *   ZCU_K_SAMPLE       the dispatch of phase 0 (prep) makes the whole draw in one cooperative launch; phases 1-10 are
+ *                      accepted and launch nothing; phase 11 (unbump) undoes the count (src/kernels/sample.wgsl)
+ *   ZCU_K_REPAD, ZCU_K_REPACK_Q3_K   file blocks -> kernels.blockStride layouts; ZCU_K_MATVEC_Q3_K/Q5_K/Q6_K and the
+ *                      matching embeds read those (Embed.stride != 0: file layout)
+ * Kernel identities: @intFromEnum(kernels.Kernel), src/kernels/kernels.zig:24-101.
  * Only the identities of the decode/prefill path are implemented; the rest
  * report "missing" (an empty artifact) exactly as a backend that lacks a
  * kernel does (src/kernels/kernels.zig:752-755). */
