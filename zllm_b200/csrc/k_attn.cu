@@ -243,10 +243,9 @@ __global__ void __launch_bounds__(attn::AM_THREADS, 3) attn_split_mma(PAttention
                                                                      const uint32_t* __restrict__ seq_pos, int* __restrict__ status) {
     extern __shared__ __align__(128) unsigned char dyn_smem[];
     ATRACE(0);
-    // launched as a programmatic dependent: the queries and the newest cache row come from the kernel before
-    asm volatile("griddepcontrol.wait;\n" ::: "memory");
-    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
-    attn::attn_split_mma_body<HD>(dyn_smem, p, qg, kc, vc, part, step, seq_pos, (int)blockIdx.x, (int)blockIdx.y, (int)blockIdx.z, status);
+    // (a programmatic dependent: the body waits for the kernel before - after its first copies where those read only
+    // rows of earlier steps)
+    attn::attn_split_mma_body<HD, true>(dyn_smem, p, qg, kc, vc, part, step, seq_pos, (int)blockIdx.x, (int)blockIdx.y, (int)blockIdx.z, status);
 }
 
 __global__ void __launch_bounds__(attn::AC_THREADS) attn_combine_kernel(PAttention p, const float* __restrict__ qg,

@@ -261,7 +261,7 @@ __device__ __forceinline__ uint32_t split_pair(float x0, float x1, bool low) {
     return (uint32_t)__half_as_ushort(h0) | ((uint32_t)__half_as_ushort(h1) << 16);
 }
 
-template <int HD>
+template <int HD, bool PDL = false>
 __device__ __forceinline__ void attn_split_mma_body(unsigned char* smem, const PAttention& p, const float* __restrict__ qg,
                                                     const __half* __restrict__ kc, const __half* __restrict__ vc,
                                                     float* __restrict__ part, const PStep* __restrict__ step,
@@ -291,6 +291,12 @@ __device__ __forceinline__ void attn_split_mma_body(unsigned char* smem, const P
     const size_t kv_stride = (size_t)p.kv_heads * HD;
     const int q_head = p.gated ? 2 * HD : HD;
     const int r0 = 16 * warp;                    // this warp's rows of the tiles
+    // Launched as a programmatic dependent: the queries and the step's new cache rows come from the kernel before.
+    // The step's new rows start at the sequence's position (a sequence's own, or the step's first); a block that
+    // ends before them holds only rows of earlier steps, and its copies may start while that kernel still runs.
+    const int first_new = seq_pos ? (int)seq_pos[row] : (int)step->pos0;
+    const bool early = PDL && k0 + AF_KEYS <= first_new;
+    if (PDL && !early) asm volatile("griddepcontrol.wait;\n" ::: "memory");
 
     // ---- this warp's rows of K, then of V, on their way (two groups: the scores need only the first)
     ATRACE(1);
@@ -308,6 +314,8 @@ __device__ __forceinline__ void attn_split_mma_body(unsigned char* smem, const P
         asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(vt_s + (uint32_t)key * RS + 16u * piece), "l"(vc + src) : "memory");
     }
     asm volatile("cp.async.commit_group;\n" ::: "memory");
+    if (early) asm volatile("griddepcontrol.wait;\n" ::: "memory");
+    if (PDL) asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
     // ---- the group's queries as A fragments: entry (k-step, lane) = {a0, a2} of that lane (head g & 3; hi for g < 4,
     //      lo for g >= 4; rows 8-15 of A stay zero). One entry per thread for head_dim 128.
     for (int e = tid; e < KSTEPS * 32; e += AM_THREADS) {
