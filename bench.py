@@ -339,7 +339,7 @@ class DecodeStep:
     context = 8192
 
     def __init__(self, dist: Dist, batch: int = 1, variant: int = 0, layers: int = 32,
-                 exchange: str = "peer", attn_variant: int = 0, batched: str = "auto", tune: bool = True):
+                 exchange: str = "peer", attn_variant: int = 0, batched: str = "auto", tune: bool = True, early: bool = False):
         import torch
 
         from zllm_b200 import abi
@@ -377,7 +377,7 @@ class DecodeStep:
                                   DenseProgram.arena_slots(self.cfg), handles)
         self.prog = DenseProgram(self.ctx, self.cfg, self.weights, batch, alloc, self.shard, arena=arena,
                                  variants={"attn_split": attn_variant} if attn_variant else None,
-                                 batched=None if batched == "auto" else batched == "on",
+                                 batched=None if batched == "auto" else batched == "on", early=early,
                                  gather=nccl_gather(dist.dist, dist.rank, dist.world) if self.exchange == "nccl" else None)
         if arena is not None:
             class _View:  # the arena's logits as a torch tensor (zero copy), for the read-back of the e2e leg
@@ -482,19 +482,28 @@ class DecodeStep:
         shapes = layer_weight_shapes(cfg, self.shard)
         p = self.prog
         if self.mv_graph is None:
-            # the body multiplies of a step as the step launches them, without the attention between them (inputs as
-            # they lie: nothing pushes exchange slots here, so no multiply waits for one)
+            # the body multiplies of a step as the step launches them, without the attention between them. On one
+            # GPU they hand their vectors on through the exchange slots exactly as in the step (x after wo -> gate|up
+            # -> down -> the next layer's Q|K|V); only wo, whose input the attention would push, reads plain memory,
+            # and the last down pushes nothing (the head, its consumer, is not part of this list).
+            chained = p.arena is not None and self.dist.world == 1   # (a world-of-one exchange, when the program was given an arena)
             self.ctx.capture_begin()
             for il in range(cfg.layers):
                 lw = self.weights["layers"][il]
+                _, s_xwo, s_act, s_xdown, s_prev = p._slots(il) if chained else (None,) * 5
+                if chained and il == cfg.layers - 1:
+                    s_xdown = None
                 p._matvec(cfg.body_type, p.x, lw["wqkv"], p.qkv, p.qkv_row, cfg.hidden, flags=K.NORM, eps=cfg.eps,
-                          norm_w=lw["attn_norm"])
+                          norm_w=lw["attn_norm"], wait=s_prev)
                 p._matvec(cfg.body_type, p.att, lw["wo"], p.x, p.le, cfg.q_dim, col0=self.shard.rank * p.le,
-                          out_stride=cfg.hidden, flags=K.ACCUMULATE)
+                          out_stride=cfg.hidden, flags=K.ACCUMULATE, push=s_xwo)
                 p._matvec(cfg.body_type, p.x, lw["wgu"], p.act, p.lff, cfg.hidden, col0=self.shard.rank * p.lff,
-                          out_stride=cfg.ff, flags=K.NORM | K.SILU_PAIR, eps=cfg.eps, half=p.lff, norm_w=lw["ffn_norm"])
+                          out_stride=cfg.ff, flags=K.NORM | K.SILU_PAIR, eps=cfg.eps, half=p.lff, norm_w=lw["ffn_norm"],
+                          wait=s_xwo, push=s_act)
                 p._matvec(cfg.body_type, p.act, lw["wdown"], p.x, p.le, cfg.ff, col0=self.shard.rank * p.le,
-                          out_stride=cfg.hidden, flags=K.ACCUMULATE)
+                          out_stride=cfg.hidden, flags=K.ACCUMULATE, wait=s_act, push=s_xdown)
+            if chained:
+                p.L.peer_next()
             self.mv_graph = self.ctx.capture_end()
         for _ in range(3):
             self.ctx.graph_launch(self.mv_graph)
@@ -1134,6 +1143,7 @@ def run_cuda(args):
         kw["attn_variant"] = args.attn_variant
         kw["batched"] = args.batched
         kw["tune"] = not args.no_tune
+        kw["early"] = args.early
         if args.layers:
             kw["layers"] = args.layers
     wl = WORKLOADS[args.workload](dist, **kw)
@@ -1336,6 +1346,8 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
     ap.add_argument("--batched", default="auto", choices=["auto", "on", "off"],
                     help="decode: Q4_K multiplies in one pass for all sequences (tcgen05 family; auto = for 5..64 sequences on one GPU)")
+    ap.add_argument("--early", action="store_true",
+                    help="decode with the peer exchange: multiplies wait for their activations' tags only, not for the kernel before them")
     ap.add_argument("--no-tune", action="store_true", help="decode: skip the load-time sweep over the multiply's variants")
     ap.add_argument("--attn-variant", type=int, default=0, help="decode: form of attn_split's fast path (0 default, 1-4: k_attn.cu)")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],

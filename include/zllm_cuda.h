@@ -103,7 +103,8 @@ enum {
     ZCU_K_EMBED_IQ4_XS = 56,
     ZCU_K_COUNT = 57,
     /* identities of this backend only (above the reference's enum) */
-    ZCU_K_EXT_PEER_WAIT = 64   /* waits for one tensor-parallel exchange; parameter block = zcu_peer_ext, no bindings */
+    ZCU_K_EXT_PEER_WAIT = 64,  /* waits for one tensor-parallel exchange; parameter block = zcu_peer_ext; binding: the vector */
+    ZCU_K_EXT_PEER_NEXT = 65   /* ends a run of a launch list that uses exchanges; parameter block = zcu_peer_ext, its slots unused */
 };
 
 /* Variant ids of a matvec pipeline (create_kernel's `variant`). 0 is the
@@ -271,7 +272,10 @@ zcu_result zcu_graph_destroy(zcu_context *context, uint32_t graph);
  * to its parameter block: matvec_q4_k/q8_0 (tensor-core family) and attn_combine with `push_slot` also store each
  * output, tagged, into the slot of every rank; matvec_* with `wait_slot` read their activations from the slots
  * and wait, element by element, for the tag of the exchange; ZCU_K_EXT_PEER_WAIT (binding: the vector) waits the
- * same way and fills in the plain floats, for a host about to read them. The reference has no multi-GPU path;
+ * same way and fills in the plain floats, for a host about to read them. Tags derive from the slot and from an
+ * epoch, a local word that counts the runs of the launch list: a list that uses exchanges and runs more than once
+ * (a replayed step) ends with ZCU_K_EXT_PEER_NEXT, which moves the epoch on; within a run a slot is written by at
+ * most one dispatch (however many launches that dispatch takes). The reference has no multi-GPU path;
  * this is the row/head sharding its kernels allow (every output row, head and state column is computed by one
  * rank with unchanged arithmetic, so results are bitwise those of one GPU). A wait gives up after 2 s (or the limit
  * set by zcu_peer_wait_limit) with ZCU_E_GPU at the next sync; every later wait of the context then gives up at once
@@ -284,8 +288,15 @@ typedef struct zcu_peer_ext {
     uint32_t magic;     /* ZCU_PEER_MAGIC */
     uint32_t wait_slot; /* or ZCU_PEER_NONE */
     uint32_t push_slot; /* or ZCU_PEER_NONE */
-    uint32_t reserved;
+    uint32_t flags;     /* ZCU_PEER_EARLY or 0 */
 } zcu_peer_ext;
+/* With ZCU_PEER_EARLY a matvec_q4_k / matvec_q8_0 (tensor-core family) that reads its activations from `wait_slot`
+ * waits for nothing but their tags: it starts its arithmetic while the kernel before it is still ending (it does
+ * not pass the kernel boundary first; it does so only before it writes its outputs, so that "this kernel has ended"
+ * still means "everything before it has"). The caller promises that whatever else the dispatch reads or
+ * overwrites (the output it accumulates onto, the cache rows and Step of a fused rope_append) was finished with
+ * before the dispatch that precedes it began. */
+#define ZCU_PEER_EARLY 1u
 zcu_result zcu_ipc_export(zcu_context *context, void *ptr, void *out_handle64);
 zcu_result zcu_ipc_open(zcu_context *context, const void *handle64, void **out_ptr);
 zcu_result zcu_peer_config(zcu_context *context, uint32_t rank, uint32_t world, const uint64_t *bases, uint64_t arena_bytes,

@@ -39,7 +39,7 @@ def test_attn_decode_f16_cache(ref, gpu, launcher, heads, kv_heads, hd, gated):
     q_head = 2 * hd if gated else hd
     q_rows = uniform(rng, (m, heads * q_head), 1.0)
     fast = heads // kv_heads <= 4 and hd in (64, 128)
-    for variant in ((0, 1, 3) if fast else (0,)):  # both arithmetics of the fast path; the generic path otherwise
+    for variant in ((0, 1, 3, 4) if fast else (0,)):  # both arithmetics of the fast path; the generic path otherwise
         got = run_attention(gpu, launcher, q_rows, kcf.view(np.uint16), vcf.view(np.uint16), pos0, heads, kv_heads, hd,
                             gated, K.KV_F16, 256, variant=variant)
         _check_rows(ref, got, q_rows, kcf, vcf, pos0, m, heads, kv_heads, hd, gated, q_head)
@@ -73,7 +73,8 @@ def test_attn_decode_f32_cache_and_single_key(ref, gpu, launcher):
         assert rel_err(got[0, h], want) < TOL
 
 
-def test_attn_decode_llama_shape_8192(ref, gpu, launcher):
+@pytest.mark.parametrize("variant", [0, 4])
+def test_attn_decode_llama_shape_8192(ref, gpu, launcher, variant):
     # The decode-step configuration: 32 query / 8 KV heads of 128, f16 cache ~ N(0,1) with 8192 positions.
     rng = synth.rng_for("cfg5", "kv0")
     heads, kv_heads, hd, pos0 = 32, 8, 128, 8192
@@ -81,7 +82,7 @@ def test_attn_decode_llama_shape_8192(ref, gpu, launcher):
     vcf = rng.normal(size=(pos0 + 1, kv_heads, hd)).astype(np.float16)
     q = rng.normal(size=(1, heads * hd)).astype(np.float32)
     got = run_attention(gpu, launcher, q, kcf.view(np.uint16), vcf.view(np.uint16), pos0, heads, kv_heads, hd, False,
-                        K.KV_F16, pos0 + 1)
+                        K.KV_F16, pos0 + 1, variant=variant)
     want = ref.attend_decode(q.reshape(heads, hd), kcf.view(np.uint16), vcf.view(np.uint16), pos0 + 1, heads, kv_heads,
                              hd, K.attention_scale(hd))
     assert rel_err(got[0], want) < TOL
@@ -160,20 +161,22 @@ def test_both_arithmetics_of_the_split_agree(gpu, launcher):
     dq, dk, dv = gpu.put(q), gpu.put(kc.view(np.uint16)), gpu.put(vc.view(np.uint16))
     step, dpos = gpu.put(np.array([rows, 0, 0, 0], dtype=np.uint32)), gpu.put(positions)
     got = []
-    for variant in (1, 3):
+    for variant in (1, 3, 4):
         part = gpu.zeros(rows * heads * max_blocks * (hd + 2) * 4)
         out = gpu.zeros(rows * heads * hd * 4)
         launcher.launch(K.ATTN_SPLIT, p, [dq, dk, dv, part, step, dpos], (kv_heads, max_blocks, rows), variant)
         launcher.launch(K.ATTN_COMBINE, p, [dq, part, out, step, dpos], (heads, rows, 1))
         gpu.sync()
         got.append((part.download(np.uint32), out.download(np.uint32)))
-    assert rel_err(got[1][1].view(np.float32), got[0][1].view(np.float32)) < TOL
     assert np.abs(got[0][1].view(np.float32)).max() > 0
-    # a block's partial {max, sum exp, sum exp * v} is the same softmax state in both forms
-    pa, pb = (g[0].view(np.float32).reshape(rows, heads, max_blocks, hd + 2) for g in got)
-    for t in range(rows):
-        used = -(-(int(positions[t]) + 1) // 128)
-        assert rel_err(pb[t, :, :used, 0], pa[t, :, :used, 0]) < TOL and rel_err(pb[t, :, :used, 1:], pa[t, :, :used, 1:]) < TOL, t
+    pa = got[0][0].view(np.float32).reshape(rows, heads, max_blocks, hd + 2)
+    for other in got[1:]:   # the tensor-core forms (K staged in shared memory, K through registers) against the CUDA-core form
+        assert rel_err(other[1].view(np.float32), got[0][1].view(np.float32)) < TOL
+        # a block's partial {max, sum exp, sum exp * v} is the same softmax state in every form
+        pb = other[0].view(np.float32).reshape(rows, heads, max_blocks, hd + 2)
+        for t in range(rows):
+            used = -(-(int(positions[t]) + 1) // 128)
+            assert rel_err(pb[t, :, :used, 0], pa[t, :, :used, 0]) < TOL and rel_err(pb[t, :, :used, 1:], pa[t, :, :used, 1:]) < TOL, t
 
 
 def test_fp8_cache_append_and_attention(ref, gpu, launcher):

@@ -161,11 +161,12 @@ def test_exchange_slots_chain_through_the_sharded_launch_list():
     prog = DenseProgram(ctx, cfg, weights, 1, ctx.alloc, Shard(1, 2), arena=FakeArena())
     per_layer = 6
     prog.set_rope_table(ctx.alloc(256))
-    seen = []
+    seen, raws = [], []
     real = prog.L.launch
 
     def spy(kernel, params, args, groups, variant=0):
         raw = bytes(params)
+        raws.append(raw)
         ext = K.PeerExt.from_buffer_copy(raw[-16:]) if len(raw) >= 16 else None
         seen.append((kernel, (ext.wait_slot, ext.push_slot) if ext is not None and ext.magic == K.PEER_MAGIC else None))
         real(kernel, params, args, groups, variant)
@@ -173,7 +174,7 @@ def test_exchange_slots_chain_through_the_sharded_launch_list():
     prog.L.launch = spy
     before = ctx.launch_count()
     prog.record_step(17)
-    assert ctx.launch_count() - before == len(seen) == 2 + per_layer * cfg.layers + 1 == prog.launches_per_step
+    assert ctx.launch_count() - before == len(seen) == 2 + per_layer * cfg.layers + 2 == prog.launches_per_step
     none = K.PEER_NONE
     exts = [e for _, e in seen]
     assert exts[0] is None                                    # embed: every rank decodes the row itself
@@ -183,8 +184,19 @@ def test_exchange_slots_chain_through_the_sharded_launch_list():
         assert qkv == (None if il == 0 else (4 * il - 1, none))  # the residual stream of the layer before
         assert ops[1] is None and ops[2] == (none, 4 * il)       # attn_split, then attn_combine pushes the heads' columns
         assert wo == (4 * il, 4 * il + 1) and gu == (4 * il + 1, 4 * il + 2) and down == (4 * il + 2, 4 * il + 3)
-    assert exts[-2] == (4 * cfg.layers - 1, 4 * cfg.layers)       # the head
-    assert seen[-1] == (K.EXT_PEER_WAIT, (4 * cfg.layers, none))  # the host's wait for the logits
+    assert exts[-3] == (4 * cfg.layers - 1, 4 * cfg.layers)       # the head
+    assert seen[-2] == (K.EXT_PEER_WAIT, (4 * cfg.layers, none))  # the host's wait for the logits
+    assert seen[-1] == (K.EXT_PEER_NEXT, (none, none))            # the run ends: the next one tags its exchanges anew
+    def early_flags():
+        return sum(K.PeerExt.from_buffer_copy(raw[-16:]).flags & K.PEER_EARLY for raw in raws
+                   if len(raw) >= 16 and K.PeerExt.from_buffer_copy(raw[-16:]).magic == K.PEER_MAGIC)
+
+    waits = [e for e in exts if e is not None and e[0] != none]
+    assert early_flags() == 0                                     # by default every multiply passes the kernel boundary first
+    raws.clear()
+    prog.early = True
+    prog.record_step(17)
+    assert early_flags() == len(waits) - 1                        # as an option all that wait do so early (not the host's wait)
     pushed = [e[1] for e in exts if e is not None and e[1] != none]
     assert sorted(pushed) == list(range(DenseProgram.arena_slots(cfg)))
     assert len(bytes(K.with_peer(K.Matvec(1, 2, 3, 4, 0.0, 0, 0, 0), wait=3))) == C.sizeof(K.Matvec) + 16
@@ -343,11 +355,12 @@ def test_exchange_slots_chain_through_the_sharded_hybrid_launch_list():
     prog.set_rope_table(ctx.alloc(256))
     assert (prog.lvh, prog.lkh, prog.v0, prog.k0) == (2, 2, 2, 0)
     assert [c is not None for c in prog.kc] == [False, False, False, True]
-    seen = []
+    seen, raws = [], []
     real = prog.L.launch
 
     def spy(kernel, params, args, groups, variant=0):
         raw = bytes(params)
+        raws.append(raw)
         ext = K.PeerExt.from_buffer_copy(raw[-16:]) if len(raw) >= 16 else None
         seen.append((kernel, (ext.wait_slot, ext.push_slot) if ext is not None and ext.magic == K.PEER_MAGIC else None))
         real(kernel, params, args, groups, variant)

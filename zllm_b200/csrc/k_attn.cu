@@ -248,6 +248,16 @@ __global__ void __launch_bounds__(attn::AM_THREADS, 3) attn_split_mma(PAttention
     attn::attn_split_mma_body<HD, true>(dyn_smem, p, qg, kc, vc, part, step, seq_pos, (int)blockIdx.x, (int)blockIdx.y, (int)blockIdx.z, status);
 }
 
+template <int HD>
+__global__ void __launch_bounds__(attn::AM_THREADS, 4) attn_split_kreg(PAttention p, const float* __restrict__ qg,
+                                                                      const __half* __restrict__ kc,
+                                                                      const __half* __restrict__ vc, float* __restrict__ part,
+                                                                      const PStep* __restrict__ step,
+                                                                      const uint32_t* __restrict__ seq_pos, int* __restrict__ status) {
+    extern __shared__ __align__(128) unsigned char dyn_smem[];
+    attn::attn_split_kreg_body<HD, true>(dyn_smem, p, qg, kc, vc, part, step, seq_pos, (int)blockIdx.x, (int)blockIdx.y, (int)blockIdx.z, status);
+}
+
 __global__ void __launch_bounds__(attn::AC_THREADS) attn_combine_kernel(PAttention p, const float* __restrict__ qg,
                                                                        const float* __restrict__ part, float* __restrict__ out,
                                                                        const PStep* __restrict__ step,
@@ -259,7 +269,6 @@ __global__ void __launch_bounds__(attn::AC_THREADS) attn_combine_kernel(PAttenti
     asm volatile("griddepcontrol.wait;\n" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
     attn::attn_combine_body(vblock_of_cta(dyn_smem), p, qg, part, out, step, seq_pos, kb, status, &pu);
-    peer::finish(pu, gridDim.x * gridDim.y);
 }
 
 // Copies an exchanged vector out of its exchange slots into the plain floats beside them, waiting for every
@@ -329,6 +338,18 @@ zcu_result launch_attn_split(const LaunchArgs& a) {
             // one CTA per block on the f16 tensor cores (queries and probabilities as two f16 terms)
             const size_t msmem = attn::attn_mma_smem(hd);
             auto mk = hd == 128 ? attn_split_mma<128> : attn_split_mma<64>;
+            if (cudaFuncSetAttribute(mk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)msmem) != cudaSuccess) {
+                cudaGetLastError();
+                return zcu_fail(a, ZCU_E_GPU, "attn_split: %zu bytes of shared memory refused", msmem);
+            }
+            cudaError_t e = launch_pdl(mk, grid, dim3(attn::AM_THREADS), msmem, a.stream, p, qg, kc, vc, part, step, seq_pos, a.status);
+            if (e != cudaSuccess) return zcu_fail(a, ZCU_E_GPU, "attn_split: launch failed: %s", cudaGetErrorString(e));
+            return ZCU_OK;
+        }
+        if (a.variant == 4) {
+            // the same arithmetic with K loaded straight into the tensor cores' B fragments: four CTAs per SM
+            const size_t msmem = attn::attn_kreg_smem(hd);
+            auto mk = hd == 128 ? attn_split_kreg<128> : attn_split_kreg<64>;
             if (cudaFuncSetAttribute(mk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)msmem) != cudaSuccess) {
                 cudaGetLastError();
                 return zcu_fail(a, ZCU_E_GPU, "attn_split: %zu bytes of shared memory refused", msmem);
@@ -473,6 +494,21 @@ zcu_result launch_peer_wait(const LaunchArgs& a) {
     if (count == 0) return ZCU_OK;
     const int blocks = (int)((count + 255) / 256 < (uint32_t)(a.sm_count * 4) ? (count + 255) / 256 : (uint32_t)(a.sm_count * 4));
     peer_unpack_kernel<<<blocks, 256, 0, a.stream>>>(pu, (float*)a.b[0].ptr, count, a.status);
+    ZCU_CHECK_LAUNCH(a);
+    return ZCU_OK;
+}
+
+// Ends a run of the launch list (ZCU_K_EXT_PEER_NEXT; parameter block: a PPeer, its slots unused): the epoch that
+// every exchange tag of the list derives from moves on. An ordinary launch: it starts after everything before it in
+// the stream has ended, and what follows starts after it.
+__global__ void peer_next_kernel(uint32_t* epoch) { epoch[0] += 1; }
+
+zcu_result launch_peer_next(const LaunchArgs& a) {
+    PeerUse pu;
+    zcu_result pr = parse_peer(a, pu, nullptr, nullptr);
+    if (pr != ZCU_OK) return pr;
+    ZCU_NEED(a, pu.t.epoch != nullptr, "peer_next: the parameter block is not a peer block");
+    peer_next_kernel<<<1, 1, 0, a.stream>>>(pu.t.epoch);
     ZCU_CHECK_LAUNCH(a);
     return ZCU_OK;
 }

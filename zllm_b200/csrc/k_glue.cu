@@ -125,7 +125,6 @@ __global__ void __launch_bounds__(256) gated_norm_kernel(PGatedNorm p, float* __
         o[base + b] = res;
         if (pu.push_slot != PEER_NONE) peer::push(pu, o + base + b, res, peer::push_tag(pu));
     }
-    peer::finish(pu, gridDim.x * gridDim.y);
 }
 
 // ---- delta_prep (src/kernels/delta_prep.wgsl): bindings proj, conv_w, hist,

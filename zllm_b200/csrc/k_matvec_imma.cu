@@ -52,6 +52,10 @@ constexpr int SMEM_MAX = 220 * 1024;   // (a fifth stage at k = 4096 would fit i
 #ifdef ZCU_TRACE
 // Debug build only: per-CTA timestamps of the kernel's phases (globaltimer, ns).
 __device__ unsigned long long g_mv_trace[256 * 12];
+__device__ int g_mv_box = 16 * 160;   // bytes a box copy delivers (debug: other box shapes)
+__device__ int g_mv_dbg;   // bit 0: the tile stream without its arithmetic; bit 1: the arithmetic without copies or waits
+#define MV_DBG g_mv_dbg
+#define MV_BOX (uint32_t)g_mv_box
 #define TRACE(i)                                                                    \
     do {                                                                            \
         if (threadIdx.x == 0 && blockIdx.x < 256) {                                 \
@@ -62,6 +66,14 @@ __device__ unsigned long long g_mv_trace[256 * 12];
     } while (0)
 #else
 #define TRACE(i) do {} while (0)
+#define MV_DBG 0
+#define MV_BOX (16u * TILE_ROW)
+#endif
+
+#ifdef ZCU_TRACE
+int g_dbg_box_bytes = 0, g_dbg_box_rows = 0;
+const uint8_t* g_pf_base = nullptr;
+size_t g_pf_size = 0, g_pf_total = 0;
 #endif
 
 // Tensor map of a weight matrix for these tiles: the matrix as bytes, boxes of 16 rows x 160 bytes (or x 16
@@ -71,6 +83,9 @@ __device__ unsigned long long g_mv_trace[256 * 12];
 // row's end. `rows`: every row the multiply may touch (both halves of a SILU_PAIR matrix).
 bool weight_map(CUtensorMap* map, const void* w, bool q4, int k, size_t rows, bool scales) {
     const uint64_t rb = q4 ? (uint64_t)(k / 256) * 144 : (((uint64_t)k + k / 16 + 15) & ~(uint64_t)15);
+#ifdef ZCU_TRACE
+    if (g_dbg_box_bytes && !scales) return tma::bytes_2d(map, w, rows, rb, (uint32_t)g_dbg_box_bytes, (uint32_t)g_dbg_box_rows);
+#endif
     return tma::bytes_2d(map, w, rows, rb, scales ? 16u : (uint32_t)TILE_ROW, 16u);
 }
 
@@ -160,7 +175,8 @@ __global__ void __launch_bounds__(W * 32, 16 / W) matvec_imma(PMatvec p, const f
                                                              const __grid_constant__ CUtensorMap smap, float* __restrict__ out,
                                                              const float* __restrict__ norm_w, int t0, int seg_max,
                                                              int* __restrict__ status, const __grid_constant__ MvRope rope_arg,
-                                                             const __grid_constant__ PeerUse pu_arg) {
+                                                             const __grid_constant__ PeerUse pu_arg, const uint8_t* __restrict__ next_w,
+                                                             uint32_t next_bytes) {
     constexpr bool Q4 = TYPE == W_Q4_K;
     constexpr int NB = Q4 ? NT : (NT + 1) / 2;   // 8-column blocks: one per token (Q4_K), one per two tokens (Q8_0)
     constexpr int SLOTS = Q4 ? NT : 2 * NB;       // token slots of a parked segment
@@ -216,7 +232,7 @@ __global__ void __launch_bounds__(W * 32, 16 / W) matvec_imma(PMatvec p, const f
             const int rtl = pair ? is_rp >> 1 : is_rp;
             const int y = ((pair && (is_rp & 1)) ? (int)p.half : 0) + (rt_lo + rtl) * 16;
             if constexpr (Q4) {
-                mbar_expect_tx(mb, 16u * TILE_ROW);
+                mbar_expect_tx(mb, MV_BOX);
                 tma_tile(dst, &wmap, is_unit * 144, y, mb);
             } else {
                 // four blocks of values, and the 16 bytes that hold the scales of blocks (b0 & ~7) .. +7 (k is a
@@ -234,8 +250,30 @@ __global__ void __launch_bounds__(W * 32, 16 / W) matvec_imma(PMatvec p, const f
             is_rp++;
         }
     };
-#pragma unroll
-    for (int i = 0; i < STAGES - 1; i++) issue();
+    const int dbg = MV_DBG;
+    // The copy engine takes a box every few tens of cycles, and an issuing lane waits while its queue is full:
+    // 16 warps x (STAGES - 1) boxes keep it busy for more than a microsecond. Each warp asks for its first tile
+    // here and for the rest of its ring between the steps of the activation staging below.
+    int fill = (dbg & 2) ? 0 : STAGES - 2;
+    if (!(dbg & 2)) issue();
+    auto fill_one = [&]() {
+        if (fill > 0) {
+            issue();
+            fill--;
+        }
+    };
+
+    // the weights of the launch after this one: asked into L2 now, so that HBM keeps streaming through this
+    // kernel's fixed phases and across the boundary (this kernel's own tiles were asked for by its predecessor)
+    if (next_w != nullptr) {
+        constexpr uint32_t PF = 4096;
+        const uint32_t pieces = (next_bytes + PF - 1) / PF;
+        const uint32_t p_lo = (uint32_t)(((uint64_t)cta * pieces) / (uint32_t)ncta), p_hi = (uint32_t)(((uint64_t)(cta + 1) * pieces) / (uint32_t)ncta);
+        for (uint32_t i = p_lo + (uint32_t)tid; i < p_hi; i += THREADS) {
+            const uint32_t off = i * PF, len = min(PF, next_bytes - off) & ~15u;
+            if (len) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n" ::"l"(next_w + off), "r"(len) : "memory");
+        }
+    }
 
     int8_t* xd = reinterpret_cast<int8_t*>(smem + L.xd);
     int8_t* sxd = reinterpret_cast<int8_t*>(smem + L.sxd);
@@ -269,12 +307,17 @@ __global__ void __launch_bounds__(W * 32, 16 / W) matvec_imma(PMatvec p, const f
     // everything before touched only the weights, which no kernel writes; from here on the activations are
     // read, so the kernels before this one must have finished on this GPU (in a tensor-parallel exchange the
     // reads themselves wait for the other ranks' slices)
-    asm volatile("griddepcontrol.wait;\n" ::: "memory");
+    // the exchange tags of this run of the launch list
+    const bool x_exchanged = pu->wait_slot != PEER_NONE, pushing = pu->push_slot != PEER_NONE;
+    const uint32_t x_tag = x_exchanged ? peer::want_tag(*pu) : 0u, out_tag = pushing ? peer::push_tag(*pu) : 0u;
+    // (an early consumer waits for nothing but the tags of its activations: see PEER_EARLY)
+    const bool early = pu->early != 0;
+    if (!early && !(dbg & 8)) asm volatile("griddepcontrol.wait;\n" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
     TRACE(2);
     // the value this thread's first output accumulates onto: asked for now, needed after the tile stream
     float first_old = 0.f;
-    if ((p.flags & MV_ACCUMULATE) && tid < (rt_hi - rt_lo) * 16 * NT) {
+    if ((p.flags & MV_ACCUMULATE) && !early && tid < (rt_hi - rt_lo) * 16 * NT) {
         const int j0 = (rt_lo + tid / (NT * 16)) * 16 + (tid / NT) % 16;
         if (j0 < n) first_old = __ldcg(out + (size_t)(t0 + tid % NT) * p.out_stride + p.col0 + j0);
     }
@@ -297,30 +340,48 @@ __global__ void __launch_bounds__(W * 32, 16 / W) matvec_imma(PMatvec p, const f
     //      split into four balanced byte digits (planes of xd), and the exact sums of X over each 32 elements
     //      into four digits too (sxd, the Q4_K min term). 1 / s goes to inv[]. With NORM the RMS scale is a
     //      factor of every output and is applied in the epilogue; the warps leave their sums of squares in ss[].
-    {
+    if (!(dbg & 4)) {
         const int xr = p.x_stride ? (int)p.x_stride * 4 : k;
-        const bool x_exchanged = pu->wait_slot != PEER_NONE;
-        const uint32_t x_tag = x_exchanged ? peer::want_tag(*pu) : 0u;
-        auto ldx = [&](const float* row, int i) {
-            return x_exchanged ? peer::read4(*pu, row + 4 * i, x_tag, status) : __ldcg(reinterpret_cast<const float4*>(row) + i);
-        };
+        constexpr int ub = 4;   // blocks per round
+        if (early) {
+            // one lane a warp looks out for the warp's first slot; the others sleep meanwhile instead of polling
+            if (lane == 0 && warp < nblk) (void)peer::read1(*pu, x + (size_t)t0 * xr + (size_t)warp * 256, x_tag, status);
+            __syncwarp();
+        }
 #pragma unroll 1
         for (int tk = 0; tk < NT; tk++) {
             const float* xt = x + (size_t)(t0 + tk) * xr;
             double ss = 0.0;
 #pragma unroll 1
-            for (int b0 = warp; b0 < nblk; b0 += 4 * W) {
+            for (int b0 = warp; b0 < nblk; b0 += ub * W) {
                 // up to four blocks per round: their loads are in flight together
                 float4 a[4][2];
 #pragma unroll
-                for (int u = 0; u < 4; u++) {
-                    const int blk = b0 + u * W;
-                    a[u][0] = a[u][1] = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (blk < nblk) {
-                        a[u][0] = ldx(xt, blk * 64 + lane);
-                        a[u][1] = ldx(xt, blk * 64 + 32 + lane);
+                for (int u = 0; u < 4; u++) a[u][0] = a[u][1] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (x_exchanged) {
+                    uint4 raw[4][2][2];
+#pragma unroll
+                    for (int u = 0; u < 4; u++)
+#pragma unroll
+                        for (int h = 0; h < 2; h++)
+                            if (b0 + u * W < nblk) peer::look4(*pu, xt + 4 * ((b0 + u * W) * 64 + 32 * h + lane), raw[u][h][0], raw[u][h][1]);
+#pragma unroll
+                    for (int u = 0; u < 4; u++)
+#pragma unroll
+                        for (int h = 0; h < 2; h++)
+                            if (b0 + u * W < nblk)
+                                a[u][h] = peer::take4(*pu, xt + 4 * ((b0 + u * W) * 64 + 32 * h + lane), x_tag, raw[u][h][0], raw[u][h][1], status);
+                } else {
+#pragma unroll
+                    for (int u = 0; u < 4; u++) {
+                        const int blk = b0 + u * W;
+                        if (blk < nblk) {
+                            a[u][0] = __ldcg(reinterpret_cast<const float4*>(xt) + blk * 64 + lane);
+                            a[u][1] = __ldcg(reinterpret_cast<const float4*>(xt) + blk * 64 + 32 + lane);
+                        }
                     }
                 }
+                fill_one();
 #pragma unroll
                 for (int u = 0; u < 4; u++) {
                     const int blk = b0 + u * W;
@@ -344,6 +405,8 @@ __global__ void __launch_bounds__(W * 32, 16 / W) matvec_imma(PMatvec p, const f
                     }
 #pragma unroll
                     for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+                    fill_one();
+                    TRACE(9);
                     float sc = 1.0f, is = 1.0f;
                     if (amax > 0.f && amax < 3.0e38f) {
                         // amax = f * 2^e with f in [1, 2): scale 2^(24 - e), so |x * scale| < 2^25
@@ -384,6 +447,9 @@ __global__ void __launch_bounds__(W * 32, 16 / W) matvec_imma(PMatvec p, const f
             }
         }
     }
+    TRACE(10);
+    while (fill > 0) fill_one();
+    TRACE(11);
     __syncthreads();  // every warp reads every block of xd
     TRACE(3);
     if (norm && warp < NT && lane == 0) {
@@ -459,8 +525,10 @@ __global__ void __launch_bounds__(W * 32, 16 / W) matvec_imma(PMatvec p, const f
 #ifdef ZCU_TRACE
         const long long tr0 = clock64();
 #endif
-        issue();  // tile tau + STAGES - 1
-        if (!mbar_wait(mbar + 8 * cs_stage, (phase_bits >> cs_stage) & 1u)) timed_out = true;
+        if (!(dbg & 2)) {
+            issue();  // tile tau + STAGES - 1
+            if (!mbar_wait(mbar + 8 * cs_stage, (phase_bits >> cs_stage) & 1u)) timed_out = true;
+        }
 #ifdef ZCU_TRACE
         const long long tr1 = clock64();
         tr_wait += tr1 - tr0;
@@ -469,7 +537,8 @@ __global__ void __launch_bounds__(W * 32, 16 / W) matvec_imma(PMatvec p, const f
         const uint32_t tile = ring + (uint32_t)cs_stage * TILE_BYTES;
         cs_stage = cs_stage + 1 == STAGES ? 0 : cs_stage + 1;
         const int unit = cur_unit;
-        if constexpr (Q4) {
+        if (dbg & 1) {
+        } else if constexpr (Q4) {
             const uint4 h0 = lds128(tile + hoff), h1 = lds128(tile + hoff + 8 * TILE_ROW);
             // 6-bit scales and mins of the eight sub-blocks, four per register (src/ref/tensor.zig:95-98)
             const uint32_t sc0[2] = {h0.y & 0x3f3f3f3fu, (h0.w & 0x0f0f0f0fu) | ((h0.y >> 2) & 0x30303030u)};
@@ -576,6 +645,10 @@ __global__ void __launch_bounds__(W * 32, 16 / W) matvec_imma(PMatvec p, const f
 #endif
     if (timed_out && lane == 0 && status) atomicExch(status, 1);
     TRACE(4);
+    // An early consumer passes the kernel boundary here, before it reads an output to accumulate onto or writes
+    // anything: the kernel before it delivered its last tag several microseconds ago, so this does not wait, and
+    // "this kernel has ended" keeps meaning "everything before it has".
+    if (early) asm volatile("griddepcontrol.wait;\n" ::: "memory");
     __syncthreads();
     TRACE(5);
 
@@ -585,8 +658,6 @@ __global__ void __launch_bounds__(W * 32, 16 / W) matvec_imma(PMatvec p, const f
     //      written rotated, k and v go to the cache at the token's position (rope_append's arithmetic,
     //      src/kernels/rope_append.wgsl; every product rounded, src/ref/ops.zig:64-86).
     const int local_rts = rt_hi - rt_lo;
-    const bool pushing = pu->push_slot != PEER_NONE;
-    const uint32_t out_tag = pushing ? peer::push_tag(*pu) : 0u;
     const int total = local_rts * 16 * NT;
     // the candidates of all W warps are loaded together (a warp that holds no tile of rp contributes zero) and
     // added as a fixed pairwise tree: the order does not depend on the step's token count
@@ -650,11 +721,10 @@ __global__ void __launch_bounds__(W * 32, 16 / W) matvec_imma(PMatvec p, const f
             continue;
         }
         if (!valid) continue;
-        if (p.flags & MV_ACCUMULATE) v = __fadd_rn(v, i == tid ? first_old : __ldcg(out + o));
+        if (p.flags & MV_ACCUMULATE) v = __fadd_rn(v, (i == tid && !early) ? first_old : __ldcg(out + o));
         out[o] = v;
         if (pushing) peer::push(*pu, out + o, v, out_tag);  // this rank's slice, to every rank's exchange slots
     }
-    peer::finish(*pu, (unsigned)ncta);
     TRACE(6);
 }
 
@@ -689,7 +759,15 @@ zcu_result launch_staged(const LaunchArgs& a, const MvArgs& v, int t0, int grid,
     CUtensorMap wmap, smap;
     if (!weight_map(&wmap, v.w, Q4, (int)v.p.k, rows, false) || !weight_map(&smap, v.w, Q4, (int)v.p.k, rows, !Q4))
         return zcu_fail(a, ZCU_E_GPU, "matvec_imma: the driver refused a tensor map (n %u, k %u)", v.p.n, v.p.k);
-    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, v.p, v.x, wmap, smap, v.out, v.nw, t0, seg_max, a.status, v.rope, v.peer);
+    const uint8_t* next_w = nullptr;
+    uint32_t next_bytes = 0;
+#ifdef ZCU_TRACE
+    if (g_pf_total) {
+        next_w = g_pf_base + ((size_t)(v.w - g_pf_base) + g_pf_size) % g_pf_total;
+        next_bytes = (uint32_t)g_pf_size;
+    }
+#endif
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, v.p, v.x, wmap, smap, v.out, v.nw, t0, seg_max, a.status, v.rope, v.peer, next_w, next_bytes);
     if (e != cudaSuccess) return zcu_fail(a, ZCU_E_GPU, "matvec_imma: launch failed: %s", cudaGetErrorString(e));
     return ZCU_OK;
 }
@@ -738,8 +816,6 @@ zcu_result launch_type(const LaunchArgs& a, const MvArgs& v, int stages, bool ev
     MvArgs pass = v;
     for (int t0 = 0; t0 < v.m;) {
         const int mt = (v.m - t0) < cap ? (v.m - t0) : cap;
-        // every pass of one dispatch pushes under the same exchange tag: only the last one advances the slot's count
-        pass.peer.hold = t0 + mt < v.m ? 1u : 0u;
         zcu_result r;
         switch (mt) {
             case 1: r = launch_one<TYPE, 1, W>(a, pass, t0, stages, every_sm); break;
@@ -774,6 +850,20 @@ zcu_result launch_matvec_imma(const LaunchArgs& a, const mv::MvArgs& v, int type
 #ifdef ZCU_TRACE
 extern "C" __attribute__((visibility("default"))) int zcu_dbg_trace_read(unsigned long long* out, size_t count) {
     return (int)cudaMemcpyFromSymbol(out, g_mv_trace, count * sizeof(unsigned long long));
+}
+extern "C" __attribute__((visibility("default"))) void zcu_dbg_prefetch(const void* base, size_t size, size_t total) {
+    g_pf_base = (const uint8_t*)base;
+    g_pf_size = size;
+    g_pf_total = total;
+}
+extern "C" __attribute__((visibility("default"))) int zcu_dbg_box(int bytes, int rows) {
+    g_dbg_box_bytes = bytes;
+    g_dbg_box_rows = rows;
+    const int tx = bytes * rows;
+    return (int)cudaMemcpyToSymbol(g_mv_box, &tx, sizeof(int));
+}
+extern "C" __attribute__((visibility("default"))) int zcu_dbg_mode(int mode) {
+    return (int)cudaMemcpyToSymbol(g_mv_dbg, &mode, sizeof(int));
 }
 extern "C" __attribute__((visibility("default"))) int zcu_dbg_trace_clear() {
     void* ptr = nullptr;

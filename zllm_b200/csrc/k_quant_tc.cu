@@ -814,7 +814,6 @@ __global__ void __launch_bounds__(256) cols_reduce_kernel(const float* __restric
         // this rank's slice of an exchanged vector: to every rank's exchange slots
         if (pu.push_slot != PEER_NONE) peer::push(pu, out + o, v, peer::push_tag(pu));
     }
-    peer::finish(pu, gridDim.x);
 }
 
 // ---------------------------------------------------------------------------------------------- host side

@@ -7,10 +7,13 @@
 // expects. An 8-byte store arrives whole, so a matching tag proves its value: no flag, no fence, no round trip -
 // the data is its own signal (the idea of NCCL's low-latency protocol). No multicast: plain stores and loads.
 //
-// Tags: exchange `slot` of a step list, executed for the c-th time, uses tag c * slots + slot + 1. A buffer that
+// Tags: a run of the launch list is an epoch; exchange `slot` uses tag epoch * slots + slot + 1 in it. A buffer that
 // several exchanges of a step write in turn (the residual stream) therefore never shows the same tag twice, and
-// tags are never 0 (the arena starts zeroed). Every rank runs the same list, so a consumer computes the expected
-// tag from its own count of the slot, which its own producer advanced before (stream order).
+// tags are never 0 (the arena starts zeroed). The epoch is one local word that every kernel of the list reads
+// at its start and that only the list's closing dispatch (ZCU_K_EXT_PEER_NEXT, ordered after everything before it)
+// advances: producer and consumer of a slot agree on its tag without telling each other anything, there is no
+// per-kernel counting, and a consumer may start - and wait for the tags - while its producer still runs. Every
+// rank runs the same list, so the epochs of all ranks agree. A slot is written at most once per epoch.
 // A fast rank cannot overwrite a slot that a slow rank still has to read: to reach the next write of a buffer it
 // must have read, through the exchanges in between, data that the slow rank produces only after that read.
 // Every wait is bounded in time (2 s unless the host sets another limit); a rank that gives up sets the context's
@@ -28,8 +31,12 @@ struct PPeer {
     uint32_t magic;      // PEER_MAGIC
     uint32_t wait_slot;  // the input vector comes from this exchange (PEER_NONE: it is local)
     uint32_t push_slot;  // outputs go to every rank as this exchange (PEER_NONE: local only)
-    uint32_t _pad;
+    uint32_t flags;      // PEER_EARLY
 };
+// The tags of wait_slot are the ONLY thing this dispatch has to wait for: whatever else it reads or overwrites was
+// finished with before the dispatch that precedes it began. A multiply with this flag does not wait for the kernel
+// before it to end (only, at its own end, so that kernel completion stays transitive along the stream).
+constexpr uint32_t PEER_EARLY = 1u;
 
 struct PeerTable {
     int32_t rank, world;
@@ -38,16 +45,13 @@ struct PeerTable {
     uint64_t base[PEER_MAX];   // every rank's arena as mapped here (base[rank] is the local one)
     uint64_t arena_bytes;
     uint64_t ll_off;           // arena offset of the exchange region: the float at offset q has its slot at ll_off + 2 q
-    uint32_t* counts;          // local: executions of each slot's producer on this rank
-    uint32_t* tickets;         // local: CTAs of the producing kernel that have finished, per slot; tickets[slots] is
-                               // the abort word
+    uint32_t* epoch;           // local: epoch[0] = runs of the launch list so far; epoch[1] = the abort word
 };
 
 struct PeerUse {  // what one launch does with the table
     PeerTable t;
     uint32_t wait_slot, push_slot;
-    uint32_t hold, _pad;   // hold != 0: another launch of the same dispatch follows (a step of more tokens than one pass takes):
-                           // it pushes under the same tag, so this launch leaves the slot's count alone
+    uint32_t early, _pad;  // early: PEER_EARLY was given
 };
 
 #ifdef __CUDACC__
@@ -59,10 +63,10 @@ __device__ __forceinline__ unsigned long long now_ns() {
     return t;
 }
 
-// The tag the consumer of `slot` expects (its own producer has run: the count is already advanced) and the tag a
-// producer of `slot` writes (the count advances when its kernel ends).
-__device__ __forceinline__ uint32_t want_tag(const PeerUse& u) { return __ldcg(u.t.counts + u.wait_slot) * u.t.slots + u.wait_slot + 1; }
-__device__ __forceinline__ uint32_t push_tag(const PeerUse& u) { return (__ldcg(u.t.counts + u.push_slot) + 1) * u.t.slots + u.push_slot + 1; }
+// The tag of `slot` in this run of the list (read once, at the kernel's start).
+__device__ __forceinline__ uint32_t tag_of(const PeerUse& u, uint32_t slot) { return __ldcg(u.t.epoch) * u.t.slots + slot + 1; }
+__device__ __forceinline__ uint32_t want_tag(const PeerUse& u) { return tag_of(u, u.wait_slot); }
+__device__ __forceinline__ uint32_t push_tag(const PeerUse& u) { return tag_of(u, u.push_slot); }
 
 // The exchange slot of the float at `local` (an address inside the local arena's data region), in rank r's arena.
 __device__ __forceinline__ uint2* slot_of(const PeerUse& u, const float* local, int r) {
@@ -74,16 +78,17 @@ __device__ __forceinline__ uint2* slot_of(const PeerUse& u, const float* local, 
 __device__ __forceinline__ void push(const PeerUse& u, const float* local, float v, uint32_t tag) {
     for (int r = 0; r < u.t.world; r++) {
         uint2* s = slot_of(u, local, r);
-        asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};\n" ::"l"(s), "r"(__float_as_uint(v)), "r"(tag) : "memory");
+        if (r == u.t.rank) asm volatile("st.relaxed.gpu.global.v2.u32 [%0], {%1, %2};\n" ::"l"(s), "r"(__float_as_uint(v)), "r"(tag) : "memory");
+        else asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};\n" ::"l"(s), "r"(__float_as_uint(v)), "r"(tag) : "memory");
     }
 }
 
 __device__ __forceinline__ bool gave_up(const PeerUse& u, unsigned long long t0, unsigned spins, int* status) {
     if ((spins & 1023u) != 1023u) return false;
-    if (__ldcg(u.t.tickets + u.t.slots) != 0) return true;  // another wait of this context gave up
+    if (__ldcg(u.t.epoch + 1) != 0) return true;  // another wait of this context gave up
     if (now_ns() - t0 > (unsigned long long)(u.t.wait_ms ? u.t.wait_ms : 2000u) * 1000000ull) {
         if (status) atomicExch(status, 5);
-        atomicExch(u.t.tickets + u.t.slots, 1u);
+        atomicExch(u.t.epoch + 1, 1u);
         return true;
     }
     return false;
@@ -100,8 +105,22 @@ __device__ __forceinline__ float4 read4(const PeerUse& u, const float* local, ui
         if (a.y == tag && a.w == tag && b.y == tag && b.w == tag) break;
         if (spins == 0) t0 = now_ns();
         if (gave_up(u, t0, spins, status)) break;
+        __nanosleep(spins < 8 ? 100u : 400u);   // (a consumer that started early looks many times: not back to back)
     }
     return make_float4(__uint_as_float(a.x), __uint_as_float(a.z), __uint_as_float(b.x), __uint_as_float(b.z));
+}
+
+// The same in two steps, for a reader that wants several pieces in flight at once: look4 only issues the two loads;
+// take4 checks the tags and, where one is missing, falls back to read4's loop.
+__device__ __forceinline__ void look4(const PeerUse& u, const float* local, uint4& a, uint4& b) {
+    const uint2* s = slot_of(u, local, u.t.rank);
+    asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(a.x), "=r"(a.y), "=r"(a.z), "=r"(a.w) : "l"(s) : "memory");
+    asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(b.x), "=r"(b.y), "=r"(b.z), "=r"(b.w) : "l"(s + 2) : "memory");
+}
+__device__ __forceinline__ float4 take4(const PeerUse& u, const float* local, uint32_t tag, const uint4& a, const uint4& b, int* status) {
+    if (a.y == tag && a.w == tag && b.y == tag && b.w == tag)
+        return make_float4(__uint_as_float(a.x), __uint_as_float(a.z), __uint_as_float(b.x), __uint_as_float(b.z));
+    return read4(u, local, tag, status);
 }
 
 __device__ __forceinline__ float read1(const PeerUse& u, const float* local, uint32_t tag, int* status) {
@@ -113,22 +132,9 @@ __device__ __forceinline__ float read1(const PeerUse& u, const float* local, uin
         if (a.y == tag) break;
         if (spins == 0) t0 = now_ns();
         if (gave_up(u, t0, spins, status)) break;
+        __nanosleep(spins < 8 ? 100u : 400u);
     }
     return __uint_as_float(a.x);
-}
-
-// Every thread of a producing CTA calls it after its last push. The last CTA of the grid advances the slot's count
-// (local memory only: the consumers on this rank run after this kernel).
-__device__ __forceinline__ void finish(const PeerUse& u, unsigned ncta) {
-    if (u.push_slot == PEER_NONE) return;
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        __threadfence();
-        if (atomicAdd(u.t.tickets + u.push_slot, 1u) == ncta - 1) {
-            u.t.tickets[u.push_slot] = 0;
-            if (!u.hold) u.t.counts[u.push_slot] += 1;
-        }
-    }
 }
 
 }  // namespace peer

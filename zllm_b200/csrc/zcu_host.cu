@@ -100,7 +100,7 @@ struct zcu_context {
     std::vector<cudaGraphExec_t> graphs;
     PeerTable peers = {};                 // tensor-parallel exchange (world == 0: not configured)
     std::vector<void*> ipc_open;          // peer arenas this context mapped
-    std::vector<void*> retired;           // count words of earlier peer configurations
+    std::vector<void*> retired;           // epoch words of earlier peer configurations
     uint8_t* pinned = nullptr;  // staging for readbacks
     // uploads go through a small ring of pinned chunks: the payload is copied once (mapping or write_data -> chunk)
     // and the chunk is handed to the copy engine; a chunk is reused once its copy has finished
@@ -273,6 +273,7 @@ zcu_result dispatch_kernel(zcu_context* c, uint32_t kernel, uint32_t variant, co
         case ZCU_K_SAMPLE: return launch_sample(a);
         case ZCU_K_DRAFT: return launch_draft(a);
         case ZCU_K_EXT_PEER_WAIT: return launch_peer_wait(a);
+        case ZCU_K_EXT_PEER_NEXT: return launch_peer_next(a);
         case ZCU_K_QUANTIZE_Q8: return launch_quantize_q8(a);
         case ZCU_K_MATMUL_Q4_K: return variant == ZCU_VARIANT_PREFILL_BF16_TC ? launch_matmul_q4_k_tc(a) : launch_matmul_q4_k(a);
         case ZCU_K_MATMUL_Q8_0: return launch_matmul_q8_0(a);
@@ -696,6 +697,7 @@ const char* kernel_name(uint32_t k) {
         case ZCU_K_SAMPLE: return "sample";
         case ZCU_K_DRAFT: return "draft";
         case ZCU_K_EXT_PEER_WAIT: return "ext_peer_wait";
+        case ZCU_K_EXT_PEER_NEXT: return "ext_peer_next";
         case ZCU_K_GATED_NORM: return "gated_norm";
         case ZCU_K_REPACK_Q8_0: return "repack_q8_0";
         case ZCU_K_MATVEC_Q8_0: return "matvec_q8_0";
@@ -740,6 +742,7 @@ zcu_result parse_peer(const LaunchArgs& a, PeerUse& u, const void* out_lo, const
              "peer exchange: slot out of range (%u, %u of %u)", pp.wait_slot, pp.push_slot, u.t.slots);
     u.wait_slot = pp.wait_slot;
     u.push_slot = pp.push_slot;
+    u.early = (pp.flags & PEER_EARLY) != 0 && pp.wait_slot != PEER_NONE;
     if (u.push_slot != PEER_NONE) {
         const uint64_t lo = reinterpret_cast<uint64_t>(out_lo), hi = reinterpret_cast<uint64_t>(out_hi), base = u.t.base[u.t.rank];
         ZCU_NEED(a, lo >= base && hi <= base + u.t.ll_off && lo <= hi, "peer exchange: the output is not inside the local arena");
@@ -764,7 +767,7 @@ ZCU_EXPORT size_t zcu_artifact(uint32_t kernel, uint32_t variant, char* out, siz
         if (is_matvec) ok = matvec_variant_ok(kernel, variant);
         else ok = variant == 0 || (has_rung && variant == ZCU_VARIANT_PREFILL_BF16_TC) ||
                   (kernel == ZCU_K_DELTA_RULE && (variant == ZCU_VARIANT_DELTA_CHUNK64 || variant == ZCU_VARIANT_DELTA_CHUNK64_F32)) ||
-                  (kernel == ZCU_K_ATTN_SPLIT && (variant == 1 || variant == 3));  // the forms of the fast path (k_attn.cu)
+                  (kernel == ZCU_K_ATTN_SPLIT && (variant == 1 || variant == 3 || variant == 4));  // the forms of the fast path (k_attn.cu)
     }
     if (!ok) {
         if (out && capacity) out[0] = 0;
@@ -843,7 +846,7 @@ ZCU_EXPORT zcu_result zcu_destroy(zcu_context* c, uint32_t timeout_ms) {
         if (r == ZCU_E_TIMEOUT) return r;  // the handle stays valid for a retry
     }
     for (void* m : c->ipc_open) cudaIpcCloseMemHandle(m);
-    if (c->peers.counts) cudaFree(c->peers.counts);
+    if (c->peers.epoch) cudaFree(c->peers.epoch);
     for (void* w : c->retired) cudaFree(w);
     for (cudaGraphExec_t g : c->graphs)
         if (g) cudaGraphExecDestroy(g);
@@ -1173,14 +1176,13 @@ ZCU_EXPORT zcu_result zcu_peer_config(zcu_context* c, uint32_t rank, uint32_t wo
     t.arena_bytes = arena_bytes;
     t.ll_off = exchange_offset;
     uint32_t* words = nullptr;
-    CU(c, cudaMalloc((void**)&words, ((size_t)slots * 2 + 1) * sizeof(uint32_t)));
-    CU(c, cudaMemset(words, 0, ((size_t)slots * 2 + 1) * sizeof(uint32_t)));
+    CU(c, cudaMalloc((void**)&words, 2 * sizeof(uint32_t)));
+    CU(c, cudaMemset(words, 0, 2 * sizeof(uint32_t)));
     CU(c, cudaMemset(reinterpret_cast<void*>(t.base[rank] + exchange_offset), 0, (size_t)exchange_offset * 2));  // tag 0: nothing yet
-    t.counts = words;
-    t.tickets = words + slots;
-    // (the old count words stay allocated until the context goes: graphs captured under the old configuration hold
+    t.epoch = words;
+    // (the old epoch words stay allocated until the context goes: graphs captured under the old configuration hold
     // their address)
-    if (c->peers.counts) c->retired.push_back(c->peers.counts);
+    if (c->peers.epoch) c->retired.push_back(c->peers.epoch);
     t.wait_ms = c->peers.wait_ms;
     c->peers = t;
     return ZCU_OK;

@@ -147,6 +147,7 @@ zcu_result launch_delta_chunked(const LaunchArgs& a);          // 64-token chunk
 zcu_result launch_gated_norm(const LaunchArgs& a);
 zcu_result launch_attn_static(const LaunchArgs& a, uint32_t max_keys, uint32_t rows);
 zcu_result launch_peer_wait(const LaunchArgs& a);
+zcu_result launch_peer_next(const LaunchArgs& a);
 zcu_result launch_quantize_q8(const LaunchArgs& a);
 zcu_result launch_matmul_q4_k(const LaunchArgs& a);
 zcu_result launch_matmul_q8_0(const LaunchArgs& a);

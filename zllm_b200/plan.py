@@ -123,7 +123,8 @@ class DenseProgram:
     """
 
     def __init__(self, ctx, cfg: DenseConfig, weights, batch: int, alloc, shard: Shard | None = None, gather=None,
-                 variants: dict | None = None, fuse_rope: bool | None = None, arena=None, batched: bool | None = None):
+                 variants: dict | None = None, fuse_rope: bool | None = None, arena=None, batched: bool | None = None,
+                 early: bool = False):
         self.ctx, self.cfg, self.w, self.B = ctx, cfg, weights, batch
         self.sh = shard or Shard()
         self.gather = gather
@@ -131,6 +132,7 @@ class DenseProgram:
         # reads whole; their producers store into every rank's arena and publish an exchange slot, their
         # consumers wait for it. Slots: 4 per layer (att, x after wo, act, x after down), then the logits.
         self.arena = arena
+        self.early = early
         assert arena is None or gather is None
         self.L = K.Launcher(ctx)
         self.variants = variants or {}
@@ -194,6 +196,11 @@ class DenseProgram:
 
     # ---- the launch list
     def _matvec(self, ttype, x, w, out, n, k, **kw):
+        # A multiply that takes its activations from an exchange waits for their tags and for nothing else: all it
+        # reads or overwrites besides (the residual slice it accumulates onto, the cache rows and Q|K|V row of a
+        # fused rope_append) was last touched at least two dispatches earlier.
+        if kw.get("wait") is not None:
+            kw["early"] = self.early
         v = self.variants.get((ttype, n, k), 0)
         if v == 0 and self.batched and ttype == "q4_k" and k % 256 == 0 and "rope" not in kw:
             v = K.MATVEC_BATCHED
@@ -321,7 +328,8 @@ class DenseProgram:
         self._gather(self.logits, cfg.vocab)
         if peer:
             self.L.peer_wait(s_logits, self.logits)  # the host may read the logits once this has run
-            self.launches_per_step += 1
+            self.L.peer_next()                       # the next run of the list tags its exchanges anew
+            self.launches_per_step += 2
 
     def algorithmic_bytes(self, positions: np.ndarray) -> dict:
         """Bytes one step must move on this rank: every weight once, K and V of every cached position."""
