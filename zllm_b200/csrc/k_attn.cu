@@ -248,16 +248,6 @@ __global__ void __launch_bounds__(attn::AM_THREADS, 3) attn_split_mma(PAttention
     attn::attn_split_mma_body<HD, true>(dyn_smem, p, qg, kc, vc, part, step, seq_pos, (int)blockIdx.x, (int)blockIdx.y, (int)blockIdx.z, status);
 }
 
-template <int HD>
-__global__ void __launch_bounds__(attn::AM_THREADS, 4) attn_split_kreg(PAttention p, const float* __restrict__ qg,
-                                                                      const __half* __restrict__ kc,
-                                                                      const __half* __restrict__ vc, float* __restrict__ part,
-                                                                      const PStep* __restrict__ step,
-                                                                      const uint32_t* __restrict__ seq_pos, int* __restrict__ status) {
-    extern __shared__ __align__(128) unsigned char dyn_smem[];
-    attn::attn_split_kreg_body<HD, true>(dyn_smem, p, qg, kc, vc, part, step, seq_pos, (int)blockIdx.x, (int)blockIdx.y, (int)blockIdx.z, status);
-}
-
 __global__ void __launch_bounds__(attn::AC_THREADS) attn_combine_kernel(PAttention p, const float* __restrict__ qg,
                                                                        const float* __restrict__ part, float* __restrict__ out,
                                                                        const PStep* __restrict__ step,
@@ -338,18 +328,6 @@ zcu_result launch_attn_split(const LaunchArgs& a) {
             // one CTA per block on the f16 tensor cores (queries and probabilities as two f16 terms)
             const size_t msmem = attn::attn_mma_smem(hd);
             auto mk = hd == 128 ? attn_split_mma<128> : attn_split_mma<64>;
-            if (cudaFuncSetAttribute(mk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)msmem) != cudaSuccess) {
-                cudaGetLastError();
-                return zcu_fail(a, ZCU_E_GPU, "attn_split: %zu bytes of shared memory refused", msmem);
-            }
-            cudaError_t e = launch_pdl(mk, grid, dim3(attn::AM_THREADS), msmem, a.stream, p, qg, kc, vc, part, step, seq_pos, a.status);
-            if (e != cudaSuccess) return zcu_fail(a, ZCU_E_GPU, "attn_split: launch failed: %s", cudaGetErrorString(e));
-            return ZCU_OK;
-        }
-        if (a.variant == 4) {
-            // the same arithmetic with K loaded straight into the tensor cores' B fragments: four CTAs per SM
-            const size_t msmem = attn::attn_kreg_smem(hd);
-            auto mk = hd == 128 ? attn_split_kreg<128> : attn_split_kreg<64>;
             if (cudaFuncSetAttribute(mk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)msmem) != cudaSuccess) {
                 cudaGetLastError();
                 return zcu_fail(a, ZCU_E_GPU, "attn_split: %zu bytes of shared memory refused", msmem);

@@ -424,158 +424,6 @@ __device__ __forceinline__ void attn_split_mma_body(unsigned char* smem, const P
     ATRACE(6);
 }
 
-// ---- the same block with K through registers. A CTA's K and V tiles take 68 KB of shared memory, so three CTAs
-// fit an SM and a cache of 8193 keys x 8 KV heads (520 blocks) needs a second, nearly empty wave on 148 SMs.
-// Here only V is staged (ldmatrix.trans needs it there); a lane loads its B fragments of K straight from the cache:
-// the contraction runs over the head's dims in any order, as long as Q uses the same one, so k-step ks, lane tq
-// takes dims 8 p + 4 (ks & 1) .. + 3 of 16-byte piece p = 4 (ks >> 1) + tq of its key's row: four lanes read 64
-// consecutive bytes, a lane holds its two keys' fragments of all k-steps in 8 (head_dim 128) 16-byte registers.
-// With at most 64 registers a thread, four CTAs share an SM: one wave.
-constexpr size_t attn_kreg_smem(int hd) {
-    return (size_t)AF_KEYS * (hd * 2 + 16) + (size_t)8 * 4 * hd * sizeof(float) + (size_t)(hd / 16) * 32 * 8 + 8 * 4 * 2 * sizeof(float);
-}
-
-template <int HD, bool PDL = false>
-__device__ __forceinline__ void attn_split_kreg_body(unsigned char* smem, const PAttention& p, const float* __restrict__ qg,
-                                                     const __half* __restrict__ kc, const __half* __restrict__ vc,
-                                                     float* __restrict__ part, const PStep* __restrict__ step,
-                                                     const uint32_t* __restrict__ seq_pos, int g_kv, int b, int t,
-                                                     int* __restrict__ status = nullptr) {
-    constexpr int RS = HD * 2 + 16;              // bytes between the rows of the staged V tile
-    constexpr int KSTEPS = HD / 16;              // k-steps of the score product
-    constexpr int CPR = HD / 8;                  // 16-byte pieces per cache row
-    constexpr int PIECES = 16 * CPR / 32;        // V pieces of the warp's 16 rows per lane
-    constexpr int KP = CPR / 4;                  // K pieces per lane and key
-    unsigned char* Vt = smem;
-    float* pvs = reinterpret_cast<float*>(Vt + (size_t)AF_KEYS * RS);   // [8 warps][4 heads][HD]
-    uint2* qf = reinterpret_cast<uint2*>(pvs + 8 * 4 * HD);             // [KSTEPS][32]: the lanes' A registers per k-step
-    float* ml = reinterpret_cast<float*>(qf + KSTEPS * 32);             // [8 warps][4 heads] {max, sum}
-    const uint32_t vt_s = (uint32_t)__cvta_generic_to_shared(Vt);
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int g = lane >> 2, tq = lane & 3;
-    const int group = (int)(p.heads / p.kv_heads);
-    const int row = (int)p.row0 + t;
-    const size_t seq_off = (size_t)row * p._pad[0];
-    int keys = (seq_pos ? (int)seq_pos[row] : (int)step->pos0 + row) + 1;
-    if (keys > (int)gridDim.y * AF_KEYS) {   // a step past the launch's blocks: reported, not followed
-        keys = (int)gridDim.y * AF_KEYS;
-        if (tid == 0 && status) atomicExch(status, 6);
-    }
-    const int k0 = b * AF_KEYS;
-    const size_t kv_stride = (size_t)p.kv_heads * HD;
-    const int q_head = p.gated ? 2 * HD : HD;
-    const int r0 = 16 * warp;
-    const int first_new = seq_pos ? (int)seq_pos[row] : (int)step->pos0;
-    const bool early = PDL && k0 + AF_KEYS <= first_new;   // only rows of earlier steps: no need to wait for the producer
-    if (PDL && !early) asm volatile("griddepcontrol.wait;\n" ::: "memory");
-
-    // ---- K fragments of keys r0 + g and r0 + 8 + g, then the warp's rows of V on their way
-    uint4 kr[2][KP];
-#pragma unroll
-    for (int nb = 0; nb < 2; nb++) {
-        const size_t src = seq_off + (size_t)min(k0 + r0 + 8 * nb + g, keys - 1) * kv_stride + (size_t)g_kv * HD;
-#pragma unroll
-        for (int m = 0; m < KP; m++) kr[nb][m] = __ldcg(reinterpret_cast<const uint4*>(kc + src) + 4 * m + tq);
-    }
-#pragma unroll
-    for (int i = 0; i < PIECES; i++) {
-        const int j = lane + 32 * i, key = r0 + j / CPR, piece = j % CPR;
-        const size_t src = seq_off + (size_t)min(k0 + key, keys - 1) * kv_stride + (size_t)g_kv * HD + 8 * piece;
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(vt_s + (uint32_t)key * RS + 16u * piece), "l"(vc + src) : "memory");
-    }
-    asm volatile("cp.async.commit_group;\n" ::: "memory");
-    if (early) asm volatile("griddepcontrol.wait;\n" ::: "memory");
-    if (PDL) asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
-    // ---- the group's queries as A fragments in the same order of dims: entry (k-step, lane) = {a0, a2}
-    for (int e = tid; e < KSTEPS * 32; e += AM_THREADS) {
-        const int ks = e >> 5, ln = e & 31, gg = ln >> 2, tt = ln & 3;
-        const float* qp = qg + (size_t)row * p.q_row + (size_t)(g_kv * group + min(gg & 3, group - 1)) * q_head + 8 * (4 * (ks >> 1) + tt) + 4 * (ks & 1);
-        const float4 q4 = __ldcg(reinterpret_cast<const float4*>(qp));
-        qf[e] = make_uint2(split_pair(q4.x, q4.y, gg >= 4), split_pair(q4.z, q4.w, gg >= 4));
-    }
-    __syncthreads();
-
-    // ---- scores of the warp's 16 keys for the group's heads
-    float c[2][4];
-#pragma unroll
-    for (int nb = 0; nb < 2; nb++) c[nb][0] = c[nb][1] = c[nb][2] = c[nb][3] = 0.f;
-#pragma unroll
-    for (int ks = 0; ks < KSTEPS; ks++) {
-        const uint2 a = qf[ks * 32 + lane];
-#pragma unroll
-        for (int nb = 0; nb < 2; nb++) {
-            const uint4 kk = kr[nb][ks >> 1];
-            mma_f16_16816(c[nb], a.x, a.y, (ks & 1) ? kk.z : kk.x, (ks & 1) ? kk.w : kk.y);
-        }
-    }
-    float s[4];
-#pragma unroll
-    for (int nb = 0; nb < 2; nb++)
-#pragma unroll
-        for (int i = 0; i < 2; i++) {
-            const float v = __fadd_rn(c[nb][i], __shfl_xor_sync(0xffffffffu, c[nb][i], 16));   // hi rows + lo rows
-            s[2 * nb + i] = k0 + r0 + 8 * nb + 2 * tq + i < keys ? v * p.scale : -FLT_MAX;
-        }
-    float mx = fmaxf(fmaxf(s[0], s[1]), fmaxf(s[2], s[3]));
-    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-    float pr[4], sum = 0.f;
-#pragma unroll
-    for (int i = 0; i < 4; i++) pr[i] = s[i] != -FLT_MAX ? expf(s[i] - mx) : 0.f;
-    sum = __fadd_rn(__fadd_rn(pr[0], pr[1]), __fadd_rn(pr[2], pr[3]));
-    sum = __fadd_rn(sum, __shfl_xor_sync(0xffffffffu, sum, 1));
-    sum = __fadd_rn(sum, __shfl_xor_sync(0xffffffffu, sum, 2));
-    if (g < group && tq == 0) {
-        ml[(warp * 4 + g) * 2] = mx;
-        ml[(warp * 4 + g) * 2 + 1] = sum;
-    }
-    // ---- sum exp * v over the warp's 16 keys
-    const uint32_t pa0 = split_pair(pr[0], pr[1], g >= 4), pa2 = split_pair(pr[2], pr[3], g >= 4);
-    asm volatile("cp.async.wait_group 0;\n" ::: "memory");
-    __syncwarp();
-    float* pv = pvs + (size_t)warp * 4 * HD;   // [4 heads][HD]
-    {
-        const uint32_t vrow = vt_s + (uint32_t)(r0 + (lane & 15)) * RS + 16u * (lane >> 4);
-#pragma unroll
-        for (int nb = 0; nb < HD / 16; nb++) {
-            uint32_t b0, b1, b2, b3;
-            asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3) : "r"(vrow + 32u * nb));
-            float o0[4] = {0.f, 0.f, 0.f, 0.f}, o1[4] = {0.f, 0.f, 0.f, 0.f};
-            mma_f16_16816(o0, pa0, pa2, b0, b1);
-            mma_f16_16816(o1, pa0, pa2, b2, b3);
-            const float v00 = __fadd_rn(o0[0], __shfl_xor_sync(0xffffffffu, o0[0], 16)), v01 = __fadd_rn(o0[1], __shfl_xor_sync(0xffffffffu, o0[1], 16));
-            const float v10 = __fadd_rn(o1[0], __shfl_xor_sync(0xffffffffu, o1[0], 16)), v11 = __fadd_rn(o1[1], __shfl_xor_sync(0xffffffffu, o1[1], 16));
-            if (g < group) {
-                *reinterpret_cast<float2*>(pv + g * HD + 16 * nb + 2 * tq) = make_float2(v00, v01);
-                *reinterpret_cast<float2*>(pv + g * HD + 16 * nb + 8 + 2 * tq) = make_float2(v10, v11);
-            }
-        }
-    }
-    __syncthreads();
-    // ---- the eight warps' results merged in warp order (attn_combine's arithmetic): the block's partial
-    for (int e = tid; e < group * HD; e += AM_THREADS) {
-        const int h = e / HD, d = e % HD;
-        float M = -FLT_MAX;
-#pragma unroll
-        for (int w = 0; w < 8; w++) M = fmaxf(M, ml[(w * 4 + h) * 2]);
-        float L = 0.f, o = 0.f;
-#pragma unroll
-        for (int w = 0; w < 8; w++) {
-            const float mw = ml[(w * 4 + h) * 2];
-            const float wt = mw != -FLT_MAX ? expf(mw - M) : 0.f;
-            L = __fmaf_rn(ml[(w * 4 + h) * 2 + 1], wt, L);
-            o = __fmaf_rn(pvs[((size_t)w * 4 + h) * HD + d], wt, o);
-        }
-        const int head = g_kv * group + h;
-        const size_t base = (((size_t)t * p.heads + head) * p.max_blocks + b) * (HD + 2);
-        part[base + 2 + d] = o;
-        if (d == 0) {
-            part[base] = M;
-            part[base + 1] = L;
-        }
-    }
-}
-
 // grid (heads, rows). Merges the blocks' partials (src/kernels/attn_combine.wgsl):
 //   M = max m_b,  L = sum l_b e^(m_b - M),  o = sum o_b e^(m_b - M) / L,  times sigmoid(gate) when gated.
 // Bindings: qg, part, out, step (+ per-row positions for batched sequences). `kb`: cache positions per block.

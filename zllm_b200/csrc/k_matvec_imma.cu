@@ -317,19 +317,20 @@ __global__ void __launch_bounds__(W * 32, 16 / W) matvec_imma(PMatvec p, const f
     TRACE(2);
     // the value this thread's first output accumulates onto: asked for now, needed after the tile stream
     float first_old = 0.f;
-    if ((p.flags & MV_ACCUMULATE) && !early && tid < (rt_hi - rt_lo) * 16 * NT) {
-        const int j0 = (rt_lo + tid / (NT * 16)) * 16 + (tid / NT) % 16;
-        if (j0 < n) first_old = __ldcg(out + (size_t)(t0 + tid % NT) * p.out_stride + p.col0 + j0);
+    const int ep = tid >> 2;   // the first output this thread's quad writes in the epilogue
+    if ((p.flags & MV_ACCUMULATE) && !early && ep < (rt_hi - rt_lo) * 16 * NT) {
+        const int j0 = (rt_lo + ep / (NT * 16)) * 16 + (ep / NT) % 16;
+        if (j0 < n) first_old = __ldcg(out + (size_t)(t0 + ep % NT) * p.out_stride + p.col0 + j0);
     }
 
     // MV_ROPE_APPEND: the position and the (cos, sin) pair of this thread's first output, asked for now too
     uint32_t rope_pos = 0;
     float2 rope_cs = make_float2(1.f, 0.f);
-    if (rope != nullptr && tid < (rt_hi - rt_lo) * 16 * NT) {
-        const int tok = t0 + tid % NT;
+    if (rope != nullptr && ep < (rt_hi - rt_lo) * 16 * NT) {
+        const int tok = t0 + ep % NT;
         rope_pos = rope->seq_pos ? __ldcg(rope->seq_pos + tok) : __ldcg(&rope->step->pos0) + (uint32_t)tok;
         const PRopeAppend& r = rope->p;
-        const uint32_t col = p.col0 + (uint32_t)((rt_lo + tid / (NT * 16)) * 16 + (tid / NT) % 16), hd = r.head_dim;
+        const uint32_t col = p.col0 + (uint32_t)((rt_lo + ep / (NT * 16)) * 16 + (ep / NT) % 16), hd = r.head_dim;
         const bool is_q = col < r.k_off, is_k = !is_q && col < r.v_off;
         const uint32_t d = is_q ? col % (r.gated ? 2 * hd : hd) : (col - (is_k ? r.k_off : r.v_off)) % hd;
         if ((is_q || is_k) && d < r.n_rot) rope_cs = __ldg(rope->table + (size_t)rope_pos * (r.n_rot / 2) + d / 2);
@@ -654,60 +655,67 @@ __global__ void __launch_bounds__(W * 32, 16 / W) matvec_imma(PMatvec p, const f
 
     // ---- add each output's segments in warp order and write it. The warps that hold tiles of (row tile, part)
     //      rp are consecutive, and rp is segment rp - (first rp of the warp) of each. With MV_ROPE_APPEND the row
-    //      is Q|K|V: adjacent outputs (2i, 2i+1) of a q or k head are a RoPE pair held by lanes NT apart; q is
+    //      is Q|K|V: adjacent outputs (2i, 2i+1) of a q or k head are a RoPE pair held by quads NT apart; q is
     //      written rotated, k and v go to the cache at the token's position (rope_append's arithmetic,
     //      src/kernels/rope_append.wgsl; every product rounded, src/ref/ops.zig:64-86).
     const int local_rts = rt_hi - rt_lo;
     const int total = local_rts * 16 * NT;
-    // the candidates of all W warps are loaded together (a warp that holds no tile of rp contributes zero) and
-    // added as a fixed pairwise tree: the order does not depend on the step's token count
+    // Four adjacent lanes (a quad) work on one output: lane q loads the candidates of warps q W/4 .. (a warp that
+    // holds no tile of rp contributes zero) and adds them pairwise; two shuffles add the quads' sums. Together this
+    // is one fixed pairwise tree over the W warps: the order does not depend on the step's token count.
+    constexpr int CPT = W / 4;
+    const int q4 = tid & 3;
     auto seg_sum = [&](int rp, int row, int tk) {
         const int T0 = rp * units, T1 = T0 + units;
-        float c[W];
+        float c[CPT];
 #pragma unroll
-        for (int w = 0; w < W; w++) {
+        for (int e = 0; e < CPT; e++) {
+            const int w = q4 * CPT + e;
             const int wlo = tab_lo[w], whi = tab_lo[w + 1];
             const bool has = wlo < T1 && whi > T0 && whi > wlo;   // (an empty range holds nothing)
             const int sg = has ? rp - tab_rp[w] : 0;
             const float r = red[((size_t)(w * seg_max + sg) * 16 + row) * SLOTS + tk];
-            c[w] = has ? r : 0.f;
+            c[e] = has ? r : 0.f;
         }
 #pragma unroll
-        for (int span = 1; span < W; span *= 2)
+        for (int span = 1; span < CPT; span *= 2)
 #pragma unroll
-            for (int w = 0; w < W; w += 2 * span) c[w] = __fadd_rn(c[w], c[w + span]);
-        return c[0];
+            for (int e = 0; e < CPT; e += 2 * span) c[e] = __fadd_rn(c[e], c[e + span]);
+        float sum = c[0];
+        sum = __fadd_rn(sum, __shfl_xor_sync(0xffffffffu, sum, 1));
+        sum = __fadd_rn(sum, __shfl_xor_sync(0xffffffffu, sum, 2));
+        return sum;
     };
-    for (int i0 = 0; i0 < total; i0 += THREADS) {
-        const int i = i0 + tid;
-        const int tk = i % NT, row = (i / NT) % 16, rtl = i / (NT * 16);
+    for (int i0 = 0; i0 < total; i0 += THREADS / 4) {
+        const int i = i0 + ep;
+        const bool in_range = i < total;
+        const int ic = in_range ? i : total - 1;   // (whole warps take part in the shuffles)
+        const int tk = ic % NT, row = (ic / NT) % 16, rtl = ic / (NT * 16);
         const int j = (rt_lo + rtl) * 16 + row;
-        const bool valid = i < total && j < n;
-        float v = 0.f, u = 0.f;
-        if (valid) {
-            v = seg_sum(rtl * nparts, row, tk);
-            if (pair) u = seg_sum(rtl * nparts + 1, row, tk);
-            if (norm) {
-                // (explicitly rounded: a product that the compiler fused with the accumulation below in one
-                // instantiation and not in another would change a token's bits with the step's token count)
-                v = __fmul_rn(v, nsc[tk]);
-                u = __fmul_rn(u, nsc[tk]);
-            }
+        const bool valid = in_range && j < n;
+        float v = seg_sum(rtl * nparts, row, tk), u = 0.f;
+        if (pair) u = seg_sum(rtl * nparts + 1, row, tk);
+        if (norm) {
+            // (explicitly rounded: a product that the compiler fused with the accumulation below in one
+            // instantiation and not in another would change a token's bits with the step's token count)
+            v = __fmul_rn(v, nsc[tk]);
+            u = __fmul_rn(u, nsc[tk]);
         }
+        if (!valid) v = u = 0.f;
         if (pair) v = __fmul_rn(silu_f(v), u);
         const size_t o = (size_t)(t0 + tk) * p.out_stride + p.col0 + j;
         if (rope != nullptr) {
-            const float other = __shfl_xor_sync(0xffffffffu, v, NT);  // the pair's other element (whole warps run this loop)
-            if (!valid) continue;
+            const float other = __shfl_xor_sync(0xffffffffu, v, 4 * NT);  // the pair's other element (whole warps run this loop)
+            if (!valid || q4 != 0) continue;
             const PRopeAppend& r = rope->p;
             const int tok = t0 + tk;
-            const uint32_t pos = i == tid ? rope_pos : (rope->seq_pos ? rope->seq_pos[tok] : rope->step->pos0 + (uint32_t)tok);
+            const uint32_t pos = i0 == 0 ? rope_pos : (rope->seq_pos ? rope->seq_pos[tok] : rope->step->pos0 + (uint32_t)tok);
             const uint32_t col = p.col0 + (uint32_t)j, hd = r.head_dim, q_head = r.gated ? 2 * hd : hd;
             const bool is_q = col < r.k_off, is_k = !is_q && col < r.v_off;
             const uint32_t d = is_q ? col % q_head : (col - (is_k ? r.k_off : r.v_off)) % hd;
             float val = v;
             if ((is_q || is_k) && d < r.n_rot) {
-                const float2 cs = i == tid ? rope_cs : rope->table[(size_t)pos * (r.n_rot / 2) + d / 2];
+                const float2 cs = i0 == 0 ? rope_cs : rope->table[(size_t)pos * (r.n_rot / 2) + d / 2];
                 val = (d & 1) ? __fadd_rn(__fmul_rn(other, cs.y), __fmul_rn(v, cs.x)) : __fsub_rn(__fmul_rn(v, cs.x), __fmul_rn(other, cs.y));
             }
             out[o] = is_q ? val : v;  // the row keeps rotated q and, like rope_append, unrotated k and v
@@ -720,8 +728,8 @@ __global__ void __launch_bounds__(W * 32, 16 / W) matvec_imma(PMatvec p, const f
             }
             continue;
         }
-        if (!valid) continue;
-        if (p.flags & MV_ACCUMULATE) v = __fadd_rn(v, (i == tid && !early) ? first_old : __ldcg(out + o));
+        if (!valid || q4 != 0) continue;
+        if (p.flags & MV_ACCUMULATE) v = __fadd_rn(v, (i0 == 0 && !early) ? first_old : __ldcg(out + o));
         out[o] = v;
         if (pushing) peer::push(*pu, out + o, v, out_tag);  // this rank's slice, to every rank's exchange slots
     }

@@ -767,7 +767,7 @@ ZCU_EXPORT size_t zcu_artifact(uint32_t kernel, uint32_t variant, char* out, siz
         if (is_matvec) ok = matvec_variant_ok(kernel, variant);
         else ok = variant == 0 || (has_rung && variant == ZCU_VARIANT_PREFILL_BF16_TC) ||
                   (kernel == ZCU_K_DELTA_RULE && (variant == ZCU_VARIANT_DELTA_CHUNK64 || variant == ZCU_VARIANT_DELTA_CHUNK64_F32)) ||
-                  (kernel == ZCU_K_ATTN_SPLIT && (variant == 1 || variant == 3 || variant == 4));  // the forms of the fast path (k_attn.cu)
+                  (kernel == ZCU_K_ATTN_SPLIT && (variant == 1 || variant == 3));  // the forms of the fast path (k_attn.cu)
     }
     if (!ok) {
         if (out && capacity) out[0] = 0;
