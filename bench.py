@@ -339,7 +339,7 @@ class DecodeStep:
     context = 8192
 
     def __init__(self, dist: Dist, batch: int = 1, variant: int = 0, layers: int = 32,
-                 exchange: str = "peer", attn_variant: int = 0, batched: str = "auto", tune: bool = True, early: bool = False):
+                 exchange: str = "peer", attn_variant: int = 0, batched: str = "auto", tune: bool = True):
         import torch
 
         from zllm_b200 import abi
@@ -377,7 +377,7 @@ class DecodeStep:
                                   DenseProgram.arena_slots(self.cfg), handles)
         self.prog = DenseProgram(self.ctx, self.cfg, self.weights, batch, alloc, self.shard, arena=arena,
                                  variants={"attn_split": attn_variant} if attn_variant else None,
-                                 batched=None if batched == "auto" else batched == "on", early=early,
+                                 batched=None if batched == "auto" else batched == "on",
                                  gather=nccl_gather(dist.dist, dist.rank, dist.world) if self.exchange == "nccl" else None)
         if arena is not None:
             class _View:  # the arena's logits as a torch tensor (zero copy), for the read-back of the e2e leg
@@ -1143,7 +1143,6 @@ def run_cuda(args):
         kw["attn_variant"] = args.attn_variant
         kw["batched"] = args.batched
         kw["tune"] = not args.no_tune
-        kw["early"] = args.early
         if args.layers:
             kw["layers"] = args.layers
     wl = WORKLOADS[args.workload](dist, **kw)
@@ -1346,8 +1345,6 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
     ap.add_argument("--batched", default="auto", choices=["auto", "on", "off"],
                     help="decode: Q4_K multiplies in one pass for all sequences (tcgen05 family; auto = for 5..64 sequences on one GPU)")
-    ap.add_argument("--early", action="store_true",
-                    help="decode with the peer exchange: multiplies wait for their activations' tags only, not for the kernel before them")
     ap.add_argument("--no-tune", action="store_true", help="decode: skip the load-time sweep over the multiply's variants")
     ap.add_argument("--attn-variant", type=int, default=0, help="decode: form of attn_split's fast path (0 default, 1-4: k_attn.cu)")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],

@@ -288,15 +288,8 @@ typedef struct zcu_peer_ext {
     uint32_t magic;     /* ZCU_PEER_MAGIC */
     uint32_t wait_slot; /* or ZCU_PEER_NONE */
     uint32_t push_slot; /* or ZCU_PEER_NONE */
-    uint32_t flags;     /* ZCU_PEER_EARLY or 0 */
+    uint32_t reserved;
 } zcu_peer_ext;
-/* With ZCU_PEER_EARLY a matvec_q4_k / matvec_q8_0 (tensor-core family) that reads its activations from `wait_slot`
- * waits for nothing but their tags: it starts its arithmetic while the kernel before it is still ending (it does
- * not pass the kernel boundary first; it does so only before it writes its outputs, so that "this kernel has ended"
- * still means "everything before it has"). The caller promises that whatever else the dispatch reads or
- * overwrites (the output it accumulates onto, the cache rows and Step of a fused rope_append) was finished with
- * before the dispatch that precedes it began. */
-#define ZCU_PEER_EARLY 1u
 zcu_result zcu_ipc_export(zcu_context *context, void *ptr, void *out_handle64);
 zcu_result zcu_ipc_open(zcu_context *context, const void *handle64, void **out_ptr);
 zcu_result zcu_peer_config(zcu_context *context, uint32_t rank, uint32_t world, const uint64_t *bases, uint64_t arena_bytes,

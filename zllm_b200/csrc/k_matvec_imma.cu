@@ -310,15 +310,13 @@ __global__ void __launch_bounds__(W * 32, 16 / W) matvec_imma(PMatvec p, const f
     // the exchange tags of this run of the launch list
     const bool x_exchanged = pu->wait_slot != PEER_NONE, pushing = pu->push_slot != PEER_NONE;
     const uint32_t x_tag = x_exchanged ? peer::want_tag(*pu) : 0u, out_tag = pushing ? peer::push_tag(*pu) : 0u;
-    // (an early consumer waits for nothing but the tags of its activations: see PEER_EARLY)
-    const bool early = pu->early != 0;
-    if (!early && !(dbg & 8)) asm volatile("griddepcontrol.wait;\n" ::: "memory");
+    if (!(dbg & 8)) asm volatile("griddepcontrol.wait;\n" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
     TRACE(2);
     // the value this thread's first output accumulates onto: asked for now, needed after the tile stream
     float first_old = 0.f;
     const int ep = tid >> 2;   // the first output this thread's quad writes in the epilogue
-    if ((p.flags & MV_ACCUMULATE) && !early && ep < (rt_hi - rt_lo) * 16 * NT) {
+    if ((p.flags & MV_ACCUMULATE) && ep < (rt_hi - rt_lo) * 16 * NT) {
         const int j0 = (rt_lo + ep / (NT * 16)) * 16 + (ep / NT) % 16;
         if (j0 < n) first_old = __ldcg(out + (size_t)(t0 + ep % NT) * p.out_stride + p.col0 + j0);
     }
@@ -344,11 +342,6 @@ __global__ void __launch_bounds__(W * 32, 16 / W) matvec_imma(PMatvec p, const f
     if (!(dbg & 4)) {
         const int xr = p.x_stride ? (int)p.x_stride * 4 : k;
         constexpr int ub = 4;   // blocks per round
-        if (early) {
-            // one lane a warp looks out for the warp's first slot; the others sleep meanwhile instead of polling
-            if (lane == 0 && warp < nblk) (void)peer::read1(*pu, x + (size_t)t0 * xr + (size_t)warp * 256, x_tag, status);
-            __syncwarp();
-        }
 #pragma unroll 1
         for (int tk = 0; tk < NT; tk++) {
             const float* xt = x + (size_t)(t0 + tk) * xr;
@@ -646,10 +639,6 @@ __global__ void __launch_bounds__(W * 32, 16 / W) matvec_imma(PMatvec p, const f
 #endif
     if (timed_out && lane == 0 && status) atomicExch(status, 1);
     TRACE(4);
-    // An early consumer passes the kernel boundary here, before it reads an output to accumulate onto or writes
-    // anything: the kernel before it delivered its last tag several microseconds ago, so this does not wait, and
-    // "this kernel has ended" keeps meaning "everything before it has".
-    if (early) asm volatile("griddepcontrol.wait;\n" ::: "memory");
     __syncthreads();
     TRACE(5);
 
@@ -729,7 +718,7 @@ __global__ void __launch_bounds__(W * 32, 16 / W) matvec_imma(PMatvec p, const f
             continue;
         }
         if (!valid || q4 != 0) continue;
-        if (p.flags & MV_ACCUMULATE) v = __fadd_rn(v, (i0 == 0 && !early) ? first_old : __ldcg(out + o));
+        if (p.flags & MV_ACCUMULATE) v = __fadd_rn(v, i0 == 0 ? first_old : __ldcg(out + o));
         out[o] = v;
         if (pushing) peer::push(*pu, out + o, v, out_tag);  // this rank's slice, to every rank's exchange slots
     }

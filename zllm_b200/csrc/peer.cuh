@@ -11,8 +11,8 @@
 // several exchanges of a step write in turn (the residual stream) therefore never shows the same tag twice, and
 // tags are never 0 (the arena starts zeroed). The epoch is one local word that every kernel of the list reads
 // at its start and that only the list's closing dispatch (ZCU_K_EXT_PEER_NEXT, ordered after everything before it)
-// advances: producer and consumer of a slot agree on its tag without telling each other anything, there is no
-// per-kernel counting, and a consumer may start - and wait for the tags - while its producer still runs. Every
+// advances: producer and consumer of a slot agree on its tag without telling each other anything, and there is no
+// per-kernel counting. Every
 // rank runs the same list, so the epochs of all ranks agree. A slot is written at most once per epoch.
 // A fast rank cannot overwrite a slot that a slow rank still has to read: to reach the next write of a buffer it
 // must have read, through the exchanges in between, data that the slow rank produces only after that read.
@@ -31,12 +31,8 @@ struct PPeer {
     uint32_t magic;      // PEER_MAGIC
     uint32_t wait_slot;  // the input vector comes from this exchange (PEER_NONE: it is local)
     uint32_t push_slot;  // outputs go to every rank as this exchange (PEER_NONE: local only)
-    uint32_t flags;      // PEER_EARLY
+    uint32_t _pad;
 };
-// The tags of wait_slot are the ONLY thing this dispatch has to wait for: whatever else it reads or overwrites was
-// finished with before the dispatch that precedes it began. A multiply with this flag does not wait for the kernel
-// before it to end (only, at its own end, so that kernel completion stays transitive along the stream).
-constexpr uint32_t PEER_EARLY = 1u;
 
 struct PeerTable {
     int32_t rank, world;
@@ -51,7 +47,7 @@ struct PeerTable {
 struct PeerUse {  // what one launch does with the table
     PeerTable t;
     uint32_t wait_slot, push_slot;
-    uint32_t early, _pad;  // early: PEER_EARLY was given
+    uint32_t _pad[2];
 };
 
 #ifdef __CUDACC__
@@ -105,7 +101,7 @@ __device__ __forceinline__ float4 read4(const PeerUse& u, const float* local, ui
         if (a.y == tag && a.w == tag && b.y == tag && b.w == tag) break;
         if (spins == 0) t0 = now_ns();
         if (gave_up(u, t0, spins, status)) break;
-        __nanosleep(spins < 8 ? 100u : 400u);   // (a consumer that started early looks many times: not back to back)
+        if (spins >= 32) __nanosleep(64u);   // (a long wait does not poll back to back)
     }
     return make_float4(__uint_as_float(a.x), __uint_as_float(a.z), __uint_as_float(b.x), __uint_as_float(b.z));
 }
@@ -132,7 +128,7 @@ __device__ __forceinline__ float read1(const PeerUse& u, const float* local, uin
         if (a.y == tag) break;
         if (spins == 0) t0 = now_ns();
         if (gave_up(u, t0, spins, status)) break;
-        __nanosleep(spins < 8 ? 100u : 400u);
+        if (spins >= 32) __nanosleep(64u);
     }
     return __uint_as_float(a.x);
 }

@@ -742,7 +742,6 @@ zcu_result parse_peer(const LaunchArgs& a, PeerUse& u, const void* out_lo, const
              "peer exchange: slot out of range (%u, %u of %u)", pp.wait_slot, pp.push_slot, u.t.slots);
     u.wait_slot = pp.wait_slot;
     u.push_slot = pp.push_slot;
-    u.early = (pp.flags & PEER_EARLY) != 0 && pp.wait_slot != PEER_NONE;
     if (u.push_slot != PEER_NONE) {
         const uint64_t lo = reinterpret_cast<uint64_t>(out_lo), hi = reinterpret_cast<uint64_t>(out_hi), base = u.t.base[u.t.rank];
         ZCU_NEED(a, lo >= base && hi <= base + u.t.ll_off && lo <= hi, "peer exchange: the output is not inside the local arena");

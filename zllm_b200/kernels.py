@@ -204,16 +204,14 @@ VARIANT_DELTA_CHUNK64_F32 = 0xFFFD0001   # the same form in f32 on the CUDA core
 
 # The tensor-parallel exchange a dispatch takes part in (zcu_peer_ext): appended to its parameter block.
 PEER_MAGIC, PEER_NONE, EXT_PEER_WAIT, EXT_PEER_NEXT = 0x52454550, 0xFFFFFFFF, 64, 65
-PeerExt = _struct("PeerExt", [("magic", u32), ("wait_slot", u32), ("push_slot", u32), ("flags", u32)])
-PEER_EARLY = 1  # the tags of wait_slot are all the dispatch waits for (include/zllm_cuda.h)
+PeerExt = _struct("PeerExt", [("magic", u32), ("wait_slot", u32), ("push_slot", u32), ("reserved", u32)])
 
 
-def with_peer(params, wait=None, push=None, early=False):
+def with_peer(params, wait=None, push=None):
     """`params` followed by a PeerExt (or `params` itself when the dispatch takes no part in an exchange)."""
     if wait is None and push is None:
         return params
-    ext = PeerExt(PEER_MAGIC, PEER_NONE if wait is None else wait, PEER_NONE if push is None else push,
-                  PEER_EARLY if (early and wait is not None) else 0)
+    ext = PeerExt(PEER_MAGIC, PEER_NONE if wait is None else wait, PEER_NONE if push is None else push, 0)
     raw = bytes(params) + bytes(ext)
     return (C.c_uint8 * len(raw)).from_buffer_copy(raw)
 
@@ -229,7 +227,7 @@ class Launcher:
 
     # -- the decode multiply: grid (ceil(n / groupRows), m, 1) in the reference; only m matters here
     def matvec(self, ttype, x, w, out, n, k, m=1, col0=0, out_stride=None, flags=0, eps=0.0, half=0, x_stride=0,
-               norm_w=None, variant=0, rope=None, wait=None, push=None, early=False):
+               norm_w=None, variant=0, rope=None, wait=None, push=None):
         """`rope` = (RopeAppend, [table, kc, vc, step(, positions)]) fuses rope_append into the multiply that
         produces the Q|K|V row (ROPE_APPEND_FUSED; needs norm_w as binding 3)."""
         p = Matvec(n, k, col0, out_stride if out_stride is not None else n, eps, flags, half, x_stride)
@@ -239,7 +237,7 @@ class Launcher:
             p.flags |= ROPE_APPEND_FUSED
             p = MatvecRope(p, rope[0])
             args += list(rope[1])
-        self.launch(MATVEC_KERNEL[ttype], with_peer(p, wait, push, early), args, (-(-n // 8), m, 1), variant)
+        self.launch(MATVEC_KERNEL[ttype], with_peer(p, wait, push), args, (-(-n // 8), m, 1), variant)
 
     def peer_wait(self, slot: int, vector):
         """Waits (on the device, in stream order) for every rank's slice of exchange `slot` and fills in the plain

@@ -123,8 +123,7 @@ class DenseProgram:
     """
 
     def __init__(self, ctx, cfg: DenseConfig, weights, batch: int, alloc, shard: Shard | None = None, gather=None,
-                 variants: dict | None = None, fuse_rope: bool | None = None, arena=None, batched: bool | None = None,
-                 early: bool = False):
+                 variants: dict | None = None, fuse_rope: bool | None = None, arena=None, batched: bool | None = None):
         self.ctx, self.cfg, self.w, self.B = ctx, cfg, weights, batch
         self.sh = shard or Shard()
         self.gather = gather
@@ -132,7 +131,6 @@ class DenseProgram:
         # reads whole; their producers store into every rank's arena and publish an exchange slot, their
         # consumers wait for it. Slots: 4 per layer (att, x after wo, act, x after down), then the logits.
         self.arena = arena
-        self.early = early
         assert arena is None or gather is None
         self.L = K.Launcher(ctx)
         self.variants = variants or {}
@@ -196,11 +194,6 @@ class DenseProgram:
 
     # ---- the launch list
     def _matvec(self, ttype, x, w, out, n, k, **kw):
-        # A multiply that takes its activations from an exchange waits for their tags and for nothing else: all it
-        # reads or overwrites besides (the residual slice it accumulates onto, the cache rows and Q|K|V row of a
-        # fused rope_append) was last touched at least two dispatches earlier.
-        if kw.get("wait") is not None:
-            kw["early"] = self.early
         v = self.variants.get((ttype, n, k), 0)
         if v == 0 and self.batched and ttype == "q4_k" and k % 256 == 0 and "rope" not in kw:
             v = K.MATVEC_BATCHED
