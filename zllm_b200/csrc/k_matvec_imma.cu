@@ -52,10 +52,8 @@ constexpr int SMEM_MAX = 220 * 1024;   // (a fifth stage at k = 4096 would fit i
 #ifdef ZCU_TRACE
 // Debug build only: per-CTA timestamps of the kernel's phases (globaltimer, ns).
 __device__ unsigned long long g_mv_trace[256 * 12];
-__device__ int g_mv_box = 16 * 160;   // bytes a box copy delivers (debug: other box shapes)
 __device__ int g_mv_dbg;   // bit 0: the tile stream without its arithmetic; bit 1: the arithmetic without copies or waits
 #define MV_DBG g_mv_dbg
-#define MV_BOX (uint32_t)g_mv_box
 #define TRACE(i)                                                                    \
     do {                                                                            \
         if (threadIdx.x == 0 && blockIdx.x < 256) {                                 \
@@ -67,13 +65,6 @@ __device__ int g_mv_dbg;   // bit 0: the tile stream without its arithmetic; bit
 #else
 #define TRACE(i) do {} while (0)
 #define MV_DBG 0
-#define MV_BOX (16u * TILE_ROW)
-#endif
-
-#ifdef ZCU_TRACE
-int g_dbg_box_bytes = 0, g_dbg_box_rows = 0;
-const uint8_t* g_pf_base = nullptr;
-size_t g_pf_size = 0, g_pf_total = 0;
 #endif
 
 // Tensor map of a weight matrix for these tiles: the matrix as bytes, boxes of 16 rows x 160 bytes (or x 16
@@ -83,9 +74,6 @@ size_t g_pf_size = 0, g_pf_total = 0;
 // row's end. `rows`: every row the multiply may touch (both halves of a SILU_PAIR matrix).
 bool weight_map(CUtensorMap* map, const void* w, bool q4, int k, size_t rows, bool scales) {
     const uint64_t rb = q4 ? (uint64_t)(k / 256) * 144 : (((uint64_t)k + k / 16 + 15) & ~(uint64_t)15);
-#ifdef ZCU_TRACE
-    if (g_dbg_box_bytes && !scales) return tma::bytes_2d(map, w, rows, rb, (uint32_t)g_dbg_box_bytes, (uint32_t)g_dbg_box_rows);
-#endif
     return tma::bytes_2d(map, w, rows, rb, scales ? 16u : (uint32_t)TILE_ROW, 16u);
 }
 
@@ -175,8 +163,7 @@ __global__ void __launch_bounds__(W * 32, 16 / W) matvec_imma(PMatvec p, const f
                                                              const __grid_constant__ CUtensorMap smap, float* __restrict__ out,
                                                              const float* __restrict__ norm_w, int t0, int seg_max,
                                                              int* __restrict__ status, const __grid_constant__ MvRope rope_arg,
-                                                             const __grid_constant__ PeerUse pu_arg, const uint8_t* __restrict__ next_w,
-                                                             uint32_t next_bytes) {
+                                                             const __grid_constant__ PeerUse pu_arg) {
     constexpr bool Q4 = TYPE == W_Q4_K;
     constexpr int NB = Q4 ? NT : (NT + 1) / 2;   // 8-column blocks: one per token (Q4_K), one per two tokens (Q8_0)
     constexpr int SLOTS = Q4 ? NT : 2 * NB;       // token slots of a parked segment
@@ -232,7 +219,7 @@ __global__ void __launch_bounds__(W * 32, 16 / W) matvec_imma(PMatvec p, const f
             const int rtl = pair ? is_rp >> 1 : is_rp;
             const int y = ((pair && (is_rp & 1)) ? (int)p.half : 0) + (rt_lo + rtl) * 16;
             if constexpr (Q4) {
-                mbar_expect_tx(mb, MV_BOX);
+                mbar_expect_tx(mb, 16u * TILE_ROW);
                 tma_tile(dst, &wmap, is_unit * 144, y, mb);
             } else {
                 // four blocks of values, and the 16 bytes that hold the scales of blocks (b0 & ~7) .. +7 (k is a
@@ -262,18 +249,6 @@ __global__ void __launch_bounds__(W * 32, 16 / W) matvec_imma(PMatvec p, const f
             fill--;
         }
     };
-
-    // the weights of the launch after this one: asked into L2 now, so that HBM keeps streaming through this
-    // kernel's fixed phases and across the boundary (this kernel's own tiles were asked for by its predecessor)
-    if (next_w != nullptr) {
-        constexpr uint32_t PF = 4096;
-        const uint32_t pieces = (next_bytes + PF - 1) / PF;
-        const uint32_t p_lo = (uint32_t)(((uint64_t)cta * pieces) / (uint32_t)ncta), p_hi = (uint32_t)(((uint64_t)(cta + 1) * pieces) / (uint32_t)ncta);
-        for (uint32_t i = p_lo + (uint32_t)tid; i < p_hi; i += THREADS) {
-            const uint32_t off = i * PF, len = min(PF, next_bytes - off) & ~15u;
-            if (len) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n" ::"l"(next_w + off), "r"(len) : "memory");
-        }
-    }
 
     int8_t* xd = reinterpret_cast<int8_t*>(smem + L.xd);
     int8_t* sxd = reinterpret_cast<int8_t*>(smem + L.sxd);
@@ -756,15 +731,7 @@ zcu_result launch_staged(const LaunchArgs& a, const MvArgs& v, int t0, int grid,
     CUtensorMap wmap, smap;
     if (!weight_map(&wmap, v.w, Q4, (int)v.p.k, rows, false) || !weight_map(&smap, v.w, Q4, (int)v.p.k, rows, !Q4))
         return zcu_fail(a, ZCU_E_GPU, "matvec_imma: the driver refused a tensor map (n %u, k %u)", v.p.n, v.p.k);
-    const uint8_t* next_w = nullptr;
-    uint32_t next_bytes = 0;
-#ifdef ZCU_TRACE
-    if (g_pf_total) {
-        next_w = g_pf_base + ((size_t)(v.w - g_pf_base) + g_pf_size) % g_pf_total;
-        next_bytes = (uint32_t)g_pf_size;
-    }
-#endif
-    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, v.p, v.x, wmap, smap, v.out, v.nw, t0, seg_max, a.status, v.rope, v.peer, next_w, next_bytes);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, v.p, v.x, wmap, smap, v.out, v.nw, t0, seg_max, a.status, v.rope, v.peer);
     if (e != cudaSuccess) return zcu_fail(a, ZCU_E_GPU, "matvec_imma: launch failed: %s", cudaGetErrorString(e));
     return ZCU_OK;
 }
@@ -847,17 +814,6 @@ zcu_result launch_matvec_imma(const LaunchArgs& a, const mv::MvArgs& v, int type
 #ifdef ZCU_TRACE
 extern "C" __attribute__((visibility("default"))) int zcu_dbg_trace_read(unsigned long long* out, size_t count) {
     return (int)cudaMemcpyFromSymbol(out, g_mv_trace, count * sizeof(unsigned long long));
-}
-extern "C" __attribute__((visibility("default"))) void zcu_dbg_prefetch(const void* base, size_t size, size_t total) {
-    g_pf_base = (const uint8_t*)base;
-    g_pf_size = size;
-    g_pf_total = total;
-}
-extern "C" __attribute__((visibility("default"))) int zcu_dbg_box(int bytes, int rows) {
-    g_dbg_box_bytes = bytes;
-    g_dbg_box_rows = rows;
-    const int tx = bytes * rows;
-    return (int)cudaMemcpyToSymbol(g_mv_box, &tx, sizeof(int));
 }
 extern "C" __attribute__((visibility("default"))) int zcu_dbg_mode(int mode) {
     return (int)cudaMemcpyToSymbol(g_mv_dbg, &mode, sizeof(int));
