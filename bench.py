@@ -339,7 +339,9 @@ class DecodeStep:
     context = 8192
 
     def __init__(self, dist: Dist, batch: int = 1, variant: int = 0, layers: int = 32,
-                 exchange: str = "peer", attn_variant: int = 0, batched: str = "auto", tune: bool = True):
+                 exchange: str = "peer", attn_variant: int = 0, batched: str = "auto", tune: bool = True, e2e: str = "sample"):
+        import ctypes as C
+
         import torch
 
         from zllm_b200 import abi
@@ -413,6 +415,19 @@ class DecodeStep:
         self.tgraph = None
         self.mv_graph = None
         self.bytes = self.prog.algorithmic_bytes(self.positions)
+        # The end-to-end leg draws each sequence's next token on the GPU (the reference's sampler at temperature 0:
+        # src/sampler/sampler.zig), so a step costs the host 4 bytes in and 16 bytes out per sequence, not a row of logits.
+        self.e2e = e2e
+        vocab = self.cfg.vocab
+        self.s_block = K.sample_params(vocab, temperature=0.0)
+        self.s_params = alloc(C.sizeof(K.Sample)).upload(np.frombuffer(bytes(self.s_block), dtype=np.uint8))
+        self.s_bias, self.s_mask = alloc(256), alloc(vocab * 4)
+        self.s_counts, self.s_work = alloc(vocab * 4), alloc(vocab * 4)
+        self.s_state = [alloc(K.sample_state_words(vocab) * 4) for _ in range(batch)]
+        self.s_next = alloc(16 * batch)
+        self.s_step = alloc(16).upload(np.array([1, 0, 0, 0], dtype=np.uint32))
+        self.pinned_next = torch.empty((batch, 4), dtype=torch.int32).pin_memory()
+        torch.cuda.synchronize()
 
     def _record(self):
         self.prog.record_step(self.context + 1)
@@ -436,17 +451,42 @@ class DecodeStep:
         with torch.cuda.stream(self.stream):
             self.tgraph.replay()
 
+    def draw(self):
+        """One greedy draw per sequence from the step's logits (one launch each); the tokens land in s_next."""
+        vocab, K = self.cfg.vocab, self.K
+        for b in range(self.batch):
+            logits = (self.logits_view.data_ptr() + 4 * b * vocab, 4 * vocab)
+            self.prog.L.sample(self.s_block, self.s_params, logits, self.s_bias, self.s_mask, self.s_counts, self.s_work,
+                               self.s_state[b], self.s_next.at(16 * b, 16), self.s_step, steps=[(K.PH_PREP, 0)])
+
     def e2e_step(self):
         torch = self.torch
         with torch.cuda.stream(self.stream):
             self.prog.tokens.t[: 4 * self.batch].view(torch.int32).copy_(self.pinned_tokens, non_blocking=True)
         self.step()
-        with torch.cuda.stream(self.stream):
-            self.pinned_logits.copy_(self.logits_view.view(self.batch, self.cfg.vocab), non_blocking=True)
+        if self.e2e == "sample":
+            self.draw()
+            with torch.cuda.stream(self.stream):
+                self.pinned_next.copy_(self.s_next.t[: 16 * self.batch].view(torch.int32).view(self.batch, 4), non_blocking=True)
+        else:
+            with torch.cuda.stream(self.stream):
+                self.pinned_logits.copy_(self.logits_view.view(self.batch, self.cfg.vocab), non_blocking=True)
         self.stream.synchronize()
 
+    def e2e_check(self) -> bool:
+        """After an e2e step: the drawn tokens are the logits' largest entries (the first of equals)."""
+        if self.e2e != "sample":
+            return True
+        logits = self.logits_view.view(self.batch, self.cfg.vocab).float().cpu().numpy()
+        return bool((self.pinned_next[:, 0].numpy().astype(np.int64) == logits.argmax(axis=1)).all())
+
     def e2e_bytes(self):
+        if self.e2e == "sample":
+            return self.tokens.nbytes, self.pinned_next.numel() * 4
         return self.tokens.nbytes, self.pinned_logits.numel() * 4
+
+    def e2e_launches(self) -> int:
+        return self.batch if self.e2e == "sample" else 0
 
     def launches_per_step(self) -> int:
         return self.prog.launches_per_step or (2 + 7 * self.cfg.layers)
@@ -1143,6 +1183,7 @@ def run_cuda(args):
         kw["attn_variant"] = args.attn_variant
         kw["batched"] = args.batched
         kw["tune"] = not args.no_tune
+        kw["e2e"] = args.e2e
         if args.layers:
             kw["layers"] = args.layers
     wl = WORKLOADS[args.workload](dist, **kw)
@@ -1176,6 +1217,7 @@ def run_cuda(args):
         wl.e2e_step()
     torch.cuda.synchronize()
     e2e_s = dist.max(time.perf_counter() - t0)
+    e2e_ok = wl.e2e_check() if hasattr(wl, "e2e_check") else True
     clocks = sampler.stop() if dist.rank == 0 else {}
     sec_per_step = ms / 1e3 / args.steps
     metric, unit = wl.metric()
@@ -1185,19 +1227,24 @@ def run_cuda(args):
         "warmup": warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
         "scaling": getattr(wl, "scaling", "strong"), "vs_baseline": None, "dtype": getattr(wl, "dtype", "f32"), "data": "synthetic", "config": wl.config(),
         "clocks": clocks,
-        "e2e": {"value": wl.value(e2e_s / args.steps), "unit": unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "e2e": {"value": wl.value(e2e_s / args.steps), "unit": unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                **({"result": "the next token of every sequence, drawn by the GPU sampler at temperature 0; equal to the logits' argmax: "
+                              + str(e2e_ok), "launches_per_step": wl.launches_per_step() + wl.e2e_launches()}
+                   if getattr(wl, "e2e", None) == "sample" else {})},
         "gpu_launches": wl.launches_per_step() * args.steps,
         "roofline": wl.roofline(ms / args.steps),
     }
     if dist.rank == 0 and dist.world == 1 and not args.no_cpu:
         line["cpu_baseline"] = wl.cpu_baseline()
-    failed = False
+    failed = not e2e_ok
     if parity is not None:
         line["tp_parity"] = parity
-        failed = not (parity["max_rel_l2"] <= 1e-4 and parity["argmax_equal"])
+        failed = failed or not (parity["max_rel_l2"] <= 1e-4 and parity["argmax_equal"])
     if dist.rank == 0:
         print(json.dumps(line), flush=True)
-        if failed:
+        if not e2e_ok:
+            print("bench: a drawn token is not its logits' largest entry", file=sys.stderr)
+        elif failed:
             print(f"bench: the sharded step differs from the unsharded one: {parity}", file=sys.stderr)
     if dist.on:
         # Leave without tearing NCCL down: captured graphs still hold its kernels, and a teardown that
@@ -1209,6 +1256,8 @@ def run_cuda(args):
         sys.stderr.flush()
         os._exit(1 if failed else 0)
     dist.close()
+    if failed:
+        sys.exit(1)
 
 
 def run_reference(args):
@@ -1345,6 +1394,8 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
     ap.add_argument("--batched", default="auto", choices=["auto", "on", "off"],
                     help="decode: Q4_K multiplies in one pass for all sequences (tcgen05 family; auto = for 5..64 sequences on one GPU)")
+    ap.add_argument("--e2e", default="sample", choices=["sample", "logits"],
+                    help="decode, end-to-end leg: the next token drawn on the GPU and read back (16 bytes a sequence), or the logits read back")
     ap.add_argument("--no-tune", action="store_true", help="decode: skip the load-time sweep over the multiply's variants")
     ap.add_argument("--attn-variant", type=int, default=0, help="decode: form of attn_split's fast path (0 default, 1-4: k_attn.cu)")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
