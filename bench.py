@@ -411,6 +411,12 @@ class DecodeStep:
         if tune and batch <= 4:
             self.tuned = self.prog.sweep()
             torch.cuda.synchronize()
+            # ... and the best few of each shape tried inside the replayed step (every rank runs the same trials)
+            if self.exchange != "nccl":
+                dist.barrier()
+                self.tuned = {k: v for k, v in self.prog.refine(self.context + 1).items() if isinstance(k, tuple)}
+                torch.cuda.synchronize()
+                dist.barrier()
         self.graph = None
         self.tgraph = None
         self.mv_graph = None
@@ -420,7 +426,7 @@ class DecodeStep:
         self.e2e = e2e
         vocab = self.cfg.vocab
         self.s_block = K.sample_params(vocab, temperature=0.0)
-        self.s_params = alloc(C.sizeof(K.Sample)).upload(np.frombuffer(bytes(self.s_block), dtype=np.uint8))
+        self.s_params = alloc(C.sizeof(K.Sample)).upload(np.frombuffer(bytes(self.s_block), dtype=np.uint8).copy())
         self.s_bias, self.s_mask = alloc(256), alloc(vocab * 4)
         self.s_counts, self.s_work = alloc(vocab * 4), alloc(vocab * 4)
         self.s_state = [alloc(K.sample_state_words(vocab) * 4) for _ in range(batch)]

@@ -359,6 +359,9 @@ class Context:
     def graph_launch(self, graph: int):
         self._check(lib().zcu_graph_launch(self.h, graph))
 
+    def graph_destroy(self, graph: int):
+        self._check(lib().zcu_graph_destroy(self.h, graph))
+
     def close(self):
         if self.h:
             for b in self._bufs:

@@ -213,6 +213,48 @@ class DenseProgram:
         self.sweep_report = s.report
         return table
 
+    def refine(self, max_keys: int, top: int = 3, reps: int = 6) -> dict:
+        """After sweep(): the candidates that were fastest on their own are tried inside the replayed step, shape by
+        shape (largest first), and the one with the fastest STEP stays. A multiply's time in the step depends on its
+        neighbours (what the kernel before it leaves in flight, how its ring depth meets the next kernel's start), and
+        the sweep's figures of the best few lie within its noise of each other. Every rank of a tensor-parallel program
+        runs the same number of steps here (`top` trials per shape), as the exchange requires."""
+        import time
+
+        by_shape = {}
+        for ttype, n, k, variant, ns in getattr(self, "sweep_report", []):
+            if ns is not None:
+                by_shape.setdefault((ttype, n, k), []).append((ns, variant))
+
+        def step_seconds() -> float:
+            self.ctx.capture_begin()
+            self.record_step(max_keys)
+            g = self.ctx.capture_end()
+            for _ in range(2):
+                self.ctx.graph_launch(g)
+            self.ctx.sync()
+            best = float("inf")
+            for _ in range(3):
+                t0 = time.perf_counter()
+                for _ in range(reps):
+                    self.ctx.graph_launch(g)
+                self.ctx.sync()
+                best = min(best, (time.perf_counter() - t0) / reps)
+            self.ctx.graph_destroy(g)
+            return best
+
+        self.refine_report = []
+        for shape in sorted(by_shape, key=lambda s: -s[1] * s[2]):
+            trials = [v for _, v in sorted(by_shape[shape])[:top]]
+            trials += [trials[0]] * (top - len(trials))
+            timed = []
+            for v in trials:
+                self.variants[shape] = v
+                timed.append((step_seconds(), v))
+            self.variants[shape] = min(timed)[1]
+            self.refine_report.append((shape, timed))
+        return self.variants
+
     def _sweep_shapes(self, s):
         cfg, e = self.cfg, self.cfg.hidden
         layers = self.w["layers"]
