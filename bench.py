@@ -339,7 +339,7 @@ class DecodeStep:
     context = 8192
 
     def __init__(self, dist: Dist, batch: int = 1, variant: int = 0, layers: int = 32,
-                 exchange: str = "peer", attn_variant: int = 0, batched: str = "auto", tune: bool = True, e2e: str = "sample"):
+                 exchange: str = "peer", attn_variant: int = 0, batched: str = "auto", tune: bool = True, e2e: str = "sample", arena1: bool = False, fuse_combine: bool = True):
         import ctypes as C
 
         import torch
@@ -367,7 +367,7 @@ class DecodeStep:
 
         # N ranks exchange output slices either by the kernels themselves (stores into every rank's arena over
         # NVLink, counters instead of collectives) or by NCCL all-gathers between the kernels
-        self.exchange = exchange if dist.on else "none"
+        self.exchange = exchange if (dist.on or (arena1 and exchange == "peer")) else "none"
         arena = None
         if self.exchange == "peer":
             def handles(h: bytes):
@@ -381,6 +381,7 @@ class DecodeStep:
                                  variants={"attn_split": attn_variant} if attn_variant else None,
                                  batched=None if batched == "auto" else batched == "on",
                                  gather=nccl_gather(dist.dist, dist.rank, dist.world) if self.exchange == "nccl" else None)
+        self.prog.fuse_combine = self.prog.fuse_combine and fuse_combine
         if arena is not None:
             class _View:  # the arena's logits as a torch tensor (zero copy), for the read-back of the e2e leg
                 __cuda_array_interface__ = {"shape": (batch * self.cfg.vocab,), "typestr": "<f4",
@@ -1190,6 +1191,8 @@ def run_cuda(args):
         kw["batched"] = args.batched
         kw["tune"] = not args.no_tune
         kw["e2e"] = args.e2e
+        kw["arena1"] = args.arena
+        kw["fuse_combine"] = not args.no_fuse_combine
         if args.layers:
             kw["layers"] = args.layers
     wl = WORKLOADS[args.workload](dist, **kw)
@@ -1400,6 +1403,11 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
     ap.add_argument("--batched", default="auto", choices=["auto", "on", "off"],
                     help="decode: Q4_K multiplies in one pass for all sequences (tcgen05 family; auto = for 5..64 sequences on one GPU)")
+    ap.add_argument("--arena", action="store_true",
+                    help="decode on one GPU: the vectors between the kernels go through the tagged slots of a world-of-one exchange, "
+                         "and the output projection merges the attention's partials itself (one launch fewer per layer)")
+    ap.add_argument("--no-fuse-combine", action="store_true",
+                    help="decode with the peer exchange: attn_combine as its own launch instead of the output projection's first phase")
     ap.add_argument("--e2e", default="sample", choices=["sample", "logits"],
                     help="decode, end-to-end leg: the next token drawn on the GPU and read back (16 bytes a sequence), or the logits read back")
     ap.add_argument("--no-tune", action="store_true", help="decode: skip the load-time sweep over the multiply's variants")

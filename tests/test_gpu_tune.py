@@ -55,6 +55,14 @@ def test_the_sweep_times_a_shape_as_the_plan_uses_it_and_a_plan_takes_the_table(
     assert all(prog.variants[key] == v for key, v in table.items())
     tuned = step(prog)
     assert np.linalg.norm(tuned - plain) / np.linalg.norm(plain) <= 1e-5
+    # the best few of each shape tried inside the replayed step: three trials a shape, a choice among them, same logits
+    prog.write_step(np.array([7], dtype=np.uint32), np.array([33], dtype=np.uint32))
+    refined = prog.refine(34, top=3, reps=2)
+    assert len(prog.refine_report) == len(table) and all(len(timed) == 3 for _, timed in prog.refine_report)
+    for shape, timed in prog.refine_report:
+        assert refined[shape] == min(timed)[1] and refined[shape] in [v for _, v in timed]
+    again = step(prog)
+    assert np.linalg.norm(again - plain) / np.linalg.norm(plain) <= 1e-5
 
 
 def test_a_diverging_candidate_is_dropped(gpu, monkeypatch):

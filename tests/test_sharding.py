@@ -159,7 +159,7 @@ def test_exchange_slots_chain_through_the_sharded_launch_list():
     weights = {"embed": ctx.alloc(256), "head": ctx.alloc(256), "out_norm": ctx.alloc(256),
                "layers": [{k: ctx.alloc(256) for k in ("wqkv", "wo", "wgu", "wdown", "attn_norm", "ffn_norm")} for _ in range(cfg.layers)]}
     prog = DenseProgram(ctx, cfg, weights, 1, ctx.alloc, Shard(1, 2), arena=FakeArena())
-    per_layer = 6
+    per_layer = 5   # Q|K|V with rope_append, attn_split, the output projection with attn_combine as its first phase, gate|up, down
     prog.set_rope_table(ctx.alloc(256))
     seen = []
     real = prog.L.launch
@@ -181,13 +181,19 @@ def test_exchange_slots_chain_through_the_sharded_launch_list():
         ops = exts[1 + per_layer * il: 1 + per_layer * (il + 1)]
         qkv, (wo, gu, down) = ops[0], ops[-3:]
         assert qkv == (None if il == 0 else (4 * il - 1, none))  # the residual stream of the layer before
-        assert ops[1] is None and ops[2] == (none, 4 * il)       # attn_split, then attn_combine pushes the heads' columns
+        assert ops[1] is None                                    # attn_split
+        # the output projection merges the partials, pushes the heads' columns under the slot it waits for, and pushes x
         assert wo == (4 * il, 4 * il + 1) and gu == (4 * il + 1, 4 * il + 2) and down == (4 * il + 2, 4 * il + 3)
     assert exts[-3] == (4 * cfg.layers - 1, 4 * cfg.layers)       # the head
     assert seen[-2] == (K.EXT_PEER_WAIT, (4 * cfg.layers, none))  # the host's wait for the logits
     assert seen[-1] == (K.EXT_PEER_NEXT, (none, none))            # the run ends: the next one tags its exchanges anew
     pushed = [e[1] for e in exts if e is not None and e[1] != none]
-    assert sorted(pushed) == list(range(DenseProgram.arena_slots(cfg)))
+    assert sorted(pushed + [4 * il for il in range(cfg.layers)]) == list(range(DenseProgram.arena_slots(cfg)))
+    # without the fusion attn_combine is its own launch and pushes the heads' columns itself
+    seen.clear()
+    prog.fuse_combine = False
+    prog.record_step(17)
+    assert len(seen) == 2 + 6 * cfg.layers + 2 and [e for _, e in seen][3] == (none, 0)
     assert len(bytes(K.with_peer(K.Matvec(1, 2, 3, 4, 0.0, 0, 0, 0), wait=3))) == C.sizeof(K.Matvec) + 16
     ctx.close()
 
@@ -359,7 +365,7 @@ def test_exchange_slots_chain_through_the_sharded_hybrid_launch_list():
     assert len(seen) == prog.launches_per_step                  # the host's wait for the logits included
     i = 1
     for il in range(cfg.layers):
-        n = 6 if cfg.is_attention(il) else 7
+        n = 5 if cfg.is_attention(il) else 7   # (an attention layer's output projection merges the attention's partials itself)
         ops = seen[i:i + n]
         i += n
         assert ops[0][1] == (None if il == 0 else (4 * il - 1, none))
@@ -368,5 +374,6 @@ def test_exchange_slots_chain_through_the_sharded_hybrid_launch_list():
             assert ops[1][1] is None and ops[2][1] is None and ops[3][1] == (none, 4 * il)
         assert [e for _, e in ops[-3:]] == [(4 * il, 4 * il + 1), (4 * il + 1, 4 * il + 2), (4 * il + 2, 4 * il + 3)]
     pushed = [e[1] for _, e in seen if e is not None and e[1] != none]
+    pushed += [4 * il for il in range(cfg.layers) if cfg.is_attention(il)]   # pushed by the output projection's first phase
     assert sorted(pushed) == list(range(HybridProgram.arena_slots(cfg)))
     ctx.close()

@@ -274,12 +274,16 @@ using attn::AF_KEYS;
 using attn::AF_THREADS;
 using attn::AC_MAX_BLOCKS;
 
+}  // namespace
+
 // Cache positions per partial block: 128 on the fast path, else the reference's 64.
 int attn_keys_per_block(const PAttention& p) {
     const uint32_t group = p.kv_heads ? p.heads / p.kv_heads : 0;
     const bool fast = p.kv == KV_F16 && group >= 1 && group <= 4 && (p.head_dim == 64 || p.head_dim == 128);
-    return fast ? AF_KEYS : AT_BLOCK;
+    return fast ? attn::AF_KEYS : AT_BLOCK;
 }
+
+namespace {
 
 template <int FMT>
 zcu_result launch_split_fmt(const LaunchArgs& a, const PAttention& p, dim3 grid, size_t smem, int group) {

@@ -414,6 +414,32 @@ zcu_result parse_matvec(const LaunchArgs& a, MvArgs& v, uint32_t elem_block, boo
         v.rope.step = static_cast<const PStep*>(a.b[7].ptr);
         v.rope.seq_pos = (a.nb >= 9 && r._pad[0] != 0) ? static_cast<const uint32_t*>(a.b[8].ptr) : nullptr;
     }
+    memset(&v.combine, 0, sizeof(v.combine));
+    if (v.p.flags & MV_ATTN_COMBINE) {
+        // an extension: attn_combine as a first phase of the multiply that reads the attention output. The
+        // parameter block is PMatvec followed by params.Attention; bindings 4.. are attn_combine's qg, part, out,
+        // step[, positions]. The merged heads reach the multiply's other CTAs through the exchange slots of its own
+        // wait_slot, so the dispatch must take its input from an exchange.
+        ZCU_NEED(a, !v.has_rope && a.params_bytes >= sizeof(PMatvec) + sizeof(PAttention) && a.nb >= 8, "matvec + attn_combine: parameter block or bindings too short");
+        ZCU_NEED(a, v.peer.wait_slot != PEER_NONE, "matvec + attn_combine: the multiply must read its input from an exchange (zcu_peer_ext.wait_slot)");
+        MvCombine& c = v.combine;
+        memcpy(&c.p, static_cast<const char*>(a.params) + sizeof(PMatvec), sizeof(PAttention));
+        ZCU_NEED(a, c.p.head_dim <= 256 && c.p.heads > 0 && c.p.max_blocks > 0 && c.p.max_blocks <= 1024, "matvec + attn_combine: head_dim %u, %u heads, max_blocks %u", c.p.head_dim, c.p.heads, c.p.max_blocks);
+        c.qg = static_cast<const float*>(a.b[4].ptr);
+        c.part = static_cast<const float*>(a.b[5].ptr);
+        c.out = static_cast<float*>(a.b[6].ptr);
+        c.step = static_cast<const PStep*>(a.b[7].ptr);
+        c.seq_pos = (a.nb >= 9 && c.p._pad[0] != 0) ? static_cast<const uint32_t*>(a.b[8].ptr) : nullptr;
+        c.kb = attn_keys_per_block(c.p);
+        c.blocks = (int)c.p.heads * v.m;
+        {
+            // the merged heads are pushed as the exchange the multiply waits for: they must lie inside the local arena
+            const size_t orow = c.p._pad[1] ? (size_t)c.p._pad[1] : (size_t)c.p.heads * c.p.head_dim;
+            const uint64_t lo = reinterpret_cast<uint64_t>(c.out + (size_t)c.p.row0 * orow);
+            const uint64_t hi = lo + 4 * ((size_t)(v.m - 1) * orow + (size_t)c.p.heads * c.p.head_dim), base = v.peer.t.base[v.peer.t.rank];
+            ZCU_NEED(a, lo >= base && hi <= base + v.peer.t.ll_off, "matvec + attn_combine: the attention output is not inside the local arena");
+        }
+    }
     return ZCU_OK;
 }
 
@@ -433,6 +459,7 @@ zcu_result launch_quant(const LaunchArgs& a, uint32_t block) {
     if ((a.variant == 0 && imma_ok) || family == ZCU_FAMILY_MMA)
         return launch_matvec_imma(a, v, TYPE, (int)(a.variant & 0xffu), (int)((a.variant >> 8) & 0xffu));
     if (v.has_rope) return zcu_fail(a, ZCU_E_UNSUPPORTED_KERNEL, "matvec + rope_append: only the tensor-core family fuses it");
+    if (v.combine.blocks) return zcu_fail(a, ZCU_E_UNSUPPORTED_KERNEL, "matvec + attn_combine: only the tensor-core family fuses it");
     if (v.peer.wait_slot != PEER_NONE || v.peer.push_slot != PEER_NONE)
         return zcu_fail(a, ZCU_E_UNSUPPORTED_KERNEL, "matvec in a peer exchange: only the tensor-core family takes part");
     if (a.variant == 0) return launch_scalar<TYPE>(a, v);
@@ -468,7 +495,7 @@ static zcu_result launch_kquant(const LaunchArgs& a) {
     zcu_result r = parse_matvec(a, v, 256, true);
     if (r != ZCU_OK) return r;
     if (v.p.n == 0) return ZCU_OK;
-    if (v.has_rope || v.peer.wait_slot != PEER_NONE || v.peer.push_slot != PEER_NONE)
+    if (v.has_rope || v.combine.blocks || v.peer.wait_slot != PEER_NONE || v.peer.push_slot != PEER_NONE)
         return zcu_fail(a, ZCU_E_UNSUPPORTED_KERNEL, "matvec: this weight type runs the scalar family, which takes no fused rope_append or peer exchange");
     return launch_scalar<TYPE>(a, v);
 }

@@ -71,6 +71,7 @@ struct MvArgs {
     PeerUse peer;    // tensor-parallel exchange this launch waits for / publishes (slots PEER_NONE: none)
     bool has_rope;   // MV_ROPE_APPEND: the outputs are a Q|K|V row that is rotated and appended to the cache
     MvRope rope;
+    MvCombine combine;   // MV_ATTN_COMBINE: combine.blocks != 0
 };
 
 }  // namespace mv

@@ -33,6 +33,7 @@
 // lane's B registers are 8 consecutive activation bytes too.
 
 #include "imma_util.cuh"
+#include "k_attn_fast.cuh"
 #include "k_matvec_common.cuh"
 #include "tma_util.cuh"
 
@@ -85,7 +86,8 @@ struct Layout {
 // inverse block scales inv[tokens][k / 256], the warps' parked sums red[warps][seg_max][16][slots], the warps'
 // partial sums of squares ss[tokens][warps], and the epilogue's tables tab[]: where each warp's range of tiles
 // starts (warps + 1), the first (row tile, part) of each warp (warps), then the tokens' RMS scales.
-__host__ __device__ inline Layout layout(int warps, int tokens, int k, bool q4, int slots, int seg_max, int stages) {
+// (`xd_min`: bytes the digit planes' region must hold at least: attn_combine's shared memory, when it runs first)
+__host__ __device__ inline Layout layout(int warps, int tokens, int k, bool q4, int slots, int seg_max, int stages, int xd_min = 0) {
     Layout L;
     int off = 0;
     L.ring = off;
@@ -94,7 +96,7 @@ __host__ __device__ inline Layout layout(int warps, int tokens, int k, bool q4, 
     off += warps * stages * 8;
     off = (off + 127) & ~127;
     L.xd = off;
-    off += 4 * tokens * (k + XPAD);
+    off += max(4 * tokens * (k + XPAD), (xd_min + 15) & ~15);
     L.sxd = off;
     if (q4) off += 4 * tokens * (k / 32 + 16);
     off = (off + 15) & ~15;
@@ -163,7 +165,7 @@ __global__ void __launch_bounds__(W * 32, 16 / W) matvec_imma(PMatvec p, const f
                                                              const __grid_constant__ CUtensorMap smap, float* __restrict__ out,
                                                              const float* __restrict__ norm_w, int t0, int seg_max,
                                                              int* __restrict__ status, const __grid_constant__ MvRope rope_arg,
-                                                             const __grid_constant__ PeerUse pu_arg) {
+                                                             const __grid_constant__ PeerUse pu_arg, const __grid_constant__ MvCombine comb) {
     constexpr bool Q4 = TYPE == W_Q4_K;
     constexpr int NB = Q4 ? NT : (NT + 1) / 2;   // 8-column blocks: one per token (Q4_K), one per two tokens (Q8_0)
     constexpr int SLOTS = Q4 ? NT : 2 * NB;       // token slots of a parked segment
@@ -178,7 +180,7 @@ __global__ void __launch_bounds__(W * 32, 16 / W) matvec_imma(PMatvec p, const f
     const bool norm = (p.flags & MV_NORM) != 0, pair = (p.flags & MV_SILU_PAIR) != 0;
     const MvRope* rope = (p.flags & MV_ROPE_APPEND) ? &rope_arg : nullptr;
     const PeerUse* pu = &pu_arg;
-    const Layout L = layout(W, NT, k, Q4, SLOTS, seg_max, STAGES);
+    const Layout L = layout(W, NT, k, Q4, SLOTS, seg_max, STAGES, comb.blocks ? (int)attn::attn_combine_smem((int)comb.p.max_blocks) : 0);
     const int xcol = k + XPAD, sxcol = k / 32 + 16, nblk = k / 256;
     const int nparts = pair ? 2 : 1;
     const int units = Q4 ? k / 256 : (k / 32 + Q8_UNIT - 1) / Q8_UNIT;  // tiles along k
@@ -288,6 +290,25 @@ __global__ void __launch_bounds__(W * 32, 16 / W) matvec_imma(PMatvec p, const f
     if (!(dbg & 8)) asm volatile("griddepcontrol.wait;\n" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
     TRACE(2);
+    // MV_ATTN_COMBINE: the input is the attention output, and nobody has merged the attention's partials into it yet.
+    // The first CTAs do (one head of one row each, attn_combine's own code on this CTA's 512 threads, its shared
+    // memory where the digit planes will be); they push the heads under the tag this multiply's staging waits for,
+    // so every CTA - on this rank and on the others - sees them arrive element by element.
+    if (comb.blocks != 0) {
+        if constexpr (W * 32 == attn::AC_THREADS) {
+            PeerUse cpu = *pu;
+            cpu.push_slot = pu->wait_slot;
+            cpu.wait_slot = PEER_NONE;
+            for (int c = cta; comb.p.heads != 0 && c < comb.blocks; c += ncta) {
+                VBlock vb;
+                vb.x = c % (int)comb.p.heads, vb.y = c / (int)comb.p.heads, vb.z = 0;
+                vb.tid = tid, vb.nthreads = W * 32, vb.bar = 1;
+                vb.smem = smem + L.xd;
+                attn::attn_combine_body(vb, comb.p, comb.qg, comb.part, comb.out, comb.step, comb.seq_pos, comb.kb, status, &cpu);
+                vb.sync();   // the next merge, or the staging, reuses the shared memory
+            }
+        }
+    }
     // the value this thread's first output accumulates onto: asked for now, needed after the tile stream
     float first_old = 0.f;
     const int ep = tid >> 2;   // the first output this thread's quad writes in the epilogue
@@ -316,7 +337,8 @@ __global__ void __launch_bounds__(W * 32, 16 / W) matvec_imma(PMatvec p, const f
     //      factor of every output and is applied in the epilogue; the warps leave their sums of squares in ss[].
     if (!(dbg & 4)) {
         const int xr = p.x_stride ? (int)p.x_stride * 4 : k;
-        constexpr int ub = 4;   // blocks per round
+        constexpr int UBX = 2;   // blocks per round of an exchanged vector (a slot is twice a float)
+        const int ub = x_exchanged ? UBX : 4;   // blocks per round
 #pragma unroll 1
         for (int tk = 0; tk < NT; tk++) {
             const float* xt = x + (size_t)(t0 + tk) * xr;
@@ -328,14 +350,14 @@ __global__ void __launch_bounds__(W * 32, 16 / W) matvec_imma(PMatvec p, const f
 #pragma unroll
                 for (int u = 0; u < 4; u++) a[u][0] = a[u][1] = make_float4(0.f, 0.f, 0.f, 0.f);
                 if (x_exchanged) {
-                    uint4 raw[4][2][2];
+                    uint4 raw[UBX][2][2];
 #pragma unroll
-                    for (int u = 0; u < 4; u++)
+                    for (int u = 0; u < UBX; u++)
 #pragma unroll
                         for (int h = 0; h < 2; h++)
                             if (b0 + u * W < nblk) peer::look4(*pu, xt + 4 * ((b0 + u * W) * 64 + 32 * h + lane), raw[u][h][0], raw[u][h][1]);
 #pragma unroll
-                    for (int u = 0; u < 4; u++)
+                    for (int u = 0; u < UBX; u++)
 #pragma unroll
                         for (int h = 0; h < 2; h++)
                             if (b0 + u * W < nblk)
@@ -354,7 +376,7 @@ __global__ void __launch_bounds__(W * 32, 16 / W) matvec_imma(PMatvec p, const f
 #pragma unroll
                 for (int u = 0; u < 4; u++) {
                     const int blk = b0 + u * W;
-                    if (blk >= nblk) break;   // warp-uniform
+                    if (blk >= nblk || u >= ub) break;   // warp-uniform
                     float amax = 0.f;
 #pragma unroll
                     for (int h = 0; h < 2; h++) {
@@ -704,7 +726,9 @@ template <int TYPE, int NT, int STAGES, int W>
 zcu_result launch_staged(const LaunchArgs& a, const MvArgs& v, int t0, int grid, int seg_max) {
     constexpr bool Q4 = TYPE == W_Q4_K;
     constexpr int SLOTS = Q4 ? NT : 2 * ((NT + 1) / 2);
-    const Layout L = layout(W, NT, (int)v.p.k, Q4, SLOTS, seg_max, STAGES);
+    // (every pass of a dispatch with MV_ATTN_COMBINE reserves the merge's shared memory: one layout per dispatch)
+    const int xd_min = v.combine.blocks ? (int)attn::attn_combine_smem((int)v.combine.p.max_blocks) : 0;
+    const Layout L = layout(W, NT, (int)v.p.k, Q4, SLOTS, seg_max, STAGES, xd_min);
     auto kern = matvec_imma<TYPE, NT, STAGES, W>;
     static bool configured[64] = {};
     int dev = 0;
@@ -731,19 +755,24 @@ zcu_result launch_staged(const LaunchArgs& a, const MvArgs& v, int t0, int grid,
     CUtensorMap wmap, smap;
     if (!weight_map(&wmap, v.w, Q4, (int)v.p.k, rows, false) || !weight_map(&smap, v.w, Q4, (int)v.p.k, rows, !Q4))
         return zcu_fail(a, ZCU_E_GPU, "matvec_imma: the driver refused a tensor map (n %u, k %u)", v.p.n, v.p.k);
-    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, v.p, v.x, wmap, smap, v.out, v.nw, t0, seg_max, a.status, v.rope, v.peer);
+    if (v.combine.blocks != 0) {
+        if (W * 32 != attn::AC_THREADS) return zcu_fail(a, ZCU_E_UNSUPPORTED_KERNEL, "matvec + attn_combine: needs CTAs of 16 warps");
+    }
+    MvCombine comb = v.combine;
+    if (t0 != 0) comb.p.heads = 0;   // (the dispatch's first pass merges every row; blocks != 0 keeps the layout)
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, v.p, v.x, wmap, smap, v.out, v.nw, t0, seg_max, a.status, v.rope, v.peer, comb);
     if (e != cudaSuccess) return zcu_fail(a, ZCU_E_GPU, "matvec_imma: launch failed: %s", cudaGetErrorString(e));
     return ZCU_OK;
 }
 
 // The deepest ring (at most `want`, 0 = 6) that fits beside the staged activations; 0 when not even two stages fit.
 template <int TYPE, int NT, int W>
-int stages_that_fit(int k, int seg_max, int want, int smem_cap) {
+int stages_that_fit(int k, int seg_max, int want, int smem_cap, int xd_min) {
     constexpr bool Q4 = TYPE == W_Q4_K;
     constexpr int SLOTS = Q4 ? NT : 2 * ((NT + 1) / 2);
     int stages = want ? want : 6;
-    while (stages > 2 && layout(W, NT, k, Q4, SLOTS, seg_max, stages).total > smem_cap) stages--;
-    return layout(W, NT, k, Q4, SLOTS, seg_max, stages).total > smem_cap ? 0 : stages;
+    while (stages > 2 && layout(W, NT, k, Q4, SLOTS, seg_max, stages, xd_min).total > smem_cap) stages--;
+    return layout(W, NT, k, Q4, SLOTS, seg_max, stages, xd_min).total > smem_cap ? 0 : stages;
 }
 
 template <int TYPE, int NT, int W>
@@ -754,7 +783,8 @@ zcu_result launch_one(const LaunchArgs& a, const MvArgs& v, int t0, int want_sta
     const int seg_max = segments_needed((int)v.p.n, (int)v.p.k, q4, pair, grid, W);
     // two CTAs of eight warps share an SM (this kernel's and its neighbour's in the stream): half the memory each
     const int cap = W == 16 ? SMEM_MAX : 110 * 1024;
-    const int stages = stages_that_fit<TYPE, NT, W>((int)v.p.k, seg_max, want_stages, cap);
+    const int stages = stages_that_fit<TYPE, NT, W>((int)v.p.k, seg_max, want_stages, cap,
+                                                    v.combine.blocks ? (int)attn::attn_combine_smem((int)v.combine.p.max_blocks) : 0);
     switch (stages) {
         case 2: return launch_staged<TYPE, NT, 2, W>(a, v, t0, grid, seg_max);
         case 3: return launch_staged<TYPE, NT, 3, W>(a, v, t0, grid, seg_max);

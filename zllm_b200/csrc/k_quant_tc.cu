@@ -976,6 +976,7 @@ zcu_result launch_matmul_q4_k_tc(const LaunchArgs& a) {
 
 // matvec_q4_k, the batched family: one pass over the weights for up to 64 tokens.
 zcu_result launch_matvec_q4_k_tc(const LaunchArgs& a, const mv::MvArgs& v) {
+    if (v.combine.blocks) return zcu_fail(a, ZCU_E_UNSUPPORTED_KERNEL, "matvec_q4_k (tcgen05): attn_combine is not fused into this family");
     const PMatvec& p = v.p;
     const int m = v.m, k = (int)p.k, n = (int)p.n, nsb = k / 256;
     ZCU_NEED(a, m <= 64, "matvec_q4_k (tcgen05): %d tokens in one step (at most 64)", m);

@@ -34,7 +34,7 @@ struct PMatvec {  // kernels.zig:472-494 (MatvecBf16, shared by every matvec ide
     float eps;
     uint32_t flags, half, x_stride;
 };
-enum : uint32_t { MV_NORM = 1u, MV_ACCUMULATE = 2u, MV_SILU_PAIR = 4u, MV_ROPE_APPEND = 8u };
+enum : uint32_t { MV_NORM = 1u, MV_ACCUMULATE = 2u, MV_SILU_PAIR = 4u, MV_ROPE_APPEND = 8u, MV_ATTN_COMBINE = 16u };
 struct PQuantizeQ8 {  // kernels.zig:495-501
     uint32_t k, block, mode;
     float eps;
@@ -81,6 +81,20 @@ struct MvRope {
     void* vc;
     const PStep* step;
     const uint32_t* seq_pos;
+};
+
+// What a multiply with MV_ATTN_COMBINE needs beyond its own block: it reads the attention output, and merges the
+// attention's partials into it itself before it does (attn_combine's parameters follow PMatvec in the parameter
+// block; attn_combine's bindings follow the multiply's).
+struct MvCombine {
+    PAttention p;
+    const float* qg;
+    const float* part;
+    float* out;              // where attn_combine would write: this rank's head columns of the multiply's input
+    const PStep* step;
+    const uint32_t* seq_pos;
+    int kb;                  // cache positions per partial block
+    int blocks;              // heads * rows merges (0: none)
 };
 
 static_assert(sizeof(PStep) == 16, "Step");
@@ -146,6 +160,7 @@ zcu_result launch_delta_recurrent(const LaunchArgs& a, uint32_t t_first, uint32_
 zcu_result launch_delta_chunked(const LaunchArgs& a);          // 64-token chunks, then the recurrent tail
 zcu_result launch_gated_norm(const LaunchArgs& a);
 zcu_result launch_attn_static(const LaunchArgs& a, uint32_t max_keys, uint32_t rows);
+int attn_keys_per_block(const PAttention& p);   // cache positions per partial block of this attention (k_attn.cu)
 zcu_result launch_peer_wait(const LaunchArgs& a);
 zcu_result launch_peer_next(const LaunchArgs& a);
 zcu_result launch_quantize_q8(const LaunchArgs& a);

@@ -30,6 +30,9 @@ NORM, ACCUMULATE, SILU_PAIR = 1, 2, 4
 # an extension of this backend: the multiply's outputs are a Q|K|V row, rotated and appended to the cache in its
 # epilogue (rope_append without its own launch); the parameter block is Matvec followed by RopeAppend
 ROPE_APPEND_FUSED = 8
+# likewise: the multiply reads the attention output and merges the attention's partials into it first (attn_combine
+# without its own launch); the parameter block is Matvec followed by Attention, the multiply waits on an exchange
+ATTN_COMBINE_FUSED = 16
 
 # plan.common.KvFormat
 KV_F32, KV_F16, KV_FP8 = 0, 1, 2
@@ -99,6 +102,7 @@ MatvecRope = _struct("MatvecRope", [("mv", Matvec), ("rope", RopeAppend)])
 Attention = _struct("Attention", [("heads", u32), ("kv_heads", u32), ("head_dim", u32), ("kv", u32), ("scale", f32),
                                   ("max_blocks", u32), ("q_row", u32), ("row0", u32), ("gated", u32), ("scales", u32),
                                   ("_pad", u32 * 2)])
+MatvecCombine = _struct("MatvecCombine", [("mv", Matvec), ("attn", Attention)])
 DeltaPrep = _struct("DeltaPrep", [("channels", u32), ("taps", u32), ("key_channels", u32), ("head", u32), ("row", u32),
                                   ("v_heads", u32), ("beta_off", u32), ("alpha_off", u32), ("eps", f32),
                                   ("_pad", u32 * 3)])
@@ -227,11 +231,18 @@ class Launcher:
 
     # -- the decode multiply: grid (ceil(n / groupRows), m, 1) in the reference; only m matters here
     def matvec(self, ttype, x, w, out, n, k, m=1, col0=0, out_stride=None, flags=0, eps=0.0, half=0, x_stride=0,
-               norm_w=None, variant=0, rope=None, wait=None, push=None):
+               norm_w=None, variant=0, rope=None, wait=None, push=None, combine=None):
         """`rope` = (RopeAppend, [table, kc, vc, step(, positions)]) fuses rope_append into the multiply that
-        produces the Q|K|V row (ROPE_APPEND_FUSED; needs norm_w as binding 3)."""
+        produces the Q|K|V row (ROPE_APPEND_FUSED; needs norm_w as binding 3). `combine` = (Attention, [qg, part,
+        out, step(, positions)]) fuses attn_combine into the multiply that reads the attention output
+        (ATTN_COMBINE_FUSED; the multiply must `wait` on the exchange the merged heads are pushed under)."""
         p = Matvec(n, k, col0, out_stride if out_stride is not None else n, eps, flags, half, x_stride)
         args = [x, w, out] + ([norm_w] if norm_w is not None else [])
+        if combine is not None:
+            assert rope is None and wait is not None
+            p.flags |= ATTN_COMBINE_FUSED
+            p = MatvecCombine(p, combine[0])
+            args = (args + [x])[:4] + list(combine[1])   # binding 3 (norm weights) is a placeholder when there is no norm
         if rope is not None:
             assert norm_w is not None and len(args) == 4
             p.flags |= ROPE_APPEND_FUSED

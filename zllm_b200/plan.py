@@ -141,6 +141,9 @@ class DenseProgram:
         # 2-4 sequences
         can_batch = 4 < batch <= K.MATVEC_BATCHED_MAX_TOKENS
         self.batched = can_batch if batched is None else (bool(batched) and batch <= K.MATVEC_BATCHED_MAX_TOKENS)
+        # attn_combine inside the output projection (one launch fewer per attention layer) where the projection takes
+        # its input from an exchange and runs the tensor-core family of up to four sequences
+        self.fuse_combine = arena is not None and not self.batched and batch <= 4 and cfg.body_type in ("q4_k", "q8_0")
         self.launches_per_step = 0
         sh, hd = self.sh, cfg.head_dim
         h0, h1 = sh.heads(cfg)
@@ -199,6 +202,14 @@ class DenseProgram:
             v = K.MATVEC_BATCHED
         self.L.matvec(ttype, x, w, out, n, k, m=self.B, variant=v, **kw)
         self.launches_per_step += 3 if v == K.MATVEC_BATCHED else 1  # columns, multiply, reduction
+
+    def _runs_16_warp_mma(self, ttype, n, k) -> bool:
+        """Whether the shape's multiply runs the tensor-core family in CTAs of 16 warps (the form that can take
+        attn_combine as its first phase)."""
+        v = self.variants.get((ttype, n, k), 0)
+        if v == 0:
+            return k % 256 == 0
+        return (v >> 16) & 0xFF == K.FAMILY_MMA and (v >> 8) & 0x0F == K.SHAPE_16_WARPS
 
     def sweep(self, tokens: int | None = None) -> dict:
         """The load-time sweep over this program's multiply shapes on the model's own weights (tune.Sweep, the
@@ -328,13 +339,17 @@ class DenseProgram:
         # 3-4. split attention over each sequence's cache, merged into this rank's head columns of att
         self.L.launch(K.ATTN_SPLIT, ap, [self.qkv, self.kc[il], self.vc[il], self.part, self.step, self.positions],
                       (self.lg, blocks, B), self.variants.get("attn_split", 0))
-        self.L.launch(K.ATTN_COMBINE, K.with_peer(ap, push=s_att), [self.qkv, self.part, att_cols, self.step, self.positions],
-                      (self.lh, B, 1))
-        self.launches_per_step += 2
+        fused = self.fuse_combine and self._runs_16_warp_mma(cfg.body_type, self.le, cfg.q_dim)
+        if not fused:
+            self.L.launch(K.ATTN_COMBINE, K.with_peer(ap, push=s_att), [self.qkv, self.part, att_cols, self.step, self.positions],
+                          (self.lh, B, 1))
+        self.launches_per_step += 1 if fused else 2
         self._gather(self.att, cfg.q_dim)
-        # 5. Wo rows of this rank, accumulated into the residual stream's slice
+        # 5. Wo rows of this rank, accumulated into the residual stream's slice (with the merge of the attention's
+        #    partials as its first phase, when fused)
         self._matvec(cfg.body_type, self.att, lw["wo"], self.x, self.le, cfg.q_dim, col0=sh.rank * self.le,
-                     out_stride=e, flags=K.ACCUMULATE, wait=s_att, push=s_xwo)
+                     out_stride=e, flags=K.ACCUMULATE, wait=s_att, push=s_xwo,
+                     **({"combine": (ap, [self.qkv, self.part, att_cols, self.step, self.positions])} if fused else {}))
         self._gather(self.x, e)
 
     def _ffn(self, il):
