@@ -197,6 +197,17 @@ size_t zcu_artifact(uint32_t kernel, uint32_t variant, char *out, size_t capacit
 /* Device.supportsPrefill(rung) (src/gpu/host.zig:120-128): 1 or 0. */
 int32_t zcu_supports_prefill(zcu_context *context, uint32_t rung_variant);
 
+/* Flags of the matvec_* parameter block beyond the reference's (NORM = 1, ACCUMULATE = 2, SILU_PAIR = 4), both for
+ * the tensor-core family of matvec_q4_k / matvec_q8_0:
+ *   8  the outputs are a Q|K|V row: rope_append's work happens in the multiply's epilogue. Parameter block: MatvecBf16
+ *      followed by RopeAppend; bindings 4.. = rope_append's table, kc, vc, step[, positions] (binding 3 = norm weights).
+ *   16 the input is the attention output and attn_combine has not run: the multiply's first CTAs merge attn_split's
+ *      partials and push the heads as the exchange the multiply itself waits for. Parameter block: MatvecBf16 followed
+ *      by Attention, then a zcu_peer_ext with a wait_slot; bindings 4.. = attn_combine's qg, part, out, step[, positions]
+ *      (`out` = where attn_combine would write, inside the local arena). */
+#define ZCU_MV_ROPE_APPEND 8u
+#define ZCU_MV_ATTN_COMBINE 16u
+
 /* The RoPE table rope_append reads: f32 (cos, sin) at (pos * n_rot/2 + i) * 2 with
  * theta = pos * base^(-2i/n_rot) / factors[i], all in f32 (kernels.ropeTableScaled,
  * src/kernels/kernels.zig:730-744; formula of src/ref/ops.zig:95-99). `factors` may be NULL.
