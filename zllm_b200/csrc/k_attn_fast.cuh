@@ -242,7 +242,7 @@ __device__ __forceinline__ void attn_split_fast_body(const VBlock& vb, const PAt
 // overlaps the copies of another. K and V tiles: rows padded to head_dim * 2 + 16 bytes (conflict-free ldmatrix).
 constexpr int AM_THREADS = 256;
 __host__ __device__ constexpr size_t attn_mma_smem(int hd) {
-    return (size_t)2 * AF_KEYS * (hd * 2 + 16) + (size_t)(hd / 16) * 32 * 8 + 8 * 4 * 2 * sizeof(float);
+    return (size_t)2 * AF_KEYS * (hd * 2 + 16) + (size_t)(hd / 16) * 32 * 8 + (8 * 4 * 2 + 8 * 4 + 4) * sizeof(float);
 }
 
 __device__ __forceinline__ void mma_f16_16816(float* c, uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
@@ -399,25 +399,33 @@ __device__ __forceinline__ void attn_split_mma_body(unsigned char* smem, const P
         }
     }
     __syncthreads();
-    // ---- the eight warps' results merged in warp order (attn_combine's arithmetic): the block's partial
-    for (int e = tid; e < group * HD; e += AM_THREADS) {
-        const int h = e / HD, d = e % HD;
+    // ---- the eight warps' results merged in warp order (attn_combine's arithmetic): the block's partial. The
+    //      weight of a warp's result, exp(its maximum - the block's), is the same for every dim of a head: the
+    //      first 32 threads compute the 8 x 4 weights once.
+    float* wts = ml + 8 * 4 * 2;   // [8 warps][4 heads], then the heads' maxima [4]
+    if (tid < 32) {
+        const int w = tid >> 2, h = tid & 3;
         float M = -FLT_MAX;
 #pragma unroll
-        for (int w = 0; w < 8; w++) M = fmaxf(M, ml[(w * 4 + h) * 2]);
-        float L = 0.f, o = 0.f;
+        for (int ww = 0; ww < 8; ww++) M = fmaxf(M, ml[(ww * 4 + h) * 2]);
+        const float mw = ml[(w * 4 + h) * 2];
+        wts[w * 4 + h] = mw != -FLT_MAX ? expf(mw - M) : 0.f;
+        if (w == 0) wts[32 + h] = M;
+    }
+    __syncthreads();
+    for (int e = tid; e < group * HD; e += AM_THREADS) {
+        const int h = e / HD, d = e % HD;
+        float o = 0.f;
 #pragma unroll
-        for (int w = 0; w < 8; w++) {
-            const float mw = ml[(w * 4 + h) * 2];
-            const float wt = mw != -FLT_MAX ? expf(mw - M) : 0.f;
-            L = __fmaf_rn(ml[(w * 4 + h) * 2 + 1], wt, L);
-            o = __fmaf_rn(reinterpret_cast<const float*>(Kt + (size_t)16 * w * RS)[h * HD + d], wt, o);
-        }
+        for (int w = 0; w < 8; w++) o = __fmaf_rn(reinterpret_cast<const float*>(Kt + (size_t)16 * w * RS)[h * HD + d], wts[w * 4 + h], o);
         const int head = g_kv * group + h;
         const size_t base = (((size_t)t * p.heads + head) * p.max_blocks + b) * (HD + 2);
         part[base + 2 + d] = o;
         if (d == 0) {
-            part[base] = M;
+            float L = 0.f;
+#pragma unroll
+            for (int w = 0; w < 8; w++) L = __fmaf_rn(ml[(w * 4 + h) * 2 + 1], wts[w * 4 + h], L);
+            part[base] = wts[32 + h];
             part[base + 1] = L;
         }
     }
