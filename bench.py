@@ -195,7 +195,7 @@ class MatvecQ4K:
     n, k = 14336, 4096
     name = "matvec_q4_k"
 
-    def __init__(self, dist: Dist, batch: int = 1, variant: int = 0, **_):
+    def __init__(self, dist: Dist, batch: int = 1, variant: int = 0, tune: bool = True, **_):
         import torch
 
         from zllm_b200 import abi, synth
@@ -230,6 +230,15 @@ class MatvecQ4K:
         self.pinned_out = torch.empty((batch, self.n), dtype=torch.float32).pin_memory()
         self.graph = None
         torch.cuda.synchronize()
+        # the load-time sweep over the multiply's variants on this shape (src/tune/tune.zig), unless one was asked for
+        self.tuned = None
+        if variant == 0 and batch <= 4 and tune:
+            from zllm_b200 import tune as T
+
+            sweep = T.Sweep(self.ctx, tokens=batch)
+            sweep.add("q4_k", [(self.w[c].data_ptr(), self.w[c].numel()) for c in range(self.copies)], self.rows, self.k)
+            self.variant = self.tuned = sweep.run()[("q4_k", self.rows, self.k)]
+            torch.cuda.synchronize()
 
     # algorithmic bytes of one launch on one rank (weights + x + out)
     def bytes_per_launch(self) -> int:
@@ -304,7 +313,8 @@ class MatvecQ4K:
 
     def config(self):
         return {"workload": f"Q4_K matvec, Llama-3-8B FFN-up shape 14336x4096, batch {self.batch}",
-                "matrices_per_step": self.copies,
+                "matrices_per_step": self.copies, "variant": hex(self.variant),
+                "tuned": self.tuned is not None,
                 "l2": f"inputs larger than L2: {self.copies} distinct weight matrices per rank, "
                       f"{self.copies * self.bytes_per_launch() / 1e6:.0f} MB per step per rank",
                 "parallelism": f"tp{self.dist.world} (rows sharded, NCCL all-gather of output slices)" if self.dist.on else "1 GPU"}
@@ -1185,6 +1195,8 @@ def run_cuda(args):
     dist = Dist(args.gpus)
     parity = tp_parity(dist, args) if (dist.on and args.workload == "decode") else None
     kw = {"batch": args.batch, "variant": int(args.variant, 0)}
+    if args.workload == "matvec_q4_k":
+        kw["tune"] = not args.no_tune
     if args.workload == "decode":
         kw["exchange"] = args.exchange
         kw["attn_variant"] = args.attn_variant

@@ -511,23 +511,9 @@ __global__ void __launch_bounds__(W * 32, 16 / W) matvec_imma(PMatvec p, const f
 #ifdef ZCU_TRACE
     long long tr_wait = 0, tr_comp = 0;
 #endif
-#pragma unroll 1
-    for (int tau = lo; tau < hi; tau++) {
-#ifdef ZCU_TRACE
-        const long long tr0 = clock64();
-#endif
-        if (!(dbg & 2)) {
-            issue();  // tile tau + STAGES - 1
-            if (!mbar_wait(mbar + 8 * cs_stage, (phase_bits >> cs_stage) & 1u)) timed_out = true;
-        }
-#ifdef ZCU_TRACE
-        const long long tr1 = clock64();
-        tr_wait += tr1 - tr0;
-#endif
-        phase_bits ^= 1u << cs_stage;
-        const uint32_t tile = ring + (uint32_t)cs_stage * TILE_BYTES;
-        cs_stage = cs_stage + 1 == STAGES ? 0 : cs_stage + 1;
-        const int unit = cur_unit;
+    int freed = 1;   // stages without a tile on its way (all but one were asked for before the loop)
+    // the arithmetic of one tile (its sums join accf)
+    auto tile_math = [&](const uint32_t tile, const int unit) {
         if (dbg & 1) {
         } else if constexpr (Q4) {
             const uint4 h0 = lds128(tile + hoff), h1 = lds128(tile + hoff + 8 * TILE_ROW);
@@ -618,9 +604,37 @@ __global__ void __launch_bounds__(W * 32, 16 / W) matvec_imma(PMatvec p, const f
                 }
             }
         }
-        __syncwarp();  // every lane is done with this stage before a later copy overwrites it
+    };
+#pragma unroll 1
+    for (int tau = lo; tau < hi;) {
+#ifdef ZCU_TRACE
+        const long long tr0 = clock64();
+#endif
+        // two tiles a round where the next one belongs to the same (row tile, part): both are waited for before either
+        // is touched, so that the arithmetic of the second fills the latencies at the end of the first (the sums keep
+        // their order: the first tile's join accf before the second's)
+        const bool two = STAGES >= 4 && tau + 1 < hi && cur_unit + 1 < units;
+        const int sa = cs_stage, sb = cs_stage + 1 == STAGES ? 0 : cs_stage + 1;
+        if (!(dbg & 2)) {
+            for (int f = 0; f < freed; f++) issue();  // a tile into every stage that the round before left
+            if (!mbar_wait(mbar + 8 * sa, (phase_bits >> sa) & 1u)) timed_out = true;
+            if (two && !mbar_wait(mbar + 8 * sb, (phase_bits >> sb) & 1u)) timed_out = true;
+        }
+#ifdef ZCU_TRACE
+        const long long tr1 = clock64();
+        tr_wait += tr1 - tr0;
+#endif
+        phase_bits ^= 1u << sa;
+        if (two) phase_bits ^= 1u << sb;
+        cs_stage = two ? (sb + 1 == STAGES ? 0 : sb + 1) : sb;
+        tile_math(ring + (uint32_t)sa * TILE_BYTES, cur_unit);
+        if (two) tile_math(ring + (uint32_t)sb * TILE_BYTES, cur_unit + 1);
+        __syncwarp();  // every lane is done with these stages before a later copy overwrites them
         // step to the next tile; on leaving this (row tile, part), park the sums
-        if (++cur_unit == units || tau + 1 == hi) {
+        freed = two ? 2 : 1;
+        tau += freed;
+        cur_unit += freed;
+        if (cur_unit == units || tau == hi) {
             park();
             if (cur_unit == units) {
                 cur_unit = 0;

@@ -3,7 +3,8 @@
 (kernels.MATVEC_CANDIDATES: tiles in flight per warp, CTA shape and CTA count of the tensor-core family, and the
 scalar family) runs on the shape's real weights: it is first checked against the default variant (relative L2 error above `TOLERANCE`
 drops it: candidates differ only in the order of each row's sums), then timed - `WARMUP` batches, then the median
-of `TIMED` batches, each batch repeating the dispatch so that it lasts about a millisecond. The fastest per shape
+of `TIMED` batches, each batch repeating the dispatch so that it lasts about a millisecond and replayed as a CUDA
+graph, the way a plan replays its step. The fastest per shape
 goes into the table a plan passes as `variants`.
 
 The inputs are the reference's: x[i] = sin(0.7 i), of RMS about 1 like normed activations."""
@@ -33,6 +34,7 @@ class Sweep:
         assert self.candidates[0] == 0, "the default first: it is the reference the others must match"
         self.shapes, self.dropped, self.report = [], 0, []
         self.L = K.Launcher(ctx)
+        self._graph = None   # ((shape, variant), graph) of the batch captured last
 
     def add(self, ttype: str, weights, n: int, k: int, **flags):
         """`weights`: the shape's matrix, or a list of matrices of this shape (every layer's): a batch then rotates
@@ -49,11 +51,25 @@ class Sweep:
         self.shapes.append((ttype, ws, n, k, reps, flags))
 
     def _batch(self, shape, variant, x, out) -> float:
+        """Seconds per dispatch of one batch. The batch is replayed as a CUDA graph (captured on its first use), as a
+        plan replays its step: the dispatches then follow each other on the device the way they do in a step, and the
+        host's launch cost stays out of the figure."""
         ttype, ws, n, k, reps, flags = shape
+        key = (id(shape), variant)
+        if self._graph is None or self._graph[0] != key:
+            if self._graph is not None:
+                self.ctx.graph_destroy(self._graph[1])
+                self._graph = None
+            self.ctx.capture_begin()
+            try:
+                for i in range(reps):
+                    self.L.matvec(ttype, x, ws[i % len(ws)], out, n, k, m=self.tokens, variant=variant, **flags)
+            finally:
+                g = self.ctx.capture_end()
+            self._graph = (key, g)
         self.ctx.sync()
         t0 = time.perf_counter()
-        for i in range(reps):
-            self.L.matvec(ttype, x, ws[i % len(ws)], out, n, k, m=self.tokens, variant=variant, **flags)
+        self.ctx.graph_launch(self._graph[1])
         self.ctx.sync()
         return (time.perf_counter() - t0) / reps
 
@@ -88,4 +104,7 @@ class Sweep:
                 if best is None or ns < best[1]:
                     best = (variant, ns)
             table[(ttype, n, k)] = best[0]
+        if self._graph is not None:
+            self.ctx.graph_destroy(self._graph[1])
+            self._graph = None
         return table
