@@ -24,8 +24,13 @@
 //
 // Shape: one CTA per SM stages the activations and owns a contiguous set of 16-row tiles; its warps split the
 // (row tile, k) tiles of those rows into contiguous ranges. A tile is ONE TMA box copy (16 rows x 160 bytes)
-// into the warp's private ring of stages, several tiles ahead of the multiply. The kernel is launched as a
-// programmatic dependent: ring and first copies start while the kernel before it drains.
+// into the warp's private ring of stages, several tiles ahead of the multiply; every warp issues its own copies
+// (an issuing lane waits about 170 cycles for the copy engine to take a box: sixteen warps issue in parallel, a
+// warp that only copied for the others could not keep up), the first before the kernel boundary, the rest of the
+// ring between the steps of the activation staging. A warp takes two tiles per round of its loop where the next
+// one continues the row tile (both waited for first; the round's requests, waits and warp barrier paid once).
+// The kernel is launched as a programmatic dependent: ring and first copies start while the kernel before it drains.
+// Optional phases: attn_combine's merge in front (MV_ATTN_COMBINE), rope_append in the epilogue (MV_ROPE_APPEND).
 //
 // Fragment layout of mma.m16n8k32 (lane = 4 g + t): A regs {row g, k 4t..4t+3}, {row g+8, same},
 // {row g, k 16+4t..}, {row g+8, same}; B regs {k 4t..4t+3, col g}, {k 16+4t.., col g}; C regs
