@@ -163,6 +163,20 @@ __device__ __forceinline__ void digits4(const int* X, uint32_t* dg) {
     dg[3] = __byte_perm(t2, t3, 0x7632);
 }
 
+// attn_combine's merge for the multiply's MV_ATTN_COMBINE phase, out of line: the multiplies that do not use it
+// (all but one per layer) keep its code out of their instruction stream.
+__device__ __noinline__ void combine_phase(const MvCombine& comb, const PeerUse& cpu, unsigned char* smem, int cta, int ncta, int tid,
+                                           int nthreads, int* status) {
+    for (int c = cta; c < comb.blocks; c += ncta) {
+        VBlock vb;
+        vb.x = c % (int)comb.p.heads, vb.y = c / (int)comb.p.heads, vb.z = 0;
+        vb.tid = tid, vb.nthreads = nthreads, vb.bar = 1;
+        vb.smem = smem;
+        attn::attn_combine_body(vb, comb.p, comb.qg, comb.part, comb.out, comb.step, comb.seq_pos, comb.kb, status, &cpu);
+        vb.sync();   // the next merge, or the staging, reuses the shared memory
+    }
+}
+
 // TYPE: W_Q4_K or W_Q8_0. NT: tokens of the pass (1..4). STAGES: tiles in flight per warp. W: warps per CTA.
 template <int TYPE, int NT, int STAGES, int W>
 __global__ void __launch_bounds__(W * 32, 16 / W) matvec_imma(PMatvec p, const float* __restrict__ x,
@@ -304,14 +318,7 @@ __global__ void __launch_bounds__(W * 32, 16 / W) matvec_imma(PMatvec p, const f
             PeerUse cpu = *pu;
             cpu.push_slot = pu->wait_slot;
             cpu.wait_slot = PEER_NONE;
-            for (int c = cta; comb.p.heads != 0 && c < comb.blocks; c += ncta) {
-                VBlock vb;
-                vb.x = c % (int)comb.p.heads, vb.y = c / (int)comb.p.heads, vb.z = 0;
-                vb.tid = tid, vb.nthreads = W * 32, vb.bar = 1;
-                vb.smem = smem + L.xd;
-                attn::attn_combine_body(vb, comb.p, comb.qg, comb.part, comb.out, comb.step, comb.seq_pos, comb.kb, status, &cpu);
-                vb.sync();   // the next merge, or the staging, reuses the shared memory
-            }
+            if (comb.p.heads != 0) combine_phase(comb, cpu, smem + L.xd, cta, ncta, tid, W * 32, status);
         }
     }
     // the value this thread's first output accumulates onto: asked for now, needed after the tile stream
