@@ -91,7 +91,8 @@ __device__ __forceinline__ bool gave_up(const PeerUse& u, unsigned long long t0,
 }
 
 // Four consecutive floats of an exchanged vector (`local` is 16-byte aligned): waits until all four slots carry `tag`.
-__device__ __forceinline__ float4 read4(const PeerUse& u, const float* local, uint32_t tag, int* status) {
+// (out of line: a kernel that reads many pieces calls it only for a piece whose tags were not there at first look)
+static __device__ __noinline__ float4 read4(const PeerUse& u, const float* local, uint32_t tag, int* status) {
     const uint2* s = slot_of(u, local, u.t.rank);
     uint4 a, b;
     unsigned long long t0 = 0;   // the clock is read only once a first look has failed
