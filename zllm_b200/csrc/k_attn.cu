@@ -256,8 +256,8 @@ __global__ void __launch_bounds__(attn::AC_THREADS) attn_combine_kernel(PAttenti
     extern __shared__ __align__(16) unsigned char dyn_smem[];
     // launched as a programmatic dependent of attn_split; what follows it (a multiply) may move in and start its
     // weight copies at once
-    asm volatile("griddepcontrol.wait;\n" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");
     attn::attn_combine_body(vblock_of_cta(dyn_smem), p, qg, part, out, step, seq_pos, kb, status, &pu);
 }
 

@@ -296,6 +296,7 @@ __device__ __forceinline__ void attn_split_mma_body(unsigned char* smem, const P
     // ends before them holds only rows of earlier steps, and its copies may start while that kernel still runs.
     const int first_new = seq_pos ? (int)seq_pos[row] : (int)step->pos0;
     const bool early = PDL && k0 + AF_KEYS <= first_new;
+    if (PDL) asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");   // (what follows waits for this kernel's end itself)
     if (PDL && !early) asm volatile("griddepcontrol.wait;\n" ::: "memory");
 
     // ---- this warp's rows of K, then of V, on their way (two groups: the scores need only the first)
@@ -315,7 +316,6 @@ __device__ __forceinline__ void attn_split_mma_body(unsigned char* smem, const P
     }
     asm volatile("cp.async.commit_group;\n" ::: "memory");
     if (early) asm volatile("griddepcontrol.wait;\n" ::: "memory");
-    if (PDL) asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
     // ---- the group's queries as A fragments: entry (k-step, lane) = {a0, a2} of that lane (head g & 3; hi for g < 4,
     //      lo for g >= 4; rows 8-15 of A stay zero). One entry per thread for head_dim 128.
     for (int e = tid; e < KSTEPS * 32; e += AM_THREADS) {

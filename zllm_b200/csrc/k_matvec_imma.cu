@@ -212,6 +212,9 @@ __global__ void __launch_bounds__(W * 32, 16 / W) matvec_imma(PMatvec p, const f
     const int nt = (rt_hi - rt_lo) * per_rt;
     const int lo = (int)(((unsigned)warp * (unsigned)nt) / W), hi = (int)(((unsigned)(warp + 1) * (unsigned)nt) / W);
     TRACE(0);
+    // (the kernel after this one may be scheduled as soon as every CTA of this one has started: it waits for this
+    // one's end itself, before it reads what this one writes)
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
 
     // ---- the ring: this warp's stages and their barriers; the first STAGES - 1 tiles are asked for at once
     constexpr int TILE_BYTES = tile_bytes(Q4);
@@ -307,7 +310,6 @@ __global__ void __launch_bounds__(W * 32, 16 / W) matvec_imma(PMatvec p, const f
     const bool x_exchanged = pu->wait_slot != PEER_NONE, pushing = pu->push_slot != PEER_NONE;
     const uint32_t x_tag = x_exchanged ? peer::want_tag(*pu) : 0u, out_tag = pushing ? peer::push_tag(*pu) : 0u;
     if (!(dbg & 8)) asm volatile("griddepcontrol.wait;\n" ::: "memory");
-    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
     TRACE(2);
     // MV_ATTN_COMBINE: the input is the attention output, and nobody has merged the attention's partials into it yet.
     // The first CTAs do (one head of one row each, attn_combine's own code on this CTA's 512 threads, its shared
