@@ -110,11 +110,15 @@ enum {
 /* Variant ids of a matvec pipeline (create_kernel's `variant`). 0 is the
  * default. The reference packs (wg/32) | lanes<<8 | rows<<16 | act_div<<24
  * (src/kernels/kernels.zig:330-333); this backend reads the same word as
- * weight tiles in flight per warp (byte 0: 2, 4 or 6; 0 = as deep as fits),
- * byte 1 reserved (0), and kernel family (byte 2: 1 = scalar f32 FMA,
+ * weight tiles in flight per warp (byte 0: 2..6; 0 = as deep as fits),
+ * the CTA shape (byte 1: low nibble 0 = CTAs of 16 warps, 1 = of 8 warps, two
+ * per SM; bit 4 = a CTA on every SM instead of the count that divides the row
+ * tiles evenly), and kernel family (byte 2: 1 = scalar f32 FMA,
  * 2 = integer tensor-core fragments, 3 = matvec_q4_k for up to 64 tokens in
  * one pass over the weights: tcgen05 with accumulators in tensor memory, the
- * tokens as two f16 terms; bytes 0 and 1 zero). Reserved
+ * tokens as two f16 terms; bytes 0 and 1 zero). The whole word 0 on
+ * matvec_q4_k is ZCU_VARIANT(3, 0x10, ZCU_FAMILY_MMA), what a load-time
+ * sweep ends up choosing for the shapes of a decode step. Reserved
  * prefill rungs keep the reference's ids (src/kernels/kernels.zig:798-822). */
 #define ZCU_VARIANT(tiles, splitk, family) ((uint32_t)(tiles) | ((uint32_t)(splitk) << 8) | ((uint32_t)(family) << 16))
 #define ZCU_FAMILY_SCALAR 1u

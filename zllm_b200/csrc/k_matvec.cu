@@ -456,6 +456,10 @@ zcu_result launch_quant(const LaunchArgs& a, uint32_t block) {
     }
     // Q8_0 rows that are not whole 256-weight pieces have ragged tiles: the scalar family takes them.
     const bool imma_ok = TYPE != W_Q8_0 || v.p.k % 256 == 0;
+    // The default of Q4_K is what the sweep ends up choosing for every shape of a decode step: a ring of three tiles
+    // and a CTA on every SM (a shorter ring means fewer requests in front of the activation staging, and the CTAs
+    // that end a row tile early let the next kernel's CTAs in early).
+    if (a.variant == 0 && imma_ok && TYPE == W_Q4_K) return launch_matvec_imma(a, v, TYPE, 3, 0x10);
     if ((a.variant == 0 && imma_ok) || family == ZCU_FAMILY_MMA)
         return launch_matvec_imma(a, v, TYPE, (int)(a.variant & 0xffu), (int)((a.variant >> 8) & 0xffu));
     if (v.has_rope) return zcu_fail(a, ZCU_E_UNSUPPORTED_KERNEL, "matvec + rope_append: only the tensor-core family fuses it");
