@@ -378,7 +378,8 @@ __device__ __forceinline__ void attn_split_mma_body(unsigned char* smem, const P
     asm volatile("cp.async.wait_group 0;\n" ::: "memory");
     __syncwarp();
     ATRACE(5);
-    float* pv = reinterpret_cast<float*>(Kt + (size_t)r0 * RS);   // [4 heads][HD], in the place of this warp's K rows
+    constexpr int PVS = HD + 8;   // floats between the heads' rows of a warp's result (the four heads' stores hit different banks)
+    float* pv = reinterpret_cast<float*>(Kt + (size_t)r0 * RS);   // [4 heads][PVS], in the place of this warp's K rows
     __syncwarp();                                                  // every lane has read its K fragments
     {
         // ldmatrix.x4.trans: lanes 0-15 name the 16 key rows at dims d .. d+7, lanes 16-31 the same rows at d+8 .. d+15
@@ -393,8 +394,8 @@ __device__ __forceinline__ void attn_split_mma_body(unsigned char* smem, const P
             const float v00 = __fadd_rn(o0[0], __shfl_xor_sync(0xffffffffu, o0[0], 16)), v01 = __fadd_rn(o0[1], __shfl_xor_sync(0xffffffffu, o0[1], 16));
             const float v10 = __fadd_rn(o1[0], __shfl_xor_sync(0xffffffffu, o1[0], 16)), v11 = __fadd_rn(o1[1], __shfl_xor_sync(0xffffffffu, o1[1], 16));
             if (g < group) {
-                *reinterpret_cast<float2*>(pv + g * HD + 16 * nb + 2 * tq) = make_float2(v00, v01);
-                *reinterpret_cast<float2*>(pv + g * HD + 16 * nb + 8 + 2 * tq) = make_float2(v10, v11);
+                *reinterpret_cast<float2*>(pv + g * PVS + 16 * nb + 2 * tq) = make_float2(v00, v01);
+                *reinterpret_cast<float2*>(pv + g * PVS + 16 * nb + 8 + 2 * tq) = make_float2(v10, v11);
             }
         }
     }
@@ -417,7 +418,7 @@ __device__ __forceinline__ void attn_split_mma_body(unsigned char* smem, const P
         const int h = e / HD, d = e % HD;
         float o = 0.f;
 #pragma unroll
-        for (int w = 0; w < 8; w++) o = __fmaf_rn(reinterpret_cast<const float*>(Kt + (size_t)16 * w * RS)[h * HD + d], wts[w * 4 + h], o);
+        for (int w = 0; w < 8; w++) o = __fmaf_rn(reinterpret_cast<const float*>(Kt + (size_t)16 * w * RS)[h * PVS + d], wts[w * 4 + h], o);
         const int head = g_kv * group + h;
         const size_t base = (((size_t)t * p.heads + head) * p.max_blocks + b) * (HD + 2);
         part[base + 2 + d] = o;
