@@ -301,20 +301,27 @@ __device__ __forceinline__ void attn_split_mma_body(unsigned char* smem, const P
 
     // ---- this warp's rows of K, then of V, on their way (two groups: the scores need only the first)
     ATRACE(1);
+    // (lane l copies piece l % CPR of rows r0 + l / CPR + (32 / CPR) i; a row past the sequence's last key repeats that
+    // key: the offsets are clamped, not the addresses recomputed)
+    {
+        constexpr int RPI = 32 / CPR;   // rows a warp covers per instruction
+        const int row0 = r0 + lane / CPR, piece = lane % CPR;
+        const size_t col = seq_off + (size_t)g_kv * HD + 8 * piece;
+        const int last = keys - 1 - k0;   // the block's last valid row
+        const uint32_t dst0 = (uint32_t)row0 * RS + 16u * piece;
 #pragma unroll
-    for (int i = 0; i < PIECES; i++) {
-        const int j = lane + 32 * i, key = r0 + j / CPR, piece = j % CPR;
-        const size_t src = seq_off + (size_t)min(k0 + key, keys - 1) * kv_stride + (size_t)g_kv * HD + 8 * piece;
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(kt_s + (uint32_t)key * RS + 16u * piece), "l"(kc + src) : "memory");
-    }
-    asm volatile("cp.async.commit_group;\n" ::: "memory");
+        for (int i = 0; i < PIECES; i++) {
+            const size_t src = col + (size_t)(k0 + min(row0 + RPI * i, last)) * kv_stride;
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(kt_s + dst0 + (uint32_t)(RPI * i) * RS), "l"(kc + src) : "memory");
+        }
+        asm volatile("cp.async.commit_group;\n" ::: "memory");
 #pragma unroll
-    for (int i = 0; i < PIECES; i++) {
-        const int j = lane + 32 * i, key = r0 + j / CPR, piece = j % CPR;
-        const size_t src = seq_off + (size_t)min(k0 + key, keys - 1) * kv_stride + (size_t)g_kv * HD + 8 * piece;
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(vt_s + (uint32_t)key * RS + 16u * piece), "l"(vc + src) : "memory");
+        for (int i = 0; i < PIECES; i++) {
+            const size_t src = col + (size_t)(k0 + min(row0 + RPI * i, last)) * kv_stride;
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(vt_s + dst0 + (uint32_t)(RPI * i) * RS), "l"(vc + src) : "memory");
+        }
+        asm volatile("cp.async.commit_group;\n" ::: "memory");
     }
-    asm volatile("cp.async.commit_group;\n" ::: "memory");
     if (early) asm volatile("griddepcontrol.wait;\n" ::: "memory");
     // ---- the group's queries as A fragments: entry (k-step, lane) = {a0, a2} of that lane (head g & 3; hi for g < 4,
     //      lo for g >= 4; rows 8-15 of A stay zero). One entry per thread for head_dim 128.
