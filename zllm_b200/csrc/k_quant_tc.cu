@@ -712,8 +712,8 @@ __global__ void __launch_bounds__(64) cols_from_f32_kernel(const float* __restri
                                                           float eps, int cols_pad, const __grid_constant__ PeerUse pu, int* __restrict__ status) {
     __shared__ double red[2];
     __shared__ float amax_s[2];
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");   // the multiply may start its weight copies now (it waits for this kernel itself)
     asm volatile("griddepcontrol.wait;\n" ::: "memory");                // the kernels before this one are done (inputs, and the scratch's last readers)
-    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");   // the multiply may start its weight copies now
     const int li = threadIdx.x, sb = blockIdx.x, tok = blockIdx.y, nsb = k / 256;
     const float* xt = x + (size_t)tok * x_stride;
     // the activations: local memory, or the slots of a tensor-parallel exchange (each read waits for its tag)
@@ -795,8 +795,8 @@ __global__ void __launch_bounds__(64) cols_from_f32_kernel(const float* __restri
 __global__ void __launch_bounds__(256) cols_reduce_kernel(const float* __restrict__ part, float* __restrict__ out, int n, int m, int slices,
                                                          int cols, int pair, int accumulate, uint32_t out_stride, uint32_t col0,
                                                          const __grid_constant__ PeerUse pu) {
-    asm volatile("griddepcontrol.wait;\n" ::: "memory");                // the multiply is done
     asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");   // a dependent kernel after this one may be scheduled
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");                // the multiply is done
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < (size_t)n * m) {
         const int tok = (int)(i / n), j = (int)(i % n);
