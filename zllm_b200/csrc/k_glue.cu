@@ -98,6 +98,9 @@ __global__ void __launch_bounds__(256) rope_append_kernel(PRopeAppend p, float* 
                                                          uint32_t* __restrict__ vc, const PStep* __restrict__ step,
                                                          const uint32_t* __restrict__ seq_pos) {
     __shared__ __align__(16) unsigned char sm[glue::ROPE_SMEM];
+    // (attn_split, a programmatic dependent, may be scheduled now: its blocks of earlier steps' rows start their copies,
+    // the others wait for this kernel's end)
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
     glue::rope_append_body(vblock_of_cta(sm), p, qkv, q_norm, k_norm, rope, kc, vc, step, seq_pos);
 }
 
