@@ -88,6 +88,7 @@ using glue::E_F16;
 template <int TYPE>
 __global__ void __launch_bounds__(256) embed_kernel(PEmbed p, const uint32_t* __restrict__ tokens,
                                                    const uint8_t* __restrict__ w, float* __restrict__ out) {
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");   // (the first multiply may start its weight copies)
     glue::embed_body<TYPE>(vblock_of_cta(nullptr), p, tokens, w, out);
 }
 
@@ -112,6 +113,7 @@ __global__ void __launch_bounds__(256) gated_norm_kernel(PGatedNorm p, float* __
                                                         const float* __restrict__ z, const float* __restrict__ w,
                                                         const __grid_constant__ PeerUse pu) {
     __shared__ double red[32];
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");   // (the output projection may start its weight copies)
     const uint32_t b = threadIdx.x;
     const size_t base = ((size_t)blockIdx.y * p.v_heads + blockIdx.x) * p.dim;
     const bool in_head = b < p.dim;
