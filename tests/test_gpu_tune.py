@@ -55,12 +55,15 @@ def test_the_sweep_times_a_shape_as_the_plan_uses_it_and_a_plan_takes_the_table(
     assert all(prog.variants[key] == v for key, v in table.items())
     tuned = step(prog)
     assert np.linalg.norm(tuned - plain) / np.linalg.norm(plain) <= 1e-5
-    # the best few of each shape tried inside the replayed step: three trials a shape, a choice among them, same logits
+    # the default and the best few of each shape tried inside the replayed step: four trials a shape, the default
+    # first; a candidate stays only where it beat the default by the margin; same logits
     prog.write_step(np.array([7], dtype=np.uint32), np.array([33], dtype=np.uint32))
-    refined = prog.refine(34, top=3, reps=2)
-    assert len(prog.refine_report) == len(table) and all(len(timed) == 3 for _, timed in prog.refine_report)
+    refined = prog.refine(34, top=3, reps=2, margin=0.003)
+    assert len(prog.refine_report) == len(table) and all(len(timed) == 4 for _, timed in prog.refine_report)
     for shape, timed in prog.refine_report:
-        assert refined[shape] == min(timed)[1] and refined[shape] in [v for _, v in timed]
+        assert timed[0][1] == 0 and refined[shape] in [v for _, v in timed]
+        best = min(timed)
+        assert refined[shape] == (best[1] if best[0] < timed[0][0] * 0.997 else 0)
     again = step(prog)
     assert np.linalg.norm(again - plain) / np.linalg.norm(plain) <= 1e-5
 

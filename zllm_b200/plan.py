@@ -224,12 +224,16 @@ class DenseProgram:
         self.sweep_report = s.report
         return table
 
-    def refine(self, max_keys: int, top: int = 3, reps: int = 6) -> dict:
-        """After sweep(): the candidates that were fastest on their own are tried inside the replayed step, shape by
-        shape (largest first), and the one with the fastest STEP stays. A multiply's time in the step depends on its
-        neighbours (what the kernel before it leaves in flight, how its ring depth meets the next kernel's start), and
-        the sweep's figures of the best few lie within its noise of each other. Every rank of a tensor-parallel program
-        runs the same number of steps here (`top` trials per shape), as the exchange requires."""
+    def refine(self, max_keys: int, top: int = 3, reps: int = 10, margin: float = 0.003) -> dict:
+        """After sweep(): every shape goes back to the library's default form; then, shape by shape (largest first),
+        the default and the `top` candidates that were fastest on their own are tried inside the replayed step, and a
+        candidate replaces the default only where it makes the STEP faster by more than `margin`. A multiply's time
+        in the step depends on its neighbours (what the kernel before it leaves in flight, how its ring depth meets
+        the next kernel's start): the form that wins alone is often not the one that wins there, and the best few
+        lie within the sweep's noise of each other, so the stand-alone figures only nominate. Starting from the
+        defaults makes the result no slower than an untuned program (up to the margin). Every rank of a
+        tensor-parallel program runs the same number of steps here (`top` + 1 trials per shape), as the exchange
+        requires."""
         import time
 
         by_shape = {}
@@ -254,15 +258,18 @@ class DenseProgram:
             self.ctx.graph_destroy(g)
             return best
 
+        for shape in by_shape:
+            self.variants[shape] = 0
         self.refine_report = []
         for shape in sorted(by_shape, key=lambda s: -s[1] * s[2]):
-            trials = [v for _, v in sorted(by_shape[shape])[:top]]
-            trials += [trials[0]] * (top - len(trials))
+            trials = [v for _, v in sorted(by_shape[shape]) if v != 0][:top]
+            trials = [0] + trials + [0] * (top - len(trials))
             timed = []
             for v in trials:
                 self.variants[shape] = v
                 timed.append((step_seconds(), v))
-            self.variants[shape] = min(timed)[1]
+            best = min(timed)
+            self.variants[shape] = best[1] if best[0] < timed[0][0] * (1.0 - margin) else 0
             self.refine_report.append((shape, timed))
         return self.variants
 
