@@ -180,6 +180,16 @@ class Dist:
         self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
         return float(t.item())
 
+    def max_each(self, values):
+        """Element-wise maximum over ranks of a short list of floats (every rank passes the same count)."""
+        if not self.on:
+            return list(values)
+        import torch
+
+        t = torch.tensor(list(values), dtype=torch.float64, device="cuda")
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return [float(v) for v in t.tolist()]
+
     def close(self):
         if self.on:
             self.dist.destroy_process_group()
@@ -425,7 +435,7 @@ class DecodeStep:
             # ... and the best few of each shape tried inside the replayed step (every rank runs the same trials)
             if self.exchange != "nccl":
                 dist.barrier()
-                self.tuned = {k: v for k, v in self.prog.refine(self.context + 1).items() if isinstance(k, tuple)}
+                self.tuned = {k: v for k, v in self.prog.refine(self.context + 1, agree=dist.max_each).items() if isinstance(k, tuple)}
                 torch.cuda.synchronize()
                 dist.barrier()
         self.graph = None

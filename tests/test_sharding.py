@@ -377,3 +377,50 @@ def test_exchange_slots_chain_through_the_sharded_hybrid_launch_list():
     pushed += [4 * il for il in range(cfg.layers) if cfg.is_attention(il)]   # pushed by the output projection's first phase
     assert sorted(pushed) == list(range(HybridProgram.arena_slots(cfg)))
     ctx.close()
+
+
+def test_pick_trial_keeps_the_default_unless_a_trial_beats_it_by_the_margin():
+    from zllm_b200.plan import DenseProgram
+
+    pick = DenseProgram.pick_trial
+    assert pick([1.000, 0.999, 0.998, 1.2], 0.003) == 0          # within the margin: the default stays
+    assert pick([1.000, 0.990, 0.985, 1.2], 0.003) == 2          # the fastest trial beyond the margin
+    assert pick([1.000, 1.1, 1.2, 1.3], 0.003) == 0
+    assert pick([1.000], 0.003) == 0
+    # the ranks decide by the times `agree` returns (here: another rank was slow in trial 2)
+    assert pick([1.000, 0.990, 0.985, 1.2], 0.003, agree=lambda t: [max(a, b) for a, b in zip(t, [1.0, 0.991, 1.05, 1.0])]) == 1
+
+
+def _agree_main(rank, world, port, out_dir):
+    import torch
+    import torch.distributed as dist
+
+    from zllm_b200.plan import DenseProgram
+
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+
+    def agree(times):
+        t = torch.tensor(times, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.tolist()
+
+    # each rank alone would keep another trial (rank 0: trial 1, rank 1: trial 2); together they keep trial 3, the one
+    # whose slowest rank is fastest
+    mine = [[1.0, 0.90, 1.10, 0.95], [1.0, 1.10, 0.90, 0.94]][rank]
+    alone = DenseProgram.pick_trial(mine, 0.003)
+    together = DenseProgram.pick_trial(mine, 0.003, agree)
+    with open(os.path.join(out_dir, f"pick{rank}.txt"), "w") as f:
+        f.write(f"{alone} {together}")
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_gloo_ranks_keep_the_same_trial():
+    import torch.multiprocessing as mp
+
+    with tempfile.TemporaryDirectory() as tmp:
+        port = 29900 + os.getpid() % 90
+        mp.spawn(_agree_main, args=(2, port, tmp), nprocs=2, join=True)
+        picks = [open(os.path.join(tmp, f"pick{r}.txt")).read().split() for r in range(2)]
+    assert picks == [["1", "3"], ["2", "3"]]

@@ -224,7 +224,17 @@ class DenseProgram:
         self.sweep_report = s.report
         return table
 
-    def refine(self, max_keys: int, top: int = 3, reps: int = 10, margin: float = 0.003) -> dict:
+    @staticmethod
+    def pick_trial(times, margin: float, agree=None) -> int:
+        """Which of a shape's trials stays (times[0] is the default form's step): the fastest, if it beats the default
+        by more than `margin`, else the default. `agree` maps this rank's times to the ones every rank decides by
+        (the maximum over ranks: a step ends when its slowest rank does), so that all ranks keep the SAME trial - a
+        combination of forms that was timed, not one per rank from different trials."""
+        times = list(times) if agree is None else list(agree(list(times)))
+        best = min(range(len(times)), key=lambda i: times[i])
+        return best if times[best] < times[0] * (1.0 - margin) else 0
+
+    def refine(self, max_keys: int, top: int = 3, reps: int = 10, margin: float = 0.003, agree=None) -> dict:
         """After sweep(): every shape goes back to the library's default form; then, shape by shape (largest first),
         the default and the `top` candidates that were fastest on their own are tried inside the replayed step, and a
         candidate replaces the default only where it makes the STEP faster by more than `margin`. A multiply's time
@@ -233,7 +243,7 @@ class DenseProgram:
         lie within the sweep's noise of each other, so the stand-alone figures only nominate. Starting from the
         defaults makes the result no slower than an untuned program (up to the margin). Every rank of a
         tensor-parallel program runs the same number of steps here (`top` + 1 trials per shape), as the exchange
-        requires."""
+        requires, and with `agree` (see pick_trial) they all keep the same trial of a shape."""
         import time
 
         by_shape = {}
@@ -268,8 +278,7 @@ class DenseProgram:
             for v in trials:
                 self.variants[shape] = v
                 timed.append((step_seconds(), v))
-            best = min(timed)
-            self.variants[shape] = best[1] if best[0] < timed[0][0] * (1.0 - margin) else 0
+            self.variants[shape] = trials[self.pick_trial([t for t, _ in timed], margin, agree)]
             self.refine_report.append((shape, timed))
         return self.variants
 
