@@ -57,6 +57,8 @@ def variant(tiles: int = 0, splitk: int = 0, family: int = 0) -> int:
 # warps and two), CTA count (byte 1, bit 4: 0 = the count that divides the row tiles evenly, 1 = a CTA on every SM);
 # scalar family: one shape.
 SHAPE_16_WARPS, SHAPE_8_WARPS, GRID_EVERY_SM = 0, 1, 0x10
+# what variant word 0 resolves to in the library, where a candidate names the same form (such a candidate is a repeat)
+MATVEC_DEFAULT_FORM = {"q4_k": variant(3, SHAPE_16_WARPS | GRID_EVERY_SM, FAMILY_MMA)}
 MATVEC_CANDIDATES = ([variant(st, shape | grid, FAMILY_MMA) for st in (3, 4, 5, 6) for shape in (SHAPE_16_WARPS, SHAPE_8_WARPS)
                       for grid in (0, GRID_EVERY_SM)] + [variant(0, 0, FAMILY_SCALAR)])
 # matvec_q4_k for up to 64 tokens in one pass over the weights (tcgen05, accumulators in tensor memory).

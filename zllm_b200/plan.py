@@ -234,7 +234,7 @@ class DenseProgram:
         best = min(range(len(times)), key=lambda i: times[i])
         return best if times[best] < times[0] * (1.0 - margin) else 0
 
-    def refine(self, max_keys: int, top: int = 3, reps: int = 10, margin: float = 0.003, agree=None) -> dict:
+    def refine(self, max_keys: int, top: int = 3, reps: int = 10, margin: float = 0.005, agree=None) -> dict:
         """After sweep(): every shape goes back to the library's default form; then, shape by shape (largest first),
         the default and the `top` candidates that were fastest on their own are tried inside the replayed step, and a
         candidate replaces the default only where it makes the STEP faster by more than `margin`. A multiply's time
@@ -272,7 +272,7 @@ class DenseProgram:
             self.variants[shape] = 0
         self.refine_report = []
         for shape in sorted(by_shape, key=lambda s: -s[1] * s[2]):
-            trials = [v for _, v in sorted(by_shape[shape]) if v != 0][:top]
+            trials = [v for _, v in sorted(by_shape[shape]) if v != 0 and v != K.MATVEC_DEFAULT_FORM.get(shape[0])][:top]
             trials = [0] + trials + [0] * (top - len(trials))
             timed = []
             for v in trials:
