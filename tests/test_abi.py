@@ -227,3 +227,16 @@ def test_recorder_round_trip():
     assert (r.next == [1, 1, 1])
     with pytest.raises(ValueError):
         list(cmd.iterate(r.batch()[:-1]))
+
+
+def test_the_default_form_named_in_the_header_is_the_one_the_tuning_skips():
+    # Variant word 0 of matvec_q4_k resolves to one of the sweep's candidates; the in-step trials must know which, so
+    # that they do not time the default against itself. The header states it; the host mirror and the library agree.
+    root = Path(__file__).resolve().parent.parent
+    text = (root / "include" / "zllm_cuda.h").read_text()
+    m = re.search(r"matvec_q4_k is ZCU_VARIANT\((\d+), (0x[0-9a-f]+), ZCU_FAMILY_MMA\)", text)
+    assert m, "the header no longer states matvec_q4_k's default form"
+    stated = K.variant(int(m.group(1)), int(m.group(2), 16), K.FAMILY_MMA)
+    assert stated == K.MATVEC_DEFAULT_FORM["q4_k"] and stated in K.MATVEC_CANDIDATES
+    src = (root / "zllm_b200" / "csrc" / "k_matvec.cu").read_text()
+    assert f"launch_matvec_imma(a, v, TYPE, {m.group(1)}, {m.group(2)})" in src
